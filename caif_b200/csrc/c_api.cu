@@ -1,0 +1,615 @@
+// The extern "C" surface declared in include/caifq.h: argument checks, kernel
+// family selection, and the compositions (LoRA, grouped experts) that are
+// several launches.  No entry point allocates device memory or synchronises.
+#include <cstdarg>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace caifq
+{
+
+namespace
+{
+thread_local char t_error[512] = "";
+thread_local const char *t_path = "none";
+}  // namespace
+
+void set_error(const char *fmt, ...)
+{
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_error, sizeof(t_error), fmt, ap);
+  va_end(ap);
+}
+
+void set_path(const char *name) { t_path = name; }
+
+// moe.cu
+int launch_moe_topk(const void *probs, int dtype, int *indices, void *values, int batch, int dim, int k,
+                    cudaStream_t s);
+int launch_moe_normalize_rows(const void *input, void *output, int dtype, int batch, int dim, cudaStream_t s);
+int launch_moe_build_dispatch(const int *expert_indices, int num_tokens, int top_k, int num_experts, int capacity,
+                              int *dispatch_map, int *expert_offsets, cudaStream_t s);
+int launch_moe_dispatch(const void *input, int dtype, const int *expert_indices, const int *dispatch_map,
+                        const int *expert_offsets, void *buffer, int num_tokens, int dim, int top_k, cudaStream_t s);
+int launch_moe_combine(const void *buffer, int dtype, const int *expert_indices, const void *expert_weights,
+                       const int *dispatch_map, const int *expert_offsets, void *output, int num_tokens, int dim,
+                       int top_k, cudaStream_t s);
+int launch_swiglu_fwd(const void *gate, const void *up, void *hidden, int dtype, int64_t n, cudaStream_t s);
+int launch_swiglu_bwd(const void *g_hidden, const void *gate, const void *up, void *g_gate, void *g_up, int dtype,
+                      int64_t n, cudaStream_t s);
+int launch_add(const void *a, const void *b, void *out, int dtype, int64_t n, cudaStream_t s);
+// lora.cu
+size_t gemm_tn_scratch_bytes(int p, int q);
+int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
+                   float u_prescale, int64_t m, int p, int q, cudaStream_t s);
+int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
+
+namespace
+{
+
+int check_weight(const caifq_weight *w, const char *who)
+{
+  CAIFQ_CHECK_ARG(w != nullptr, "%s: weight is null", who);
+  CAIFQ_CHECK_ARG(w->codes != nullptr, "%s: weight not loaded", who);
+  CAIFQ_CHECK_ARG(w->in_dim > 0 && w->out_dim > 0, "%s: bad dims in=%d out=%d", who, w->in_dim, w->out_dim);
+  switch (w->storage)
+  {
+    case CAIFQ_F32:
+    case CAIFQ_F16:
+    case CAIFQ_BF16:
+      break;
+    case CAIFQ_I8:
+      CAIFQ_CHECK_ARG(w->scheme == CAIFQ_PER_TENSOR || w->scheme == CAIFQ_PER_CHANNEL, "%s: bad int8 scheme %d", who,
+                      w->scheme);
+      break;
+    case CAIFQ_I4:
+      CAIFQ_CHECK_ARG(w->scales != nullptr, "%s: int4 weight needs scales", who);
+      CAIFQ_CHECK_ARG(w->group_size > 0, "%s: bad group size %d", who, w->group_size);
+      break;
+    default:
+      set_error("%s: unsupported storage dtype %d", who, w->storage);
+      return CAIFQ_ERR_INVALID;
+  }
+  return CAIFQ_OK;
+}
+
+enum class Force
+{
+  None,
+  Generic,
+  Umma,
+  Decode
+};
+
+Force forced_path()
+{
+  const char *e = std::getenv("CAIFQ_FORCE_PATH");
+  if (e == nullptr || e[0] == '\0')
+  {
+    return Force::None;
+  }
+  if (std::strcmp(e, "generic") == 0)
+  {
+    return Force::Generic;
+  }
+  if (std::strcmp(e, "umma") == 0)
+  {
+    return Force::Umma;
+  }
+  if (std::strcmp(e, "decode") == 0)
+  {
+    return Force::Decode;
+  }
+  return Force::None;
+}
+
+int linear_any(const caifq_weight *w, bool backward, const void *a, int a_dtype, float a_prescale, int64_t m,
+               void *c, int c_dtype, bool accumulate, int compute_dtype, cudaStream_t s, const char *who)
+{
+  const int rc = check_weight(w, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(m >= 0, "%s: negative m", who);
+  CAIFQ_CHECK_ARG(is_float_dtype(a_dtype) && is_float_dtype(c_dtype) && is_float_dtype(compute_dtype),
+                  "%s: activation/output/compute dtypes must be F32, F16 or BF16", who);
+  if (m == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(a != nullptr && c != nullptr, "%s: null activation or output pointer", who);
+  LinearArgs args{};
+  args.w = *w;
+  args.backward = backward;
+  args.a = a;
+  args.a_dtype = a_dtype;
+  args.a_prescale = a_prescale;
+  args.m = m;
+  args.c = c;
+  args.c_dtype = c_dtype;
+  args.accumulate = accumulate;
+  args.compute_dtype = compute_dtype;
+  const Force force = forced_path();
+  if ((force == Force::None || force == Force::Decode) && decode_supported(args))
+  {
+    set_path("decode");
+    return launch_linear_decode(args, s);
+  }
+  if ((force == Force::None || force == Force::Umma) && umma_supported(args))
+  {
+    set_path("umma");
+    return launch_linear_umma(args, s);
+  }
+  if (force == Force::Umma || force == Force::Decode)
+  {
+    set_error("%s: forced kernel family does not support this call", who);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  set_path("generic");
+  return launch_linear_generic(args, s);
+}
+
+caifq_weight float_weight(const void *data, int dtype, int out_dim, int in_dim)
+{
+  caifq_weight w{};
+  w.codes = data;
+  w.scales = nullptr;
+  w.storage = dtype;
+  w.scheme = CAIFQ_PER_TENSOR;
+  w.group_size = 128;
+  w.in_dim = in_dim;
+  w.out_dim = out_dim;
+  return w;
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+}  // namespace
+}  // namespace caifq
+
+using namespace caifq;
+
+extern "C" {
+
+const char *caifq_last_error(void) { return t_error; }
+
+const char *caifq_last_path(void) { return t_path; }
+
+const char *caifq_version(void) { return "caifq 0.1 (sm_100a)"; }
+
+int caifq_device_ok(void)
+{
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess)
+  {
+    cudaGetLastError();
+    return 0;
+  }
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+  {
+    cudaGetLastError();
+    return 0;
+  }
+  return major == 10 ? 1 : 0;
+}
+
+int caifq_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int64_t n, void *stream)
+{
+  CAIFQ_CHECK_ARG(n >= 0, "quantize_int8_per_tensor: negative n");
+  CAIFQ_CHECK_ARG(n == 0 || (x && q && scale), "quantize_int8_per_tensor: null pointer");
+  return launch_quantize_int8_per_tensor(x, q, scale, n, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, int32_t rows, int32_t cols, void *stream)
+{
+  CAIFQ_CHECK_ARG(rows >= 0 && cols >= 0, "quantize_int8_per_channel: negative shape");
+  CAIFQ_CHECK_ARG(rows == 0 || cols == 0 || (x && q && scales), "quantize_int8_per_channel: null pointer");
+  return launch_quantize_int8_per_channel(x, q, scales, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_quantize_int4_per_group(const float *x, uint8_t *packed, uint16_t *scales_f16, int64_t n, int32_t group_size,
+                                  void *stream)
+{
+  CAIFQ_CHECK_ARG(n >= 0, "quantize_int4_per_group: negative n");
+  CAIFQ_CHECK_ARG(group_size > 0, "quantize_int4_per_group: group_size must be positive");
+  CAIFQ_CHECK_ARG(n == 0 || (x && packed && scales_f16), "quantize_int4_per_group: null pointer");
+  return launch_quantize_int4(x, packed, scales_f16, n, group_size, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_dequantize_int8_per_tensor(const int8_t *q, float *out, const float *scale, int64_t n, void *stream)
+{
+  CAIFQ_CHECK_ARG(n >= 0, "dequantize_int8_per_tensor: negative n");
+  CAIFQ_CHECK_ARG(n == 0 || (q && out && scale), "dequantize_int8_per_tensor: null pointer");
+  return launch_dequantize_int8_per_tensor(q, out, scale, n, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_dequantize_int8_per_channel(const int8_t *q, float *out, const float *scales, int32_t rows, int32_t cols,
+                                      void *stream)
+{
+  CAIFQ_CHECK_ARG(rows >= 0 && cols >= 0, "dequantize_int8_per_channel: negative shape");
+  CAIFQ_CHECK_ARG(rows == 0 || cols == 0 || (q && out && scales), "dequantize_int8_per_channel: null pointer");
+  return launch_dequantize_int8_per_channel(q, out, scales, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_dequantize_int4(const uint8_t *packed, const uint16_t *scales_f16, float *out, int64_t n, int32_t group_size,
+                          void *stream)
+{
+  CAIFQ_CHECK_ARG(n >= 0, "dequantize_int4: negative n");
+  CAIFQ_CHECK_ARG(group_size > 0, "dequantize_int4: group_size must be positive");
+  CAIFQ_CHECK_ARG(n == 0 || (packed && scales_f16 && out), "dequantize_int4: null pointer");
+  return launch_dequantize_int4(packed, scales_f16, out, n, group_size, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_cast(const void *src, int32_t src_dtype, void *dst, int32_t dst_dtype, int64_t n, void *stream)
+{
+  CAIFQ_CHECK_ARG(n >= 0, "cast: negative n");
+  CAIFQ_CHECK_ARG(n == 0 || (src && dst), "cast: null pointer");
+  return launch_cast(src, src_dtype, dst, dst_dtype, n, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_weight_materialize(const caifq_weight *w, void *dst, int32_t dst_dtype, void *stream)
+{
+  const int rc = check_weight(w, "caifq_weight_materialize");
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(dst != nullptr && is_float_dtype(dst_dtype), "caifq_weight_materialize: bad destination");
+  return launch_weight_materialize(*w, dst, dst_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *y, int32_t y_dtype,
+                     int32_t compute_dtype, void *stream)
+{
+  return linear_any(w, false, x, x_dtype, 1.0f, m, y, y_dtype, false, compute_dtype,
+                    static_cast<cudaStream_t>(stream), "caifq_linear_fwd");
+}
+
+int caifq_linear_dx(const caifq_weight *w, const void *dy, int32_t dy_dtype, int64_t m, void *dx, int32_t dx_dtype,
+                    int32_t compute_dtype, void *stream)
+{
+  return linear_any(w, true, dy, dy_dtype, 1.0f, m, dx, dx_dtype, false, compute_dtype,
+                    static_cast<cudaStream_t>(stream), "caifq_linear_dx");
+}
+
+// ---------------------------------------------------------------------- LoRA
+
+static int check_lora(const caifq_weight *w, const caifq_lora *l, const char *who)
+{
+  const int rc = check_weight(w, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(l != nullptr && l->a != nullptr && l->b != nullptr, "%s: LoRA factors are null", who);
+  CAIFQ_CHECK_ARG(l->rank > 0, "%s: LoRA rank must be positive", who);
+  CAIFQ_CHECK_ARG(is_float_dtype(l->dtype), "%s: LoRA dtype must be F32, F16 or BF16", who);
+  return CAIFQ_OK;
+}
+
+int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
+                          void *hidden, int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_lora_linear_fwd";
+  const int rc = check_lora(w, lora, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(m >= 0, "%s: negative m", who);
+  if (m == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(x && y && hidden, "%s: x, y and hidden must be non-null", who);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int sd = lora->dtype;
+  // hidden = x . A^T, rounded to the storage dtype as the reference materialises it
+  const caifq_weight wa = float_weight(lora->a, sd, lora->rank, w->in_dim);
+  int r = linear_any(&wa, false, x, sd, 1.0f, m, hidden, sd, false, compute_dtype, s, who);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  // y = hidden . B^T, then y *= alpha/r (two roundings in the reference)
+  const caifq_weight wb = float_weight(lora->b, sd, w->out_dim, lora->rank);
+  r = linear_any(&wb, false, hidden, sd, 1.0f, m, y, sd, false, compute_dtype, s, who);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  r = launch_scale(y, y, sd, lora->alpha / static_cast<float>(lora->rank), m * static_cast<int64_t>(w->out_dim), s);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  // frozen base on top: y = round(round(x . W^T) + y)
+  return linear_any(w, false, x, sd, 1.0f, m, y, sd, true, compute_dtype, s, who);
+}
+
+size_t caifq_lora_bwd_workspace_bytes(const caifq_weight *w, const caifq_lora *lora, int64_t m)
+{
+  if (w == nullptr || lora == nullptr || m <= 0 || lora->rank <= 0)
+  {
+    return 0;
+  }
+  const size_t d_hidden = align256(static_cast<size_t>(m) * static_cast<size_t>(lora->rank) * 4);
+  const size_t big = static_cast<size_t>(w->in_dim > w->out_dim ? w->in_dim : w->out_dim);
+  return d_hidden + align256(big * static_cast<size_t>(lora->rank) * sizeof(float));
+}
+
+int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
+                          const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
+                          int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_lora_linear_bwd";
+  const int rc = check_lora(w, lora, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(m >= 0, "%s: negative m", who);
+  if (m == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(dy && x && hidden && dx && d_a && d_b && workspace, "%s: null pointer", who);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int sd = lora->dtype;
+  const float scale = lora->alpha / static_cast<float>(lora->rank);
+  void *d_hidden = workspace;
+  float *scratch = reinterpret_cast<float *>(static_cast<char *>(workspace) +
+                                             align256(static_cast<size_t>(m) * static_cast<size_t>(lora->rank) * 4));
+  // dB[out, r] = (scale . dy)^T . hidden
+  int r = launch_gemm_tn(dy, hidden, d_b, scratch, sd, compute_dtype, scale, m, w->out_dim, lora->rank, s);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  // dH[m, r] = (scale . dy) . B
+  const caifq_weight wb = float_weight(lora->b, sd, w->out_dim, lora->rank);
+  r = linear_any(&wb, true, dy, sd, scale, m, d_hidden, sd, false, compute_dtype, s, who);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  // dA[r, in] = dH^T . x
+  r = launch_gemm_tn(d_hidden, x, d_a, scratch, sd, compute_dtype, 1.0f, m, lora->rank, w->in_dim, s);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  // dx = dH . A, then the frozen base on top: dx = round(round(dy . W) + dx)
+  const caifq_weight wa = float_weight(lora->a, sd, lora->rank, w->in_dim);
+  r = linear_any(&wa, true, d_hidden, sd, 1.0f, m, dx, sd, false, compute_dtype, s, who);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  return linear_any(w, true, dy, sd, 1.0f, m, dx, sd, true, compute_dtype, s, who);
+}
+
+// ----------------------------------------------------------------------- MoE
+
+int caifq_moe_topk(const void *probs, int32_t dtype, int32_t *indices, void *values, int32_t batch, int32_t dim,
+                   int32_t k, void *stream)
+{
+  CAIFQ_CHECK_ARG(batch >= 0 && dim > 0 && k > 0, "caifq_moe_topk: bad shape");
+  CAIFQ_CHECK_ARG(k <= dim, "caifq_moe_topk: k=%d exceeds dim=%d", k, dim);
+  CAIFQ_CHECK_ARG(batch == 0 || (probs && indices && values), "caifq_moe_topk: null pointer");
+  return launch_moe_topk(probs, dtype, indices, values, batch, dim, k, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_normalize_rows(const void *input, void *output, int32_t dtype, int32_t batch, int32_t dim, void *stream)
+{
+  CAIFQ_CHECK_ARG(batch >= 0 && dim > 0, "caifq_moe_normalize_rows: bad shape");
+  CAIFQ_CHECK_ARG(batch == 0 || (input && output), "caifq_moe_normalize_rows: null pointer");
+  return launch_moe_normalize_rows(input, output, dtype, batch, dim, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_build_dispatch(const int32_t *expert_indices, int32_t num_tokens, int32_t top_k, int32_t num_experts,
+                             int32_t capacity, int32_t *dispatch_map, int32_t *expert_offsets, void *stream)
+{
+  CAIFQ_CHECK_ARG(num_tokens >= 0 && top_k > 0 && num_experts > 0, "caifq_moe_build_dispatch: bad shape");
+  CAIFQ_CHECK_ARG(expert_offsets != nullptr, "caifq_moe_build_dispatch: null expert_offsets");
+  CAIFQ_CHECK_ARG(num_tokens == 0 || (expert_indices && dispatch_map), "caifq_moe_build_dispatch: null pointer");
+  return launch_moe_build_dispatch(expert_indices, num_tokens, top_k, num_experts, capacity, dispatch_map,
+                                   expert_offsets, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_dispatch(const void *input, int32_t dtype, const int32_t *expert_indices, const int32_t *dispatch_map,
+                       const int32_t *expert_offsets, void *expert_buffer, int32_t num_tokens, int32_t dim,
+                       int32_t top_k, void *stream)
+{
+  CAIFQ_CHECK_ARG(num_tokens >= 0 && dim > 0 && top_k > 0, "caifq_moe_dispatch: bad shape");
+  CAIFQ_CHECK_ARG(num_tokens == 0 || (input && expert_indices && dispatch_map && expert_offsets && expert_buffer),
+                  "caifq_moe_dispatch: null pointer");
+  return launch_moe_dispatch(input, dtype, expert_indices, dispatch_map, expert_offsets, expert_buffer, num_tokens,
+                             dim, top_k, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_combine(const void *expert_buffer, int32_t dtype, const int32_t *expert_indices,
+                      const void *expert_weights, const int32_t *dispatch_map, const int32_t *expert_offsets,
+                      void *output, int32_t num_tokens, int32_t dim, int32_t top_k, void *stream)
+{
+  CAIFQ_CHECK_ARG(num_tokens >= 0 && dim > 0 && top_k > 0, "caifq_moe_combine: bad shape");
+  CAIFQ_CHECK_ARG(num_tokens == 0 ||
+                      (expert_buffer && expert_indices && expert_weights && dispatch_map && expert_offsets && output),
+                  "caifq_moe_combine: null pointer");
+  return launch_moe_combine(expert_buffer, dtype, expert_indices, expert_weights, dispatch_map, expert_offsets,
+                            output, num_tokens, dim, top_k, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------ grouped experts
+
+static int check_experts(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                         int32_t num_experts, const int32_t *offsets, const char *who)
+{
+  CAIFQ_CHECK_ARG(gate && up && down && offsets, "%s: null expert table", who);
+  CAIFQ_CHECK_ARG(num_experts > 0, "%s: num_experts must be positive", who);
+  const int in_dim = up[0].in_dim;
+  const int hidden = up[0].out_dim;
+  for (int e = 0; e < num_experts; ++e)
+  {
+    int rc = check_weight(&gate[e], who);
+    if (rc == CAIFQ_OK)
+    {
+      rc = check_weight(&up[e], who);
+    }
+    if (rc == CAIFQ_OK)
+    {
+      rc = check_weight(&down[e], who);
+    }
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+    CAIFQ_CHECK_ARG(gate[e].in_dim == in_dim && up[e].in_dim == in_dim && down[e].out_dim == in_dim &&
+                        gate[e].out_dim == hidden && up[e].out_dim == hidden && down[e].in_dim == hidden,
+                    "%s: expert %d has inconsistent dims", who, e);
+    CAIFQ_CHECK_ARG(offsets[e + 1] >= offsets[e], "%s: expert offsets must be non-decreasing", who);
+  }
+  return CAIFQ_OK;
+}
+
+int caifq_grouped_expert_fwd(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                             int32_t num_experts, const int32_t *expert_offsets_host, const void *x, void *out,
+                             void *gate_out, void *up_out, void *hidden_ws, int32_t dtype, int32_t compute_dtype,
+                             void *stream)
+{
+  const char *who = "caifq_grouped_expert_fwd";
+  const int rc = check_experts(gate, up, down, num_experts, expert_offsets_host, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  const int64_t total = expert_offsets_host[num_experts];
+  if (total == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(x && out && gate_out && up_out && hidden_ws, "%s: null pointer", who);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t es = dtype_bytes(dtype);
+  const int64_t in_dim = up[0].in_dim;
+  const int64_t hid = up[0].out_dim;
+  for (int e = 0; e < num_experts; ++e)
+  {
+    const int64_t off = expert_offsets_host[e];
+    const int64_t cnt = expert_offsets_host[e + 1] - off;
+    if (cnt == 0)
+    {
+      continue;
+    }
+    const char *xe = static_cast<const char *>(x) + off * in_dim * es;
+    int r = linear_any(&up[e], false, xe, dtype, 1.0f, cnt, static_cast<char *>(up_out) + off * hid * es, dtype, false,
+                       compute_dtype, s, who);
+    if (r == CAIFQ_OK)
+    {
+      r = linear_any(&gate[e], false, xe, dtype, 1.0f, cnt, static_cast<char *>(gate_out) + off * hid * es, dtype,
+                     false, compute_dtype, s, who);
+    }
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+  }
+  int r = launch_swiglu_fwd(gate_out, up_out, hidden_ws, dtype, total * hid, s);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  for (int e = 0; e < num_experts; ++e)
+  {
+    const int64_t off = expert_offsets_host[e];
+    const int64_t cnt = expert_offsets_host[e + 1] - off;
+    if (cnt == 0)
+    {
+      continue;
+    }
+    r = linear_any(&down[e], false, static_cast<const char *>(hidden_ws) + off * hid * es, dtype, 1.0f, cnt,
+                   static_cast<char *>(out) + off * in_dim * es, dtype, false, compute_dtype, s, who);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+  }
+  return CAIFQ_OK;
+}
+
+int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                             int32_t num_experts, const int32_t *expert_offsets_host, const void *dy,
+                             const void *gate_out, const void *up_out, void *dx, void *ws, int32_t dtype,
+                             int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_grouped_expert_bwd";
+  const int rc = check_experts(gate, up, down, num_experts, expert_offsets_host, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  const int64_t total = expert_offsets_host[num_experts];
+  if (total == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(dy && gate_out && up_out && dx && ws, "%s: null pointer", who);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t es = dtype_bytes(dtype);
+  const int64_t in_dim = up[0].in_dim;
+  const int64_t hid = up[0].out_dim;
+  char *g_hidden = static_cast<char *>(ws);
+  char *g_gate = g_hidden + total * hid * es;
+  char *g_up = g_gate + total * hid * es;
+  for (int e = 0; e < num_experts; ++e)
+  {
+    const int64_t off = expert_offsets_host[e];
+    const int64_t cnt = expert_offsets_host[e + 1] - off;
+    if (cnt == 0)
+    {
+      continue;
+    }
+    const int r = linear_any(&down[e], true, static_cast<const char *>(dy) + off * in_dim * es, dtype, 1.0f, cnt,
+                             g_hidden + off * hid * es, dtype, false, compute_dtype, s, who);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+  }
+  int r = launch_swiglu_bwd(g_hidden, gate_out, up_out, g_gate, g_up, dtype, total * hid, s);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  for (int e = 0; e < num_experts; ++e)
+  {
+    const int64_t off = expert_offsets_host[e];
+    const int64_t cnt = expert_offsets_host[e + 1] - off;
+    if (cnt == 0)
+    {
+      continue;
+    }
+    char *dxe = static_cast<char *>(dx) + off * in_dim * es;
+    // dx = round(up.Bwd(g_up)); dx = round(round(gate.Bwd(g_gate)) + dx): the reference's Add(gi_up, gi_gate)
+    r = linear_any(&up[e], true, g_up + off * hid * es, dtype, 1.0f, cnt, dxe, dtype, false, compute_dtype, s, who);
+    if (r == CAIFQ_OK)
+    {
+      r = linear_any(&gate[e], true, g_gate + off * hid * es, dtype, 1.0f, cnt, dxe, dtype, true, compute_dtype, s,
+                     who);
+    }
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+  }
+  return CAIFQ_OK;
+}
+
+}  // extern "C"

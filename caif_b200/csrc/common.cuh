@@ -1,0 +1,208 @@
+// Shared declarations of the caifq kernels: dtype codes, error plumbing,
+// scalar conversions and the launcher prototypes that c_api.cu calls.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+
+#include "caifq.h"
+
+namespace caifq
+{
+
+void set_error(const char *fmt, ...);
+void set_path(const char *name);
+
+#define CAIFQ_CHECK_ARG(cond, ...)        \
+  do                                      \
+  {                                       \
+    if (!(cond))                          \
+    {                                     \
+      ::caifq::set_error(__VA_ARGS__);    \
+      return CAIFQ_ERR_INVALID;           \
+    }                                     \
+  } while (0)
+
+#define CAIFQ_CHECK_CUDA(expr)                                                            \
+  do                                                                                      \
+  {                                                                                       \
+    cudaError_t err__ = (expr);                                                           \
+    if (err__ != cudaSuccess)                                                             \
+    {                                                                                     \
+      ::caifq::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, __LINE__); \
+      return CAIFQ_ERR_CUDA;                                                              \
+    }                                                                                     \
+  } while (0)
+
+#define CAIFQ_CHECK_LAUNCH() CAIFQ_CHECK_CUDA(cudaGetLastError())
+
+inline bool is_float_dtype(int d) { return d == CAIFQ_F32 || d == CAIFQ_F16 || d == CAIFQ_BF16; }
+
+inline size_t dtype_bytes(int d)
+{
+  switch (d)
+  {
+    case CAIFQ_F32:
+      return 4;
+    case CAIFQ_F16:
+    case CAIFQ_BF16:
+      return 2;
+    case CAIFQ_I8:
+      return 1;
+    default:
+      return 0;
+  }
+}
+
+// ---- device-side scalar helpers -------------------------------------------
+
+__device__ __forceinline__ float load_as_float(const void *p, int64_t i, int dtype)
+{
+  if (dtype == CAIFQ_F32)
+  {
+    return static_cast<const float *>(p)[i];
+  }
+  if (dtype == CAIFQ_BF16)
+  {
+    return __bfloat162float(static_cast<const __nv_bfloat16 *>(p)[i]);
+  }
+  return __half2float(static_cast<const __half *>(p)[i]);
+}
+
+__device__ __forceinline__ void store_from_float(void *p, int64_t i, int dtype, float v)
+{
+  if (dtype == CAIFQ_F32)
+  {
+    static_cast<float *>(p)[i] = v;
+  }
+  else if (dtype == CAIFQ_BF16)
+  {
+    static_cast<__nv_bfloat16 *>(p)[i] = __float2bfloat16(v);
+  }
+  else
+  {
+    static_cast<__half *>(p)[i] = __float2half(v);
+  }
+}
+
+// Round an fp32 value through a 16-bit float dtype (nearest even) and back.
+template <int DTYPE>
+__device__ __forceinline__ float round_through(float v)
+{
+  if constexpr (DTYPE == CAIFQ_BF16)
+  {
+    return __bfloat162float(__float2bfloat16(v));
+  }
+  else if constexpr (DTYPE == CAIFQ_F16)
+  {
+    return __half2float(__float2half(v));
+  }
+  else
+  {
+    return v;
+  }
+}
+
+__device__ __forceinline__ float round_through_rt(float v, int dtype)
+{
+  if (dtype == CAIFQ_BF16)
+  {
+    return __bfloat162float(__float2bfloat16(v));
+  }
+  if (dtype == CAIFQ_F16)
+  {
+    return __half2float(__float2half(v));
+  }
+  return v;
+}
+
+__device__ __forceinline__ int sign_extend_nibble(int v) { return (v ^ 8) - 8; }
+
+// Element (flat index) of a frozen weight as the fp32 value the reference's
+// dequantize kernels produce, before any rounding to a compute dtype.
+template <int STORAGE>
+__device__ __forceinline__ float weight_value(const caifq_weight &w, int64_t flat)
+{
+  if constexpr (STORAGE == CAIFQ_F32)
+  {
+    return static_cast<const float *>(w.codes)[flat];
+  }
+  else if constexpr (STORAGE == CAIFQ_F16)
+  {
+    return __half2float(static_cast<const __half *>(w.codes)[flat]);
+  }
+  else if constexpr (STORAGE == CAIFQ_BF16)
+  {
+    return __bfloat162float(static_cast<const __nv_bfloat16 *>(w.codes)[flat]);
+  }
+  else if constexpr (STORAGE == CAIFQ_I8)
+  {
+    const float q = static_cast<float>(static_cast<const int8_t *>(w.codes)[flat]);
+    if (w.scales == nullptr)
+    {
+      return q;
+    }
+    const float *s = static_cast<const float *>(w.scales);
+    if (w.scheme == CAIFQ_PER_TENSOR)
+    {
+      return __fmul_rn(q, s[0]);
+    }
+    return __fmul_rn(q, s[flat % w.out_dim]);
+  }
+  else
+  {
+    const uint8_t b = static_cast<const uint8_t *>(w.codes)[flat >> 1];
+    const int nib = (flat & 1) ? (b >> 4) : (b & 0xF);
+    const float q = static_cast<float>(sign_extend_nibble(nib));
+    const float s = __half2float(static_cast<const __half *>(w.scales)[flat / w.group_size]);
+    return __fmul_rn(q, s);
+  }
+}
+
+// ---- launchers implemented in the individual .cu files ----------------------
+
+int launch_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int64_t n, cudaStream_t s);
+int launch_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, int rows, int cols, cudaStream_t s);
+int launch_quantize_int4(const float *x, uint8_t *packed, uint16_t *scales, int64_t n, int group, cudaStream_t s);
+int launch_dequantize_int8_per_tensor(const int8_t *q, float *out, const float *scale, int64_t n, cudaStream_t s);
+int launch_dequantize_int8_per_channel(const int8_t *q, float *out, const float *scales, int rows, int cols,
+                                       cudaStream_t s);
+int launch_dequantize_int4(const uint8_t *packed, const uint16_t *scales, float *out, int64_t n, int group,
+                           cudaStream_t s);
+int launch_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, cudaStream_t s);
+int launch_weight_materialize(const caifq_weight &w, void *dst, int dst_dtype, cudaStream_t s);
+
+// One frozen-linear product.  forward: c[m,out] = a[m,in] . W^T;  backward:
+// c[m,in] = a[m,out] . W.  `a_prescale` != 1 multiplies a on load and rounds the
+// product to a_dtype (LoRA's alpha/r on dY).  `accumulate` makes the epilogue
+// c = round_c( round_c(acc) + c_old ), the reference's cast-then-Add.
+struct LinearArgs
+{
+  caifq_weight w;
+  bool backward;
+  const void *a;
+  int a_dtype;
+  float a_prescale;
+  int64_t m;
+  void *c;
+  int c_dtype;
+  bool accumulate;
+  int compute_dtype;
+};
+
+// generic tiled fp32-FMA GEMM over every (storage, compute) cell
+int launch_linear_generic(const LinearArgs &args, cudaStream_t s);
+
+// weight-streaming kernel for few tokens (forward only)
+bool decode_supported(const LinearArgs &args);
+int launch_linear_decode(const LinearArgs &args, cudaStream_t s);
+
+// tcgen05 / TMEM tensor-core kernel for many tokens
+bool umma_supported(const LinearArgs &args);
+int launch_linear_umma(const LinearArgs &args, cudaStream_t s);
+
+}  // namespace caifq

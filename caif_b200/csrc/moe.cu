@@ -1,0 +1,518 @@
+// Routing, dispatch and expert elementwise kernels of the frozen-MoE path.
+//
+// Integer results (top-k indices, dispatch map, offsets) are bit-identical to
+// the reference (src/caif_cuda_kernels_moe.cu:280-334 top-k,
+// src/caif_ops_device.cpp:4876-4950 dispatch map); float results follow the
+// same fp32 operation order per element (normalize :43-85, combine :705-745,
+// SiLU src/caif_cuda_kernels_activations.cu:499-566).
+#include "common.cuh"
+
+namespace caifq
+{
+
+namespace
+{
+
+constexpr float kNegSentinel = -1e30f;
+constexpr float kRowSumEps = 1e-10f;
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f<__half>(float v) { return __float2half(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+// ------------------------------------------------------------------------ top-k
+// One warp per row.  The reference lets thread 0 scan the row k times with a
+// strict '>' from index 0 against a -1e30 sentinel: the winner of each round is
+// the largest value, lowest index among equals, and (-1e30, index 0) when
+// nothing exceeds the sentinel.  The warp version keeps exactly that order.
+template <typename T>
+__global__ void topk_kernel(const T *__restrict__ input, int *__restrict__ indices, T *__restrict__ values,
+                            int batch, int dim, int k)
+{
+  extern __shared__ float s_rows[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * warps_per_block + warp;
+  if (row >= batch)
+  {
+    return;
+  }
+  float *temp = s_rows + static_cast<size_t>(warp) * dim;
+  const T *src = input + static_cast<size_t>(row) * dim;
+  for (int d = lane; d < dim; d += 32)
+  {
+    temp[d] = to_f<T>(src[d]);
+  }
+  __syncwarp();
+  for (int i = 0; i < k; ++i)
+  {
+    float best = kNegSentinel;
+    int best_idx = 0;
+    for (int d = lane; d < dim; d += 32)
+    {
+      const float v = temp[d];
+      if (v > best)
+      {
+        best = v;
+        best_idx = d;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, best_idx, o);
+      if (ov > best || (ov == best && oi < best_idx))
+      {
+        best = ov;
+        best_idx = oi;
+      }
+    }
+    if (lane == 0)
+    {
+      indices[static_cast<size_t>(row) * k + i] = best_idx;
+      values[static_cast<size_t>(row) * k + i] = from_f<T>(best);
+      temp[best_idx] = kNegSentinel;
+    }
+    __syncwarp();
+  }
+}
+
+// -------------------------------------------------------------- normalize rows
+// The reference uses a block of 256 threads: thread t sums elements t, t+256,
+// ... and a shared-memory tree (stride 128..1) adds the 256 partials.  A warp
+// reproduces that order: lane l owns partials l, l+32, ..., l+224.
+template <typename T>
+__global__ void normalize_rows_kernel(const T *__restrict__ input, T *__restrict__ output, int batch, int dim)
+{
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (row >= batch)
+  {
+    return;
+  }
+  const T *src = input + static_cast<size_t>(row) * dim;
+  T *dst = output + static_cast<size_t>(row) * dim;
+  float part[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+  {
+    float acc = 0.0f;
+    for (int d = lane + 32 * j; d < dim; d += 256)
+    {
+      acc += to_f<T>(src[d]);
+    }
+    part[j] = acc;
+  }
+  // strides 128, 64, 32 stay inside the lane
+  part[0] += part[4];
+  part[1] += part[5];
+  part[2] += part[6];
+  part[3] += part[7];
+  part[0] += part[2];
+  part[1] += part[3];
+  float v = part[0] + part[1];
+  // strides 16..1 cross lanes: slot t takes slot t+stride
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+  {
+    const float other = __shfl_down_sync(0xFFFFFFFFu, v, o);
+    if (lane < o)
+    {
+      v += other;
+    }
+  }
+  v = __shfl_sync(0xFFFFFFFFu, v, 0);
+  const float sum = fmaxf(v, kRowSumEps);
+  const float inv = __fdiv_rn(1.0f, sum);
+  for (int d = lane; d < dim; d += 32)
+  {
+    dst[d] = from_f<T>(__fmul_rn(to_f<T>(src[d]), inv));
+  }
+}
+
+// ------------------------------------------------------------------ dispatch map
+// Stable counting rank on the device.  One CTA walks the [T*k] index list in
+// chunks of blockDim entries; inside a chunk, warps rank equal experts with
+// match_any, a per-warp histogram is scanned over warps, and a running count per
+// expert carries across chunks.  The rank of an entry is the number of earlier
+// entries (token-major, k-minor) with the same expert -- what the reference's
+// host loop assigns.
+constexpr int kMapThreads = 1024;
+constexpr int kMapWarps = kMapThreads / 32;
+
+__global__ void __launch_bounds__(kMapThreads)
+build_dispatch_kernel(const int *__restrict__ expert_indices, int64_t total, int num_experts, int capacity,
+                      int *__restrict__ dispatch_map, int *__restrict__ expert_offsets)
+{
+  extern __shared__ int s_map[];
+  int *running = s_map;                      // [E]
+  int *warp_hist = s_map + num_experts;      // [warps][E]
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  for (int e = tid; e < num_experts; e += kMapThreads)
+  {
+    running[e] = 0;
+  }
+  __syncthreads();
+  for (int64_t base = 0; base < total; base += kMapThreads)
+  {
+    for (int e = lane; e < num_experts; e += 32)
+    {
+      warp_hist[warp * num_experts + e] = 0;
+    }
+    __syncwarp();
+    const int64_t i = base + tid;
+    int e = -1;
+    if (i < total)
+    {
+      const int v = expert_indices[i];
+      if (v >= 0 && v < num_experts)
+      {
+        e = v;
+      }
+    }
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+    const int lane_rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && lane_rank == 0)
+    {
+      warp_hist[warp * num_experts + e] = __popc(peers);
+    }
+    __syncthreads();
+    // exclusive scan over warps, per expert; fold the chunk into the running count
+    for (int x = tid; x < num_experts; x += kMapThreads)
+    {
+      int acc = running[x];
+      for (int w = 0; w < kMapWarps; ++w)
+      {
+        const int c = warp_hist[w * num_experts + x];
+        warp_hist[w * num_experts + x] = acc;
+        acc += c;
+      }
+      running[x] = acc;
+    }
+    __syncthreads();
+    if (i < total)
+    {
+      int pos = -1;
+      if (e >= 0)
+      {
+        const int rank = warp_hist[warp * num_experts + e] + lane_rank;
+        if (capacity <= 0 || rank < capacity)
+        {
+          pos = rank;
+        }
+      }
+      dispatch_map[i] = pos;
+    }
+    __syncthreads();
+  }
+  if (tid == 0)
+  {
+    int acc = 0;
+    expert_offsets[0] = 0;
+    for (int e = 0; e < num_experts; ++e)
+    {
+      int c = running[e];
+      if (capacity > 0 && c > capacity)
+      {
+        c = capacity;
+      }
+      acc += c;
+      expert_offsets[e + 1] = acc;
+    }
+  }
+}
+
+// ------------------------------------------------------------- dispatch / combine
+template <typename T>
+__global__ void moe_dispatch_kernel(const T *__restrict__ input, const int *__restrict__ expert_indices,
+                                    const int *__restrict__ dispatch_map, const int *__restrict__ expert_offsets,
+                                    T *__restrict__ buffer, int64_t assignments, int dim, int top_k)
+{
+  const int lane = threadIdx.x & 31;
+  const int64_t a = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (a >= assignments)
+  {
+    return;
+  }
+  const int e = expert_indices[a];
+  const int pos = dispatch_map[a];
+  if (e < 0 || pos < 0)
+  {
+    return;
+  }
+  const T *src = input + (a / top_k) * dim;
+  T *dst = buffer + (static_cast<int64_t>(expert_offsets[e]) + pos) * dim;
+  const int vec = 16 / static_cast<int>(sizeof(T));
+  if ((dim % vec) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0)
+  {
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+    uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+    for (int i = lane; i < dim / vec; i += 32)
+    {
+      d4[i] = s4[i];
+    }
+  }
+  else
+  {
+    for (int i = lane; i < dim; i += 32)
+    {
+      dst[i] = src[i];
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T *__restrict__ buffer, const int *__restrict__ expert_indices,
+                                   const T *__restrict__ expert_weights, const int *__restrict__ dispatch_map,
+                                   const int *__restrict__ expert_offsets, T *__restrict__ output, int num_tokens,
+                                   int dim, int top_k)
+{
+  const int64_t total = static_cast<int64_t>(num_tokens) * dim;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    const int token = static_cast<int>(i / dim);
+    const int d = static_cast<int>(i % dim);
+    float sum = 0.0f;
+    for (int k = 0; k < top_k; ++k)
+    {
+      const int e = expert_indices[token * top_k + k];
+      const int pos = dispatch_map[token * top_k + k];
+      if (e >= 0 && pos >= 0)
+      {
+        const float w = to_f<T>(expert_weights[token * top_k + k]);
+        const float v = to_f<T>(buffer[(static_cast<int64_t>(expert_offsets[e]) + pos) * dim + d]);
+        sum = fmaf(w, v, sum);
+      }
+    }
+    output[i] = from_f<T>(sum);
+  }
+}
+
+// ------------------------------------------------------------------- SwiGLU
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ hidden,
+                                  int64_t n)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+  {
+    const float x = to_f<T>(gate[i]);
+    const T act = from_f<T>(x / (1.0f + expf(-x)));
+    hidden[i] = from_f<T>(to_f<T>(act) * to_f<T>(up[i]));
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T *__restrict__ g_hidden, const T *__restrict__ gate,
+                                  const T *__restrict__ up, T *__restrict__ g_gate, T *__restrict__ g_up, int64_t n)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+  {
+    const float x = to_f<T>(gate[i]);
+    const float gh = to_f<T>(g_hidden[i]);
+    const T act = from_f<T>(x / (1.0f + expf(-x)));
+    g_up[i] = from_f<T>(gh * to_f<T>(act));
+    const float gv = to_f<T>(from_f<T>(gh * to_f<T>(up[i])));
+    const float s = 1.0f / (1.0f + expf(-x));
+    g_gate[i] = from_f<T>(gv * s * (1.0f + x * (1.0f - s)));
+  }
+}
+
+template <typename T>
+__global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ out, int64_t n)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+  {
+    out[i] = from_f<T>(to_f<T>(a[i]) + to_f<T>(b[i]));
+  }
+}
+
+inline int ew_grid(int64_t n)
+{
+  int64_t g = (n + 255) / 256;
+  if (g > 148 * 16)
+  {
+    g = 148 * 16;
+  }
+  return static_cast<int>(g < 1 ? 1 : g);
+}
+
+}  // namespace
+
+#define CAIFQ_DISPATCH_FLOAT(dtype, CALL)          \
+  switch (dtype)                                   \
+  {                                                \
+    case CAIFQ_F32:                                \
+    {                                              \
+      using T = float;                             \
+      CALL;                                        \
+      break;                                       \
+    }                                              \
+    case CAIFQ_F16:                                \
+    {                                              \
+      using T = __half;                            \
+      CALL;                                        \
+      break;                                       \
+    }                                              \
+    case CAIFQ_BF16:                               \
+    {                                              \
+      using T = __nv_bfloat16;                     \
+      CALL;                                        \
+      break;                                       \
+    }                                              \
+    default:                                       \
+      set_error("unsupported dtype %d", dtype);    \
+      return CAIFQ_ERR_INVALID;                    \
+  }
+
+int launch_moe_topk(const void *probs, int dtype, int *indices, void *values, int batch, int dim, int k,
+                    cudaStream_t s)
+{
+  if (batch <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  int warps = 8;
+  while (warps > 1 && static_cast<size_t>(warps) * dim * sizeof(float) > 40 * 1024)
+  {
+    warps >>= 1;
+  }
+  const size_t smem = static_cast<size_t>(warps) * dim * sizeof(float);
+  if (smem > 48 * 1024)
+  {
+    set_error("moe_topk: dim=%d too large", dim);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  const int grid = (batch + warps - 1) / warps;
+  CAIFQ_DISPATCH_FLOAT(dtype, (topk_kernel<T><<<grid, warps * 32, smem, s>>>(
+                                  static_cast<const T *>(probs), indices, static_cast<T *>(values), batch, dim, k)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_normalize_rows(const void *input, void *output, int dtype, int batch, int dim, cudaStream_t s)
+{
+  if (batch <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const int warps = 8;
+  const int grid = (batch + warps - 1) / warps;
+  CAIFQ_DISPATCH_FLOAT(dtype, (normalize_rows_kernel<T><<<grid, warps * 32, 0, s>>>(
+                                  static_cast<const T *>(input), static_cast<T *>(output), batch, dim)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_build_dispatch(const int *expert_indices, int num_tokens, int top_k, int num_experts, int capacity,
+                              int *dispatch_map, int *expert_offsets, cudaStream_t s)
+{
+  const size_t smem = static_cast<size_t>(num_experts) * (kMapWarps + 1) * sizeof(int);
+  if (smem > 48 * 1024)
+  {
+    set_error("moe_build_dispatch: num_experts=%d exceeds the supported %d", num_experts,
+              static_cast<int>(48 * 1024 / ((kMapWarps + 1) * sizeof(int))));
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  const int64_t total = static_cast<int64_t>(num_tokens) * top_k;
+  build_dispatch_kernel<<<1, kMapThreads, smem, s>>>(expert_indices, total, num_experts, capacity, dispatch_map,
+                                                     expert_offsets);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_dispatch(const void *input, int dtype, const int *expert_indices, const int *dispatch_map,
+                        const int *expert_offsets, void *buffer, int num_tokens, int dim, int top_k, cudaStream_t s)
+{
+  const int64_t assignments = static_cast<int64_t>(num_tokens) * top_k;
+  if (assignments <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const int64_t grid = (assignments * 32 + 255) / 256;
+  CAIFQ_DISPATCH_FLOAT(dtype, (moe_dispatch_kernel<T><<<static_cast<unsigned>(grid), 256, 0, s>>>(
+                                  static_cast<const T *>(input), expert_indices, dispatch_map, expert_offsets,
+                                  static_cast<T *>(buffer), assignments, dim, top_k)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_combine(const void *buffer, int dtype, const int *expert_indices, const void *expert_weights,
+                       const int *dispatch_map, const int *expert_offsets, void *output, int num_tokens, int dim,
+                       int top_k, cudaStream_t s)
+{
+  const int64_t total = static_cast<int64_t>(num_tokens) * dim;
+  if (total <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (moe_combine_kernel<T><<<ew_grid(total), 256, 0, s>>>(
+                                  static_cast<const T *>(buffer), expert_indices,
+                                  static_cast<const T *>(expert_weights), dispatch_map, expert_offsets,
+                                  static_cast<T *>(output), num_tokens, dim, top_k)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_swiglu_fwd(const void *gate, const void *up, void *hidden, int dtype, int64_t n, cudaStream_t s)
+{
+  if (n <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (swiglu_fwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
+                                  static_cast<const T *>(gate), static_cast<const T *>(up), static_cast<T *>(hidden),
+                                  n)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_swiglu_bwd(const void *g_hidden, const void *gate, const void *up, void *g_gate, void *g_up, int dtype,
+                      int64_t n, cudaStream_t s)
+{
+  if (n <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (swiglu_bwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
+                                  static_cast<const T *>(g_hidden), static_cast<const T *>(gate),
+                                  static_cast<const T *>(up), static_cast<T *>(g_gate), static_cast<T *>(g_up), n)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_add(const void *a, const void *b, void *out, int dtype, int64_t n, cudaStream_t s)
+{
+  if (n <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (add_kernel<T><<<ew_grid(n), 256, 0, s>>>(
+                                  static_cast<const T *>(a), static_cast<const T *>(b), static_cast<T *>(out), n)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+}  // namespace caifq

@@ -1,0 +1,390 @@
+"""ctypes binding of libcaifq.so (the C ABI in include/caifq.h) for torch tensors.
+
+PyTorch is used for device memory and streams only: every function here hands
+raw device pointers to the shared library.  There is no fallback: if the
+library is missing or the call fails, a CaifqError is raised.
+"""
+import ctypes
+import os
+
+import torch
+
+F32, F16, BF16, I4, I8 = 0, 2, 3, 4, 5
+PER_TENSOR, PER_CHANNEL = 0, 1
+
+_TORCH_TO_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: I8}
+_CODE_TO_TORCH = {F32: torch.float32, F16: torch.float16, BF16: torch.bfloat16, I8: torch.int8}
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libcaifq.so")
+
+
+class CaifqError(RuntimeError):
+    pass
+
+
+class CWeight(ctypes.Structure):
+    _fields_ = [
+        ("codes", ctypes.c_void_p),
+        ("scales", ctypes.c_void_p),
+        ("storage", ctypes.c_int32),
+        ("scheme", ctypes.c_int32),
+        ("group_size", ctypes.c_int32),
+        ("in_dim", ctypes.c_int32),
+        ("out_dim", ctypes.c_int32),
+    ]
+
+
+class CLora(ctypes.Structure):
+    _fields_ = [
+        ("a", ctypes.c_void_p),
+        ("b", ctypes.c_void_p),
+        ("dtype", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("alpha", ctypes.c_float),
+    ]
+
+
+_lib = None
+
+_vp = ctypes.c_void_p
+_i32 = ctypes.c_int32
+_i64 = ctypes.c_int64
+
+_SIGNATURES = {
+    "caifq_last_error": (ctypes.c_char_p, []),
+    "caifq_last_path": (ctypes.c_char_p, []),
+    "caifq_version": (ctypes.c_char_p, []),
+    "caifq_device_ok": (ctypes.c_int, []),
+    "caifq_quantize_int8_per_tensor": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp]),
+    "caifq_quantize_int8_per_channel": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _vp]),
+    "caifq_quantize_int4_per_group": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "caifq_dequantize_int8_per_tensor": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp]),
+    "caifq_dequantize_int8_per_channel": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _vp]),
+    "caifq_dequantize_int4": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "caifq_cast": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _vp]),
+    "caifq_weight_materialize": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _vp]),
+    "caifq_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_linear_dx": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
+                                             _i32, _vp]),
+    "caifq_lora_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
+    "caifq_lora_linear_bwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _vp, _vp, _i64,
+                                             _vp, _vp, _vp, _vp, _i32, _vp]),
+    "caifq_moe_topk": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_normalize_rows": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_build_dispatch": (ctypes.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "caifq_moe_dispatch": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_combine": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_grouped_expert_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
+                                                ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp, _vp,
+                                                _vp, _vp, _i32, _i32, _vp]),
+    "caifq_grouped_expert_bwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
+                                                ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp, _vp,
+                                                _vp, _vp, _i32, _i32, _vp]),
+}
+
+
+def exported_names():
+    """Names this binding expects libcaifq.so to export."""
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    """The loaded shared library; raises CaifqError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise CaifqError("%s is missing: run `python -m caif_b200.build` (there is no fallback path)" % LIB_PATH)
+        loaded = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(loaded, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = loaded
+    return _lib
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise CaifqError("%s failed (%d): %s" % (what, rc, lib().caifq_last_error().decode()))
+
+
+def last_path():
+    return lib().caifq_last_path().decode()
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    if t is None:
+        return ctypes.c_void_p(None)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise CaifqError("caifq works on CUDA tensors only (no CPU fallback)")
+        if t is not None and not t.is_contiguous():
+            raise CaifqError("caifq needs contiguous tensors")
+
+
+def dtype_code(t):
+    return _TORCH_TO_CODE[t] if isinstance(t, torch.dtype) else _TORCH_TO_CODE[t.dtype]
+
+
+class Weight:
+    """A frozen weight: codes + scales as the reference's quantize ops produce them."""
+
+    def __init__(self, codes, storage, in_dim, out_dim, scales=None, scheme=PER_TENSOR, group_size=128):
+        _need_cuda(codes, scales)
+        self.codes = codes
+        self.scales = scales
+        self.storage = storage
+        self.scheme = scheme
+        self.group_size = group_size
+        self.in_dim = in_dim
+        self.out_dim = out_dim
+        self.c = CWeight(codes.data_ptr(), scales.data_ptr() if scales is not None else None, storage, scheme,
+                         group_size, in_dim, out_dim)
+
+    def ref(self):
+        return ctypes.byref(self.c)
+
+    def rows(self, begin, end):
+        """Column-parallel shard: output features [begin, end) -- a contiguous slice of codes and scales."""
+        n = end - begin
+        if self.storage == I4:
+            if self.in_dim % self.group_size != 0 or (self.in_dim % 2) != 0:
+                raise CaifqError("int4 row shards need in_dim to be a multiple of the group size")
+            gpr = self.in_dim // self.group_size
+            codes = self.codes.view(-1)[begin * self.in_dim // 2: end * self.in_dim // 2]
+            scales = self.scales.view(-1)[begin * gpr: end * gpr]
+            return Weight(codes, I4, self.in_dim, n, scales, self.scheme, self.group_size)
+        codes = self.codes.view(-1)[begin * self.in_dim: end * self.in_dim]
+        scales = self.scales
+        if self.storage == I8 and self.scheme == PER_CHANNEL and scales is not None:
+            raise CaifqError("per-channel int8 scales are indexed by flat % out_dim and do not shard by rows")
+        return Weight(codes, self.storage, self.in_dim, n, scales, self.scheme, self.group_size)
+
+
+# ---- quantize / dequantize ---------------------------------------------------
+
+def quantize_int8_per_tensor(x):
+    _need_cuda(x)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    _check(lib().caifq_quantize_int8_per_tensor(_ptr(x), _ptr(q), _ptr(scale), x.numel(), _stream()),
+           "quantize_int8_per_tensor")
+    return q, scale
+
+
+def quantize_int8_per_channel(x):
+    _need_cuda(x)
+    rows, cols = x.shape
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scales = torch.empty(cols, dtype=torch.float32, device=x.device)
+    _check(lib().caifq_quantize_int8_per_channel(_ptr(x), _ptr(q), _ptr(scales), rows, cols, _stream()),
+           "quantize_int8_per_channel")
+    return q, scales
+
+
+def quantize_int4(x, group_size=128):
+    _need_cuda(x)
+    n = x.numel()
+    packed = torch.zeros((n + 1) // 2, dtype=torch.uint8, device=x.device)
+    scales = torch.zeros((n + group_size - 1) // group_size, dtype=torch.float16, device=x.device)
+    _check(lib().caifq_quantize_int4_per_group(_ptr(x), _ptr(packed), _ptr(scales), n, group_size, _stream()),
+           "quantize_int4_per_group")
+    return packed, scales
+
+
+def dequantize_int8_per_tensor(q, scale):
+    _need_cuda(q, scale)
+    out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    _check(lib().caifq_dequantize_int8_per_tensor(_ptr(q), _ptr(out), _ptr(scale), q.numel(), _stream()),
+           "dequantize_int8_per_tensor")
+    return out
+
+
+def dequantize_int8_per_channel(q, scales):
+    _need_cuda(q, scales)
+    rows, cols = q.shape
+    out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    _check(lib().caifq_dequantize_int8_per_channel(_ptr(q), _ptr(out), _ptr(scales), rows, cols, _stream()),
+           "dequantize_int8_per_channel")
+    return out
+
+
+def dequantize_int4(packed, scales, n, group_size=128):
+    _need_cuda(packed, scales)
+    out = torch.empty(n, dtype=torch.float32, device=packed.device)
+    _check(lib().caifq_dequantize_int4(_ptr(packed), _ptr(scales), _ptr(out), n, group_size, _stream()),
+           "dequantize_int4")
+    return out
+
+
+def cast(x, dtype):
+    _need_cuda(x)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(lib().caifq_cast(_ptr(x), dtype_code(x), _ptr(out), dtype_code(dtype), x.numel(), _stream()), "cast")
+    return out
+
+
+def weight_materialize(w, dtype=torch.float32):
+    out = torch.empty((w.out_dim, w.in_dim), dtype=dtype, device=w.codes.device)
+    _check(lib().caifq_weight_materialize(w.ref(), _ptr(out), dtype_code(dtype), _stream()), "weight_materialize")
+    return out
+
+
+# ---- frozen linear -----------------------------------------------------------
+
+def linear_fwd(w, x, out_dtype=torch.float32, compute=F32, out=None):
+    _need_cuda(x)
+    m = x.numel() // w.in_dim
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (w.out_dim,), dtype=out_dtype, device=x.device)
+    _check(lib().caifq_linear_fwd(w.ref(), _ptr(x), dtype_code(x), m, _ptr(out), dtype_code(out), compute, _stream()),
+           "linear_fwd")
+    return out
+
+
+def linear_dx(w, dy, out_dtype=torch.float32, compute=F32, out=None):
+    _need_cuda(dy)
+    m = dy.numel() // w.out_dim
+    if out is None:
+        out = torch.empty(tuple(dy.shape[:-1]) + (w.in_dim,), dtype=out_dtype, device=dy.device)
+    _check(lib().caifq_linear_dx(w.ref(), _ptr(dy), dtype_code(dy), m, _ptr(out), dtype_code(out), compute, _stream()),
+           "linear_dx")
+    return out
+
+
+# ---- LoRA --------------------------------------------------------------------
+
+class Lora:
+    def __init__(self, a, b, alpha):
+        _need_cuda(a, b)
+        self.a = a
+        self.b = b
+        self.alpha = float(alpha)
+        self.rank = a.shape[0]
+        self.c = CLora(a.data_ptr(), b.data_ptr(), dtype_code(a), self.rank, self.alpha)
+
+    def ref(self):
+        return ctypes.byref(self.c)
+
+
+def lora_linear_fwd(w, lora, x, compute=F32):
+    _need_cuda(x)
+    m = x.numel() // w.in_dim
+    y = torch.empty(tuple(x.shape[:-1]) + (w.out_dim,), dtype=x.dtype, device=x.device)
+    hidden = torch.empty((m, lora.rank), dtype=x.dtype, device=x.device)
+    _check(lib().caifq_lora_linear_fwd(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), compute, _stream()),
+           "lora_linear_fwd")
+    return y, hidden
+
+
+def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32):
+    _need_cuda(dy, x, hidden)
+    m = dy.numel() // w.out_dim
+    dx = torch.empty(tuple(dy.shape[:-1]) + (w.in_dim,), dtype=dy.dtype, device=dy.device)
+    d_a = torch.empty_like(lora.a)
+    d_b = torch.empty_like(lora.b)
+    ws_bytes = lib().caifq_lora_bwd_workspace_bytes(w.ref(), lora.ref(), m)
+    ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=dy.device)
+    _check(lib().caifq_lora_linear_bwd(w.ref(), lora.ref(), _ptr(dy), _ptr(x), _ptr(hidden), m, _ptr(dx), _ptr(d_a),
+                                       _ptr(d_b), _ptr(ws), compute, _stream()), "lora_linear_bwd")
+    return dx, d_a, d_b
+
+
+# ---- MoE ---------------------------------------------------------------------
+
+def moe_topk(probs, k):
+    _need_cuda(probs)
+    batch, dim = probs.shape
+    idx = torch.empty((batch, k), dtype=torch.int32, device=probs.device)
+    val = torch.empty((batch, k), dtype=probs.dtype, device=probs.device)
+    _check(lib().caifq_moe_topk(_ptr(probs), dtype_code(probs), _ptr(idx), _ptr(val), batch, dim, k, _stream()),
+           "moe_topk")
+    return idx, val
+
+
+def moe_normalize_rows(x):
+    _need_cuda(x)
+    batch, dim = x.shape
+    out = torch.empty_like(x)
+    _check(lib().caifq_moe_normalize_rows(_ptr(x), _ptr(out), dtype_code(x), batch, dim, _stream()),
+           "moe_normalize_rows")
+    return out
+
+
+def moe_build_dispatch(expert_indices, num_experts, capacity=0):
+    _need_cuda(expert_indices)
+    tokens, top_k = expert_indices.shape
+    dmap = torch.empty((tokens, top_k), dtype=torch.int32, device=expert_indices.device)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=expert_indices.device)
+    _check(lib().caifq_moe_build_dispatch(_ptr(expert_indices), tokens, top_k, num_experts, capacity, _ptr(dmap),
+                                          _ptr(offsets), _stream()), "moe_build_dispatch")
+    return dmap, offsets
+
+
+def moe_dispatch(x, expert_indices, dispatch_map, expert_offsets, total_assigned):
+    _need_cuda(x, expert_indices, dispatch_map, expert_offsets)
+    tokens, dim = x.shape
+    top_k = expert_indices.shape[1]
+    buf = torch.zeros((total_assigned, dim), dtype=x.dtype, device=x.device)
+    _check(lib().caifq_moe_dispatch(_ptr(x), dtype_code(x), _ptr(expert_indices), _ptr(dispatch_map),
+                                    _ptr(expert_offsets), _ptr(buf), tokens, dim, top_k, _stream()), "moe_dispatch")
+    return buf
+
+
+def moe_combine(buf, expert_indices, weights, dispatch_map, expert_offsets, num_tokens):
+    _need_cuda(buf, expert_indices, weights, dispatch_map, expert_offsets)
+    dim = buf.shape[1]
+    top_k = expert_indices.shape[1]
+    out = torch.empty((num_tokens, dim), dtype=buf.dtype, device=buf.device)
+    _check(lib().caifq_moe_combine(_ptr(buf), dtype_code(buf), _ptr(expert_indices), _ptr(weights),
+                                   _ptr(dispatch_map), _ptr(expert_offsets), _ptr(out), num_tokens, dim, top_k,
+                                   _stream()), "moe_combine")
+    return out
+
+
+def _weight_array(ws):
+    arr = (CWeight * len(ws))()
+    for i, w in enumerate(ws):
+        arr[i] = w.c
+    return arr
+
+
+def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32):
+    """gate/up/down: lists of Weight; offsets_host: list of E+1 ints; x: packed [total, in]."""
+    _need_cuda(x)
+    n_exp = len(gate)
+    total = int(offsets_host[-1])
+    hid = up[0].out_dim
+    out = torch.empty((total, up[0].in_dim), dtype=x.dtype, device=x.device)
+    gate_out = torch.empty((total, hid), dtype=x.dtype, device=x.device)
+    up_out = torch.empty((total, hid), dtype=x.dtype, device=x.device)
+    hidden = torch.empty((total, hid), dtype=x.dtype, device=x.device)
+    offs = (ctypes.c_int32 * (n_exp + 1))(*[int(v) for v in offsets_host])
+    _check(lib().caifq_grouped_expert_fwd(_weight_array(gate), _weight_array(up), _weight_array(down), n_exp, offs,
+                                          _ptr(x), _ptr(out), _ptr(gate_out), _ptr(up_out), _ptr(hidden),
+                                          dtype_code(x), compute, _stream()), "grouped_expert_fwd")
+    return out, gate_out, up_out
+
+
+def grouped_expert_bwd(gate, up, down, offsets_host, dy, gate_out, up_out, compute=F32):
+    _need_cuda(dy, gate_out, up_out)
+    n_exp = len(gate)
+    total = int(offsets_host[-1])
+    hid = up[0].out_dim
+    dx = torch.empty((total, up[0].in_dim), dtype=dy.dtype, device=dy.device)
+    ws = torch.empty((3, max(total, 1), hid), dtype=dy.dtype, device=dy.device)
+    offs = (ctypes.c_int32 * (n_exp + 1))(*[int(v) for v in offsets_host])
+    _check(lib().caifq_grouped_expert_bwd(_weight_array(gate), _weight_array(up), _weight_array(down), n_exp, offs,
+                                          _ptr(dy), _ptr(gate_out), _ptr(up_out), _ptr(dx), _ptr(ws),
+                                          dtype_code(dy), compute, _stream()), "grouped_expert_bwd")
+    return dx

@@ -1,0 +1,228 @@
+/*
+ * caifq -- C ABI of the B200-native quantized frozen-linear path.
+ *
+ * One shared library (libcaifq.so, sm_100a only) replaces the device work
+ * behind the reference's CAIF_DeviceFrozenLinear / CAIF_DeviceLoRAAdapter /
+ * CAIF_DeviceMoEFrozenExpert / CAIF_DeviceMoELayer hot path.  The reference has
+ * no C ABI of its own: each entry point below names the reference function
+ * whose device work it takes over (paths are relative to the reference
+ * checkout).
+ *
+ * Conventions
+ *   - every data pointer is a DEVICE pointer unless the name ends in _host;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it
+ *     and no entry point synchronises unless it says so;
+ *   - return value 0 = success, anything else = failure; the text of the last
+ *     failure on the calling thread is available from caifq_last_error();
+ *   - dtype codes equal the reference's CAIF_DataType_e
+ *     (include/caif/caif_data_type.h:32-48) so a binding can pass them through;
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point fails.
+ */
+#ifndef CAIFQ_H
+#define CAIFQ_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CAIFQ_API __attribute__((visibility("default")))
+#else
+#define CAIFQ_API
+#endif
+
+#define CAIFQ_OK 0
+#define CAIFQ_ERR_INVALID 1  /* bad argument (shape, dtype, null pointer) */
+#define CAIFQ_ERR_CUDA 2     /* a CUDA runtime call or launch failed */
+#define CAIFQ_ERR_UNSUPPORTED 3
+
+typedef enum caifq_dtype
+{
+  CAIFQ_F32 = 0,
+  CAIFQ_F16 = 2,
+  CAIFQ_BF16 = 3,
+  CAIFQ_I4 = 4, /* two codes per byte, even flat index in the low nibble */
+  CAIFQ_I8 = 5
+} caifq_dtype;
+
+/* CAIF_Ops::QuantScheme_e, include/caif/caif_ops.h:365-369 */
+typedef enum caifq_scheme
+{
+  CAIFQ_PER_TENSOR = 0,
+  CAIFQ_PER_CHANNEL = 1
+} caifq_scheme;
+
+/*
+ * A frozen weight exactly as CAIF_DeviceFrozenLinear holds it
+ * (src/caif_device_frozen_linear.cpp:126-142, 234-276): `codes` is the flat
+ * row-major [out_dim, in_dim] buffer in `storage` dtype; `scales` is
+ *   I4: fp16 [ceil(in*out/group_size)], groups over the flat index;
+ *   I8: fp32 [1] (per-tensor) or fp32 [out_dim] (per-channel, indexed by
+ *       flat index % out_dim), or NULL = plain integer-to-float cast;
+ *   float storage: NULL.
+ */
+typedef struct caifq_weight
+{
+  const void *codes;
+  const void *scales;
+  int32_t storage;    /* caifq_dtype */
+  int32_t scheme;     /* caifq_scheme, I8 only */
+  int32_t group_size; /* I4 only */
+  int32_t in_dim;
+  int32_t out_dim;
+} caifq_weight;
+
+/* LoRA factors as CAIF_DeviceLoRAAdapter holds them
+ * (src/caif_device_lora_adapter.cpp:53-60): A [rank, in], B [out, rank]. */
+typedef struct caifq_lora
+{
+  const void *a;
+  const void *b;
+  int32_t dtype; /* F32, F16 or BF16: dtype of A, B and of every LoRA intermediate */
+  int32_t rank;
+  float alpha;
+} caifq_lora;
+
+CAIFQ_API const char *caifq_last_error(void);
+/* 1 when a CUDA device of compute capability 10.x is current, else 0. */
+CAIFQ_API int caifq_device_ok(void);
+CAIFQ_API const char *caifq_version(void);
+
+/* ---- quantize / dequantize (bit-exact with the reference kernels) -------- */
+
+/* launch_quantize_int8_per_tensor, src/caif_cuda_kernels_quant.cu:458-483 */
+CAIFQ_API int caifq_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int64_t n, void *stream);
+/* launch_quantize_int8_per_channel, src/caif_cuda_kernels_quant.cu:576-600 */
+CAIFQ_API int caifq_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, int32_t rows, int32_t cols,
+                                    void *stream);
+/* launch_quantize_to_int4, src/caif_cuda_kernels_quant.cu:344-362 */
+CAIFQ_API int caifq_quantize_int4_per_group(const float *x, uint8_t *packed, uint16_t *scales_f16, int64_t n,
+                                  int32_t group_size, void *stream);
+/* launch_dequantize_int8_per_tensor, src/caif_cuda_kernels_quant.cu:485-500 */
+CAIFQ_API int caifq_dequantize_int8_per_tensor(const int8_t *q, float *out, const float *scale, int64_t n, void *stream);
+/* launch_dequantize_int8_per_channel, src/caif_cuda_kernels_quant.cu:602-620 */
+CAIFQ_API int caifq_dequantize_int8_per_channel(const int8_t *q, float *out, const float *scales, int32_t rows, int32_t cols,
+                                      void *stream);
+/* launch_dequantize_int4, src/caif_cuda_kernels_quant.cu:239-256 */
+CAIFQ_API int caifq_dequantize_int4(const uint8_t *packed, const uint16_t *scales_f16, float *out, int64_t n,
+                          int32_t group_size, void *stream);
+/* CAIF_DeviceTensor::To between F32/F16/BF16/I8, src/caif_device_tensor.cpp:604-706
+ * (kernels src/caif_cuda_kernels_quant.cu:38-199) */
+CAIFQ_API int caifq_cast(const void *src, int32_t src_dtype, void *dst, int32_t dst_dtype, int64_t n, void *stream);
+
+/* CAIF_DeviceFrozenLinear::FrozenTensorFP32 / ConvertToComputeDtype,
+ * src/caif_device_frozen_linear.cpp:288-378, 759-826: the [out,in] weight in
+ * `dst_dtype` (F32/F16/BF16), reduced dtypes by way of fp32 as the reference does. */
+CAIFQ_API int caifq_weight_materialize(const caifq_weight *w, void *dst, int32_t dst_dtype, void *stream);
+
+/* ---- frozen linear ------------------------------------------------------- */
+
+/*
+ * CAIF_DeviceFrozenLinear::ForwardImpl, src/caif_device_frozen_linear.cpp:381-524.
+ *   y[m, out] = x[m, in] . W_deq[out, in]^T, fp32 accumulate.
+ * x_dtype in {F32,F16,BF16}; compute_dtype in {F32,F16,BF16} selects the
+ * operand precision (the reference's ComputeT); y_dtype F32 (what the reference
+ * returns), or F16/BF16 for callers that cast straight after.
+ * The weight is dequantized on the fly inside the kernel: no [out,in] float
+ * copy is ever written to memory.
+ */
+CAIFQ_API int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *y, int32_t y_dtype,
+                     int32_t compute_dtype, void *stream);
+
+/*
+ * CAIF_DeviceFrozenLinear::BackwardImpl, src/caif_device_frozen_linear.cpp:526-660.
+ *   dx[m, in] = dy[m, out] . W_deq[out, in], fp32 accumulate.  No weight gradient.
+ */
+CAIFQ_API int caifq_linear_dx(const caifq_weight *w, const void *dy, int32_t dy_dtype, int64_t m, void *dx, int32_t dx_dtype,
+                    int32_t compute_dtype, void *stream);
+
+/* Name of the kernel family the last caifq_linear_fwd / caifq_linear_dx call
+ * on this thread chose ("decode", "umma", "generic"); for tests and reports. */
+CAIFQ_API const char *caifq_last_path(void);
+
+/* ---- LoRA on a frozen linear --------------------------------------------- */
+
+/*
+ * CAIF_DeviceLoRAAdapter::ForwardImpl over a frozen base,
+ * src/caif_device_lora_adapter.cpp:119-203:
+ *   hidden[m, r] = x . A^T;  y = W-path(x) + (alpha/r) . hidden . B^T
+ * x, y, hidden are in lora->dtype.  `hidden` [m, r] is required: it is the
+ * tensor the reference caches for backward, and the up-projection reads it.
+ */
+CAIFQ_API int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
+                          void *hidden, int32_t compute_dtype, void *stream);
+
+/*
+ * CAIF_DeviceLoRAAdapter::BackwardImpl, src/caif_device_lora_adapter.cpp:205-281:
+ *   g = (alpha/r) dy;  dB = g^T hidden;  dH = g B;  dA = dH^T x;
+ *   dx = dy . W_deq + dH . A
+ * dA [r,in] and dB [out,r] are OVERWRITTEN (the reference's GEMMs run with
+ * beta = 0).  All tensors in lora->dtype.  `workspace` must hold
+ * caifq_lora_bwd_workspace_bytes(w, lora, m) bytes of device memory (dH plus
+ * the fp32 scratch of the two reductions over tokens).
+ */
+CAIFQ_API size_t caifq_lora_bwd_workspace_bytes(const caifq_weight *w, const caifq_lora *lora, int64_t m);
+CAIFQ_API int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
+                          const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
+                          int32_t compute_dtype, void *stream);
+
+/* ---- MoE routing and dispatch -------------------------------------------- */
+
+/* launch_topk, src/caif_cuda_kernels_moe.cu:280-345: descending values, ties to
+ * the lowest index; `dtype` is the dtype of probs and values. */
+CAIFQ_API int caifq_moe_topk(const void *probs, int32_t dtype, int32_t *indices, void *values, int32_t batch, int32_t dim,
+                   int32_t k, void *stream);
+/* launch_normalize_rows, src/caif_cuda_kernels_moe.cu:43-97 */
+CAIFQ_API int caifq_moe_normalize_rows(const void *input, void *output, int32_t dtype, int32_t batch, int32_t dim,
+                             void *stream);
+/*
+ * CAIF_Ops::MoEBuildDispatchMap, src/caif_ops_device.cpp:4876-4950, computed on
+ * the device with the identical result: expert_offsets[E+1] (exclusive prefix
+ * sum of the capacity-clamped counts) and dispatch_map[T,k] (arrival order
+ * within the expert scanning tokens then k; -1 = dropped).  The total assigned
+ * is expert_offsets[E]; no host copy is made.  capacity 0 = unlimited.
+ */
+CAIFQ_API int caifq_moe_build_dispatch(const int32_t *expert_indices, int32_t num_tokens, int32_t top_k, int32_t num_experts,
+                             int32_t capacity, int32_t *dispatch_map, int32_t *expert_offsets, void *stream);
+/* launch_moe_dispatch, src/caif_cuda_kernels_moe.cu:616-680 */
+CAIFQ_API int caifq_moe_dispatch(const void *input, int32_t dtype, const int32_t *expert_indices, const int32_t *dispatch_map,
+                       const int32_t *expert_offsets, void *expert_buffer, int32_t num_tokens, int32_t dim,
+                       int32_t top_k, void *stream);
+/* launch_moe_combine, src/caif_cuda_kernels_moe.cu:705-790 */
+CAIFQ_API int caifq_moe_combine(const void *expert_buffer, int32_t dtype, const int32_t *expert_indices,
+                      const void *expert_weights, const int32_t *dispatch_map, const int32_t *expert_offsets,
+                      void *output, int32_t num_tokens, int32_t dim, int32_t top_k, void *stream);
+
+/* ---- grouped frozen experts ---------------------------------------------- */
+
+/*
+ * The per-expert loop of CAIF_DeviceMoELayer::ForwardImpl over
+ * CAIF_DeviceMoEFrozenExpert::ForwardInto (src/caif_device_moe_layer.cpp:534-557,
+ * src/caif_device_moe_frozen_expert.cpp:91-229) as ONE grouped call:
+ * for every expert e, rows [offsets[e], offsets[e+1]) of the packed buffer go
+ * through  down_e( silu(gate_e(x)) * up_e(x) ).
+ * gate/up/down are arrays of num_experts weights (host array of structs whose
+ * pointers are device pointers).  x, out, and the saved gate_out / up_out
+ * (each [total, hidden], may be NULL when not training) are in `dtype`.
+ * expert_offsets_host is the host copy of the offsets (E+1 ints).
+ */
+CAIFQ_API int caifq_grouped_expert_fwd(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                             int32_t num_experts, const int32_t *expert_offsets_host, const void *x, void *out,
+                             void *gate_out, void *up_out, void *hidden_ws, int32_t dtype, int32_t compute_dtype,
+                             void *stream);
+/* Backward of the same loop (src/caif_device_moe_layer.cpp:754-778,
+ * src/caif_device_moe_frozen_expert.cpp:232-332): dX only.
+ * ws must hold 3 * total * hidden elements of `dtype`. */
+CAIFQ_API int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                             int32_t num_experts, const int32_t *expert_offsets_host, const void *dy,
+                             const void *gate_out, const void *up_out, void *dx, void *ws, int32_t dtype,
+                             int32_t compute_dtype, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAIFQ_H */

@@ -1,0 +1,86 @@
+// C-linkage doorway onto the reference's own device kernels.
+//
+// TEST INFRASTRUCTURE ONLY.  oracle/build.py compiles this file together with
+// the reference's unmodified src/caif_cuda_kernels_quant.cu and
+// src/caif_cuda_kernels_moe.cu (read in place from the reference checkout,
+// never copied) into oracle/_ref/libcaif_ref_kernels.so.  The GPU tests load
+// that library to check the CPU oracle and the product kernels bit for bit
+// against what the reference itself computes.  Every pointer is a device
+// pointer; every call is asynchronous on `stream`.
+#define USE_CAIF_CUDA 1
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "caif_cuda_kernels_quant.cuh"
+#include "caif_cuda_kernels_moe.cuh"
+
+extern "C" {
+
+void ref_quantize_int8_per_tensor(const float *x, void *q, void *scale, int64_t n, void *stream)
+{
+  launch_quantize_int8_per_tensor(x, q, scale, n, static_cast<cudaStream_t>(stream));
+}
+
+void ref_dequantize_int8_per_tensor(const void *q, float *out, const void *scale, int64_t n, void *stream)
+{
+  launch_dequantize_int8_per_tensor(q, out, scale, n, static_cast<cudaStream_t>(stream));
+}
+
+void ref_quantize_int8_per_channel(const float *x, void *q, void *scales, int rows, int cols, void *stream)
+{
+  launch_quantize_int8_per_channel(x, q, scales, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+void ref_dequantize_int8_per_channel(const void *q, float *out, const void *scales, int rows, int cols, void *stream)
+{
+  launch_dequantize_int8_per_channel(q, out, scales, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+void ref_quantize_int4(const float *x, void *packed, void *scales, int64_t n, int group, void *stream)
+{
+  launch_quantize_to_int4(x, packed, scales, n, group, static_cast<cudaStream_t>(stream));
+}
+
+void ref_dequantize_int4(const void *packed, const void *scales, float *out, int64_t n, int group, void *stream)
+{
+  launch_dequantize_int4(packed, scales, out, n, group, static_cast<cudaStream_t>(stream));
+}
+
+void ref_fp32_to_bf16(const float *x, void *y, int64_t n, void *stream)
+{
+  launch_convert_fp32_to_bf16(x, y, n, static_cast<cudaStream_t>(stream));
+}
+
+void ref_fp32_to_fp16(const float *x, void *y, int64_t n, void *stream)
+{
+  launch_convert_fp32_to_fp16(x, y, n, static_cast<cudaStream_t>(stream));
+}
+
+void ref_topk_f32(const float *input, int *indices, float *values, int batch, int dim, int k, void *stream)
+{
+  launch_topk<float>(input, indices, values, batch, dim, k, static_cast<cudaStream_t>(stream));
+}
+
+void ref_normalize_rows_f32(const float *input, float *output, int batch, int dim, void *stream)
+{
+  launch_normalize_rows<float>(input, output, batch, dim, static_cast<cudaStream_t>(stream));
+}
+
+void ref_moe_dispatch_f32(const float *input, float *buffer, int num_tokens, int dim, int top_k,
+                          const int *expert_indices, const int *dispatch_map, const int *expert_offsets, void *stream)
+{
+  launch_moe_dispatch<float>(input, expert_indices, dispatch_map, buffer, expert_offsets, num_tokens, dim, top_k,
+                             static_cast<cudaStream_t>(stream));
+}
+
+void ref_moe_combine_f32(const float *buffer, float *output, int num_tokens, int dim, int top_k,
+                         const int *expert_indices, const float *expert_weights, const int *dispatch_map,
+                         const int *expert_offsets, void *stream)
+{
+  launch_moe_combine<float>(buffer, expert_indices, expert_weights, dispatch_map, expert_offsets, output, num_tokens,
+                            dim, top_k, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

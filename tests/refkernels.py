@@ -1,0 +1,105 @@
+"""ctypes binding of oracle/_ref/libcaif_ref_kernels.so: the reference's own
+quantize and MoE kernels, compiled unmodified (oracle/build.py).  Test
+infrastructure: used to pin the oracle and the product kernels against what the
+reference itself computes on the GPU."""
+import ctypes
+import os
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PATH = os.path.join(ROOT, "oracle", "_ref", "libcaif_ref_kernels.so")
+
+_lib = None
+
+
+def available():
+    return os.path.exists(PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(PATH)
+    return _lib
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _s():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def quantize_int8_per_tensor(x):
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    s = torch.empty(1, dtype=torch.float32, device=x.device)
+    lib().ref_quantize_int8_per_tensor(_p(x), _p(q), _p(s), ctypes.c_int64(x.numel()), _s())
+    return q, s
+
+
+def dequantize_int8_per_tensor(q, s):
+    out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    lib().ref_dequantize_int8_per_tensor(_p(q), _p(out), _p(s), ctypes.c_int64(q.numel()), _s())
+    return out
+
+
+def quantize_int8_per_channel(x):
+    rows, cols = x.shape
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    s = torch.empty(cols, dtype=torch.float32, device=x.device)
+    lib().ref_quantize_int8_per_channel(_p(x), _p(q), _p(s), ctypes.c_int(rows), ctypes.c_int(cols), _s())
+    return q, s
+
+
+def dequantize_int8_per_channel(q, s):
+    rows, cols = q.shape
+    out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    lib().ref_dequantize_int8_per_channel(_p(q), _p(out), _p(s), ctypes.c_int(rows), ctypes.c_int(cols), _s())
+    return out
+
+
+def quantize_int4(x, group=128):
+    n = x.numel()
+    packed = torch.zeros((n + 1) // 2, dtype=torch.uint8, device=x.device)
+    scales = torch.zeros((n + group - 1) // group, dtype=torch.float16, device=x.device)
+    lib().ref_quantize_int4(_p(x), _p(packed), _p(scales), ctypes.c_int64(n), ctypes.c_int(group), _s())
+    return packed, scales
+
+
+def dequantize_int4(packed, scales, n, group=128):
+    out = torch.empty(n, dtype=torch.float32, device=packed.device)
+    lib().ref_dequantize_int4(_p(packed), _p(scales), _p(out), ctypes.c_int64(n), ctypes.c_int(group), _s())
+    return out
+
+
+def topk(probs, k):
+    batch, dim = probs.shape
+    idx = torch.empty((batch, k), dtype=torch.int32, device=probs.device)
+    val = torch.empty((batch, k), dtype=torch.float32, device=probs.device)
+    lib().ref_topk_f32(_p(probs), _p(idx), _p(val), ctypes.c_int(batch), ctypes.c_int(dim), ctypes.c_int(k), _s())
+    return idx, val
+
+
+def normalize_rows(x):
+    batch, dim = x.shape
+    out = torch.empty_like(x)
+    lib().ref_normalize_rows_f32(_p(x), _p(out), ctypes.c_int(batch), ctypes.c_int(dim), _s())
+    return out
+
+
+def moe_dispatch(x, idx, dmap, off, total):
+    tokens, dim = x.shape
+    buf = torch.zeros((total, dim), dtype=torch.float32, device=x.device)
+    lib().ref_moe_dispatch_f32(_p(x), _p(buf), ctypes.c_int(tokens), ctypes.c_int(dim), ctypes.c_int(idx.shape[1]),
+                               _p(idx), _p(dmap), _p(off), _s())
+    return buf
+
+
+def moe_combine(buf, idx, weights, dmap, off, tokens):
+    dim = buf.shape[1]
+    out = torch.empty((tokens, dim), dtype=torch.float32, device=buf.device)
+    lib().ref_moe_combine_f32(_p(buf), _p(out), ctypes.c_int(tokens), ctypes.c_int(dim), ctypes.c_int(idx.shape[1]),
+                              _p(idx), _p(weights), _p(dmap), _p(off), _s())
+    return out

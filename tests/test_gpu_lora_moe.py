@@ -1,0 +1,169 @@
+"""GPU parity of the LoRA adapter path, routing/dispatch kernels and the grouped
+frozen experts against the CPU oracle (and the reference kernels where built)."""
+import numpy as np
+import pytest
+import torch
+
+import caif_oracle as orc
+import refkernels as ref
+from caif_b200 import native as nv
+from gpu_util import TORCH_DTYPE, act, dev, make_weight, max_rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+TOL = {orc.F32: 1e-4, orc.BF16: 2e-2, orc.F16: 2e-2}
+
+
+def _lora_case(rng, storage, sd, in_dim, out_dim, m, rank, alpha):
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, storage)
+    bound = np.sqrt(1.0 / in_dim)
+    a = orc.round_through(rng.uniform(-bound, bound, (rank, in_dim)).astype(np.float32), sd)
+    b = orc.round_through((rng.standard_normal((out_dim, rank)) * 1e-3).astype(np.float32), sd)
+    x_np, x = act(rng, m, in_dim, sd)
+    dy_np, dy = act(rng, m, out_dim, sd)
+    lora = nv.Lora(to_dev(a, TORCH_DTYPE[sd]), to_dev(b, TORCH_DTYPE[sd]), alpha)
+    return weight, codes, scales, a, b, x_np, x, dy_np, dy, lora
+
+
+@pytest.mark.parametrize("storage,sd,compute", [
+    (orc.I8, orc.F32, orc.F32),
+    (orc.I8, orc.BF16, orc.F32),   # the training config's cell: bf16 storage, fp32 compute
+    (orc.I4, orc.BF16, orc.BF16),
+    (orc.F16, orc.F16, orc.F16),
+])
+def test_lora_forward_backward(storage, sd, compute):
+    rng = np.random.default_rng(300 + storage + sd)
+    in_dim, out_dim, m, rank, alpha = 256, 192, 77, 16, 32.0
+    weight, codes, scales, a, b, x_np, x, dy_np, dy, lora = _lora_case(rng, storage, sd, in_dim, out_dim, m, rank,
+                                                                         alpha)
+    wc = orc.weight_to_compute(codes, scales, storage, in_dim, out_dim, compute, weight.scheme, weight.group_size)
+    base = orc.frozen_linear_forward(x_np, wc, compute)
+    want_y, want_h = orc.lora_forward(x_np, base, a, b, alpha, sd)
+    y, hidden = nv.lora_linear_fwd(weight, lora, x, compute)
+    tol = max(TOL[sd], TOL[compute])
+    assert y.dtype == TORCH_DTYPE[sd]
+    assert max_rel_err(y.float().cpu().numpy(), want_y) <= tol
+    assert max_rel_err(hidden.float().cpu().numpy(), want_h) <= tol
+    dx_base = orc.frozen_linear_backward(dy_np, wc, compute)
+    want_dx, want_da, want_db = orc.lora_backward(dy_np, x_np, want_h, dx_base, a, b, alpha, sd)
+    dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dy, x, hidden, compute)
+    assert max_rel_err(dx.float().cpu().numpy(), want_dx) <= tol
+    assert max_rel_err(d_a.float().cpu().numpy(), want_da) <= tol
+    assert max_rel_err(d_b.float().cpu().numpy(), want_db) <= tol
+
+
+def test_lora_zero_b_equals_base_and_gradients_overwrite():
+    rng = np.random.default_rng(301)
+    weight, codes, scales, a, b, x_np, x, dy_np, dy, lora = _lora_case(rng, orc.I8, orc.F32, 128, 96, 33, 8, 16.0)
+    zero_b = nv.Lora(lora.a, torch.zeros_like(lora.b), 16.0)
+    y, hidden = nv.lora_linear_fwd(weight, zero_b, x)
+    base = nv.linear_fwd(weight, x)
+    assert torch.equal(y, base)   # reference: tests/test_device_lora_adapter.cpp:371-442
+    dx1, da1, db1 = nv.lora_linear_bwd(weight, lora, dy, x, hidden)
+    dx2, da2, db2 = nv.lora_linear_bwd(weight, lora, dy, x, hidden)
+    assert float(da1.abs().max()) > 0 and float(db1.abs().max()) > 0
+    assert max_rel_err(da2.cpu().numpy(), da1.cpu().numpy()) <= 1e-5  # overwritten, not accumulated
+
+
+# -------------------------------------------------------------------- routing
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_topk_and_normalize_bit_exact(dtype):
+    g = torch.Generator().manual_seed(17)
+    probs = torch.softmax(torch.randn(1000, 68, generator=g), dim=-1).to(torch.bfloat16).to(dtype)
+    pd = probs.to(dev()).contiguous()
+    idx, val = nv.moe_topk(pd, 6)
+    oidx, oval = orc.topk(probs.float().numpy(), 6)
+    assert np.array_equal(idx.cpu().numpy(), oidx)
+    assert np.array_equal(val.float().cpu().numpy(), oval)
+    norm = nv.moe_normalize_rows(val)
+    code = {torch.float32: orc.F32, torch.bfloat16: orc.BF16, torch.float16: orc.F16}[dtype]
+    assert np.array_equal(norm.float().cpu().numpy(), orc.round_through(orc.normalize_rows(oval), code))
+    if dtype == torch.float32 and ref.available():
+        ridx, rval = ref.topk(pd, 6)
+        assert torch.equal(ridx, idx) and torch.equal(rval, val)
+        assert torch.equal(ref.normalize_rows(val), norm)
+
+
+def test_topk_edge_cases():
+    p = torch.tensor([[0.25, 0.25, 0.25, 0.25], [-2e30, -2e30, -2e30, -2e30], [0.0, 1.0, float("nan"), 1.0]])
+    idx, val = nv.moe_topk(p.to(dev()), 2)
+    assert idx.cpu().tolist() == [[0, 1], [0, 0], [1, 3]]
+    wide = torch.rand(5, 1000).to(dev())
+    idx, val = nv.moe_topk(wide, 8)
+    oidx, _ = orc.topk(wide.cpu().numpy(), 8)
+    assert np.array_equal(idx.cpu().numpy(), oidx)
+    n = nv.moe_normalize_rows(wide)
+    assert np.array_equal(n.cpu().numpy(), orc.normalize_rows(wide.cpu().numpy()))
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,capacity", [
+    (16384, 6, 68, 0),     # the MoE config's size
+    (1000, 2, 8, 100),     # capacity drops
+    (37, 3, 5, 0),
+    (1, 1, 1, 0),
+    (3000, 4, 256, 0),
+])
+def test_dispatch_map_bit_exact(tokens, top_k, experts, capacity):
+    rng = np.random.default_rng(tokens + experts)
+    idx = rng.integers(0, experts, (tokens, top_k)).astype(np.int32)
+    if tokens > 10:
+        idx[5, 0] = -1          # ignored entries, as the reference's range check does
+        idx[7, top_k - 1] = experts
+    dmap, off = nv.moe_build_dispatch(to_dev(idx), experts, capacity)
+    odmap, ooff, total = orc.build_dispatch_map(idx, experts, capacity)
+    assert np.array_equal(off.cpu().numpy(), ooff)
+    assert np.array_equal(dmap.cpu().numpy(), odmap)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dispatch_and_combine(dtype):
+    rng = np.random.default_rng(19)
+    tokens, dim, top_k, experts = 500, 96, 6, 68
+    code = orc.F32 if dtype == torch.float32 else orc.BF16
+    x_np, x = act(rng, tokens, dim, code)
+    probs = rng.random((tokens, experts)).astype(np.float32)
+    idx, val = orc.topk(probs, top_k)
+    w_np = orc.round_through(orc.normalize_rows(val), code)
+    dmap, off, total = orc.build_dispatch_map(idx, experts, capacity=40)
+    d_idx, d_map, d_off = to_dev(idx), to_dev(dmap), to_dev(off)
+    buf = nv.moe_dispatch(x, d_idx, d_map, d_off, total)
+    obuf = orc.moe_dispatch(x_np, idx, dmap, off, total)
+    assert np.array_equal(buf.float().cpu().numpy(), obuf)
+    out = nv.moe_combine(buf, d_idx, to_dev(w_np, dtype), d_map, d_off, tokens)
+    want = orc.round_through(orc.moe_combine(obuf, idx, w_np, dmap, off, tokens), code)
+    assert np.array_equal(out.float().cpu().numpy(), want)
+    if dtype == torch.float32 and ref.available():
+        assert torch.equal(ref.moe_dispatch(x, d_idx, d_map, d_off, total), buf)
+        assert torch.equal(ref.moe_combine(buf, d_idx, to_dev(w_np), d_map, d_off, tokens), out)
+
+
+# ------------------------------------------------------------ grouped experts
+@pytest.mark.parametrize("storage,sd,compute", [(orc.I4, orc.BF16, orc.BF16), (orc.I8, orc.F32, orc.F32),
+                                                (orc.I4, orc.F32, orc.F32)])
+def test_grouped_frozen_experts(storage, sd, compute):
+    rng = np.random.default_rng(400 + storage + sd)
+    experts, in_dim, hid = 5, 128, 256
+    counts = [13, 0, 40, 1, 27]
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    total = int(offsets[-1])
+    gate, up, down, o_gate, o_up, o_down = [], [], [], [], [], []
+    for _ in range(experts):
+        for lst, olst, (o, i) in ((gate, o_gate, (hid, in_dim)), (up, o_up, (hid, in_dim)),
+                                  (down, o_down, (in_dim, hid))):
+            w, codes, scales = make_weight(rng, o, i, storage, std=0.05)
+            lst.append(w)
+            olst.append(orc.weight_to_compute(codes, scales, storage, i, o, compute, w.scheme, w.group_size))
+    x_np, x = act(rng, total, in_dim, sd)
+    dy_np, dy = act(rng, total, in_dim, sd)
+    out, gate_out, up_out = nv.grouped_expert_fwd(gate, up, down, offsets.tolist(), x, compute)
+    dx = nv.grouped_expert_bwd(gate, up, down, offsets.tolist(), dy, gate_out, up_out, compute)
+    tol = max(TOL[sd], TOL[compute])
+    for e in range(experts):
+        lo, hi = offsets[e], offsets[e + 1]
+        if lo == hi:
+            continue
+        want, g, u = orc.frozen_expert_forward(x_np[lo:hi], o_gate[e], o_up[e], o_down[e], compute, sd)
+        assert max_rel_err(out[lo:hi].float().cpu().numpy(), want) <= tol
+        assert max_rel_err(gate_out[lo:hi].float().cpu().numpy(), g) <= tol
+        want_dx = orc.frozen_expert_backward(dy_np[lo:hi], g, u, o_gate[e], o_up[e], o_down[e], compute, sd)
+        assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
