@@ -1,0 +1,531 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized frozen-linear hot path on B200.
+
+Default workload (`--workload c2`): the decode-shaped int4 frozen linear
+in=4096, out=14336, group 128, bf16 activations, M in {1,4,16}, forward only.
+One step = one forward at each M over each of 8 independent weight copies
+(24 kernel launches); the copies total 242 MB, larger than the 126 MB L2, so
+every launch streams its codes from HBM.  Metric: algorithmic bytes per second
+(codes + scales + x + y).  Weights are seeded N(0, 0.02) quantized by the
+library's own (reference bit-exact) int4 quantizer; activations seeded N(0,1).
+
+`--workload c3`: the training-shaped int8 frozen linear 4096->4096 with a
+rank-16 LoRA adapter, M=8192 bf16: forward + dX (+dA, dB); metric TFLOP/s.
+
+Contract: `python bench.py --gpus N --steps K --warmup W` prints ONE JSON line
+from rank 0.  With N > 1 (under torchrun) the weight is column-sharded by
+output features over the ranks and Y is all-gathered with NCCL (strong
+scaling).  `--impl reference` times the reference's CPU path (dequantize +
+OpenBLAS sgemm) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+C2_IN, C2_OUT, C2_GROUP = 4096, 14336, 128
+C2_MS = (1, 4, 16)
+C2_COPIES = 8
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def c2_bytes(m, out_dim=C2_OUT):
+    """Algorithmic bytes of one decode forward: packed codes + fp16 scales + bf16 x + fp32 y."""
+    return out_dim * C2_IN // 2 + (out_dim * C2_IN // C2_GROUP) * 2 + m * C2_IN * 2 + m * out_dim * 4
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) < 9:
+                        continue
+                    try:
+                        sm.append(float(parts[1]))
+                        mx = float(parts[2])
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                         parts[5:9]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            sm.sort()
+            # median of the upper half: samples taken while the GPU was busy
+            busy = sm[len(sm) // 2:]
+            out["sm_mhz"] = busy[len(busy) // 2]
+            out["sm_max_mhz"] = mx
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ----------------------------------------------------------------------- CPU arm
+def cpu_reference_c2(steps, warmup, budget_s=20.0):
+    """The reference's Host_e path for this layer with its default cache_fp32=true: the int4
+    weight is dequantized to fp32 once (restated kernel, OpenMP, outside the timed loop, as the
+    reference's cache does after the first call), then every forward is
+    CAIF_Ops::MatMulTransposeB = OpenBLAS sgemm (numpy).  One step = one forward at each M in
+    {1,4,16} on ONE weight copy."""
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import caif_oracle as orc
+
+    rng = np.random.default_rng(1235)
+    w = (rng.standard_normal((C2_OUT, C2_IN)) * 0.02).astype(np.float32)
+    packed, scales = orc.quantize_int4(w, C2_GROUP)
+    del w
+    xs = [orc.round_through(rng.standard_normal((m, C2_IN)).astype(np.float32), orc.BF16) for m in C2_MS]
+
+    wd = orc.dequantize_int4(packed, scales, C2_OUT * C2_IN, C2_GROUP).reshape(C2_OUT, C2_IN)
+
+    def step():
+        for x in xs:
+            orc.gemm_nt(x, wd, exact=False)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        step()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    bytes_per_step = sum(c2_bytes(m) for m in C2_MS)
+    return {"value": bytes_per_step * done / dt / 1e9, "ms_per_step": dt / done * 1e3, "steps": done,
+            "cores": orc.num_threads(),
+            "sample": "%d steps of sgemm at M=1,4,16 on one cached fp32 14336x4096 weight (dequantized once)" % done}
+
+
+def cpu_reference_c3(steps, warmup, budget_s=25.0):
+    """Reference Host_e path for the training config on a bounded sample: M=512 of the 8192
+    tokens (1/16 of a step): the fp32 weight is dequantized once (the reference's default
+    cache_fp32=true), each step is sgemm forward and dX + the six LoRA matmuls."""
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import caif_oracle as orc
+
+    rng = np.random.default_rng(1236)
+    dim, rank, m = 4096, 16, 512
+    w = (rng.standard_normal((dim, dim)) * 0.02).astype(np.float32)
+    q, s = orc.quantize_int8_per_tensor(w)
+    a = rng.uniform(-1 / 64, 1 / 64, (rank, dim)).astype(np.float32)
+    b = (rng.standard_normal((dim, rank)) * 1e-3).astype(np.float32)
+    x = orc.round_through(rng.standard_normal((m, dim)).astype(np.float32), orc.BF16)
+    dy = orc.round_through(rng.standard_normal((m, dim)).astype(np.float32), orc.BF16)
+
+    wd = orc.dequantize_int8_per_tensor(q, s)  # cache_fp32=true: dequantized once, outside the loop
+
+    def step():
+        base = orc.gemm_nt(x, wd, exact=False)
+        out, hidden = orc.lora_forward(x, base, a, b, 32.0, orc.BF16, exact=False)
+        dx_base = orc.gemm_nn(dy, wd, exact=False)
+        orc.lora_backward(dy, x, hidden, dx_base, a, b, 32.0, orc.BF16, exact=False)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        step()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    flops = c3_flops(m)
+    return {"value": flops * done / dt / 1e12, "ms_per_step": dt / done * 1e3, "steps": done,
+            "cores": orc.num_threads(),
+            "sample": "%d steps at M=%d tokens (1/16 of the 8192-token step): sgemm fwd/dX on the cached fp32 weight + LoRA"
+                      % (done, m)}
+
+
+def c3_flops(m, dim=4096, rank=16):
+    return 2 * (2 * m * dim * dim) + 6 * (2 * m * dim * rank)
+
+
+# ----------------------------------------------------------------------- GPU arm
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from caif_b200 import native as nv
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus %d needs torchrun with that many ranks" % args.gpus)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if not nv.lib().caifq_device_ok():
+        raise SystemExit("caifq needs an sm_100 device; there is no fallback")
+
+    peaks = _peaks()
+    if args.workload == "c2":
+        result = bench_c2(args, nv, torch, dist, dev, world, rank, peaks)
+    else:
+        result = bench_c3(args, nv, torch, dist, dev, world, rank, peaks)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result))
+
+
+def _timed(torch, dist, world, fn, steps, dev):
+    """Barrier + synchronize on both sides, CUDA events on the current stream, max over ranks."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def _gpu_uuid(torch, dev):
+    try:
+        return "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        return str(dev.index or 0)
+
+
+def _keep_busy(torch, step, ms_per_step, target_ms=1600.0):
+    """The timed region can be shorter than the sampler's 200 ms period: run the same step,
+    untimed, straight after it so that the clock samples are taken under the same load.
+    The step count depends only on the max-over-ranks time, so every rank runs the same number."""
+    extra = int(min(max(target_ms / max(ms_per_step, 1e-3), 1), 50000))
+    for _ in range(extra):
+        step()
+    torch.cuda.synchronize()
+
+
+def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
+    shard = C2_OUT // world
+    if shard * world != C2_OUT or shard % 8 != 0:
+        raise SystemExit("out=%d does not shard over %d ranks" % (C2_OUT, world))
+    gen = torch.Generator(device=dev).manual_seed(1235)
+    weights = []
+    for c in range(C2_COPIES):
+        # every rank draws the same full weight and keeps its rows: the codes are the 1-GPU codes
+        wf = torch.randn(C2_OUT * C2_IN, generator=gen, device=dev) * 0.02
+        packed, scales = nv.quantize_int4(wf, C2_GROUP)
+        del wf
+        full = nv.Weight(packed, nv.I4, C2_IN, C2_OUT, scales, group_size=C2_GROUP)
+        if world > 1:
+            sh = full.rows(rank * shard, (rank + 1) * shard)
+            weights.append(nv.Weight(sh.codes.clone(), nv.I4, C2_IN, shard, sh.scales.clone(), group_size=C2_GROUP))
+        else:
+            weights.append(full)
+    del full
+    torch.cuda.empty_cache()
+    xs = {m: torch.randn(m, C2_IN, generator=gen, device=dev).to(torch.bfloat16) for m in C2_MS}
+    ys = {m: torch.empty(m, shard, dtype=torch.float32, device=dev) for m in C2_MS}
+    gathered = {m: torch.empty(world, m, shard, dtype=torch.float32, device=dev) for m in C2_MS} if world > 1 else None
+
+    def step_eager():
+        for w in weights:
+            for m in C2_MS:
+                nv.linear_fwd(w, xs[m], compute=nv.F32, out=ys[m])
+                if world > 1:
+                    dist.all_gather_into_tensor(gathered[m], ys[m])
+
+    launches_per_step = C2_COPIES * len(C2_MS)
+    # warm-up (also sets the kernel's shared-memory attribute outside any capture)
+    for _ in range(max(args.warmup, 3)):
+        step_eager()
+    torch.cuda.synchronize()
+    assert nv.last_path() == "decode", nv.last_path()
+
+    step = step_eager
+    graphed = False
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_eager()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step_eager()
+            step = graph.replay
+            graphed = True
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+        except Exception as e:  # capture of the collective can be refused; time eagerly then
+            if rank == 0:
+                sys.stderr.write("graph capture unavailable (%s); timing eager launches\n" % e)
+            step = step_eager
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(_gpu_uuid(torch, dev))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms = _timed(torch, dist, world, step, args.steps, dev)
+    _keep_busy(torch, step, ms / args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    bytes_per_step = C2_COPIES * sum(c2_bytes(m) for m in C2_MS)   # whole job (all shards)
+    ms_per_step = ms / args.steps
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # dominant kernel: per-launch algorithmic bytes / average launch duration over the timed region
+    per_launch_bytes = sum(c2_bytes(m, shard) for m in C2_MS) / len(C2_MS)
+    per_launch_s = ms_per_step * 1e-3 / launches_per_step
+    achieved = per_launch_bytes / per_launch_s / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_C2 if world == 1 else None,
+                "peak_source": peaks["source"], "kernel": "linear_decode_kernel<4,*,2>",
+                "note": "average over the step's 24 launches (M=1,4,16); includes inter-launch gaps"}
+
+    # end to end: host buffers in, host buffers out, through the C ABI, copies inside the timed region
+    e2e = None
+    if rank == 0 or world > 1:
+        hx = {m: xs[m].cpu().pin_memory() for m in C2_MS}
+        hy = {m: torch.empty(m, shard, dtype=torch.float32).pin_memory() for m in C2_MS}
+        dx = {m: torch.empty_like(xs[m]) for m in C2_MS}
+
+        def step_e2e():
+            for w in weights:
+                for m in C2_MS:
+                    dx[m].copy_(hx[m], non_blocking=True)
+                    nv.linear_fwd(w, dx[m], compute=nv.F32, out=ys[m])
+                    if world > 1:
+                        dist.all_gather_into_tensor(gathered[m], ys[m])
+                    hy[m].copy_(ys[m], non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(3):
+            step_e2e()
+        e2e_steps = max(3, min(args.steps, 20))
+        ms_e2e = _timed(torch, dist, world, step_e2e, e2e_steps, dev)
+        e2e = {"value": bytes_per_step / (ms_e2e / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": C2_COPIES * sum(m * C2_IN * 2 for m in C2_MS),
+               "d2h_bytes_per_step": C2_COPIES * sum(m * shard * 4 for m in C2_MS)}
+
+    result = {
+        "metric": "decode int4 frozen-linear forward, algorithmic HBM bytes per second", "value": value,
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 x int4 -> fp32", "data": "synthetic",
+        "config": {"workload": "c2: in=4096 out=14336 int4 g128, M in {1,4,16}, forward; step = 8 weight copies x 3 M",
+                   "l2": "8 weight copies = 242 MB > 126 MB L2, visited round-robin",
+                   "launch": "CUDA graph replay" if graphed else "eager",
+                   "parallelism": "1 GPU" if world == 1 else "column-parallel x%d + NCCL all-gather of Y" % world},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cb = cpu_reference_c2(steps=50, warmup=1, budget_s=15.0)
+        result["cpu_baseline"] = {"value": cb["value"], "unit": "GB/s", "cores": cb["cores"], "kind": "port",
+                                  "sample": cb["sample"]}
+    return result
+
+
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel (see profiles/); None until captured
+NCU_TRAFFIC_C2 = None
+NCU_TRAFFIC_C3 = None
+
+
+def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
+    dim, rank_r, m, alpha = 4096, 16, 8192, 32.0
+    shard = dim // world
+    gen = torch.Generator(device=dev).manual_seed(1236)
+    wf = torch.randn(dim * dim, generator=gen, device=dev) * 0.02
+    q, s = nv.quantize_int8_per_tensor(wf)
+    del wf
+    qs = q.view(dim, dim)[rank * shard:(rank + 1) * shard].contiguous()
+    weight = nv.Weight(qs, nv.I8, dim, shard, s)
+    a = ((torch.rand(rank_r, dim, generator=gen, device=dev) * 2 - 1) / 64).to(torch.bfloat16)
+    b_full = (torch.randn(dim, rank_r, generator=gen, device=dev) * 1e-3).to(torch.bfloat16)
+    b = b_full[rank * shard:(rank + 1) * shard].contiguous()
+    lora = nv.Lora(a, b, alpha)
+    n_sets = 2  # 2 x (X + dY) = 268 MB of activations > L2, alternated between steps
+    xs = [torch.randn(m, dim, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
+    dys = [torch.randn(m, dim, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
+    state = {"i": 0}
+    gathered = torch.empty(world, m, shard, dtype=torch.bfloat16, device=dev) if world > 1 else None
+
+    def step():
+        i = state["i"] % n_sets
+        state["i"] += 1
+        y, hidden = nv.lora_linear_fwd(weight, lora, xs[i], compute=nv.F32)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, y)
+            dy = dys[i][:, rank * shard:(rank + 1) * shard].contiguous()
+        else:
+            dy = dys[i]
+        dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dy, xs[i], hidden, compute=nv.F32)
+        if world > 1:
+            dist.all_reduce(dx)
+            dist.all_reduce(d_a)
+        return dx
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    path = nv.last_path()
+    sampler = ClockSampler(_gpu_uuid(torch, dev))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms = _timed(torch, dist, world, step, args.steps, dev)
+    _keep_busy(torch, step, ms / args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    flops = c3_flops(m)
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                "frac": value / world / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_C3,
+                "peak_source": peaks["source"], "kernel": "frozen linear path '%s'" % path,
+                "note": "whole step (fwd + dX + LoRA) over its duration; peak is the burst cuBLAS bf16 figure"}
+
+    hx = xs[0].cpu().pin_memory()
+    hdy = dys[0].cpu().pin_memory()
+    hdx = torch.empty(m, dim, dtype=torch.bfloat16).pin_memory()
+    dxb, dyb = torch.empty_like(xs[0]), torch.empty_like(dys[0])
+
+    def step_e2e():
+        dxb.copy_(hx, non_blocking=True)
+        dyb.copy_(hdy, non_blocking=True)
+        xs[0], dys[0] = dxb, dyb
+        state["i"] = 0
+        out = step()
+        hdx.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = _timed(torch, dist, world, step_e2e, e2e_steps, dev)
+    e2e = {"value": flops / (ms_e2e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": 2 * m * dim * 2, "d2h_bytes_per_step": m * dim * 2}
+    result = {
+        "metric": "int8 frozen linear + LoRA r16, forward + dX/dA/dB, TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": "c3: 4096->4096 int8 per-tensor + LoRA r16 a32, M=8192 bf16, fwd + dX/dA/dB",
+                   "l2": "two activation sets (268 MB) alternated between steps, larger than L2",
+                   "parallelism": "1 GPU" if world == 1 else "column-parallel x%d, all-gather Y, all-reduce dX" % world},
+        "roofline": roofline, "e2e": e2e, "gpu_launches": None, "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cb = cpu_reference_c3(steps=20, warmup=1, budget_s=20.0)
+        result["cpu_baseline"] = {"value": cb["value"], "unit": "TFLOP/s", "cores": cb["cores"], "kind": "port",
+                                  "sample": cb["sample"]}
+    return result
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if args.workload == "c2":
+        cb = cpu_reference_c2(steps=args.steps, warmup=min(args.warmup, 2), budget_s=120.0)
+        unit, metric = "GB/s", "decode int4 frozen-linear forward, algorithmic HBM bytes per second"
+        workload = "c2: in=4096 out=14336 int4 g128, M in {1,4,16}, forward; step = 8 weight copies x 3 M"
+    else:
+        cb = cpu_reference_c3(steps=args.steps, warmup=min(args.warmup, 1), budget_s=120.0)
+        unit, metric = "TFLOP/s", "int8 frozen linear + LoRA r16, forward + dX/dA/dB, TFLOP/s"
+        workload = "c3: 4096->4096 int8 per-tensor + LoRA r16 a32, M=8192 bf16, fwd + dX/dA/dB"
+    line = {
+        "impl": "reference", "metric": metric, "value": cb["value"], "unit": unit, "n_gpus": args.gpus,
+        "steps": cb["steps"], "warmup": min(args.warmup, 2), "ms_per_step": cb["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (host sgemm)",
+        "data": "synthetic", "config": {"workload": workload},
+        "cpu_baseline": {"value": cb["value"], "unit": unit, "cores": cb["cores"], "kind": "port",
+                         "sample": cb["sample"]},
+        "e2e": {"value": cb["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3"])
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -147,7 +147,7 @@ def test_decode_int4_config2(m):
     (orc.I4, 384, 64, 9, 128),       # fewer chunks than warps
     (orc.I8, 4096, 512, 2, 0),
     (orc.I8, 1024, 136, 12, 0),
-    (orc.I8, 8192, 64, 7, 0),
+    (orc.I8, 5120, 64, 7, 0),       # five chunks per warp
     (orc.I8, 320, 72, 1, 0),
 ])
 def test_decode_shapes(storage, in_dim, out_dim, m, group):
