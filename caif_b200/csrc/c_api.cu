@@ -4,6 +4,7 @@
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -392,6 +393,64 @@ int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const v
     return r;
   }
   return linear_any(w, true, dy, sd, 1.0f, m, dx, sd, true, compute_dtype, s, who);
+}
+
+// ------------------------------------------------- LoRA backward, no allocation
+//
+// Scratch for caifq_lora_linear_bwd_noalloc.  It lives in the library image, so
+// every GPU that loads libcaifq.so carries these 8 MiB until the process exits.
+// The name below is a host-side stand-in for the array, NOT a device address:
+// the device address is fetched once per device with cudaGetSymbolAddress.
+#define CAIFQ_NOALLOC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[CAIFQ_NOALLOC_SCRATCH_BYTES];
+
+namespace
+{
+constexpr int kMaxDevices = 64;
+void *g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mutex;
+}  // namespace
+
+size_t caifq_lora_bwd_noalloc_max_bytes(void) { return CAIFQ_NOALLOC_SCRATCH_BYTES; }
+
+int caifq_lora_linear_bwd_noalloc(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
+                                  const void *hidden, int64_t m, void *dx, void *d_a, void *d_b,
+                                  int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_lora_linear_bwd_noalloc";
+  const int rc = check_lora(w, lora, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(m >= 0, "%s: negative m", who);
+  const size_t need = caifq_lora_bwd_workspace_bytes(w, lora, m);
+  if (need > CAIFQ_NOALLOC_SCRATCH_BYTES)
+  {
+    set_error("%s: this call needs %zu bytes of scratch but the built-in buffer holds %u; "
+              "use caifq_lora_linear_bwd with a caller-provided workspace (m=%lld rank=%d in=%d out=%d)",
+              who, need, CAIFQ_NOALLOC_SCRATCH_BYTES, static_cast<long long>(m), lora->rank, w->in_dim, w->out_dim);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  int dev = 0;
+  CAIFQ_CHECK_CUDA(cudaGetDevice(&dev));
+  CAIFQ_CHECK_ARG(dev >= 0 && dev < kMaxDevices, "%s: device index %d out of range", who, dev);
+  void *scratch = nullptr;
+  {
+    // one-time set-up per device, with that device current: resolve the array's device address
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr)
+    {
+      void *ptr = nullptr;
+      CAIFQ_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+      g_noalloc_ptr[dev] = ptr;
+    }
+    scratch = g_noalloc_ptr[dev];
+  }
+  // Nothing in the buffer is assumed: the token reductions clear their fp32
+  // accumulator with a memset on `stream` before every use, and dH is fully
+  // overwritten before it is read.
+  return caifq_lora_linear_bwd(w, lora, dy, x, hidden, m, dx, d_a, d_b, scratch, compute_dtype, stream);
 }
 
 // ----------------------------------------------------------------------- MoE

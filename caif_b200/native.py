@@ -71,6 +71,9 @@ _SIGNATURES = {
     "caifq_lora_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_linear_bwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _vp, _vp, _i64,
                                              _vp, _vp, _vp, _vp, _i32, _vp]),
+    "caifq_lora_bwd_noalloc_max_bytes": (ctypes.c_size_t, []),
+    "caifq_lora_linear_bwd_noalloc": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _vp, _vp,
+                                                     _i64, _vp, _vp, _vp, _i32, _vp]),
     "caifq_moe_topk": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_normalize_rows": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_build_dispatch": (ctypes.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
@@ -297,6 +300,20 @@ def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32):
     ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=dy.device)
     _check(lib().caifq_lora_linear_bwd(w.ref(), lora.ref(), _ptr(dy), _ptr(x), _ptr(hidden), m, _ptr(dx), _ptr(d_a),
                                        _ptr(d_b), _ptr(ws), compute, _stream()), "lora_linear_bwd")
+    return dx, d_a, d_b
+
+
+def lora_linear_bwd_noalloc(w, lora, dy, x, hidden, compute=F32):
+    """caifq_lora_linear_bwd_noalloc: the scratch comes from the buffer built into the
+    library, so this wrapper allocates only the three result tensors."""
+    _need_cuda(dy, x, hidden)
+    m = dy.numel() // w.out_dim
+    dx = torch.empty(tuple(dy.shape[:-1]) + (w.in_dim,), dtype=dy.dtype, device=dy.device)
+    d_a = torch.empty_like(lora.a)
+    d_b = torch.empty_like(lora.b)
+    _check(lib().caifq_lora_linear_bwd_noalloc(w.ref(), lora.ref(), _ptr(dy), _ptr(x), _ptr(hidden), m, _ptr(dx),
+                                               _ptr(d_a), _ptr(d_b), compute, _stream()),
+           "lora_linear_bwd_noalloc")
     return dx, d_a, d_b
 
 

@@ -170,6 +170,38 @@ CAIFQ_API int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lor
                           const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
                           int32_t compute_dtype, void *stream);
 
+/*
+ * caifq_lora_linear_bwd for callers that cannot hand over a workspace.
+ * (No counterpart in the reference: its layers always own their scratch as
+ * CAIF_DeviceTensor objects.)
+ *
+ * Some hosts of this library hold nothing but the pointers they pass in: a
+ * plugin loaded into another runtime has no access to that runtime's caching
+ * allocator, and a serving or training step that must not stall cannot call
+ * cudaMalloc itself, because the driver synchronises the whole device around
+ * it.  For them the scratch of the backward pass (dH and the fp32 accumulator
+ * of the dA/dB reductions) comes from an 8 MiB buffer built into the library
+ * image; each GPU that loads the library holds it until the process exits.
+ *
+ *   - Same arguments and results as caifq_lora_linear_bwd, minus `workspace`.
+ *   - Calls whose scratch need (caifq_lora_bwd_workspace_bytes) exceeds
+ *     caifq_lora_bwd_noalloc_max_bytes() are rejected with CAIFQ_ERR_UNSUPPORTED
+ *     and a message naming both sizes; nothing is launched.
+ *   - No cudaMalloc / cudaFree and no allocating library routine is called.
+ *   - The first call on a device looks up the buffer's device address
+ *     (cudaGetSymbolAddress, with that device current).  Make that first call
+ *     outside any stream capture.
+ *   - All calls on a device share the one buffer and find in it whatever the
+ *     previous call left; the entry point clears what has to start at zero.
+ *     Two calls that can overlap on the GPU (different streams, no dependency)
+ *     race on it: serialise them, or use caifq_lora_linear_bwd with separate
+ *     workspaces.
+ */
+CAIFQ_API size_t caifq_lora_bwd_noalloc_max_bytes(void);
+CAIFQ_API int caifq_lora_linear_bwd_noalloc(const caifq_weight *w, const caifq_lora *lora, const void *dy,
+                                            const void *x, const void *hidden, int64_t m, void *dx, void *d_a,
+                                            void *d_b, int32_t compute_dtype, void *stream);
+
 /* ---- MoE routing and dispatch -------------------------------------------- */
 
 /* launch_topk, src/caif_cuda_kernels_moe.cu:280-345: descending values, ties to
