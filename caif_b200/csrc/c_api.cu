@@ -11,6 +11,10 @@
 namespace caifq
 {
 
+// each kernel file owns its flag and the code that reads it (device symbols are per translation unit)
+int take_decode_timeout_flag();
+int take_umma_timeout_flag();
+
 namespace
 {
 thread_local char t_error[512] = "";
@@ -181,6 +185,24 @@ const char *caifq_last_error(void) { return t_error; }
 const char *caifq_last_path(void) { return t_path; }
 
 const char *caifq_version(void) { return "caifq 0.1 (sm_100a)"; }
+
+int caifq_device_status(void)
+{
+  // 1: the decode kernel gave up on a wait; 2: the tensor-core kernel did
+  if (cudaDeviceSynchronize() != cudaSuccess)
+  {
+    set_error("caifq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
+  const int decode_flag = take_decode_timeout_flag();
+  const int umma_flag = take_umma_timeout_flag();
+  if (decode_flag < 0 || umma_flag < 0)
+  {
+    set_error("caifq_device_status: %s", cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
+  return (decode_flag ? 1 : 0) | (umma_flag ? 2 : 0);
+}
 
 int caifq_device_ok(void)
 {

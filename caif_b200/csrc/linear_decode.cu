@@ -32,6 +32,22 @@ namespace caifq
 
 __device__ unsigned int g_decode_timeout_flag = 0;
 
+// Reads and clears the flag (1 = some bounded wait ran out since the last call; -1 = query failed).
+int take_decode_timeout_flag()
+{
+  unsigned int v = 0;
+  const unsigned int zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_decode_timeout_flag, sizeof(v)) != cudaSuccess)
+  {
+    return -1;
+  }
+  if (v != 0 && cudaMemcpyToSymbol(g_decode_timeout_flag, &zero, sizeof(zero)) != cudaSuccess)
+  {
+    return -1;
+  }
+  return v ? 1 : 0;
+}
+
 namespace
 {
 

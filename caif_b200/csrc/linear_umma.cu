@@ -1,11 +1,883 @@
-// placeholder until the tcgen05 kernel lands
+// Tensor-core frozen-linear GEMM for many tokens (prefill / training shapes):
+//
+//   forward : C[m, out] = A[m, in]  . W_deq[out, in]^T     (ForwardImpl,  src/caif_device_frozen_linear.cpp:381-524)
+//   backward: C[m, in]  = A[m, out] . W_deq[out, in]       (BackwardImpl, src/caif_device_frozen_linear.cpp:526-660)
+//
+// Blackwell-native: tcgen05.mma (kind::f16, bf16 operands, fp32 accumulators in
+// TMEM), operands staged in shared memory in the canonical 128-byte-swizzled
+// layouts, activations fed by TMA.  The weight never exists as a float matrix
+// in memory (the reference dequantizes [out,in] to fp32 and hands it to cuBLAS,
+// :288-378): eight warps read the packed codes straight from global memory,
+// expand them to bf16 in registers and write the B operand tile into shared
+// memory, one k-block ahead of the MMA warp.
+//
+// One persistent CTA per SM, 14 warps:
+//   warp 0      TMA producer for the activation tiles (and the weight tiles when
+//               the weight is already bf16)
+//   warp 1      TMEM allocation, MMA issue (one elected lane)
+//   warps 2-5   epilogue: TMEM -> registers -> scale -> global
+//   warps 6-13  dequantization of the weight tile
+// Tile 256 (two 128-row MMAs that share one dequantized weight tile) x 128 x 64,
+// four pipeline stages, two accumulator sets in TMEM (4 x 128 columns) so the
+// epilogue of one tile overlaps the main loop of the next.
+//
+// Forward uses the weight tile K-major (k = in is contiguous in memory);
+// backward uses the SAME codes MN-major (n = in is contiguous), so dX needs no
+// transposed copy of the weight.
+//
+// Exactness: int8 codes are exact in bf16 and the per-tensor scale multiplies
+// the fp32 accumulator in the epilogue, so with bf16 activations the products
+// are exact and the result matches an fp32 GEMM up to summation order.  int4
+// weights are scale*code rounded to bf16, the operand the reference's bf16
+// compute cell builds (dequantize to fp32, then To(bf16)).
+//
+// Every wait is bounded; a wait that runs out sets a flag that the host can
+// read and lets the kernel finish (with wrong numbers) instead of hanging.
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace caifq
 {
-bool umma_supported(const LinearArgs &) { return false; }
-int launch_linear_umma(const LinearArgs &, cudaStream_t)
+
+__device__ unsigned int g_umma_timeout_flag = 0;
+
+// Reads and clears the flag (1 = some bounded wait ran out since the last call; -1 = query failed).
+int take_umma_timeout_flag()
 {
-  set_error("umma path not built");
+  unsigned int v = 0;
+  const unsigned int zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_umma_timeout_flag, sizeof(v)) != cudaSuccess)
+  {
+    return -1;
+  }
+  if (v != 0 && cudaMemcpyToSymbol(g_umma_timeout_flag, &zero, sizeof(zero)) != cudaSuccess)
+  {
+    return -1;
+  }
+  return v ? 1 : 0;
+}
+
+namespace
+{
+
+constexpr int BM_SUB = 128;          // rows of one MMA
+constexpr int MT = 2;                // MMAs (row sub-tiles) per weight tile
+constexpr int BM = BM_SUB * MT;      // 256
+constexpr int BN = 128;
+constexpr int BK = 64;               // one 128-byte swizzle span of bf16
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_SUB_BYTES = BM_SUB * BK * 2;       // 16 KB
+constexpr int A_STAGE_BYTES = A_SUB_BYTES * MT;    // 32 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;         // 16 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the base to 1024
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_WARPS = 14;
+constexpr int NUM_THREADS = NUM_WARPS * 32;
+constexpr int DEQ_WARP0 = 6;
+constexpr int DEQ_THREADS = 8 * 32;
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+enum WMode
+{
+  W_I8 = 0,
+  W_I4 = 1,
+  W_BF16 = 2
+};
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+  {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done)
+    {
+      return true;
+    }
+  }
+  atomicExch(&g_umma_timeout_flag, 1u);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
+{
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async()
+{
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before()
+{
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after()
+{
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate)
+{
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// arrive on an mbarrier once every MMA issued so far by this thread has finished
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait()
+{
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100): start address, leading / stride
+// byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // version
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 x bf16, A K-major,
+// B K-major (forward) or MN-major (backward), N = 128, M = 128.
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major)
+{
+  return (1u << 4)                          // D format f32
+         | (1u << 7)                        // A format bf16
+         | (1u << 10)                       // B format bf16
+         | (0u << 15)                       // A major: K
+         | ((b_mn_major ? 1u : 0u) << 16)   // B major
+         | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM_SUB >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c)
+{
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b)
+{
+  uint32_t d;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+// four int8 codes (one 32-bit word, memory order) -> two bf16x2 registers, exact
+__device__ __forceinline__ void int8x4_to_bf16(uint32_t w, uint32_t &p01, uint32_t &p23)
+{
+  const uint32_t a = __byte_perm(w, 0u, 0x4140);  // [b0, 0, b1, 0]
+  const uint32_t b = __byte_perm(w, 0u, 0x4342);  // [b2, 0, b3, 0]
+  // low 7 bits dropped into the mantissa of 128.0; the sign bit selects 128.0 or 256.0 to subtract
+  p01 = sub_bf16x2(lop3_and_or(a, 0x007F007Fu, 0x43004300u), lop3_and_or(a, 0x00800080u, 0x43004300u));
+  p23 = sub_bf16x2(lop3_and_or(b, 0x007F007Fu, 0x43004300u), lop3_and_or(b, 0x00800080u, 0x43004300u));
+}
+
+// eight int4 codes (one 32-bit word, memory order) times a scale -> four bf16x2
+// registers; each product is formed in fp32 and rounded once to bf16, the value
+// the reference's dequantize-then-cast yields
+__device__ __forceinline__ void int4x8_to_bf16(uint32_t w, float scale, uint32_t (&out)[4])
+{
+  // offset-binary nibbles u = q + 8 as the low byte of 2^23 + u, exact in fp32
+  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;         // u0 u2 u4 u6
+  const uint32_t od = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;  // u1 u3 u5 u7
+  const float base = 8388616.0f;                               // 2^23 + 8
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+  {
+    const float lo = __uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base;
+    const float hi = __uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base;
+    out[j] = pack_bf16x2(__fmul_rn(lo, scale), __fmul_rn(hi, scale));
+  }
+}
+
+struct UmmaParams
+{
+  const uint8_t *codes;
+  const void *scales;
+  void *c;
+  int c_dtype;
+  int accumulate;    // epilogue: c = round_c(round_c(acc) + c_old)
+  int64_t m;
+  int n_total;       // columns of C
+  int k_total;       // reduction length
+  int in_dim;        // row length of the code matrix
+  int group_size;    // int4
+  int num_m_tiles;
+  int num_n_tiles;
+};
+
+template <int WMODE, bool BWD>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const UmmaParams p)
+{
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bars[STAGES * 3 + 4];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  auto a_addr = [&](int s, int mt) { return smem_base + static_cast<uint32_t>(s) * STAGE_BYTES + mt * A_SUB_BYTES; };
+  auto b_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * STAGE_BYTES + A_STAGE_BYTES; };
+  const uint32_t bar0 = smem_u32(bars);
+  auto a_full = [&](int s) { return bar0 + static_cast<uint32_t>(s) * 8u; };
+  auto b_full = [&](int s) { return bar0 + static_cast<uint32_t>(STAGES + s) * 8u; };
+  auto empty = [&](int s) { return bar0 + static_cast<uint32_t>(2 * STAGES + s) * 8u; };
+  auto acc_full = [&](int a) { return bar0 + static_cast<uint32_t>(3 * STAGES + a) * 8u; };
+  auto acc_empty = [&](int a) { return bar0 + static_cast<uint32_t>(3 * STAGES + 2 + a) * 8u; };
+
+  if (threadIdx.x == 0)
+  {
+    for (int s = 0; s < STAGES; ++s)
+    {
+      mbar_init(a_full(s), 1);
+      mbar_init(b_full(s), (WMODE == W_BF16) ? 1 : 8);
+      mbar_init(empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a)
+    {
+      mbar_init(acc_full(a), 1);
+      mbar_init(acc_empty(a), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1)
+  {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+  const int num_kb = p.k_total / BK;
+
+  if (warp == 0)
+  {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0)
+    {
+      int s = 0;
+      uint32_t par = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+      {
+        const int m_tile = tile % p.num_m_tiles;
+        const int n_tile = tile / p.num_m_tiles;
+        for (int kb = 0; kb < num_kb; ++kb)
+        {
+          mbar_wait(empty(s), par ^ 1u);
+          mbar_expect_tx(a_full(s), A_STAGE_BYTES);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+          {
+            tma_load_2d(a_addr(s, mt), &map_a, kb * BK, m_tile * BM + mt * BM_SUB, a_full(s));
+          }
+          if (WMODE == W_BF16)
+          {
+            mbar_expect_tx(b_full(s), B_STAGE_BYTES);
+            if (BWD)
+            {
+              // [k rows][n cols]: two boxes of 64 n x 64 k land as the two MN-major blocks
+              tma_load_2d(b_addr(s), &map_b, n_tile * BN, kb * BK, b_full(s));
+              tma_load_2d(b_addr(s) + 8192u, &map_b, n_tile * BN + 64, kb * BK, b_full(s));
+            }
+            else
+            {
+              tma_load_2d(b_addr(s), &map_b, kb * BK, n_tile * BN, b_full(s));
+            }
+          }
+          if (++s == STAGES)
+          {
+            s = 0;
+            par ^= 1u;
+          }
+        }
+      }
+    }
+  }
+  else if (warp == 1)
+  {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0)
+    {
+      constexpr uint32_t idesc = make_idesc(BWD);
+      int s = 0;
+      uint32_t par = 0;
+      int acc = 0;
+      uint32_t acc_par = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+      {
+        mbar_wait(acc_empty(acc), acc_par ^ 1u);
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb)
+        {
+          mbar_wait(a_full(s), par);
+          mbar_wait(b_full(s), par);
+          tc_fence_after();
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+          {
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((acc * MT + mt) * BN);
+#pragma unroll
+            for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
+            {
+              const uint64_t adesc = make_desc(a_addr(s, mt) + k16 * (UMMA_K * 2), 16, 1024);
+              const uint64_t bdesc = BWD ? make_desc(b_addr(s) + k16 * 2048, 8192, 1024)
+                                         : make_desc(b_addr(s) + k16 * (UMMA_K * 2), 16, 1024);
+              umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+            }
+          }
+          umma_commit(empty(s));
+          if (++s == STAGES)
+          {
+            s = 0;
+            par ^= 1u;
+          }
+        }
+        umma_commit(acc_full(acc));
+        if (++acc == 2)
+        {
+          acc = 0;
+          acc_par ^= 1u;
+        }
+      }
+    }
+  }
+  else if (warp < DEQ_WARP0)
+  {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+    float out_scale = 1.0f;
+    if (WMODE == W_I8 && p.scales != nullptr)
+    {
+      out_scale = static_cast<const float *>(p.scales)[0];
+    }
+    int acc = 0;
+    uint32_t acc_par = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+    {
+      const int m_tile = tile % p.num_m_tiles;
+      const int n_tile = tile / p.num_m_tiles;
+      mbar_wait(acc_full(acc), acc_par);
+      tc_fence_after();
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+      {
+        const int64_t row = static_cast<int64_t>(m_tile) * BM + mt * BM_SUB + quarter * 32 + lane;
+#pragma unroll
+        for (int cb = 0; cb < BN / 32; ++cb)
+        {
+          uint32_t r[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                 static_cast<uint32_t>((acc * MT + mt) * BN + cb * 32);
+          tmem_ld32(taddr, r);
+          tmem_ld_wait();
+          if (row < p.m)
+          {
+            const int64_t off = row * p.n_total + static_cast<int64_t>(n_tile) * BN + cb * 32;
+            if (p.c_dtype == CAIFQ_F32)
+            {
+              float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.c) + off);
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+              {
+                float4 v;
+                v.x = __uint_as_float(r[4 * q + 0]) * out_scale;
+                v.y = __uint_as_float(r[4 * q + 1]) * out_scale;
+                v.z = __uint_as_float(r[4 * q + 2]) * out_scale;
+                v.w = __uint_as_float(r[4 * q + 3]) * out_scale;
+                if (p.accumulate)
+                {
+                  const float4 o = dst[q];
+                  v.x += o.x;
+                  v.y += o.y;
+                  v.z += o.z;
+                  v.w += o.w;
+                }
+                dst[q] = v;
+              }
+            }
+            else
+            {
+              // 16-bit outputs: 32 values = 64 bytes = four 16-byte stores
+              uint4 *dst = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c) + off);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+              {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                {
+                  v[e] = __uint_as_float(r[8 * q + e]) * out_scale;
+                }
+                uint32_t packed[4];
+                if (p.accumulate)
+                {
+                  const uint4 o = dst[q];
+                  const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                  {
+                    float lo;
+                    float hi;
+                    if (p.c_dtype == CAIFQ_BF16)
+                    {
+                      lo = __uint_as_float(ow[e] << 16);
+                      hi = __uint_as_float(ow[e] & 0xFFFF0000u);
+                      v[2 * e] = round_through<CAIFQ_BF16>(v[2 * e]) + lo;
+                      v[2 * e + 1] = round_through<CAIFQ_BF16>(v[2 * e + 1]) + hi;
+                    }
+                    else
+                    {
+                      const __half2 h = *reinterpret_cast<const __half2 *>(&ow[e]);
+                      v[2 * e] = round_through<CAIFQ_F16>(v[2 * e]) + __low2float(h);
+                      v[2 * e + 1] = round_through<CAIFQ_F16>(v[2 * e + 1]) + __high2float(h);
+                    }
+                  }
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                {
+                  if (p.c_dtype == CAIFQ_BF16)
+                  {
+                    packed[e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
+                  }
+                  else
+                  {
+                    const __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                    packed[e] = *reinterpret_cast<const uint32_t *>(&h);
+                  }
+                }
+                dst[q] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0)
+      {
+        mbar_arrive(acc_empty(acc));
+      }
+      if (++acc == 2)
+      {
+        acc = 0;
+        acc_par ^= 1u;
+      }
+    }
+  }
+  else if (WMODE != W_BF16)
+  {
+    // ------------------------------------------------------ weight dequantization
+    const int d = threadIdx.x - DEQ_WARP0 * 32;  // 0..255
+    // 16-byte chunks of codes per k-block and thread, and where they go:
+    //   forward  (K-major B): tile rows are n, a chunk is 16 B of one row's k range
+    //   backward (MN-major B): tile rows are k, a chunk is 16 B of one k-row's n range
+    constexpr int ELEMS = (WMODE == W_I8) ? 16 : 32;                 // codes per chunk
+    constexpr int CHUNKS = (BN * BK) / ELEMS;                        // per k-block
+    constexpr int PER_THREAD = CHUNKS / DEQ_THREADS;                 // 2 (int8) or 1 (int4)
+    constexpr int CHUNKS_PER_ROW = (BWD ? BN : BK) / ELEMS;          // chunks along the contiguous direction
+    static_assert(PER_THREAD >= 1, "tile too small for the dequant warps");
+
+    int s = 0;
+    uint32_t par = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+    {
+      const int n_tile = tile / p.num_m_tiles;
+      const int n0 = n_tile * BN;
+      // chunk -> (row inside the tile, part along the contiguous direction)
+      int c_row[PER_THREAD];
+      int c_part[PER_THREAD];
+#pragma unroll
+      for (int i = 0; i < PER_THREAD; ++i)
+      {
+        const int c = d + i * DEQ_THREADS;
+        c_row[i] = c / CHUNKS_PER_ROW;
+        c_part[i] = c % CHUNKS_PER_ROW;
+      }
+      auto load = [&](int kb, uint4 (&raw)[PER_THREAD], float (&sc)[PER_THREAD])
+      {
+        const int k0 = kb * BK;
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i)
+        {
+          // element coordinates of the chunk's first code in the [out, in] matrix
+          const int64_t o = BWD ? (k0 + c_row[i]) : (n0 + c_row[i]);
+          const int64_t ii = BWD ? (n0 + c_part[i] * ELEMS) : (k0 + c_part[i] * ELEMS);
+          const int64_t flat = o * p.in_dim + ii;
+          const uint8_t *src = p.codes + ((WMODE == W_I8) ? flat : (flat >> 1));
+          raw[i] = __ldg(reinterpret_cast<const uint4 *>(src));
+          if (WMODE == W_I4)
+          {
+            sc[i] = __half2float(static_cast<const __half *>(p.scales)[flat / p.group_size]);
+          }
+          else
+          {
+            sc[i] = 1.0f;
+          }
+        }
+      };
+
+      uint4 raw[PER_THREAD];
+      float sc[PER_THREAD];
+      load(0, raw, sc);
+      for (int kb = 0; kb < num_kb; ++kb)
+      {
+        uint4 nraw[PER_THREAD];
+        float nsc[PER_THREAD];
+        if (kb + 1 < num_kb)
+        {
+          load(kb + 1, nraw, nsc);  // in flight while this block is converted
+        }
+        mbar_wait(empty(s), par ^ 1u);
+        const uint32_t bbase = b_addr(s);
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i)
+        {
+          const uint32_t words[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+          // bf16 output: ELEMS values = ELEMS/8 chunks of 16 bytes
+          uint32_t outw[ELEMS / 2];
+          if (WMODE == W_I8)
+          {
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+              int8x4_to_bf16(words[w], outw[2 * w], outw[2 * w + 1]);
+            }
+          }
+          else
+          {
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+              uint32_t o4[4];
+              int4x8_to_bf16(words[w], sc[i], o4);
+              outw[4 * w + 0] = o4[0];
+              outw[4 * w + 1] = o4[1];
+              outw[4 * w + 2] = o4[2];
+              outw[4 * w + 3] = o4[3];
+            }
+          }
+          const int r = c_row[i];
+          const int first = c_part[i] * (ELEMS / 8);  // first 16-byte bf16 chunk along the contiguous direction
+#pragma unroll
+          for (int j = 0; j < ELEMS / 8; ++j)
+          {
+            const int cb = first + j;
+            uint32_t dst;
+            if (BWD)
+            {
+              // MN-major: 64-wide n blocks (8 KB apart), 8-row k groups (1 KB), 128-byte rows, 16-byte chunks XOR row%8
+              dst = bbase + static_cast<uint32_t>((cb >> 3) * 8192 + (r >> 3) * 1024 + (r & 7) * 128 +
+                                                  (((cb & 7) ^ (r & 7)) << 4));
+            }
+            else
+            {
+              // K-major: rows n of 128 bytes, 16-byte chunks XOR row%8
+              dst = bbase + static_cast<uint32_t>(r * 128 + ((cb ^ (r & 7)) << 4));
+            }
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(outw[4 * j + 0]),
+                         "r"(outw[4 * j + 1]), "r"(outw[4 * j + 2]), "r"(outw[4 * j + 3])
+                         : "memory");
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0)
+        {
+          mbar_arrive(b_full(s));
+        }
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i)
+        {
+          raw[i] = nraw[i];
+          sc[i] = nsc[i];
+        }
+        if (++s == STAGES)
+        {
+          s = 0;
+          par ^= 1u;
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1)
+  {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr)
+  {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+    {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements per row, `outer` rows, box of 64 x box_rows, 128-byte swizzle.
+int make_map_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint32_t box_rows)
+{
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr)
+  {
+    set_error("frozen linear (umma): cuTensorMapEncodeTiled is not available from the driver");
+    return CAIFQ_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {inner * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+  {
+    set_error("frozen linear (umma): cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+    return CAIFQ_ERR_CUDA;
+  }
+  return CAIFQ_OK;
+}
+
+int sm_count_umma()
+{
+  static int cached = 0;
+  if (cached == 0)
+  {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    if (cached <= 0)
+    {
+      cached = 148;
+    }
+  }
+  return cached;
+}
+
+template <int WMODE, bool BWD>
+int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const UmmaParams &p, cudaStream_t s)
+{
+  auto kernel = linear_umma_kernel<WMODE, BWD>;
+  static bool configured = false;
+  if (!configured)
+  {
+    CAIFQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+  }
+  const int tiles = p.num_m_tiles * p.num_n_tiles;
+  const int grid = tiles < sm_count_umma() ? tiles : sm_count_umma();
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int wmode_of(const caifq_weight &w)
+{
+  if (w.storage == CAIFQ_I8)
+  {
+    return W_I8;
+  }
+  if (w.storage == CAIFQ_I4)
+  {
+    return W_I4;
+  }
+  return W_BF16;
+}
+
+}  // namespace
+
+bool umma_supported(const LinearArgs &g)
+{
+  const caifq_weight &w = g.w;
+  if (g.a_dtype != CAIFQ_BF16 || g.a_prescale != 1.0f || g.m < 32)
+  {
+    return false;
+  }
+  const int n_total = g.backward ? w.in_dim : w.out_dim;
+  const int k_total = g.backward ? w.out_dim : w.in_dim;
+  if ((n_total % BN) != 0 || (k_total % BK) != 0)
+  {
+    return false;
+  }
+  if ((reinterpret_cast<uintptr_t>(g.a) & 15u) != 0 || (reinterpret_cast<uintptr_t>(g.c) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0)
+  {
+    return false;
+  }
+  switch (w.storage)
+  {
+    case CAIFQ_I8:
+      // per-tensor scale (or none) factors out of the product: exact for fp32 and bf16 compute
+      if (w.scales != nullptr && w.scheme != CAIFQ_PER_TENSOR)
+      {
+        return false;
+      }
+      return g.compute_dtype == CAIFQ_BF16 || g.compute_dtype == CAIFQ_F32;
+    case CAIFQ_I4:
+      // scale*code is rounded to bf16: the reference's bf16 compute cell only
+      if (g.compute_dtype != CAIFQ_BF16 || w.scales == nullptr)
+      {
+        return false;
+      }
+      return (w.group_size % 32) == 0 && (w.in_dim % w.group_size) == 0;
+    case CAIFQ_BF16:
+      // bf16 x bf16 products are exact in fp32
+      return g.compute_dtype == CAIFQ_BF16 || g.compute_dtype == CAIFQ_F32;
+    default:
+      return false;
+  }
+}
+
+int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
+{
+  const caifq_weight &w = g.w;
+  UmmaParams p{};
+  p.codes = static_cast<const uint8_t *>(w.codes);
+  p.scales = w.scales;
+  p.c = g.c;
+  p.c_dtype = g.c_dtype;
+  p.accumulate = g.accumulate ? 1 : 0;
+  p.m = g.m;
+  p.n_total = g.backward ? w.in_dim : w.out_dim;
+  p.k_total = g.backward ? w.out_dim : w.in_dim;
+  p.in_dim = w.in_dim;
+  p.group_size = w.group_size;
+  p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
+  p.num_n_tiles = p.n_total / BN;
+
+  CUtensorMap map_a;
+  CUtensorMap map_b;
+  int rc = make_map_bf16(&map_a, g.a, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(g.m), BM_SUB);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  const int mode = wmode_of(w);
+  if (mode == W_BF16)
+  {
+    // the [out, in] weight itself: forward boxes are 64 k x 128 n rows, backward 64 n x 64 k rows
+    rc = make_map_bf16(&map_b, w.codes, static_cast<uint64_t>(w.in_dim), static_cast<uint64_t>(w.out_dim),
+                       g.backward ? BK : BN);
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+  }
+  else
+  {
+    map_b = map_a;
+  }
+#define CAIFQ_UMMA_CASE(MODE)                                   \
+  if (mode == MODE)                                             \
+  {                                                             \
+    return g.backward ? launch_inst<MODE, true>(map_a, map_b, p, s) \
+                      : launch_inst<MODE, false>(map_a, map_b, p, s); \
+  }
+  CAIFQ_UMMA_CASE(W_I8)
+  CAIFQ_UMMA_CASE(W_I4)
+  CAIFQ_UMMA_CASE(W_BF16)
+#undef CAIFQ_UMMA_CASE
+  set_error("frozen linear (umma): unsupported weight storage %d", w.storage);
   return CAIFQ_ERR_UNSUPPORTED;
 }
+
 }  // namespace caifq

@@ -91,6 +91,14 @@ CAIFQ_API const char *caifq_last_error(void);
 /* 1 when a CUDA device of compute capability 10.x is current, else 0. */
 CAIFQ_API int caifq_device_ok(void);
 CAIFQ_API const char *caifq_version(void);
+/*
+ * Waits inside the kernels (on copies, on other warps) are bounded.  A wait that
+ * runs out lets its kernel finish with wrong results and raises a flag.  This
+ * call synchronises the current device, returns the flags (bit 0: weight-
+ * streaming kernel, bit 1: tensor-core kernel; 0 = healthy; -1 = the query
+ * itself failed) and clears them.
+ */
+CAIFQ_API int caifq_device_status(void);
 
 /* ---- quantize / dequantize (bit-exact with the reference kernels) -------- */
 

@@ -168,3 +168,70 @@ def test_decode_int8_without_scales_and_bf16_out():
     assert nv.last_path() == "decode"
     want = orc.frozen_linear_forward(x_np, _oracle_w(weight, codes, scales, orc.F32))
     assert max_rel_err(y.float().cpu().numpy(), want) <= 1e-2  # bf16 output rounding
+
+
+# ------------------------------------------------------------ tensor-core path
+def _umma_case(storage, compute, m, in_dim, out_dim, seed, group=128):
+    rng = np.random.default_rng(seed)
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, storage, group=group)
+    x_np, x = act(rng, m, in_dim, orc.BF16)
+    dy_np, dy = act(rng, m, out_dim, orc.BF16)
+    wc = _oracle_w(weight, codes, scales, compute)
+    return weight, wc, x_np, x, dy_np, dy
+
+
+@pytest.mark.parametrize("storage,compute,tol", [
+    (orc.I8, orc.F32, TOL_F32),     # exact products: holds the fp32 bound
+    (orc.I8, orc.BF16, TOL_16),
+    (orc.I4, orc.BF16, TOL_16),
+    (orc.BF16, orc.F32, TOL_F32),
+])
+@pytest.mark.parametrize("m,in_dim,out_dim", [(300, 512, 384), (256, 128, 128), (77, 1408, 2048), (1000, 2048, 1408)])
+def test_umma_forward_and_dx(storage, compute, tol, m, in_dim, out_dim):
+    weight, wc, x_np, x, dy_np, dy = _umma_case(storage, compute, m, in_dim, out_dim, 500 + storage + m)
+    y = nv.linear_fwd(weight, x, torch.float32, compute)
+    assert nv.last_path() == "umma"
+    dx = nv.linear_dx(weight, dy, torch.float32, compute)
+    assert nv.last_path() == "umma"
+    assert nv.lib().caifq_device_status() == 0
+    assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, compute)) <= tol
+    assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, compute)) <= tol
+    if storage == orc.I4:
+        # the operand is the reference's own (scale*code rounded to bf16): far inside the bound
+        assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, compute)) <= 1e-4
+
+
+def test_umma_bf16_output_and_accumulate_epilogue():
+    weight, wc, x_np, x, dy_np, dy = _umma_case(orc.I8, orc.F32, 200, 256, 256, 42)
+    yb = nv.linear_fwd(weight, x, torch.bfloat16, orc.F32)
+    assert nv.last_path() == "umma"
+    want = orc.round_through(orc.frozen_linear_forward(x_np, wc), orc.BF16)
+    assert max_rel_err(yb.float().cpu().numpy(), want) <= 1e-2
+
+
+def test_umma_config3_shape_matches_generic_and_oracle_rows(monkeypatch):
+    """4096 -> 4096 int8 per-tensor, M = 8192 bf16 tokens (the training config): the tensor-core
+    path against the generic path on the whole output and against the oracle on 16 rows."""
+    g = torch.Generator(device="cuda").manual_seed(1236)
+    dim, m = 4096, 8192
+    wf = torch.randn(dim * dim, generator=g, device="cuda") * 0.02
+    q, s = nv.quantize_int8_per_tensor(wf)
+    weight = nv.Weight(q.view(dim, dim), nv.I8, dim, dim, s)
+    x = torch.randn(m, dim, generator=g, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(m, dim, generator=g, device="cuda").to(torch.bfloat16)
+    y = nv.linear_fwd(weight, x, torch.float32, orc.F32)
+    assert nv.last_path() == "umma"
+    dx = nv.linear_dx(weight, dy, torch.float32, orc.F32)
+    assert nv.lib().caifq_device_status() == 0
+    monkeypatch.setenv("CAIFQ_FORCE_PATH", "generic")
+    yg = nv.linear_fwd(weight, x, torch.float32, orc.F32)
+    dxg = nv.linear_dx(weight, dy, torch.float32, orc.F32)
+    assert nv.last_path() == "generic"
+    assert float((y - yg).abs().max() / yg.abs().max()) <= TOL_F32
+    assert float((dx - dxg).abs().max() / dxg.abs().max()) <= TOL_F32
+    rows = torch.arange(0, m, m // 16, device="cuda")
+    wc = orc.dequantize_int8_per_tensor(q.cpu().numpy().reshape(dim, dim), s.cpu().numpy())
+    want = orc.gemm_nt(x[rows].float().cpu().numpy(), wc)
+    assert max_rel_err(y[rows].cpu().numpy(), want) <= TOL_F32
+    want_dx = orc.gemm_nn(dy[rows].float().cpu().numpy(), wc)
+    assert max_rel_err(dx[rows].cpu().numpy(), want_dx) <= TOL_F32
