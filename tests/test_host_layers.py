@@ -1,0 +1,125 @@
+"""The C++ layer classes that mirror the reference's interface (caif_b200/host/):
+what a CPU box can check (library loads, exports, argument errors) and, on a GPU,
+the reference's own layer tests restated: shapes and output dtype
+(tests/test_device_frozen_linear.cpp), zero trainable parameters, description
+and name strings, LoRA with B = 0 equals the base, parameter order
+(tests/test_device_lora_adapter.cpp:371-530), int4 path against
+dequantize-then-fp32 within 2e-2 (tests/test_device_frozen_linear.cpp:1234-1310)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import caif_oracle as orc
+from caif_b200 import host_layers as hl
+from caif_b200 import native as nv
+
+
+def test_host_library_exports():
+    lib = hl.lib()
+    missing = [n for n in hl.EXPORTS if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_factory_rejects_illegal_pairs_without_a_gpu():
+    with pytest.raises(hl.HostLayerError, match="unsupported"):
+        hl.Layer(16, 16, storage=1)      # Float64 storage is not a cell
+    with pytest.raises(hl.HostLayerError, match="unsupported"):
+        hl.Layer(16, 16, storage=nv.I8, compute=nv.I8)
+    with pytest.raises(hl.HostLayerError):
+        hl.Layer(0, 16, storage=nv.F32)
+
+
+def test_description_and_counts_without_a_gpu():
+    layer = hl.Layer(24, 40, storage=nv.I4, compute=nv.BF16)
+    assert layer.description() == "FrozenLinear(24,40,int4)"
+    assert layer.counts() == (0, 0, 1)
+    assert layer.parameter_names("blk.") == []
+    layer.close()
+
+
+@pytest.mark.gpu
+def test_frozen_linear_layer_every_storage():
+    from gpu_util import act, make_weight, max_rel_err
+
+    rng = np.random.default_rng(3)
+    for storage in (orc.F32, orc.F16, orc.BF16, orc.I8, orc.I4):
+        in_dim, out_dim, m = 64, 48, 10
+        weight, codes, scales = make_weight(rng, out_dim, in_dim, storage)
+        layer = hl.Layer(in_dim, out_dim, storage)
+        with pytest.raises(hl.HostLayerError, match="weight not loaded"):
+            layer.forward(torch.zeros(m, in_dim, device="cuda"))
+        layer.load_weight(weight.codes, storage if storage != orc.I4 else nv.I4)
+        if scales is not None:
+            layer.load_scales_from_host(np.ascontiguousarray(scales).tobytes())
+        x_np, x = act(rng, m, in_dim, orc.F32)
+        dy_np, dy = act(rng, m, out_dim, orc.F32)
+        with pytest.raises(hl.HostLayerError, match="Forward"):
+            layer.backward(dy)                       # no training-mode forward yet
+        y = layer.forward(x.view(2, 5, in_dim).contiguous())   # 3-D input flattens to rows
+        assert y.dtype == torch.float32 and tuple(y.shape) == (m, out_dim)
+        dx = layer.backward(dy)
+        wc = orc.weight_to_compute(codes, scales, storage, in_dim, out_dim, orc.F32, weight.scheme, weight.group_size)
+        assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc)) <= 1e-4
+        assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc)) <= 1e-4
+        assert np.array_equal(layer.frozen_tensor_fp32().cpu().numpy(), wc)
+        with pytest.raises(hl.HostLayerError, match="last dim"):
+            layer.forward(torch.zeros(m, in_dim + 1, device="cuda"))
+        layer.close()
+
+
+@pytest.mark.gpu
+def test_int4_layer_against_dequantize_then_fp32_within_2e2():
+    from gpu_util import act, make_weight, max_rel_err
+
+    rng = np.random.default_rng(4)
+    in_dim, out_dim, m = 256, 128, 64
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, orc.I4)
+    layer = hl.Layer(in_dim, out_dim, orc.I4, compute=nv.BF16)
+    layer.load_weight(weight.codes, nv.I4)
+    layer.load_scales_from_host(np.ascontiguousarray(scales).tobytes())
+    x_np, x = act(rng, m, in_dim, orc.BF16)
+    y = layer.forward(x)
+    want = orc.gemm_nt(x_np, orc.dequantize_int4(codes, scales, in_dim * out_dim, 128).reshape(out_dim, in_dim))
+    assert max_rel_err(y.cpu().numpy(), want) <= 2e-2
+    layer.close()
+
+
+@pytest.mark.gpu
+def test_lora_adapter_layer():
+    from gpu_util import act, make_weight, max_rel_err
+
+    rng = np.random.default_rng(5)
+    in_dim, out_dim, m, rank, alpha = 128, 96, 40, 8, 16.0
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, orc.I8)
+    layer = hl.Layer(in_dim, out_dim, orc.I8)
+    layer.load_weight(weight.codes, nv.I8)
+    layer.load_scales_from_host(np.ascontiguousarray(scales).tobytes())
+    x_np, x = act(rng, m, in_dim, orc.F32)
+    base = layer.forward(x).clone()
+    layer.wrap_lora(rank, alpha, storage=nv.F32, seed=7)
+    assert layer.description() == "LoRA(rank=8,alpha=16,128,96)+FrozenLinear(128,96,int8)"
+    assert layer.parameter_names("q.") == ["q.lora_a.weight", "q.lora_b.weight"]
+    assert layer.counts() == (2, rank * in_dim + out_dim * rank, 1)
+    # A: Kaiming-uniform from mt19937(seed) within +-sqrt(1/in); B zero => output equals the base
+    a = layer.parameter(0, torch.empty(rank, in_dim, device="cuda"))
+    b = layer.parameter(1, torch.empty(out_dim, rank, device="cuda"))
+    assert float(a.abs().max()) <= np.sqrt(1.0 / in_dim) and float(a.abs().max()) > 0 and float(b.abs().max()) == 0
+    assert torch.equal(layer.forward(x), base)
+    # non-zero B: forward/backward against the oracle
+    b_new = torch.from_numpy((rng.standard_normal((out_dim, rank)) * 1e-2).astype(np.float32)).cuda()
+    layer.set_parameter(1, b_new)
+    wc = orc.weight_to_compute(codes, scales, orc.I8, in_dim, out_dim)
+    want_y, hidden = orc.lora_forward(x_np, orc.frozen_linear_forward(x_np, wc), a.cpu().numpy(), b_new.cpu().numpy(),
+                                      alpha)
+    y = layer.forward(x)
+    assert max_rel_err(y.cpu().numpy(), want_y) <= 1e-4
+    dy_np, dy = act(rng, m, out_dim, orc.F32)
+    dx = layer.backward(dy)
+    want_dx, want_da, want_db = orc.lora_backward(dy_np, x_np, hidden, orc.frozen_linear_backward(dy_np, wc),
+                                                  a.cpu().numpy(), b_new.cpu().numpy(), alpha)
+    assert max_rel_err(dx.cpu().numpy(), want_dx) <= 1e-4
+    assert max_rel_err(layer.parameter(0, a, gradient=True).cpu().numpy(), want_da) <= 1e-4
+    assert max_rel_err(layer.parameter(1, b, gradient=True).cpu().numpy(), want_db) <= 1e-4
+    layer.close()
