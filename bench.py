@@ -289,7 +289,7 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
     torch.cuda.empty_cache()
     xs = {m: torch.randn(m, C2_IN, generator=gen, device=dev).to(torch.bfloat16) for m in C2_MS}
     ys = {m: torch.empty(m, shard, dtype=torch.float32, device=dev) for m in C2_MS}
-    gathered = {m: torch.empty(world, m, shard, dtype=torch.float32, device=dev) for m in C2_MS} if world > 1 else None
+    gathered = {m: torch.empty(world * m, shard, dtype=torch.float32, device=dev) for m in C2_MS} if world > 1 else None
 
     def step_eager():
         for w in weights:
@@ -414,7 +414,7 @@ def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
     xs = [torch.randn(m, dim, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
     dys = [torch.randn(m, dim, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
     state = {"i": 0}
-    gathered = torch.empty(world, m, shard, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    gathered = torch.empty(world * m, shard, dtype=torch.bfloat16, device=dev) if world > 1 else None
 
     def step():
         i = state["i"] % n_sets

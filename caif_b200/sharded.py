@@ -1,0 +1,135 @@
+"""Multi-GPU forms of the path: one process per GPU, torch.distributed for the plumbing.
+
+The reference is single-device (no collective anywhere), so the contract is
+"same numbers as one GPU":
+
+* ColumnParallelFrozenLinear -- rank r holds output features [r*out/N, (r+1)*out/N) of the
+  [out, in] codes and their scales (a contiguous slice of both: the codes stay bit-identical
+  to the 1-GPU tensor).  Forward: local product on replicated X, all-gather of the Y slices
+  along the feature axis.  Backward: dX is a partial sum over the local features, all-reduce.
+* ExpertParallelFrozenMoE -- experts [r*E/N, (r+1)*E/N) live on rank r.  Each rank routes
+  its own tokens, packs them by expert, sends every row to the expert's owner with an
+  all-to-all (row counts are exchanged first), runs the grouped frozen experts on what it
+  received, returns the rows with the mirror all-to-all and combines locally.
+
+The compute itself is injected (`ops`): on a GPU box it is caif_b200.native (the CUDA
+library); the CPU tests of the collectives' bookkeeping pass the numpy oracle instead.
+No kernel of this package reads another GPU's memory: remote data always lands in local
+memory through the collective first.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_range(total, world, rank, quantum=1):
+    """Contiguous [begin, end) of `total` items for `rank`; every shard a multiple of `quantum`."""
+    if total % (world * quantum) != 0:
+        raise ValueError("%d does not split into %d shards of a multiple of %d" % (total, world, quantum))
+    per = total // world
+    return rank * per, (rank + 1) * per
+
+
+def expert_owner(expert, num_experts, world):
+    per = num_experts // world
+    return expert // per
+
+
+class ColumnParallelFrozenLinear:
+    """y = x . W^T with W's rows sharded over the ranks of `group`."""
+
+    def __init__(self, fwd, dx, out_dim, in_dim, group=None):
+        """fwd(x) -> local Y slice [m, out/N]; dx(dy_slice) -> partial dX [m, in] (fp32)."""
+        self.fwd = fwd
+        self.dx = dx
+        self.out_dim = out_dim
+        self.in_dim = in_dim
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.begin, self.end = shard_range(out_dim, self.world, self.rank)
+
+    def forward(self, x):
+        y_local = self.fwd(x)                                    # [m, out/N]
+        m = y_local.shape[0]
+        shard = y_local.shape[1]
+        # concatenated along dim 0 (the form every backend accepts): rows [r*m, (r+1)*m) come from rank r
+        gathered = torch.empty((self.world * m, shard), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(gathered, y_local.contiguous(), group=self.group)
+        # [N, m, out/N] -> [m, N, out/N] -> [m, out]: rank r's features land at columns [r*out/N, ...)
+        return gathered.view(self.world, m, shard).permute(1, 0, 2).reshape(m, self.out_dim)
+
+    def backward(self, dy):
+        part = self.dx(dy[:, self.begin:self.end].contiguous())  # partial sum over this rank's features
+        dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+        return part
+
+
+class ExpertParallelFrozenMoE:
+    """Routed frozen experts sharded by expert.  `ops` supplies, with the semantics of the
+    C ABI entry points of the same names: build_dispatch(indices) -> (dispatch_map, offsets),
+    dispatch(x, indices, dmap, offsets, total) -> packed rows, experts(packed, offsets_local)
+    -> packed outputs for the experts this rank owns, combine(buf, indices, weights, dmap,
+    offsets, tokens) -> [tokens, dim]."""
+
+    def __init__(self, ops, num_experts, group=None):
+        self.ops = ops
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.num_experts = num_experts
+        self.e_begin, self.e_end = shard_range(num_experts, self.world, self.rank)
+        self.local_experts = self.e_end - self.e_begin
+
+    def plan(self, offsets):
+        """From this rank's per-expert offsets [E+1]: rows sent to every rank, rows received from
+        every rank, and the per-(source, local expert) counts of what arrives."""
+        counts = (offsets[1:] - offsets[:-1]).to(torch.int64).cpu()              # rows per expert, local tokens
+        per = self.local_experts
+        send_counts = counts.view(self.world, per).sum(dim=1)                    # rows to each owner
+        all_counts = [torch.empty_like(counts) for _ in range(self.world)]
+        dist.all_gather(all_counts, counts, group=self.group)                    # small: E ints per rank
+        incoming = torch.stack([c[self.e_begin:self.e_end] for c in all_counts])  # [source, local expert]
+        recv_counts = incoming.sum(dim=1)
+        return send_counts, recv_counts, incoming
+
+    @staticmethod
+    def regroup_index(incoming):
+        """Rows arrive grouped by source rank, each source's rows ordered by expert.  Returns the
+        permutation that makes them contiguous per expert (sources in rank order inside an
+        expert), and the local offsets [E_local+1]."""
+        sources, experts = incoming.shape
+        src_start = torch.zeros(sources, dtype=torch.int64)
+        src_start[1:] = torch.cumsum(incoming.sum(dim=1), 0)[:-1]
+        within = torch.zeros_like(incoming)
+        within[:, 1:] = torch.cumsum(incoming, dim=1)[:, :-1]
+        order = []
+        for e in range(experts):
+            for s in range(sources):
+                n = int(incoming[s, e])
+                if n:
+                    start = int(src_start[s] + within[s, e])
+                    order.append(torch.arange(start, start + n, dtype=torch.int64))
+        perm = torch.cat(order) if order else torch.zeros(0, dtype=torch.int64)
+        local_offsets = torch.zeros(experts + 1, dtype=torch.int32)
+        local_offsets[1:] = torch.cumsum(incoming.sum(dim=0), 0).to(torch.int32)
+        return perm, local_offsets
+
+    def forward(self, x, expert_indices, expert_weights):
+        tokens = x.shape[0]
+        dmap, offsets = self.ops.build_dispatch(expert_indices)
+        total = int(offsets[-1])
+        packed = self.ops.dispatch(x, expert_indices, dmap, offsets, total)          # ordered by expert
+        send_counts, recv_counts, incoming = self.plan(offsets)
+        received = torch.empty((int(recv_counts.sum()), x.shape[1]), dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(received, packed, output_split_sizes=recv_counts.tolist(),
+                               input_split_sizes=send_counts.tolist(), group=self.group)
+        perm, local_offsets = self.regroup_index(incoming)
+        perm_dev = perm.to(x.device)
+        grouped = received.index_select(0, perm_dev)
+        out_grouped = self.ops.experts(grouped, local_offsets)
+        out_received = torch.empty_like(out_grouped)
+        out_received.index_copy_(0, perm_dev, out_grouped)                             # back to arrival order
+        returned = torch.empty_like(packed)
+        dist.all_to_all_single(returned, out_received, output_split_sizes=send_counts.tolist(),
+                               input_split_sizes=recv_counts.tolist(), group=self.group)
+        return self.ops.combine(returned, expert_indices, expert_weights, dmap, offsets, tokens)
