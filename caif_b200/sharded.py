@@ -83,12 +83,14 @@ class ExpertParallelFrozenMoE:
     def plan(self, offsets):
         """From this rank's per-expert offsets [E+1]: rows sent to every rank, rows received from
         every rank, and the per-(source, local expert) counts of what arrives."""
-        counts = (offsets[1:] - offsets[:-1]).to(torch.int64).cpu()              # rows per expert, local tokens
+        counts_dev = (offsets[1:] - offsets[:-1]).to(torch.int64)                # rows per expert, local tokens
         per = self.local_experts
+        # the exchange runs where the offsets live (device memory under NCCL, host memory under gloo)
+        all_counts = [torch.empty_like(counts_dev) for _ in range(self.world)]
+        dist.all_gather(all_counts, counts_dev, group=self.group)                # small: E ints per rank
+        counts = counts_dev.cpu()
         send_counts = counts.view(self.world, per).sum(dim=1)                    # rows to each owner
-        all_counts = [torch.empty_like(counts) for _ in range(self.world)]
-        dist.all_gather(all_counts, counts, group=self.group)                    # small: E ints per rank
-        incoming = torch.stack([c[self.e_begin:self.e_end] for c in all_counts])  # [source, local expert]
+        incoming = torch.stack([c[self.e_begin:self.e_end].cpu() for c in all_counts])  # [source, local expert]
         recv_counts = incoming.sum(dim=1)
         return send_counts, recv_counts, incoming
 
