@@ -51,6 +51,14 @@ size_t gemm_tn_scratch_bytes(int p, int q);
 int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
                    float u_prescale, int64_t m, int p, int q, cudaStream_t s);
 int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
+bool skinny_supported(int dtype, int rank, int k);
+int launch_skinny_nt(const void *x, const void *a, void *h, void *hs, float x_prescale, float hs_mul,
+                     const float *hs_div, int64_t m, int k, int rank, cudaStream_t s);
+int launch_skinny_tn(const void *u, const void *v, void *c, float *scratch, float u_prescale, int64_t m, int big,
+                     int rank, bool transpose_out, cudaStream_t s);
+int launch_lora_pad_b(const void *b, void *bp, int n, int rank, cudaStream_t s);
+int launch_lora_transpose_b(const void *b, void *bt, int n, int rank, cudaStream_t s);
+int launch_lora_pad_a(const void *a, void *ap, int n, int rank, cudaStream_t s);
 
 namespace
 {
@@ -112,7 +120,8 @@ Force forced_path()
 }
 
 int linear_any(const caifq_weight *w, bool backward, const void *a, int a_dtype, float a_prescale, int64_t m,
-               void *c, int c_dtype, bool accumulate, int compute_dtype, cudaStream_t s, const char *who)
+               void *c, int c_dtype, bool accumulate, int compute_dtype, cudaStream_t s, const char *who,
+               const void *lora_lhs = nullptr, const void *lora_rhs = nullptr)
 {
   const int rc = check_weight(w, who);
   if (rc != CAIFQ_OK)
@@ -138,6 +147,19 @@ int linear_any(const caifq_weight *w, bool backward, const void *a, int a_dtype,
   args.c_dtype = c_dtype;
   args.accumulate = accumulate;
   args.compute_dtype = compute_dtype;
+  args.lora_lhs = lora_lhs;
+  args.lora_rhs = lora_rhs;
+  if (lora_lhs != nullptr)
+  {
+    // the fused LoRA k-block exists on the tensor-core path only; callers check fused_lora_ok() first
+    if (!umma_supported(args))
+    {
+      set_error("%s: fused LoRA needs the tensor-core path", who);
+      return CAIFQ_ERR_UNSUPPORTED;
+    }
+    set_path("umma");
+    return launch_linear_umma(args, s);
+  }
   const Force force = forced_path();
   if ((force == Force::None || force == Force::Decode) && decode_supported(args))
   {
@@ -172,6 +194,85 @@ caifq_weight float_weight(const void *data, int dtype, int out_dim, int in_dim)
 }
 
 inline size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+// The fast LoRA path: bf16 adapter of rank 8/16/32/64 on a quantized base that the tensor-core
+// kernel takes (forward and backward), enough tokens, and no forced kernel family.
+bool fused_lora_ok(const caifq_weight *w, const caifq_lora *l, const void *act, int64_t m, int compute_dtype)
+{
+  if (forced_path() != Force::None || l->dtype != CAIFQ_BF16 || m < 32)
+  {
+    return false;
+  }
+  if (w->storage != CAIFQ_I8 && w->storage != CAIFQ_I4)
+  {
+    return false;
+  }
+  if (!skinny_supported(l->dtype, l->rank, w->in_dim) || !skinny_supported(l->dtype, l->rank, w->out_dim))
+  {
+    return false;
+  }
+  LinearArgs probe{};
+  probe.w = *w;
+  probe.a = act;
+  probe.a_dtype = CAIFQ_BF16;
+  probe.a_prescale = 1.0f;
+  probe.m = m;
+  probe.c = const_cast<void *>(act);  // only alignment is looked at
+  probe.c_dtype = CAIFQ_BF16;
+  probe.compute_dtype = compute_dtype;
+  probe.backward = false;
+  if (!umma_supported(probe))
+  {
+    return false;
+  }
+  probe.backward = true;
+  return umma_supported(probe);
+}
+
+// scale the base kernel applies in its epilogue (what the padded LoRA operand must be divided by)
+const float *epilogue_scale_ptr(const caifq_weight *w)
+{
+  return (w->storage == CAIFQ_I8 && w->scales != nullptr) ? static_cast<const float *>(w->scales) : nullptr;
+}
+
+struct LoraFwdWs
+{
+  size_t hs;      // [m, 64] bf16
+  size_t bp;      // [out, 64] bf16
+  size_t total;
+};
+
+LoraFwdWs lora_fwd_ws(const caifq_weight *w, int64_t m)
+{
+  LoraFwdWs l{};
+  l.hs = 0;
+  l.bp = align256(static_cast<size_t>(m) * 64 * 2);
+  l.total = l.bp + align256(static_cast<size_t>(w->out_dim) * 64 * 2);
+  return l;
+}
+
+struct LoraBwdWs
+{
+  size_t d_hidden;  // [m, r] in <= 4-byte elements
+  size_t scratch;   // fp32 [max(in,out), r]
+  size_t bt;        // [r, out] bf16
+  size_t dhs;       // [m, 64] bf16
+  size_t ap;        // [64, in] bf16
+  size_t total;
+};
+
+LoraBwdWs lora_bwd_ws(const caifq_weight *w, const caifq_lora *l, int64_t m)
+{
+  LoraBwdWs o{};
+  const size_t big = static_cast<size_t>(w->in_dim > w->out_dim ? w->in_dim : w->out_dim);
+  o.d_hidden = 0;
+  o.scratch = align256(static_cast<size_t>(m) * static_cast<size_t>(l->rank) * 4);
+  o.bt = o.scratch + align256(big * static_cast<size_t>(l->rank) * sizeof(float));
+  o.dhs = o.bt + align256(static_cast<size_t>(l->rank) * w->out_dim * 2);
+  o.ap = o.dhs + align256(static_cast<size_t>(m) * 64 * 2);
+  o.total = o.ap + align256(static_cast<size_t>(64) * w->in_dim * 2);
+  return o;
+}
 
 }  // namespace
 }  // namespace caifq
@@ -315,8 +416,17 @@ static int check_lora(const caifq_weight *w, const caifq_lora *l, const char *wh
   return CAIFQ_OK;
 }
 
+size_t caifq_lora_fwd_workspace_bytes(const caifq_weight *w, const caifq_lora *lora, int64_t m)
+{
+  if (w == nullptr || lora == nullptr || m <= 0)
+  {
+    return 0;
+  }
+  return lora_fwd_ws(w, m).total;
+}
+
 int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
-                          void *hidden, int32_t compute_dtype, void *stream)
+                          void *hidden, void *workspace, int32_t compute_dtype, void *stream)
 {
   const char *who = "caifq_lora_linear_fwd";
   const int rc = check_lora(w, lora, who);
@@ -332,6 +442,26 @@ int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const v
   CAIFQ_CHECK_ARG(x && y && hidden, "%s: x, y and hidden must be non-null", who);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int sd = lora->dtype;
+  const float scale = lora->alpha / static_cast<float>(lora->rank);
+  if (workspace != nullptr && fused_lora_ok(w, lora, x, m, compute_dtype) &&
+      (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0)
+  {
+    // hidden = x . A^T (bf16), Hs = hidden * (alpha/r) / epilogue scale, padded to 64 columns;
+    // then one tensor-core launch computes x . W^T and Hs . Bp^T into the same accumulators.
+    const LoraFwdWs ws = lora_fwd_ws(w, m);
+    char *base = static_cast<char *>(workspace);
+    int r = launch_lora_pad_b(lora->b, base + ws.bp, w->out_dim, lora->rank, s);
+    if (r == CAIFQ_OK)
+    {
+      r = launch_skinny_nt(x, lora->a, hidden, base + ws.hs, 1.0f, scale, epilogue_scale_ptr(w), m, w->in_dim,
+                           lora->rank, s);
+    }
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+    return linear_any(w, false, x, sd, 1.0f, m, y, sd, false, compute_dtype, s, who, base + ws.hs, base + ws.bp);
+  }
   // hidden = x . A^T, rounded to the storage dtype as the reference materialises it
   const caifq_weight wa = float_weight(lora->a, sd, lora->rank, w->in_dim);
   int r = linear_any(&wa, false, x, sd, 1.0f, m, hidden, sd, false, compute_dtype, s, who);
@@ -346,7 +476,7 @@ int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const v
   {
     return r;
   }
-  r = launch_scale(y, y, sd, lora->alpha / static_cast<float>(lora->rank), m * static_cast<int64_t>(w->out_dim), s);
+  r = launch_scale(y, y, sd, scale, m * static_cast<int64_t>(w->out_dim), s);
   if (r != CAIFQ_OK)
   {
     return r;
@@ -361,9 +491,7 @@ size_t caifq_lora_bwd_workspace_bytes(const caifq_weight *w, const caifq_lora *l
   {
     return 0;
   }
-  const size_t d_hidden = align256(static_cast<size_t>(m) * static_cast<size_t>(lora->rank) * 4);
-  const size_t big = static_cast<size_t>(w->in_dim > w->out_dim ? w->in_dim : w->out_dim);
-  return d_hidden + align256(big * static_cast<size_t>(lora->rank) * sizeof(float));
+  return lora_bwd_ws(w, lora, m).total;
 }
 
 int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
@@ -385,9 +513,39 @@ int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const v
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int sd = lora->dtype;
   const float scale = lora->alpha / static_cast<float>(lora->rank);
-  void *d_hidden = workspace;
-  float *scratch = reinterpret_cast<float *>(static_cast<char *>(workspace) +
-                                             align256(static_cast<size_t>(m) * static_cast<size_t>(lora->rank) * 4));
+  const LoraBwdWs ws = lora_bwd_ws(w, lora, m);
+  char *wbase = static_cast<char *>(workspace);
+  void *d_hidden = wbase + ws.d_hidden;
+  float *scratch = reinterpret_cast<float *>(wbase + ws.scratch);
+  if (fused_lora_ok(w, lora, dy, m, compute_dtype) && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0)
+  {
+    // dH = (scale . dy) . B through the transposed copy of B; dHs = dH / epilogue scale, padded
+    int r = launch_lora_transpose_b(lora->b, wbase + ws.bt, w->out_dim, lora->rank, s);
+    if (r == CAIFQ_OK)
+    {
+      r = launch_lora_pad_a(lora->a, wbase + ws.ap, w->in_dim, lora->rank, s);
+    }
+    if (r == CAIFQ_OK)
+    {
+      r = launch_skinny_nt(dy, wbase + ws.bt, d_hidden, wbase + ws.dhs, scale, 1.0f, epilogue_scale_ptr(w), m,
+                           w->out_dim, lora->rank, s);
+    }
+    // dB[out, r] = (scale . dy)^T . hidden;  dA[r, in] = dH^T . x
+    if (r == CAIFQ_OK)
+    {
+      r = launch_skinny_tn(dy, hidden, d_b, scratch, scale, m, w->out_dim, lora->rank, false, s);
+    }
+    if (r == CAIFQ_OK)
+    {
+      r = launch_skinny_tn(x, d_hidden, d_a, scratch, 1.0f, m, w->in_dim, lora->rank, true, s);
+    }
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+    // dx = dy . W + dHs . Ap in one tensor-core launch
+    return linear_any(w, true, dy, sd, 1.0f, m, dx, sd, false, compute_dtype, s, who, wbase + ws.dhs, wbase + ws.ap);
+  }
   // dB[out, r] = (scale . dy)^T . hidden
   int r = launch_gemm_tn(dy, hidden, d_b, scratch, sd, compute_dtype, scale, m, w->out_dim, lora->rank, s);
   if (r != CAIFQ_OK)

@@ -192,6 +192,12 @@ struct LinearArgs
   int c_dtype;
   bool accumulate;
   int compute_dtype;
+  // Optional rank-padded LoRA product folded into the same accumulation as one extra
+  // k-block (tensor-core path only): lora_lhs is [m, 64] bf16 (zero beyond the rank),
+  // lora_rhs is [N, 64] bf16 for forward (rows follow the output features) or [64, N] bf16
+  // for backward.  Both already carry every scale so that acc_total * epilogue scale is right.
+  const void *lora_lhs;
+  const void *lora_rhs;
 };
 
 // generic tiled fp32-FMA GEMM over every (storage, compute) cell

@@ -277,12 +277,13 @@ struct UmmaParams
   int group_size;    // int4
   int num_m_tiles;
   int num_n_tiles;
+  const uint8_t *lora_rhs;  // null = no LoRA k-block
 };
 
 template <int WMODE, bool BWD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const UmmaParams p)
+                   const __grid_constant__ CUtensorMap map_h, const UmmaParams p)
 {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[STAGES * 3 + 4];
@@ -330,6 +331,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const int num_kb = p.k_total / BK;
+  // with a LoRA product the loop runs one more k-block whose operands are the padded factors
+  const int num_kb_all = num_kb + ((p.lora_rhs != nullptr) ? 1 : 0);
 
   if (warp == 0)
   {
@@ -342,14 +345,21 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       {
         const int m_tile = tile % p.num_m_tiles;
         const int n_tile = tile / p.num_m_tiles;
-        for (int kb = 0; kb < num_kb; ++kb)
+        for (int kb = 0; kb < num_kb_all; ++kb)
         {
           mbar_wait(empty(s), par ^ 1u);
           mbar_expect_tx(a_full(s), A_STAGE_BYTES);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
           {
-            tma_load_2d(a_addr(s, mt), &map_a, kb * BK, m_tile * BM + mt * BM_SUB, a_full(s));
+            if (kb < num_kb)
+            {
+              tma_load_2d(a_addr(s, mt), &map_a, kb * BK, m_tile * BM + mt * BM_SUB, a_full(s));
+            }
+            else
+            {
+              tma_load_2d(a_addr(s, mt), &map_h, 0, m_tile * BM + mt * BM_SUB, a_full(s));
+            }
           }
           if (WMODE == W_BF16)
           {
@@ -388,7 +398,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       {
         mbar_wait(acc_empty(acc), acc_par ^ 1u);
         tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb)
+        for (int kb = 0; kb < num_kb_all; ++kb)
         {
           mbar_wait(a_full(s), par);
           mbar_wait(b_full(s), par);
@@ -679,6 +689,48 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           par ^= 1u;
         }
       }
+      if (p.lora_rhs != nullptr)
+      {
+        // LoRA k-block: the padded factor is bf16 already; copy its tile into the operand layout
+        mbar_wait(empty(s), par ^ 1u);
+        const uint32_t bbase = b_addr(s);
+#pragma unroll
+        for (int i = 0; i < (BN * BK * 2 / 16) / DEQ_THREADS; ++i)
+        {
+          const int c = d + i * DEQ_THREADS;  // 16-byte chunk of the 128 x 64 bf16 tile
+          uint32_t dst;
+          const uint8_t *src;
+          if (BWD)
+          {
+            const int r = c >> 4;   // k row (0..63) of the [64, N] factor
+            const int cb = c & 15;  // 16-byte chunk along n
+            src = p.lora_rhs + (static_cast<int64_t>(r) * p.n_total + n0 + cb * 8) * 2;
+            dst = bbase + static_cast<uint32_t>((cb >> 3) * 8192 + (r >> 3) * 1024 + (r & 7) * 128 +
+                                                (((cb & 7) ^ (r & 7)) << 4));
+          }
+          else
+          {
+            const int r = c >> 3;  // n row (0..127) of the [N, 64] factor
+            const int cb = c & 7;
+            src = p.lora_rhs + (static_cast<int64_t>(n0 + r) * 64 + cb * 8) * 2;
+            dst = bbase + static_cast<uint32_t>(r * 128 + ((cb ^ (r & 7)) << 4));
+          }
+          const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src));
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                       : "memory");
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0)
+        {
+          mbar_arrive(b_full(s));
+        }
+        if (++s == STAGES)
+        {
+          s = 0;
+          par ^= 1u;
+        }
+      }
     }
   }
 
@@ -754,7 +806,8 @@ int sm_count_umma()
 }
 
 template <int WMODE, bool BWD>
-int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const UmmaParams &p, cudaStream_t s)
+int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const UmmaParams &p,
+                cudaStream_t s)
 {
   auto kernel = linear_umma_kernel<WMODE, BWD>;
   static bool configured = false;
@@ -765,7 +818,7 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const UmmaPa
   }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < sm_count_umma() ? tiles : sm_count_umma();
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, p);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_h, p);
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
@@ -866,11 +919,26 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   {
     map_b = map_a;
   }
+  CUtensorMap map_h = map_a;
+  if (g.lora_lhs != nullptr && g.lora_rhs != nullptr)
+  {
+    if (mode == W_BF16)
+    {
+      set_error("frozen linear (umma): the fused LoRA k-block needs a quantized base weight");
+      return CAIFQ_ERR_UNSUPPORTED;
+    }
+    rc = make_map_bf16(&map_h, g.lora_lhs, 64, static_cast<uint64_t>(g.m), BM_SUB);
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+    p.lora_rhs = static_cast<const uint8_t *>(g.lora_rhs);
+  }
 #define CAIFQ_UMMA_CASE(MODE)                                   \
   if (mode == MODE)                                             \
   {                                                             \
-    return g.backward ? launch_inst<MODE, true>(map_a, map_b, p, s) \
-                      : launch_inst<MODE, false>(map_a, map_b, p, s); \
+    return g.backward ? launch_inst<MODE, true>(map_a, map_b, map_h, p, s) \
+                      : launch_inst<MODE, false>(map_a, map_b, map_h, p, s); \
   }
   CAIFQ_UMMA_CASE(W_I8)
   CAIFQ_UMMA_CASE(W_I4)

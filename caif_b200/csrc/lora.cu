@@ -114,6 +114,276 @@ __global__ void scale_kernel(const void *__restrict__ src, void *__restrict__ ds
   }
 }
 
+
+// ------------------------------------------------------------------------------
+// Fast path for bf16 adapters (rank a multiple of 8, at most 64).
+// ------------------------------------------------------------------------------
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1)
+{
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi)
+{
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+// bf16x2 register times a scalar, each product rounded back to bf16
+__device__ __forceinline__ uint32_t scale2(uint32_t v, float s)
+{
+  return pack2(__fmul_rn(__uint_as_float(v << 16), s), __fmul_rn(__uint_as_float(v & 0xFFFF0000u), s));
+}
+
+// H[m, R] = (prescale . X)[m, K] . A[R, K]^T, bf16 operands, fp32 accumulation, H rounded to bf16.
+// A warp owns 16 rows; a lane streams 16 bytes (8 consecutive k) of rows g and g+8 per step
+// straight from global memory into MMA fragments (the k order inside a fragment is the same
+// for X and A, which is all a dot product needs).  Optionally also writes
+//   Hs[m, 64] = bf16( float(H) * hs_mul / *hs_div ), zero beyond column R,
+// the padded operand the tensor-core kernel consumes as one extra k-block.
+template <int NT>  // NT = R / 8
+__global__ void __launch_bounds__(128)
+skinny_nt_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
+                 __nv_bfloat16 *__restrict__ h, __nv_bfloat16 *__restrict__ hs, float x_prescale, float hs_mul,
+                 const float *__restrict__ hs_div, int64_t m, int k)
+{
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * 4 + warp) * 16;
+  if (row0 >= m)
+  {
+    return;
+  }
+  const int64_t r_lo = row0 + g;
+  const int64_t r_hi = row0 + g + 8;
+  const bool lo_ok = r_lo < m;
+  const bool hi_ok = r_hi < m;
+  const uint4 *x_lo = reinterpret_cast<const uint4 *>(x + (lo_ok ? r_lo : 0) * k) + t;
+  const uint4 *x_hi = reinterpret_cast<const uint4 *>(x + (hi_ok ? r_hi : 0) * k) + t;
+  const uint4 *a_ptr[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+  {
+    a_ptr[nt] = reinterpret_cast<const uint4 *>(a + static_cast<int64_t>(nt * 8 + g) * k) + t;
+  }
+  float c[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+  {
+    c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
+  }
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  const int steps = k / 32;  // 32 k per step: 4 lanes x 8
+#pragma unroll 4
+  for (int st = 0; st < steps; ++st)
+  {
+    uint4 xa = lo_ok ? __ldg(x_lo + st * 4) : zero4;
+    uint4 xb = hi_ok ? __ldg(x_hi + st * 4) : zero4;
+    if (x_prescale != 1.0f)
+    {
+      xa = make_uint4(scale2(xa.x, x_prescale), scale2(xa.y, x_prescale), scale2(xa.z, x_prescale),
+                      scale2(xa.w, x_prescale));
+      xb = make_uint4(scale2(xb.x, x_prescale), scale2(xb.y, x_prescale), scale2(xb.z, x_prescale),
+                      scale2(xb.w, x_prescale));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+    {
+      const uint4 wa = __ldg(a_ptr[nt] + st * 4);
+      mma_bf16(c[nt], xa.x, xb.x, xa.y, xb.y, wa.x, wa.y);
+      mma_bf16(c[nt], xa.z, xb.z, xa.w, xb.w, wa.z, wa.w);
+    }
+  }
+  const int r = NT * 8;
+  float mul = hs_mul;
+  if (hs != nullptr && hs_div != nullptr)
+  {
+    mul = __fdividef(hs_mul, hs_div[0]);
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+  {
+    const int col = nt * 8 + 2 * t;
+    const uint32_t lo = pack2(c[nt][0], c[nt][1]);
+    const uint32_t hi = pack2(c[nt][2], c[nt][3]);
+    if (lo_ok)
+    {
+      *reinterpret_cast<uint32_t *>(h + r_lo * r + col) = lo;
+      if (hs != nullptr)
+      {
+        *reinterpret_cast<uint32_t *>(hs + r_lo * 64 + col) = scale2(lo, mul);
+      }
+    }
+    if (hi_ok)
+    {
+      *reinterpret_cast<uint32_t *>(h + r_hi * r + col) = hi;
+      if (hs != nullptr)
+      {
+        *reinterpret_cast<uint32_t *>(hs + r_hi * 64 + col) = scale2(hi, mul);
+      }
+    }
+  }
+  if (hs != nullptr)
+  {
+    for (int col = r + 2 * t; col < 64; col += 8)
+    {
+      if (lo_ok)
+      {
+        *reinterpret_cast<uint32_t *>(hs + r_lo * 64 + col) = 0u;
+      }
+      if (hi_ok)
+      {
+        *reinterpret_cast<uint32_t *>(hs + r_hi * 64 + col) = 0u;
+      }
+    }
+  }
+}
+
+// C[big, R] (+)= sum over a slice of tokens of (prescale . U)[m, big] * V[m, R]   (fp32 atomics into acc).
+// 64 threads cover 128 columns of U (one bf16 pair each), 4 such groups split R; V rows are staged in
+// shared memory as fp32.  With `transpose_out` the accumulator is indexed [R, big] (dA).
+template <int JT>  // R = 4 * JT
+__global__ void __launch_bounds__(256)
+skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__restrict__ v, float *__restrict__ acc,
+                 float u_prescale, int64_t m, int big, int transpose_out)
+{
+  constexpr int R = 4 * JT;
+  constexpr int TMS = 64;
+  __shared__ __align__(16) float sv[TMS][R];
+  const int tid = threadIdx.x;
+  const int cl = tid & 63;   // column pair
+  const int jg = tid >> 6;   // which quarter of R
+  const int c0 = blockIdx.x * 128 + cl * 2;
+  const bool col_ok = c0 < big;  // big is even
+  const int64_t per = (m + gridDim.y - 1) / gridDim.y;
+  const int64_t m_begin = per * blockIdx.y;
+  const int64_t m_end = (m_begin + per < m) ? (m_begin + per) : m;
+  float a0[JT];
+  float a1[JT];
+#pragma unroll
+  for (int j = 0; j < JT; ++j)
+  {
+    a0[j] = 0.0f;
+    a1[j] = 0.0f;
+  }
+  for (int64_t mb = m_begin; mb < m_end; mb += TMS)
+  {
+    const int rows = static_cast<int>((m_end - mb < TMS) ? (m_end - mb) : TMS);
+    for (int e = tid; e < TMS * R; e += 256)
+    {
+      const int rr = e / R;
+      const int jj = e % R;
+      sv[rr][jj] = (rr < rows) ? __bfloat162float(v[(mb + rr) * R + jj]) : 0.0f;
+    }
+    __syncthreads();
+    if (col_ok)
+    {
+      const uint32_t *up = reinterpret_cast<const uint32_t *>(u + mb * big + c0);
+      const int64_t pitch = big / 2;
+#pragma unroll 8
+      for (int rr = 0; rr < rows; ++rr)
+      {
+        uint32_t uu = __ldg(up + rr * pitch);
+        if (u_prescale != 1.0f)
+        {
+          uu = scale2(uu, u_prescale);
+        }
+        const float ulo = __uint_as_float(uu << 16);
+        const float uhi = __uint_as_float(uu & 0xFFFF0000u);
+#pragma unroll
+        for (int j4 = 0; j4 < JT; j4 += 4)
+        {
+          if (JT >= 4)
+          {
+            const float4 vv = *reinterpret_cast<const float4 *>(&sv[rr][jg * JT + j4]);
+            a0[j4 + 0] = fmaf(ulo, vv.x, a0[j4 + 0]);
+            a1[j4 + 0] = fmaf(uhi, vv.x, a1[j4 + 0]);
+            a0[j4 + 1] = fmaf(ulo, vv.y, a0[j4 + 1]);
+            a1[j4 + 1] = fmaf(uhi, vv.y, a1[j4 + 1]);
+            a0[j4 + 2] = fmaf(ulo, vv.z, a0[j4 + 2]);
+            a1[j4 + 2] = fmaf(uhi, vv.z, a1[j4 + 2]);
+            a0[j4 + 3] = fmaf(ulo, vv.w, a0[j4 + 3]);
+            a1[j4 + 3] = fmaf(uhi, vv.w, a1[j4 + 3]);
+          }
+        }
+        if (JT < 4)
+        {
+#pragma unroll
+          for (int j = 0; j < JT; ++j)
+          {
+            const float vv = sv[rr][jg * JT + j];
+            a0[j] = fmaf(ulo, vv, a0[j]);
+            a1[j] = fmaf(uhi, vv, a1[j]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (col_ok)
+  {
+#pragma unroll
+    for (int j = 0; j < JT; ++j)
+    {
+      const int jj = jg * JT + j;
+      if (transpose_out)
+      {
+        atomicAdd(&acc[static_cast<int64_t>(jj) * big + c0], a0[j]);
+        atomicAdd(&acc[static_cast<int64_t>(jj) * big + c0 + 1], a1[j]);
+      }
+      else
+      {
+        atomicAdd(&acc[static_cast<int64_t>(c0) * R + jj], a0[j]);
+        atomicAdd(&acc[static_cast<int64_t>(c0 + 1) * R + jj], a1[j]);
+      }
+    }
+  }
+}
+
+// Bp[n, 64] = B[n, R] padded with zeros (forward), or Bt[R, n] = B[n, R]^T (backward).
+__global__ void lora_pad_b_kernel(const __nv_bfloat16 *__restrict__ b, __nv_bfloat16 *__restrict__ bp, int n, int r)
+{
+  const int64_t total = static_cast<int64_t>(n) * 64;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    const int col = static_cast<int>(i & 63);
+    const int64_t row = i >> 6;
+    bp[i] = (col < r) ? b[row * r + col] : __float2bfloat16(0.0f);
+  }
+}
+
+__global__ void lora_transpose_b_kernel(const __nv_bfloat16 *__restrict__ b, __nv_bfloat16 *__restrict__ bt, int n,
+                                        int r)
+{
+  const int64_t total = static_cast<int64_t>(n) * r;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    const int64_t j = i / n;   // output row (rank index)
+    const int64_t o = i % n;   // output column
+    bt[i] = b[o * r + j];
+  }
+}
+
+// Ap[64, n] = A[R, n] followed by zero rows.
+__global__ void lora_pad_a_kernel(const __nv_bfloat16 *__restrict__ a, __nv_bfloat16 *__restrict__ ap, int n, int r)
+{
+  const int64_t total = static_cast<int64_t>(64) * n;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    ap[i] = (i < static_cast<int64_t>(r) * n) ? a[i] : __float2bfloat16(0.0f);
+  }
+}
+
 }  // namespace
 
 // fp32 scratch the reduction needs: p*q floats.
@@ -155,6 +425,120 @@ int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dt
     g = 148 * 8;
   }
   round_out_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(scratch, c, dtype, n);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+bool skinny_supported(int dtype, int rank, int k)
+{
+  return dtype == CAIFQ_BF16 && (rank == 8 || rank == 16 || rank == 32 || rank == 64) && (k % 32) == 0;
+}
+
+int launch_skinny_nt(const void *x, const void *a, void *h, void *hs, float x_prescale, float hs_mul,
+                     const float *hs_div, int64_t m, int k, int rank, cudaStream_t s)
+{
+  if (m <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const unsigned grid = static_cast<unsigned>((m + 63) / 64);
+  const __nv_bfloat16 *xp = static_cast<const __nv_bfloat16 *>(x);
+  const __nv_bfloat16 *ap = static_cast<const __nv_bfloat16 *>(a);
+  __nv_bfloat16 *hp = static_cast<__nv_bfloat16 *>(h);
+  __nv_bfloat16 *hsp = static_cast<__nv_bfloat16 *>(hs);
+  switch (rank)
+  {
+    case 8:
+      skinny_nt_kernel<1><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      break;
+    case 16:
+      skinny_nt_kernel<2><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      break;
+    case 32:
+      skinny_nt_kernel<4><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      break;
+    case 64:
+      skinny_nt_kernel<8><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      break;
+    default:
+      set_error("LoRA fast path: unsupported rank %d", rank);
+      return CAIFQ_ERR_UNSUPPORTED;
+  }
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+// C = (prescale . U)^T . V with U [m, big], V [m, rank]; C is [big, rank] or, transposed, [rank, big].
+int launch_skinny_tn(const void *u, const void *v, void *c, float *scratch, float u_prescale, int64_t m, int big,
+                     int rank, bool transpose_out, cudaStream_t s)
+{
+  const int64_t n = static_cast<int64_t>(big) * rank;
+  if (n <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_CUDA(cudaMemsetAsync(scratch, 0, static_cast<size_t>(n) * sizeof(float), s));
+  if (m > 0)
+  {
+    int64_t slices = (m + 255) / 256;
+    if (slices > 64)
+    {
+      slices = 64;
+    }
+    dim3 grid((big + 127) / 128, static_cast<unsigned>(slices));
+    const __nv_bfloat16 *up = static_cast<const __nv_bfloat16 *>(u);
+    const __nv_bfloat16 *vp = static_cast<const __nv_bfloat16 *>(v);
+    const int tr = transpose_out ? 1 : 0;
+    switch (rank)
+    {
+      case 8:
+        skinny_tn_kernel<2><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        break;
+      case 16:
+        skinny_tn_kernel<4><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        break;
+      case 32:
+        skinny_tn_kernel<8><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        break;
+      case 64:
+        skinny_tn_kernel<16><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        break;
+      default:
+        set_error("LoRA fast path: unsupported rank %d", rank);
+        return CAIFQ_ERR_UNSUPPORTED;
+    }
+    CAIFQ_CHECK_LAUNCH();
+  }
+  int64_t g = (n + 255) / 256;
+  if (g > 148 * 8)
+  {
+    g = 148 * 8;
+  }
+  round_out_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(scratch, c, CAIFQ_BF16, n);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_lora_pad_b(const void *b, void *bp, int n, int rank, cudaStream_t s)
+{
+  lora_pad_b_kernel<<<148 * 2, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(b), static_cast<__nv_bfloat16 *>(bp), n,
+                                           rank);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_lora_transpose_b(const void *b, void *bt, int n, int rank, cudaStream_t s)
+{
+  lora_transpose_b_kernel<<<148, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(b), static_cast<__nv_bfloat16 *>(bt),
+                                             n, rank);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_lora_pad_a(const void *a, void *ap, int n, int rank, cudaStream_t s)
+{
+  lora_pad_a_kernel<<<148 * 2, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(a), static_cast<__nv_bfloat16 *>(ap), n,
+                                           rank);
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

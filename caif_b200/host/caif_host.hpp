@@ -802,9 +802,12 @@ class CAIF_DeviceLoRAAdapter : public CAIF_DeviceLayerTyped<ComputeT, StorageT>
       CAIF_DeviceTensor hidden = CAIF_DeviceTensor::Uninitialized({n, _config.Rank()}, Stream(), sd);
       const caifq_weight w = _frozen->AsCaifqWeight();
       const caifq_lora l = AsCaifqLora();
+      const size_t ws_bytes = caifq_lora_fwd_workspace_bytes(&w, &l, n);
+      CAIF_DeviceTensor ws =
+          CAIF_DeviceTensor::Uninitialized({static_cast<uint32_t>(ws_bytes)}, Stream(), Dtype_e::Int8);
       CAIF_CheckCaifq(caifq_lora_linear_fwd(&w, &l, input.DeviceDataRaw(), n, output.DeviceDataRaw(),
-                                            hidden.DeviceDataRaw(), static_cast<int32_t>(Base_t::ComputeDtype()),
-                                            Stream().Handle()),
+                                            hidden.DeviceDataRaw(), ws.DeviceDataRaw(),
+                                            static_cast<int32_t>(Base_t::ComputeDtype()), Stream().Handle()),
                       "LoRAAdapter::Forward");
       if (ctx.Training())
       {

@@ -67,8 +67,9 @@ _SIGNATURES = {
     "caifq_weight_materialize": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _vp]),
     "caifq_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_linear_dx": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_lora_fwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
-                                             _i32, _vp]),
+                                             _vp, _i32, _vp]),
     "caifq_lora_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_linear_bwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _vp, _vp, _i64,
                                              _vp, _vp, _vp, _vp, _i32, _vp]),
@@ -286,8 +287,10 @@ def lora_linear_fwd(w, lora, x, compute=F32):
     m = x.numel() // w.in_dim
     y = torch.empty(tuple(x.shape[:-1]) + (w.out_dim,), dtype=x.dtype, device=x.device)
     hidden = torch.empty((m, lora.rank), dtype=x.dtype, device=x.device)
-    _check(lib().caifq_lora_linear_fwd(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), compute, _stream()),
-           "lora_linear_fwd")
+    ws_bytes = lib().caifq_lora_fwd_workspace_bytes(w.ref(), lora.ref(), m)
+    ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=x.device)
+    _check(lib().caifq_lora_linear_fwd(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), _ptr(ws), compute,
+                                       _stream()), "lora_linear_fwd")
     return y, hidden
 
 

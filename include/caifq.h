@@ -160,9 +160,16 @@ CAIFQ_API const char *caifq_last_path(void);
  *   hidden[m, r] = x . A^T;  y = W-path(x) + (alpha/r) . hidden . B^T
  * x, y, hidden are in lora->dtype.  `hidden` [m, r] is required: it is the
  * tensor the reference caches for backward, and the up-projection reads it.
+ * `workspace` (caifq_lora_fwd_workspace_bytes(w, lora, m) bytes, 256-byte
+ * aligned; may be NULL) enables the fused path for bf16 adapters of rank
+ * 8/16/32/64 on int8/int4 bases: the LoRA product rides in the tensor-core
+ * kernel as one extra k-block instead of separate launches.  There the LoRA
+ * term is rounded once with the sum (the reference rounds hidden.B^T, its
+ * scaling and the sum separately); both stay inside the bf16 tolerance.
  */
+CAIFQ_API size_t caifq_lora_fwd_workspace_bytes(const caifq_weight *w, const caifq_lora *lora, int64_t m);
 CAIFQ_API int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
-                          void *hidden, int32_t compute_dtype, void *stream);
+                                    void *hidden, void *workspace, int32_t compute_dtype, void *stream);
 
 /*
  * CAIF_DeviceLoRAAdapter::BackwardImpl, src/caif_device_lora_adapter.cpp:205-281:

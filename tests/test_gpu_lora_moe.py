@@ -167,3 +167,34 @@ def test_grouped_frozen_experts(storage, sd, compute):
         assert max_rel_err(gate_out[lo:hi].float().cpu().numpy(), g) <= tol
         want_dx = orc.frozen_expert_backward(dy_np[lo:hi], g, u, o_gate[e], o_up[e], o_down[e], compute, sd)
         assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
+
+
+@pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I4, orc.BF16)])
+@pytest.mark.parametrize("m,in_dim,out_dim,rank", [(300, 512, 384, 16), (1024, 1024, 1024, 8), (130, 256, 640, 64)])
+def test_lora_fused_tensor_core_path(storage, compute, m, in_dim, out_dim, rank):
+    """bf16 adapter on a quantized base with enough tokens: the LoRA products ride in the tensor-core
+    kernel (forward and dX) and the token reductions use the skinny kernels."""
+    rng = np.random.default_rng(700 + storage + m)
+    alpha, sd = 32.0, orc.BF16
+    weight, codes, scales, a, b, x_np, x, dy_np, dy, lora = _lora_case(rng, storage, sd, in_dim, out_dim, m, rank,
+                                                                         alpha)
+    wc = orc.weight_to_compute(codes, scales, storage, in_dim, out_dim, compute, weight.scheme, weight.group_size)
+    y, hidden = nv.lora_linear_fwd(weight, lora, x, compute)
+    assert nv.last_path() == "umma"
+    want_y, want_h = orc.lora_forward(x_np, orc.frozen_linear_forward(x_np, wc, compute), a, b, alpha, sd)
+    assert max_rel_err(hidden.float().cpu().numpy(), want_h) <= TOL[sd]
+    assert max_rel_err(y.float().cpu().numpy(), want_y) <= TOL[sd]
+    dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dy, x, hidden, compute)
+    assert nv.last_path() == "umma"
+    assert nv.lib().caifq_device_status() == 0
+    want_dx, want_da, want_db = orc.lora_backward(dy_np, x_np, want_h, orc.frozen_linear_backward(dy_np, wc, compute),
+                                                  a, b, alpha, sd)
+    assert max_rel_err(dx.float().cpu().numpy(), want_dx) <= TOL[sd]
+    assert max_rel_err(d_a.float().cpu().numpy(), want_da) <= TOL[sd]
+    assert max_rel_err(d_b.float().cpu().numpy(), want_db) <= TOL[sd]
+    # the LoRA term must really be there: with B scaled up 100x the outputs move accordingly
+    big = nv.Lora(lora.a, (lora.b.float() * 100).to(torch.bfloat16), alpha)
+    y_big, _ = nv.lora_linear_fwd(weight, big, x, compute)
+    want_big, _ = orc.lora_forward(x_np, orc.frozen_linear_forward(x_np, wc, compute), a,
+                                   orc.round_through(b * 100, sd), alpha, sd)
+    assert max_rel_err(y_big.float().cpu().numpy(), want_big) <= TOL[sd]
