@@ -147,24 +147,25 @@ __device__ __forceinline__ uint32_t scale2(uint32_t v, float s)
 //   Hs[m, 64] = bf16( float(H) * hs_mul / *hs_div ), zero beyond column R,
 // the padded operand the tensor-core kernel consumes as one extra k-block.
 template <int NT>  // NT = R / 8
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 skinny_nt_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ a,
                  __nv_bfloat16 *__restrict__ h, __nv_bfloat16 *__restrict__ hs, float x_prescale, float hs_mul,
                  const float *__restrict__ hs_div, int64_t m, int k)
 {
+  // a CTA owns 16 rows; its 8 warps split K and add their partial tiles through shared memory
+  __shared__ float part[8][16][NT * 8 + 1];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2;
   const int t = lane & 3;
-  const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * 4 + warp) * 16;
-  if (row0 >= m)
-  {
-    return;
-  }
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * 16;
   const int64_t r_lo = row0 + g;
   const int64_t r_hi = row0 + g + 8;
   const bool lo_ok = r_lo < m;
   const bool hi_ok = r_hi < m;
+  const int steps = k / 32;  // 32 k per step: 4 lanes x 8
+  const int st_begin = (steps * warp) / 8;
+  const int st_end = (steps * (warp + 1)) / 8;
   const uint4 *x_lo = reinterpret_cast<const uint4 *>(x + (lo_ok ? r_lo : 0) * k) + t;
   const uint4 *x_hi = reinterpret_cast<const uint4 *>(x + (hi_ok ? r_hi : 0) * k) + t;
   const uint4 *a_ptr[NT];
@@ -180,9 +181,8 @@ skinny_nt_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__res
     c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
   }
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-  const int steps = k / 32;  // 32 k per step: 4 lanes x 8
 #pragma unroll 4
-  for (int st = 0; st < steps; ++st)
+  for (int st = st_begin; st < st_end; ++st)
   {
     uint4 xa = lo_ok ? __ldg(x_lo + st * 4) : zero4;
     uint4 xb = hi_ok ? __ldg(x_hi + st * 4) : zero4;
@@ -201,47 +201,51 @@ skinny_nt_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__res
       mma_bf16(c[nt], xa.z, xb.z, xa.w, xb.w, wa.z, wa.w);
     }
   }
-  const int r = NT * 8;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+  {
+    part[warp][g][nt * 8 + 2 * t] = c[nt][0];
+    part[warp][g][nt * 8 + 2 * t + 1] = c[nt][1];
+    part[warp][g + 8][nt * 8 + 2 * t] = c[nt][2];
+    part[warp][g + 8][nt * 8 + 2 * t + 1] = c[nt][3];
+  }
+  __syncthreads();
+  constexpr int R = NT * 8;
   float mul = hs_mul;
   if (hs != nullptr && hs_div != nullptr)
   {
     mul = __fdividef(hs_mul, hs_div[0]);
   }
+  // 16 rows x 64 padded columns, one element pair per thread-iteration
+  for (int e = threadIdx.x; e < 16 * 32; e += 256)
+  {
+    const int rr = e >> 5;
+    const int col = (e & 31) * 2;
+    const int64_t row = row0 + rr;
+    if (row >= m)
+    {
+      continue;
+    }
+    if (col < R)
+    {
+      float v0 = 0.0f;
+      float v1 = 0.0f;
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt)
-  {
-    const int col = nt * 8 + 2 * t;
-    const uint32_t lo = pack2(c[nt][0], c[nt][1]);
-    const uint32_t hi = pack2(c[nt][2], c[nt][3]);
-    if (lo_ok)
-    {
-      *reinterpret_cast<uint32_t *>(h + r_lo * r + col) = lo;
+      for (int w = 0; w < 8; ++w)
+      {
+        v0 += part[w][rr][col];
+        v1 += part[w][rr][col + 1];
+      }
+      const uint32_t packed = pack2(v0, v1);
+      *reinterpret_cast<uint32_t *>(h + row * R + col) = packed;
       if (hs != nullptr)
       {
-        *reinterpret_cast<uint32_t *>(hs + r_lo * 64 + col) = scale2(lo, mul);
+        *reinterpret_cast<uint32_t *>(hs + row * 64 + col) = scale2(packed, mul);
       }
     }
-    if (hi_ok)
+    else if (hs != nullptr)
     {
-      *reinterpret_cast<uint32_t *>(h + r_hi * r + col) = hi;
-      if (hs != nullptr)
-      {
-        *reinterpret_cast<uint32_t *>(hs + r_hi * 64 + col) = scale2(hi, mul);
-      }
-    }
-  }
-  if (hs != nullptr)
-  {
-    for (int col = r + 2 * t; col < 64; col += 8)
-    {
-      if (lo_ok)
-      {
-        *reinterpret_cast<uint32_t *>(hs + r_lo * 64 + col) = 0u;
-      }
-      if (hi_ok)
-      {
-        *reinterpret_cast<uint32_t *>(hs + r_hi * 64 + col) = 0u;
-      }
+      *reinterpret_cast<uint32_t *>(hs + row * 64 + col) = 0u;
     }
   }
 }
@@ -287,40 +291,51 @@ skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__res
     {
       const uint32_t *up = reinterpret_cast<const uint32_t *>(u + mb * big + c0);
       const int64_t pitch = big / 2;
-#pragma unroll 8
-      for (int rr = 0; rr < rows; ++rr)
+      for (int r0 = 0; r0 < TMS; r0 += 8)
       {
-        uint32_t uu = __ldg(up + rr * pitch);
-        if (u_prescale != 1.0f)
-        {
-          uu = scale2(uu, u_prescale);
-        }
-        const float ulo = __uint_as_float(uu << 16);
-        const float uhi = __uint_as_float(uu & 0xFFFF0000u);
+        // eight independent loads in flight before any of them is used
+        uint32_t ub[8];
 #pragma unroll
-        for (int j4 = 0; j4 < JT; j4 += 4)
+        for (int q = 0; q < 8; ++q)
         {
-          if (JT >= 4)
+          ub[q] = (r0 + q < rows) ? __ldg(up + (r0 + q) * pitch) : 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+        {
+          const int rr = r0 + q;
+          uint32_t uu = ub[q];
+          if (u_prescale != 1.0f)
           {
-            const float4 vv = *reinterpret_cast<const float4 *>(&sv[rr][jg * JT + j4]);
-            a0[j4 + 0] = fmaf(ulo, vv.x, a0[j4 + 0]);
-            a1[j4 + 0] = fmaf(uhi, vv.x, a1[j4 + 0]);
-            a0[j4 + 1] = fmaf(ulo, vv.y, a0[j4 + 1]);
-            a1[j4 + 1] = fmaf(uhi, vv.y, a1[j4 + 1]);
-            a0[j4 + 2] = fmaf(ulo, vv.z, a0[j4 + 2]);
-            a1[j4 + 2] = fmaf(uhi, vv.z, a1[j4 + 2]);
-            a0[j4 + 3] = fmaf(ulo, vv.w, a0[j4 + 3]);
-            a1[j4 + 3] = fmaf(uhi, vv.w, a1[j4 + 3]);
+            uu = scale2(uu, u_prescale);
           }
-        }
-        if (JT < 4)
-        {
+          const float ulo = __uint_as_float(uu << 16);
+          const float uhi = __uint_as_float(uu & 0xFFFF0000u);
 #pragma unroll
-          for (int j = 0; j < JT; ++j)
+          for (int j4 = 0; j4 < JT; j4 += 4)
           {
-            const float vv = sv[rr][jg * JT + j];
-            a0[j] = fmaf(ulo, vv, a0[j]);
-            a1[j] = fmaf(uhi, vv, a1[j]);
+            if (JT >= 4)
+            {
+              const float4 vv = *reinterpret_cast<const float4 *>(&sv[rr][jg * JT + j4]);
+              a0[j4 + 0] = fmaf(ulo, vv.x, a0[j4 + 0]);
+              a1[j4 + 0] = fmaf(uhi, vv.x, a1[j4 + 0]);
+              a0[j4 + 1] = fmaf(ulo, vv.y, a0[j4 + 1]);
+              a1[j4 + 1] = fmaf(uhi, vv.y, a1[j4 + 1]);
+              a0[j4 + 2] = fmaf(ulo, vv.z, a0[j4 + 2]);
+              a1[j4 + 2] = fmaf(uhi, vv.z, a1[j4 + 2]);
+              a0[j4 + 3] = fmaf(ulo, vv.w, a0[j4 + 3]);
+              a1[j4 + 3] = fmaf(uhi, vv.w, a1[j4 + 3]);
+            }
+          }
+          if (JT < 4)
+          {
+#pragma unroll
+            for (int j = 0; j < JT; ++j)
+            {
+              const float vv = sv[rr][jg * JT + j];
+              a0[j] = fmaf(ulo, vv, a0[j]);
+              a1[j] = fmaf(uhi, vv, a1[j]);
+            }
           }
         }
       }
@@ -441,7 +456,7 @@ int launch_skinny_nt(const void *x, const void *a, void *h, void *hs, float x_pr
   {
     return CAIFQ_OK;
   }
-  const unsigned grid = static_cast<unsigned>((m + 63) / 64);
+  const unsigned grid = static_cast<unsigned>((m + 15) / 16);
   const __nv_bfloat16 *xp = static_cast<const __nv_bfloat16 *>(x);
   const __nv_bfloat16 *ap = static_cast<const __nv_bfloat16 *>(a);
   __nv_bfloat16 *hp = static_cast<__nv_bfloat16 *>(h);
@@ -449,16 +464,16 @@ int launch_skinny_nt(const void *x, const void *a, void *h, void *hs, float x_pr
   switch (rank)
   {
     case 8:
-      skinny_nt_kernel<1><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      skinny_nt_kernel<1><<<grid, 256, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
       break;
     case 16:
-      skinny_nt_kernel<2><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      skinny_nt_kernel<2><<<grid, 256, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
       break;
     case 32:
-      skinny_nt_kernel<4><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      skinny_nt_kernel<4><<<grid, 256, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
       break;
     case 64:
-      skinny_nt_kernel<8><<<grid, 128, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
+      skinny_nt_kernel<8><<<grid, 256, 0, s>>>(xp, ap, hp, hsp, x_prescale, hs_mul, hs_div, m, k);
       break;
     default:
       set_error("LoRA fast path: unsupported rank %d", rank);
