@@ -35,6 +35,8 @@
 // read and lets the kernel finish (with wrong numbers) instead of hanging.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace caifq
@@ -64,21 +66,28 @@ namespace
 constexpr int BM_SUB = 128;          // rows of one MMA
 constexpr int MT = 2;                // MMAs (row sub-tiles) per weight tile
 constexpr int BM = BM_SUB * MT;      // 256
-constexpr int BN = 128;
+// BN (columns of the output tile, N of one MMA) is a template parameter: 128 or 256
 constexpr int BK = 64;               // one 128-byte swizzle span of bf16
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
 constexpr int A_SUB_BYTES = BM_SUB * BK * 2;       // 16 KB
 constexpr int A_STAGE_BYTES = A_SUB_BYTES * MT;    // 32 KB
-constexpr int B_STAGE_BYTES = BN * BK * 2;         // 16 KB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the base to 1024
+constexpr int MAX_STAGES = 4;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_WARPS = 14;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int DEQ_WARP0 = 6;
 constexpr int DEQ_THREADS = 8 * 32;
 constexpr uint32_t kSpinLimit = 1u << 26;
+
+template <int BN>
+struct TileCfg
+{
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;               // 16 or 32 KB
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = (BN == 128) ? 4 : 3;              // 192 KB of operands either way
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the base to 1024
+  static constexpr int ACC_BUFS = TMEM_COLS / (MT * BN);          // 2 (epilogue overlaps the next tile) or 1
+};
 
 enum WMode
 {
@@ -204,7 +213,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
 
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 x bf16, A K-major,
 // B K-major (forward) or MN-major (backward), N = 128, M = 128.
-__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major)
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int BN)
 {
   return (1u << 4)                          // D format f32
          | (1u << 7)                        // A format bf16
@@ -280,13 +289,17 @@ struct UmmaParams
   const uint8_t *lora_rhs;  // null = no LoRA k-block
 };
 
-template <int WMODE, bool BWD>
+template <int WMODE, bool BWD, int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_h, const UmmaParams p)
 {
+  constexpr int B_STAGE_BYTES = TileCfg<BN>::B_STAGE_BYTES;
+  constexpr int STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
+  constexpr int STAGES = TileCfg<BN>::STAGES;
+  constexpr int ACC_BUFS = TileCfg<BN>::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[STAGES * 3 + 4];
+  __shared__ uint64_t bars[MAX_STAGES * 3 + 4];
   __shared__ uint32_t tmem_base_slot;
 
   const int warp = threadIdx.x >> 5;
@@ -310,7 +323,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       mbar_init(b_full(s), (WMODE == W_BF16) ? 1 : 8);
       mbar_init(empty(s), 1);
     }
-    for (int a = 0; a < 2; ++a)
+    for (int a = 0; a < ACC_BUFS; ++a)
     {
       mbar_init(acc_full(a), 1);
       mbar_init(acc_empty(a), 4);
@@ -367,8 +380,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             if (BWD)
             {
               // [k rows][n cols]: two boxes of 64 n x 64 k land as the two MN-major blocks
-              tma_load_2d(b_addr(s), &map_b, n_tile * BN, kb * BK, b_full(s));
-              tma_load_2d(b_addr(s) + 8192u, &map_b, n_tile * BN + 64, kb * BK, b_full(s));
+#pragma unroll
+              for (int nb = 0; nb < BN / 64; ++nb)
+              {
+                tma_load_2d(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, &map_b, n_tile * BN + nb * 64, kb * BK,
+                            b_full(s));
+              }
             }
             else
             {
@@ -389,7 +406,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0)
     {
-      constexpr uint32_t idesc = make_idesc(BWD);
+      constexpr uint32_t idesc = make_idesc(BWD, BN);
       int s = 0;
       uint32_t par = 0;
       int acc = 0;
@@ -424,7 +441,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           }
         }
         umma_commit(acc_full(acc));
-        if (++acc == 2)
+        if (++acc == ACC_BUFS)
         {
           acc = 0;
           acc_par ^= 1u;
@@ -549,7 +566,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       {
         mbar_arrive(acc_empty(acc));
       }
-      if (++acc == 2)
+      if (++acc == ACC_BUFS)
       {
         acc = 0;
         acc_par ^= 1u;
@@ -702,8 +719,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint8_t *src;
           if (BWD)
           {
-            const int r = c >> 4;   // k row (0..63) of the [64, N] factor
-            const int cb = c & 15;  // 16-byte chunk along n
+            const int r = c / (BN / 8);   // k row (0..63) of the [64, N] factor
+            const int cb = c % (BN / 8);  // 16-byte chunk along n
             src = p.lora_rhs + (static_cast<int64_t>(r) * p.n_total + n0 + cb * 8) * 2;
             dst = bbase + static_cast<uint32_t>((cb >> 3) * 8192 + (r >> 3) * 1024 + (r & 7) * 128 +
                                                 (((cb & 7) ^ (r & 7)) << 4));
@@ -805,11 +822,12 @@ int sm_count_umma()
   return cached;
 }
 
-template <int WMODE, bool BWD>
+template <int WMODE, bool BWD, int BN>
 int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const UmmaParams &p,
                 cudaStream_t s)
 {
-  auto kernel = linear_umma_kernel<WMODE, BWD>;
+  auto kernel = linear_umma_kernel<WMODE, BWD, BN>;
+  constexpr int SMEM_BYTES = TileCfg<BN>::SMEM_BYTES;
   static bool configured = false;
   if (!configured)
   {
@@ -847,7 +865,7 @@ bool umma_supported(const LinearArgs &g)
   }
   const int n_total = g.backward ? w.in_dim : w.out_dim;
   const int k_total = g.backward ? w.out_dim : w.in_dim;
-  if ((n_total % BN) != 0 || (k_total % BK) != 0)
+  if ((n_total % 128) != 0 || (k_total % BK) != 0)
   {
     return false;
   }
@@ -895,7 +913,20 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   p.in_dim = w.in_dim;
   p.group_size = w.group_size;
   p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
-  p.num_n_tiles = p.n_total / BN;
+  // 256-wide tiles feed the tensor core better per shared-memory byte; 128-wide ones keep a
+  // second accumulator set so the epilogue overlaps the next tile.  CAIFQ_UMMA_BN overrides.
+  int bn = ((p.n_total % 256) == 0 && static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
+               ? 256
+               : 128;
+  if (const char *e = std::getenv("CAIFQ_UMMA_BN"))
+  {
+    const int v = std::atoi(e);
+    if (v == 128 || (v == 256 && (p.n_total % 256) == 0))
+    {
+      bn = v;
+    }
+  }
+  p.num_n_tiles = p.n_total / bn;
 
   CUtensorMap map_a;
   CUtensorMap map_b;
@@ -909,7 +940,7 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   {
     // the [out, in] weight itself: forward boxes are 64 k x 128 n rows, backward 64 n x 64 k rows
     rc = make_map_bf16(&map_b, w.codes, static_cast<uint64_t>(w.in_dim), static_cast<uint64_t>(w.out_dim),
-                       g.backward ? BK : BN);
+                       g.backward ? BK : bn);
     if (rc != CAIFQ_OK)
     {
       return rc;
@@ -934,11 +965,16 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
     }
     p.lora_rhs = static_cast<const uint8_t *>(g.lora_rhs);
   }
-#define CAIFQ_UMMA_CASE(MODE)                                   \
-  if (mode == MODE)                                             \
-  {                                                             \
-    return g.backward ? launch_inst<MODE, true>(map_a, map_b, map_h, p, s) \
-                      : launch_inst<MODE, false>(map_a, map_b, map_h, p, s); \
+#define CAIFQ_UMMA_CASE(MODE)                                                        \
+  if (mode == MODE && bn == 128)                                                     \
+  {                                                                                  \
+    return g.backward ? launch_inst<MODE, true, 128>(map_a, map_b, map_h, p, s)       \
+                      : launch_inst<MODE, false, 128>(map_a, map_b, map_h, p, s);     \
+  }                                                                                  \
+  if (mode == MODE && bn == 256)                                                     \
+  {                                                                                  \
+    return g.backward ? launch_inst<MODE, true, 256>(map_a, map_b, map_h, p, s)       \
+                      : launch_inst<MODE, false, 256>(map_a, map_b, map_h, p, s);     \
   }
   CAIFQ_UMMA_CASE(W_I8)
   CAIFQ_UMMA_CASE(W_I4)
