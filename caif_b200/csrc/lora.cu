@@ -250,113 +250,121 @@ skinny_nt_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__res
   }
 }
 
-// C[big, R] (+)= sum over a slice of tokens of (prescale . U)[m, big] * V[m, R]   (fp32 atomics into acc).
-// 64 threads cover 128 columns of U (one bf16 pair each), 4 such groups split R; V rows are staged in
-// shared memory as fp32.  With `transpose_out` the accumulator is indexed [R, big] (dA).
-template <int JT>  // R = 4 * JT
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ uint32_t smem_addr(const void *p)
+{
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
+{
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t addr, uint32_t &r0, uint32_t &r1)
+{
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+// C[big, R] (+)= sum over a slice of tokens of (prescale . U)[m, big]^T * V[m, R]   (fp32 atomics into acc).
+// Both operands have the reduction index (the token) as their slow axis, so tiles of U and V are
+// staged in shared memory as they lie and the tensor-core fragments are read transposed
+// (ldmatrix.trans).  A CTA owns 64 columns of U, its 4 warps 16 each; gridDim.y slices the tokens.
+// With `transpose_out` the accumulator is indexed [R, big] (dA).
+constexpr int TN_COLS = 64;
+constexpr int TN_ROWS = 64;
+constexpr int TN_UPITCH = TN_COLS + 8;  // bf16 elements: 144-byte rows keep ldmatrix conflict-free
+
+template <int NT>  // R = 8 * NT
+__global__ void __launch_bounds__(128)
 skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__restrict__ v, float *__restrict__ acc,
                  float u_prescale, int64_t m, int big, int transpose_out)
 {
-  constexpr int R = 4 * JT;
-  constexpr int TMS = 64;
-  __shared__ __align__(16) float sv[TMS][R];
+  constexpr int R = 8 * NT;
+  constexpr int VPITCH = R + 8;
+  __shared__ __align__(16) __nv_bfloat16 su[TN_ROWS][TN_UPITCH];
+  __shared__ __align__(16) __nv_bfloat16 sv[TN_ROWS][VPITCH];
   const int tid = threadIdx.x;
-  const int cl = tid & 63;   // column pair
-  const int jg = tid >> 6;   // which quarter of R
-  const int c0 = blockIdx.x * 128 + cl * 2;
-  const bool col_ok = c0 < big;  // big is even
-  const int64_t per = (m + gridDim.y - 1) / gridDim.y;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int c0 = blockIdx.x * TN_COLS;
+  const int64_t per = ((m + gridDim.y - 1) / gridDim.y + TN_ROWS - 1) / TN_ROWS * TN_ROWS;
   const int64_t m_begin = per * blockIdx.y;
   const int64_t m_end = (m_begin + per < m) ? (m_begin + per) : m;
-  float a0[JT];
-  float a1[JT];
+  float c[NT][4];
 #pragma unroll
-  for (int j = 0; j < JT; ++j)
+  for (int nt = 0; nt < NT; ++nt)
   {
-    a0[j] = 0.0f;
-    a1[j] = 0.0f;
+    c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
   }
-  for (int64_t mb = m_begin; mb < m_end; mb += TMS)
+  for (int64_t mb = m_begin; mb < m_end; mb += TN_ROWS)
   {
-    const int rows = static_cast<int>((m_end - mb < TMS) ? (m_end - mb) : TMS);
-    for (int e = tid; e < TMS * R; e += 256)
+    // stage 64 tokens x 64 columns of U (16-byte chunks, coalesced) and 64 x R of V
+    for (int e = tid; e < TN_ROWS * (TN_COLS / 8); e += 128)
     {
-      const int rr = e / R;
-      const int jj = e % R;
-      sv[rr][jj] = (rr < rows) ? __bfloat162float(v[(mb + rr) * R + jj]) : 0.0f;
+      const int rr = e >> 3;
+      const int ch = e & 7;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (mb + rr < m_end && c0 + ch * 8 < big)
+      {
+        val = __ldg(reinterpret_cast<const uint4 *>(u + (mb + rr) * big + c0 + ch * 8));
+        if (u_prescale != 1.0f)
+        {
+          val = make_uint4(scale2(val.x, u_prescale), scale2(val.y, u_prescale), scale2(val.z, u_prescale),
+                           scale2(val.w, u_prescale));
+        }
+      }
+      *reinterpret_cast<uint4 *>(&su[rr][ch * 8]) = val;
+    }
+    for (int e = tid; e < TN_ROWS * NT; e += 128)
+    {
+      const int rr = e / NT;
+      const int ch = e % NT;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (mb + rr < m_end)
+      {
+        val = __ldg(reinterpret_cast<const uint4 *>(v + (mb + rr) * R + ch * 8));
+      }
+      *reinterpret_cast<uint4 *>(&sv[rr][ch * 8]) = val;
     }
     __syncthreads();
-    if (col_ok)
+#pragma unroll
+    for (int k16 = 0; k16 < TN_ROWS / 16; ++k16)
     {
-      const uint32_t *up = reinterpret_cast<const uint32_t *>(u + mb * big + c0);
-      const int64_t pitch = big / 2;
-      for (int r0 = 0; r0 < TMS; r0 += 8)
+      // A fragment: rows = this warp's 16 columns of U, k = 16 tokens.  Tile i of the x4 load:
+      // columns (i & 1) * 8.., tokens (i >> 1) * 8..; lane l addresses row (l & 7) of tile (l >> 3).
+      const int tile = lane >> 3;
+      const uint32_t a_addr =
+          smem_addr(&su[k16 * 16 + (tile >> 1) * 8 + (lane & 7)][warp * 16 + (tile & 1) * 8]);
+      uint32_t a0, a1, a2, a3;
+      ldmatrix_x4_trans(a_addr, a0, a1, a2, a3);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
       {
-        // eight independent loads in flight before any of them is used
-        uint32_t ub[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-        {
-          ub[q] = (r0 + q < rows) ? __ldg(up + (r0 + q) * pitch) : 0u;
-        }
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-        {
-          const int rr = r0 + q;
-          uint32_t uu = ub[q];
-          if (u_prescale != 1.0f)
-          {
-            uu = scale2(uu, u_prescale);
-          }
-          const float ulo = __uint_as_float(uu << 16);
-          const float uhi = __uint_as_float(uu & 0xFFFF0000u);
-#pragma unroll
-          for (int j4 = 0; j4 < JT; j4 += 4)
-          {
-            if (JT >= 4)
-            {
-              const float4 vv = *reinterpret_cast<const float4 *>(&sv[rr][jg * JT + j4]);
-              a0[j4 + 0] = fmaf(ulo, vv.x, a0[j4 + 0]);
-              a1[j4 + 0] = fmaf(uhi, vv.x, a1[j4 + 0]);
-              a0[j4 + 1] = fmaf(ulo, vv.y, a0[j4 + 1]);
-              a1[j4 + 1] = fmaf(uhi, vv.y, a1[j4 + 1]);
-              a0[j4 + 2] = fmaf(ulo, vv.z, a0[j4 + 2]);
-              a1[j4 + 2] = fmaf(uhi, vv.z, a1[j4 + 2]);
-              a0[j4 + 3] = fmaf(ulo, vv.w, a0[j4 + 3]);
-              a1[j4 + 3] = fmaf(uhi, vv.w, a1[j4 + 3]);
-            }
-          }
-          if (JT < 4)
-          {
-#pragma unroll
-            for (int j = 0; j < JT; ++j)
-            {
-              const float vv = sv[rr][jg * JT + j];
-              a0[j] = fmaf(ulo, vv, a0[j]);
-              a1[j] = fmaf(uhi, vv, a1[j]);
-            }
-          }
-        }
+        // B fragment: k = 16 tokens, n = 8 columns of V; lanes 0..15 address the 16 token rows
+        const uint32_t b_addr = smem_addr(&sv[k16 * 16 + (lane & 15)][nt * 8]);
+        uint32_t b0, b1;
+        ldmatrix_x2_trans(b_addr, b0, b1);
+        mma_bf16(c[nt], a0, a1, a2, a3, b0, b1);
       }
     }
     __syncthreads();
   }
-  if (col_ok)
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
   {
 #pragma unroll
-    for (int j = 0; j < JT; ++j)
+    for (int i = 0; i < 4; ++i)
     {
-      const int jj = jg * JT + j;
-      if (transpose_out)
+      const int col = c0 + warp * 16 + g + ((i >> 1) ? 8 : 0);  // column of U = row of C
+      const int jj = nt * 8 + 2 * t + (i & 1);
+      if (col < big)
       {
-        atomicAdd(&acc[static_cast<int64_t>(jj) * big + c0], a0[j]);
-        atomicAdd(&acc[static_cast<int64_t>(jj) * big + c0 + 1], a1[j]);
-      }
-      else
-      {
-        atomicAdd(&acc[static_cast<int64_t>(c0) * R + jj], a0[j]);
-        atomicAdd(&acc[static_cast<int64_t>(c0 + 1) * R + jj], a1[j]);
+        const int64_t idx = transpose_out ? (static_cast<int64_t>(jj) * big + col) : (static_cast<int64_t>(col) * R + jj);
+        atomicAdd(&acc[idx], c[nt][i]);
       }
     }
   }
@@ -495,28 +503,34 @@ int launch_skinny_tn(const void *u, const void *v, void *c, float *scratch, floa
   CAIFQ_CHECK_CUDA(cudaMemsetAsync(scratch, 0, static_cast<size_t>(n) * sizeof(float), s));
   if (m > 0)
   {
-    int64_t slices = (m + 255) / 256;
-    if (slices > 64)
+    const int col_tiles = (big + TN_COLS - 1) / TN_COLS;
+    int64_t slices = (148 * 8 + col_tiles - 1) / col_tiles;   // ~8 CTAs of 128 threads per SM
+    const int64_t max_slices = (m + TN_ROWS - 1) / TN_ROWS;
+    if (slices > max_slices)
     {
-      slices = 64;
+      slices = max_slices;
     }
-    dim3 grid((big + 127) / 128, static_cast<unsigned>(slices));
+    if (slices < 1)
+    {
+      slices = 1;
+    }
+    dim3 grid(col_tiles, static_cast<unsigned>(slices));
     const __nv_bfloat16 *up = static_cast<const __nv_bfloat16 *>(u);
     const __nv_bfloat16 *vp = static_cast<const __nv_bfloat16 *>(v);
     const int tr = transpose_out ? 1 : 0;
     switch (rank)
     {
       case 8:
-        skinny_tn_kernel<2><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<1><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       case 16:
-        skinny_tn_kernel<4><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<2><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       case 32:
-        skinny_tn_kernel<8><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<4><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       case 64:
-        skinny_tn_kernel<16><<<grid, 256, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<8><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       default:
         set_error("LoRA fast path: unsupported rank %d", rank);
