@@ -173,6 +173,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       : "memory");
 }
 
+__device__ __forceinline__ bool elect_one()
+{
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // arrive on an mbarrier once every MMA issued so far by this thread has finished
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
@@ -404,7 +415,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   else if (warp == 1)
   {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0)
+    // The whole warp runs the loop, so addresses and descriptors are warp-uniform values;
+    // one elected lane issues the MMAs and the commits.
     {
       constexpr uint32_t idesc = make_idesc(BWD, BN);
       int s = 0;
@@ -420,27 +432,37 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           mbar_wait(a_full(s), par);
           mbar_wait(b_full(s), par);
           tc_fence_after();
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
+          const uint64_t adesc0 = make_desc(a_addr(s, 0), 16, 1024);
+          const uint64_t bdesc0 = BWD ? make_desc(b_addr(s), 8192, 1024) : make_desc(b_addr(s), 16, 1024);
+          const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc * MT * BN);
+          if (elect_one())
           {
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((acc * MT + mt) * BN);
 #pragma unroll
-            for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
+            for (int mt = 0; mt < MT; ++mt)
             {
-              const uint64_t adesc = make_desc(a_addr(s, mt) + k16 * (UMMA_K * 2), 16, 1024);
-              const uint64_t bdesc = BWD ? make_desc(b_addr(s) + k16 * 2048, 8192, 1024)
-                                         : make_desc(b_addr(s) + k16 * (UMMA_K * 2), 16, 1024);
-              umma_bf16(d_tmem, adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+#pragma unroll
+              for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
+              {
+                // descriptor address fields count 16-byte units
+                const uint64_t adesc = adesc0 + static_cast<uint64_t>((mt * A_SUB_BYTES + k16 * (UMMA_K * 2)) >> 4);
+                const uint64_t bdesc = bdesc0 + static_cast<uint64_t>((BWD ? k16 * 2048 : k16 * (UMMA_K * 2)) >> 4);
+                umma_bf16(d0 + static_cast<uint32_t>(mt * BN), adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+              }
             }
+            umma_commit(empty(s));
           }
-          umma_commit(empty(s));
+          __syncwarp();
           if (++s == STAGES)
           {
             s = 0;
             par ^= 1u;
           }
         }
-        umma_commit(acc_full(acc));
+        if (elect_one())
+        {
+          umma_commit(acc_full(acc));
+        }
+        __syncwarp();
         if (++acc == ACC_BUFS)
         {
           acc = 0;
