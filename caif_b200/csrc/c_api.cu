@@ -289,7 +289,7 @@ const char *caifq_version(void) { return "caifq 0.1 (sm_100a)"; }
 
 int caifq_device_status(void)
 {
-  // 1: the decode kernel gave up on a wait; 2: the tensor-core kernel did
+  // bit 0: the decode kernel gave up on a wait; bit 1: the tensor-core kernel did
   if (cudaDeviceSynchronize() != cudaSuccess)
   {
     set_error("caifq_device_status: %s", cudaGetErrorString(cudaGetLastError()));

@@ -270,6 +270,13 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
     }
   }
 
+  // Programmatic dependent launch: the frozen codes and scales never depend on earlier work in
+  // the stream, so their copies above may start while the previous kernel is still draining.
+  // Activations and the output are touched only after that kernel has completed.  The next
+  // kernel in the stream may begin its own weight copies as soon as this CTA's resources free up.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
   // Token fragments (B operand), resident for the whole kernel.  For the 16
   // bytes of codes a lane reads at k-offset kb, the register order pairs the
   // elements the way the logic-op dequantization emits them:
@@ -587,7 +594,21 @@ int launch_decode_inst(const DecodeParams &p, cudaStream_t s)
   {
     grid = p.num_quanta;
   }
-  kernel<<<grid, kThreads, smem, s>>>(p);
+  static const bool pdl = []() {
+    const char *e = std::getenv("CAIFQ_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  CAIFQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
