@@ -716,6 +716,50 @@ static int check_experts(const caifq_weight *gate, const caifq_weight *up, const
   return CAIFQ_OK;
 }
 
+// One product for every expert of a run: a single grouped tensor-core launch when the kernel takes
+// the experts (same quantized shape, bf16 rows), else one call per expert - the reference's loop
+// (src/caif_device_moe_layer.cpp:534-557).
+int grouped_linear(const caifq_weight *ws, int num_experts, const int32_t *offsets, bool backward, const void *a,
+                   void *c, int dtype, bool accumulate, int compute_dtype, cudaStream_t s, const char *who)
+{
+  GroupedLinearArgs g{};
+  g.weights = ws;
+  g.num_experts = num_experts;
+  g.offsets = offsets;
+  g.backward = backward;
+  g.a = a;
+  g.a_dtype = dtype;
+  g.c = c;
+  g.c_dtype = dtype;
+  g.accumulate = accumulate;
+  g.compute_dtype = compute_dtype;
+  const Force force = forced_path();
+  if ((force == Force::None || force == Force::Umma) && umma_grouped_supported(g))
+  {
+    set_path("umma-grouped");
+    return launch_linear_umma_grouped(g, s);
+  }
+  const size_t es = dtype_bytes(dtype);
+  const int64_t a_cols = backward ? ws[0].out_dim : ws[0].in_dim;
+  const int64_t c_cols = backward ? ws[0].in_dim : ws[0].out_dim;
+  for (int e = 0; e < num_experts; ++e)
+  {
+    const int64_t off = offsets[e];
+    const int64_t cnt = offsets[e + 1] - off;
+    if (cnt == 0)
+    {
+      continue;
+    }
+    const int r = linear_any(&ws[e], backward, static_cast<const char *>(a) + off * a_cols * es, dtype, 1.0f, cnt,
+                             static_cast<char *>(c) + off * c_cols * es, dtype, accumulate, compute_dtype, s, who);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+  }
+  return CAIFQ_OK;
+}
+
 int caifq_grouped_expert_fwd(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
                              int32_t num_experts, const int32_t *expert_offsets_host, const void *x, void *out,
                              void *gate_out, void *up_out, void *hidden_ws, int32_t dtype, int32_t compute_dtype,
@@ -738,48 +782,23 @@ int caifq_grouped_expert_fwd(const caifq_weight *gate, const caifq_weight *up, c
   const size_t es = dtype_bytes(dtype);
   const int64_t in_dim = up[0].in_dim;
   const int64_t hid = up[0].out_dim;
-  for (int e = 0; e < num_experts; ++e)
+  int r = grouped_linear(up, num_experts, expert_offsets_host, false, x, up_out, dtype, false, compute_dtype, s, who);
+  if (r == CAIFQ_OK)
   {
-    const int64_t off = expert_offsets_host[e];
-    const int64_t cnt = expert_offsets_host[e + 1] - off;
-    if (cnt == 0)
-    {
-      continue;
-    }
-    const char *xe = static_cast<const char *>(x) + off * in_dim * es;
-    int r = linear_any(&up[e], false, xe, dtype, 1.0f, cnt, static_cast<char *>(up_out) + off * hid * es, dtype, false,
-                       compute_dtype, s, who);
-    if (r == CAIFQ_OK)
-    {
-      r = linear_any(&gate[e], false, xe, dtype, 1.0f, cnt, static_cast<char *>(gate_out) + off * hid * es, dtype,
-                     false, compute_dtype, s, who);
-    }
-    if (r != CAIFQ_OK)
-    {
-      return r;
-    }
+    r = grouped_linear(gate, num_experts, expert_offsets_host, false, x, gate_out, dtype, false, compute_dtype, s,
+                       who);
   }
-  int r = launch_swiglu_fwd(gate_out, up_out, hidden_ws, dtype, total * hid, s);
   if (r != CAIFQ_OK)
   {
     return r;
   }
-  for (int e = 0; e < num_experts; ++e)
+  r = launch_swiglu_fwd(gate_out, up_out, hidden_ws, dtype, total * hid, s);
+  if (r != CAIFQ_OK)
   {
-    const int64_t off = expert_offsets_host[e];
-    const int64_t cnt = expert_offsets_host[e + 1] - off;
-    if (cnt == 0)
-    {
-      continue;
-    }
-    r = linear_any(&down[e], false, static_cast<const char *>(hidden_ws) + off * hid * es, dtype, 1.0f, cnt,
-                   static_cast<char *>(out) + off * in_dim * es, dtype, false, compute_dtype, s, who);
-    if (r != CAIFQ_OK)
-    {
-      return r;
-    }
+    return r;
   }
-  return CAIFQ_OK;
+  return grouped_linear(down, num_experts, expert_offsets_host, false, hidden_ws, out, dtype, false, compute_dtype, s,
+                        who);
 }
 
 int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
@@ -807,48 +826,24 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
   char *g_hidden = static_cast<char *>(ws);
   char *g_gate = g_hidden + total * hid * es;
   char *g_up = g_gate + total * hid * es;
-  for (int e = 0; e < num_experts; ++e)
-  {
-    const int64_t off = expert_offsets_host[e];
-    const int64_t cnt = expert_offsets_host[e + 1] - off;
-    if (cnt == 0)
-    {
-      continue;
-    }
-    const int r = linear_any(&down[e], true, static_cast<const char *>(dy) + off * in_dim * es, dtype, 1.0f, cnt,
-                             g_hidden + off * hid * es, dtype, false, compute_dtype, s, who);
-    if (r != CAIFQ_OK)
-    {
-      return r;
-    }
-  }
-  int r = launch_swiglu_bwd(g_hidden, gate_out, up_out, g_gate, g_up, dtype, total * hid, s);
+  int r = grouped_linear(down, num_experts, expert_offsets_host, true, dy, g_hidden, dtype, false, compute_dtype, s,
+                         who);
   if (r != CAIFQ_OK)
   {
     return r;
   }
-  for (int e = 0; e < num_experts; ++e)
+  r = launch_swiglu_bwd(g_hidden, gate_out, up_out, g_gate, g_up, dtype, total * hid, s);
+  if (r != CAIFQ_OK)
   {
-    const int64_t off = expert_offsets_host[e];
-    const int64_t cnt = expert_offsets_host[e + 1] - off;
-    if (cnt == 0)
-    {
-      continue;
-    }
-    char *dxe = static_cast<char *>(dx) + off * in_dim * es;
-    // dx = round(up.Bwd(g_up)); dx = round(round(gate.Bwd(g_gate)) + dx): the reference's Add(gi_up, gi_gate)
-    r = linear_any(&up[e], true, g_up + off * hid * es, dtype, 1.0f, cnt, dxe, dtype, false, compute_dtype, s, who);
-    if (r == CAIFQ_OK)
-    {
-      r = linear_any(&gate[e], true, g_gate + off * hid * es, dtype, 1.0f, cnt, dxe, dtype, true, compute_dtype, s,
-                     who);
-    }
-    if (r != CAIFQ_OK)
-    {
-      return r;
-    }
+    return r;
   }
-  return CAIFQ_OK;
+  // dx = round(up.Bwd(g_up)); dx = round(round(gate.Bwd(g_gate)) + dx): the reference's Add(gi_up, gi_gate)
+  r = grouped_linear(up, num_experts, expert_offsets_host, true, g_up, dx, dtype, false, compute_dtype, s, who);
+  if (r != CAIFQ_OK)
+  {
+    return r;
+  }
+  return grouped_linear(gate, num_experts, expert_offsets_host, true, g_gate, dx, dtype, true, compute_dtype, s, who);
 }
 
 }  // extern "C"

@@ -204,6 +204,23 @@ struct LinearArgs
 int launch_linear_generic(const LinearArgs &args, cudaStream_t s);
 
 // weight-streaming kernel for few tokens (forward only)
+// The same product for a run of experts over one packed activation buffer:
+// rows offsets[e] .. offsets[e+1] (host array of num_experts + 1 entries) belong to weights[e].
+struct GroupedLinearArgs
+{
+  const caifq_weight *weights;
+  int num_experts;
+  const int32_t *offsets;
+  bool backward;
+  const void *a;
+  int a_dtype;
+  void *c;
+  int c_dtype;
+  bool accumulate;
+  int compute_dtype;
+};
+bool umma_grouped_supported(const GroupedLinearArgs &args);
+int launch_linear_umma_grouped(const GroupedLinearArgs &args, cudaStream_t s);
 bool decode_supported(const LinearArgs &args);
 int launch_linear_decode(const LinearArgs &args, cudaStream_t s);
 

@@ -300,10 +300,93 @@ struct UmmaParams
   const uint8_t *lora_rhs;  // null = no LoRA k-block
 };
 
-template <int WMODE, bool BWD, int BN>
+// Grouped mode: one launch covers the same product for a run of experts whose activation rows lie
+// back to back in one packed buffer (rows offsets[e] .. offsets[e+1] belong to expert e).  The table
+// travels as a kernel parameter, so nothing is read back from or copied to the device to schedule it.
+constexpr int MAX_GROUPS = 128;
+
+struct GroupTable
+{
+  int32_t offsets[MAX_GROUPS + 1];      // first packed row of every expert
+  int32_t mtile_start[MAX_GROUPS + 1];  // running count of 256-row tiles
+  const uint8_t *codes[MAX_GROUPS];
+  const void *scales[MAX_GROUPS];
+  int32_t num_groups;
+};
+
+struct NoGroupTable
+{
+  int32_t unused;
+};
+
+template <bool GROUPED>
+struct GroupSel
+{
+  typedef NoGroupTable type;
+};
+template <>
+struct GroupSel<true>
+{
+  typedef GroupTable type;
+};
+
+// What a tile of the schedule works on.
+struct TileWork
+{
+  int n_tile;
+  int64_t row0;      // first activation / output row of the tile
+  int64_t row_end;   // rows at or beyond this one belong to somebody else
+  const uint8_t *codes;
+  const void *scales;
+};
+
+template <bool GROUPED>
+__device__ __forceinline__ TileWork locate_tile(int tile, const UmmaParams &p, const typename GroupSel<GROUPED>::type &gt);
+
+template <>
+__device__ __forceinline__ TileWork locate_tile<false>(int tile, const UmmaParams &p, const NoGroupTable &)
+{
+  TileWork t;
+  t.n_tile = tile / p.num_m_tiles;
+  t.row0 = static_cast<int64_t>(tile % p.num_m_tiles) * BM;
+  t.row_end = p.m;
+  t.codes = p.codes;
+  t.scales = p.scales;
+  return t;
+}
+
+template <>
+__device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams &p, const GroupTable &gt)
+{
+  const int mt = tile % p.num_m_tiles;   // num_m_tiles = all experts' row tiles
+  int lo = 0;
+  int hi = gt.num_groups;                // mtile_start[lo] <= mt < mtile_start[hi]
+  while (hi - lo > 1)
+  {
+    const int mid = (lo + hi) >> 1;
+    if (gt.mtile_start[mid] <= mt)
+    {
+      lo = mid;
+    }
+    else
+    {
+      hi = mid;
+    }
+  }
+  TileWork t;
+  t.n_tile = tile / p.num_m_tiles;
+  t.row0 = static_cast<int64_t>(gt.offsets[lo]) + static_cast<int64_t>(mt - gt.mtile_start[lo]) * BM;
+  t.row_end = gt.offsets[lo + 1];
+  t.codes = gt.codes[lo];
+  t.scales = gt.scales[lo];
+  return t;
+}
+
+template <int WMODE, bool BWD, int BN, bool GROUPED>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const __grid_constant__ CUtensorMap map_h, const UmmaParams p)
+                   const __grid_constant__ CUtensorMap map_h, const UmmaParams p,
+                   const __grid_constant__ typename GroupSel<GROUPED>::type gt)
 {
   constexpr int B_STAGE_BYTES = TileCfg<BN>::B_STAGE_BYTES;
   constexpr int STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
@@ -367,8 +450,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       uint32_t par = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
       {
-        const int m_tile = tile % p.num_m_tiles;
-        const int n_tile = tile / p.num_m_tiles;
+        const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
+        const int n_tile = tw.n_tile;
+        const int row_tile = static_cast<int>(tw.row0);
         for (int kb = 0; kb < num_kb_all; ++kb)
         {
           mbar_wait(empty(s), par ^ 1u);
@@ -378,11 +462,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           {
             if (kb < num_kb)
             {
-              tma_load_2d(a_addr(s, mt), &map_a, kb * BK, m_tile * BM + mt * BM_SUB, a_full(s));
+              tma_load_2d(a_addr(s, mt), &map_a, kb * BK, row_tile + mt * BM_SUB, a_full(s));
             }
             else
             {
-              tma_load_2d(a_addr(s, mt), &map_h, 0, m_tile * BM + mt * BM_SUB, a_full(s));
+              tma_load_2d(a_addr(s, mt), &map_h, 0, row_tile + mt * BM_SUB, a_full(s));
             }
           }
           if (WMODE == W_BF16)
@@ -475,23 +559,23 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
-    float out_scale = 1.0f;
-    if (WMODE == W_I8 && p.scales != nullptr)
-    {
-      out_scale = static_cast<const float *>(p.scales)[0];
-    }
     int acc = 0;
     uint32_t acc_par = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
     {
-      const int m_tile = tile % p.num_m_tiles;
-      const int n_tile = tile / p.num_m_tiles;
+      const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
+      const int n_tile = tw.n_tile;
+      float out_scale = 1.0f;
+      if (WMODE == W_I8 && tw.scales != nullptr)
+      {
+        out_scale = __ldg(static_cast<const float *>(tw.scales));
+      }
       mbar_wait(acc_full(acc), acc_par);
       tc_fence_after();
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
       {
-        const int64_t row = static_cast<int64_t>(m_tile) * BM + mt * BM_SUB + quarter * 32 + lane;
+        const int64_t row = tw.row0 + mt * BM_SUB + quarter * 32 + lane;
 #pragma unroll
         for (int cb = 0; cb < BN / 32; ++cb)
         {
@@ -500,7 +584,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                  static_cast<uint32_t>((acc * MT + mt) * BN + cb * 32);
           tmem_ld32(taddr, r);
           tmem_ld_wait();
-          if (row < p.m)
+          if (row < tw.row_end)
           {
             const int64_t off = row * p.n_total + static_cast<int64_t>(n_tile) * BN + cb * 32;
             if (p.c_dtype == CAIFQ_F32)
@@ -612,7 +696,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     uint32_t par = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
     {
-      const int n_tile = tile / p.num_m_tiles;
+      const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
+      const int n_tile = tw.n_tile;
       const int n0 = n_tile * BN;
       // chunk -> (row inside the tile, part along the contiguous direction)
       int c_row[PER_THREAD];
@@ -634,11 +719,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const int64_t o = BWD ? (k0 + c_row[i]) : (n0 + c_row[i]);
           const int64_t ii = BWD ? (n0 + c_part[i] * ELEMS) : (k0 + c_part[i] * ELEMS);
           const int64_t flat = o * p.in_dim + ii;
-          const uint8_t *src = p.codes + ((WMODE == W_I8) ? flat : (flat >> 1));
+          const uint8_t *src = tw.codes + ((WMODE == W_I8) ? flat : (flat >> 1));
           raw[i] = __ldg(reinterpret_cast<const uint4 *>(src));
           if (WMODE == W_I4)
           {
-            sc[i] = __half2float(static_cast<const __half *>(p.scales)[flat / p.group_size]);
+            sc[i] = __half2float(static_cast<const __half *>(tw.scales)[flat / p.group_size]);
           }
           else
           {
@@ -844,11 +929,11 @@ int sm_count_umma()
   return cached;
 }
 
-template <int WMODE, bool BWD, int BN>
+template <int WMODE, bool BWD, int BN, bool GROUPED>
 int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const UmmaParams &p,
-                cudaStream_t s)
+                const typename GroupSel<GROUPED>::type &gt, cudaStream_t s)
 {
-  auto kernel = linear_umma_kernel<WMODE, BWD, BN>;
+  auto kernel = linear_umma_kernel<WMODE, BWD, BN, GROUPED>;
   constexpr int SMEM_BYTES = TileCfg<BN>::SMEM_BYTES;
   static bool configured = false;
   if (!configured)
@@ -856,9 +941,9 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtens
     CAIFQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     configured = true;
   }
-  const int tiles = p.num_m_tiles * p.num_n_tiles;
-  const int grid = tiles < sm_count_umma() ? tiles : sm_count_umma();
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_h, p);
+  const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
+  const int grid = tiles < sm_count_umma() ? static_cast<int>(tiles) : sm_count_umma();
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_h, p, gt);
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
@@ -990,13 +1075,13 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
 #define CAIFQ_UMMA_CASE(MODE)                                                        \
   if (mode == MODE && bn == 128)                                                     \
   {                                                                                  \
-    return g.backward ? launch_inst<MODE, true, 128>(map_a, map_b, map_h, p, s)       \
-                      : launch_inst<MODE, false, 128>(map_a, map_b, map_h, p, s);     \
+    return g.backward ? launch_inst<MODE, true, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s)   \
+                      : launch_inst<MODE, false, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s); \
   }                                                                                  \
   if (mode == MODE && bn == 256)                                                     \
   {                                                                                  \
-    return g.backward ? launch_inst<MODE, true, 256>(map_a, map_b, map_h, p, s)       \
-                      : launch_inst<MODE, false, 256>(map_a, map_b, map_h, p, s);     \
+    return g.backward ? launch_inst<MODE, true, 256, false>(map_a, map_b, map_h, p, NoGroupTable{}, s)   \
+                      : launch_inst<MODE, false, 256, false>(map_a, map_b, map_h, p, NoGroupTable{}, s); \
   }
   CAIFQ_UMMA_CASE(W_I8)
   CAIFQ_UMMA_CASE(W_I4)
@@ -1004,6 +1089,114 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
 #undef CAIFQ_UMMA_CASE
   set_error("frozen linear (umma): unsupported weight storage %d", w.storage);
   return CAIFQ_ERR_UNSUPPORTED;
+}
+
+// ------------------------------------------------------------------ grouped (frozen experts)
+bool umma_grouped_supported(const GroupedLinearArgs &g)
+{
+  if (g.num_experts < 1 || g.weights == nullptr || g.offsets == nullptr)
+  {
+    return false;
+  }
+  const caifq_weight &w0 = g.weights[0];
+  if (w0.storage != CAIFQ_I8 && w0.storage != CAIFQ_I4)
+  {
+    return false;
+  }
+  LinearArgs probe{};
+  probe.w = w0;
+  probe.backward = g.backward;
+  probe.a = g.a;
+  probe.a_dtype = g.a_dtype;
+  probe.a_prescale = 1.0f;
+  probe.m = 32;   // the row count of a single expert does not matter here
+  probe.c = g.c;
+  probe.c_dtype = g.c_dtype;
+  probe.accumulate = g.accumulate;
+  probe.compute_dtype = g.compute_dtype;
+  if (!umma_supported(probe))
+  {
+    return false;
+  }
+  for (int e = 0; e < g.num_experts; ++e)
+  {
+    const caifq_weight &w = g.weights[e];
+    if (w.storage != w0.storage || w.scheme != w0.scheme || w.group_size != w0.group_size || w.in_dim != w0.in_dim ||
+        w.out_dim != w0.out_dim || (w.scales == nullptr) != (w0.scales == nullptr) ||
+        (reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0)
+    {
+      return false;
+    }
+  }
+  return g.offsets[g.num_experts] > 0;
+}
+
+int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
+{
+  const caifq_weight &w0 = g.weights[0];
+  const int64_t total_rows = g.offsets[g.num_experts];
+  UmmaParams p{};
+  p.codes = nullptr;
+  p.scales = nullptr;
+  p.c = g.c;
+  p.c_dtype = g.c_dtype;
+  p.accumulate = g.accumulate ? 1 : 0;
+  p.m = total_rows;
+  p.n_total = g.backward ? w0.in_dim : w0.out_dim;
+  p.k_total = g.backward ? w0.out_dim : w0.in_dim;
+  p.in_dim = w0.in_dim;
+  p.group_size = w0.group_size;
+  CUtensorMap map_a;
+  int rc = make_map_bf16(&map_a, g.a, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(total_rows), BM_SUB);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  const int mode = wmode_of(w0);
+  for (int first = 0; first < g.num_experts; first += MAX_GROUPS)
+  {
+    const int count = (g.num_experts - first < MAX_GROUPS) ? (g.num_experts - first) : MAX_GROUPS;
+    GroupTable gt{};
+    int tiles = 0;
+    for (int e = 0; e < count; ++e)
+    {
+      gt.offsets[e] = g.offsets[first + e];
+      gt.mtile_start[e] = tiles;
+      tiles += (g.offsets[first + e + 1] - g.offsets[first + e] + BM - 1) / BM;
+      gt.codes[e] = static_cast<const uint8_t *>(g.weights[first + e].codes);
+      gt.scales[e] = g.weights[first + e].scales;
+    }
+    gt.offsets[count] = g.offsets[first + count];
+    gt.mtile_start[count] = tiles;
+    gt.num_groups = count;
+    if (tiles == 0)
+    {
+      continue;
+    }
+    p.num_m_tiles = tiles;
+    const int bn =
+        ((p.n_total % 256) == 0 && static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma()) ? 256 : 128;
+    p.num_n_tiles = p.n_total / bn;
+#define CAIFQ_UMMA_GROUP_CASE(MODE)                                                              \
+  if (mode == MODE && bn == 128)                                                                 \
+  {                                                                                              \
+    rc = g.backward ? launch_inst<MODE, true, 128, true>(map_a, map_a, map_a, p, gt, s)          \
+                    : launch_inst<MODE, false, 128, true>(map_a, map_a, map_a, p, gt, s);        \
+  }                                                                                              \
+  if (mode == MODE && bn == 256)                                                                 \
+  {                                                                                              \
+    rc = g.backward ? launch_inst<MODE, true, 256, true>(map_a, map_a, map_a, p, gt, s)          \
+                    : launch_inst<MODE, false, 256, true>(map_a, map_a, map_a, p, gt, s);        \
+  }
+    CAIFQ_UMMA_GROUP_CASE(W_I8)
+    CAIFQ_UMMA_GROUP_CASE(W_I4)
+#undef CAIFQ_UMMA_GROUP_CASE
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+  }
+  return CAIFQ_OK;
 }
 
 }  // namespace caifq

@@ -169,6 +169,49 @@ def test_grouped_frozen_experts(storage, sd, compute):
         assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
 
 
+@pytest.mark.parametrize("storage,compute,experts,in_dim,hid,mean_rows", [
+    (orc.I4, orc.BF16, 6, 2048, 1408, 300),    # the MoE config's expert shape, ragged row counts
+    (orc.I8, orc.F32, 4, 256, 512, 700),
+    (orc.I4, orc.BF16, 131, 128, 128, 5),      # more experts than one launch's table holds
+])
+def test_grouped_frozen_experts_single_launch(storage, compute, experts, in_dim, hid, mean_rows):
+    """Quantized experts of one shape on bf16 rows: each of the six products is one grouped
+    tensor-core launch over the packed buffer; per-expert results match the oracle's loop."""
+    rng = np.random.default_rng(4100 + experts)
+    counts = rng.integers(0, 2 * mean_rows, experts)
+    counts[1] = 0
+    counts[-1] = 1
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    total = int(offsets[-1])
+    sd = orc.BF16
+    gate, up, down, o_gate, o_up, o_down = [], [], [], [], [], []
+    for _ in range(experts):
+        for lst, olst, (o, i) in ((gate, o_gate, (hid, in_dim)), (up, o_up, (hid, in_dim)),
+                                  (down, o_down, (in_dim, hid))):
+            w, codes, scales = make_weight(rng, o, i, storage, std=0.05)
+            lst.append(w)
+            olst.append(orc.weight_to_compute(codes, scales, storage, i, o, compute, w.scheme, w.group_size))
+    x_np, x = act(rng, total, in_dim, sd)
+    dy_np, dy = act(rng, total, in_dim, sd)
+    out, gate_out, up_out = nv.grouped_expert_fwd(gate, up, down, offsets.tolist(), x, compute)
+    assert nv.last_path() == "umma-grouped"
+    dx = nv.grouped_expert_bwd(gate, up, down, offsets.tolist(), dy, gate_out, up_out, compute)
+    assert nv.last_path() == "umma-grouped"
+    assert nv.lib().caifq_device_status() == 0
+    tol = 2e-2
+    check = range(experts) if experts <= 8 else list(range(0, experts, 13)) + [experts - 1]
+    for e in check:
+        lo, hi = offsets[e], offsets[e + 1]
+        if lo == hi:
+            continue
+        want, g, u = orc.frozen_expert_forward(x_np[lo:hi], o_gate[e], o_up[e], o_down[e], compute, sd)
+        assert max_rel_err(out[lo:hi].float().cpu().numpy(), want) <= tol
+        assert max_rel_err(gate_out[lo:hi].float().cpu().numpy(), g) <= tol
+        assert max_rel_err(up_out[lo:hi].float().cpu().numpy(), u) <= tol
+        want_dx = orc.frozen_expert_backward(dy_np[lo:hi], g, u, o_gate[e], o_up[e], o_down[e], compute, sd)
+        assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
+
+
 @pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I4, orc.BF16)])
 @pytest.mark.parametrize("m,in_dim,out_dim,rank", [(300, 512, 384, 16), (1024, 1024, 1024, 8), (130, 256, 640, 64)])
 def test_lora_fused_tensor_core_path(storage, compute, m, in_dim, out_dim, rank):
