@@ -221,8 +221,10 @@ def run_gpu(args):
     peaks = _peaks()
     if args.workload == "c2":
         result = bench_c2(args, nv, torch, dist, dev, world, rank, peaks)
-    else:
+    elif args.workload == "c3":
         result = bench_c3(args, nv, torch, dist, dev, world, rank, peaks)
+    else:
+        result = bench_c5(args, nv, torch, dist, dev, world, rank, peaks)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -487,6 +489,102 @@ def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
     return result
 
 
+def c5_flops(rows, hidden=2048, ffn=1408):
+    # three products forward and three for dX, 2 flops per multiply-add
+    return 2 * 3 * 2.0 * rows * hidden * ffn
+
+
+def bench_c5(args, nv, torch, dist, dev, world, rank, peaks):
+    """Frozen int4 experts of the MoE config: 64 experts (sharded by expert over the ranks), hidden 2048,
+    expert FFN 1408, 16384 tokens routed top-6.  Step = dispatch, grouped forward, combine, grouped dX."""
+    hidden, ffn, n_exp, tokens, top_k = 2048, 1408, 64, 16384, 6
+    local = n_exp // world
+    gen = torch.Generator(device=dev).manual_seed(1238)
+    gate, up, down = [], [], []
+    for e in range(n_exp):
+        for lst, (o, i) in ((gate, (ffn, hidden)), (up, (ffn, hidden)), (down, (hidden, ffn))):
+            wf = torch.randn(o * i, generator=gen, device=dev) * 0.02   # same draws on every rank
+            if e // local == rank:
+                pk, sc = nv.quantize_int4(wf, 128)
+                lst.append(nv.Weight(pk, nv.I4, i, o, sc, group_size=128))
+            del wf
+    logits = torch.randn(tokens, n_exp, generator=gen, device=dev)
+    probs = torch.softmax(logits, dim=-1)
+    idx, wts = nv.moe_topk(probs, top_k)
+    wts = nv.moe_normalize_rows(wts).to(torch.bfloat16)
+    # this rank keeps the (token, k) picks that land on its experts: the rows an all-to-all would deliver
+    mine = (idx // local) == rank
+    idx_local = torch.where(mine, idx - rank * local, torch.full_like(idx, local))   # one overflow bin
+    dmap, offs = nv.moe_build_dispatch(idx_local.to(torch.int32).contiguous(), local + 1, 0)
+    offs_host = offs.cpu().tolist()
+    rows = int(offs_host[local])
+    offs_local = offs_host[:local + 1]
+    x = torch.randn(tokens, hidden, generator=gen, device=dev).to(torch.bfloat16)
+    dy = torch.randn(rows, hidden, generator=gen, device=dev).to(torch.bfloat16)
+    idx_i32 = idx_local.to(torch.int32).contiguous()
+    total_with_bin = int(offs_host[local + 1])
+
+    def step():
+        buf = nv.moe_dispatch(x, idx_i32, dmap, offs, total_with_bin)
+        out, g_out, u_out = nv.grouped_expert_fwd(gate, up, down, offs_local, buf[:rows], compute=nv.BF16)
+        buf[:rows].copy_(out)
+        y = nv.moe_combine(buf, idx_i32, wts, dmap, offs, tokens)
+        dx = nv.grouped_expert_bwd(gate, up, down, offs_local, dy, g_out, u_out, compute=nv.BF16)
+        return y, dx
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    path = nv.last_path()
+    sampler = ClockSampler(_gpu_uuid(torch, dev))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms = _timed(torch, dist, world, step, args.steps, dev)
+    _keep_busy(torch, step, ms / args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    rows_t = torch.tensor([rows], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(rows_t)
+    flops = c5_flops(int(rows_t.item()))
+    value = flops / (ms_per_step * 1e-3) / 1e12
+
+    hx = x.cpu().pin_memory()
+    hdy = dy.cpu().pin_memory()
+    hy = torch.empty(tokens, hidden, dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e():
+        x.copy_(hx, non_blocking=True)
+        dy.copy_(hdy, non_blocking=True)
+        y, _ = step()
+        hy.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        step_e2e()
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e = _timed(torch, dist, world, step_e2e, e2e_steps, dev)
+    e2e = {"value": flops / (ms_e2e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": (tokens + rows) * hidden * 2, "d2h_bytes_per_step": tokens * hidden * 2}
+    result = {
+        "metric": "frozen int4 experts, grouped forward + dX, TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": "c5: 64 frozen int4 experts 2048->1408->2048 (SwiGLU), 16384 tokens top-6, "
+                               "dispatch + grouped fwd + combine + grouped dX",
+                   "l2": "packed buffers of %d rows (>= 400 MB) stream through L2 every step" % int(rows_t.item()),
+                   "parallelism": "1 GPU" if world == 1 else "experts sharded x%d (rows pre-routed per rank)" % world},
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": value / world / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
+                     "kernel": "frozen experts path '%s'" % path,
+                     "note": "whole step incl. dispatch, SwiGLU and combine kernels over its duration"},
+        "e2e": e2e, "gpu_launches": 11 * args.steps, "clocks": clocks,
+    }
+    return result
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -517,7 +615,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c2", "c3"])
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"])
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()

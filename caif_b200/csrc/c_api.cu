@@ -734,7 +734,11 @@ int grouped_linear(const caifq_weight *ws, int num_experts, const int32_t *offse
   g.accumulate = accumulate;
   g.compute_dtype = compute_dtype;
   const Force force = forced_path();
-  if ((force == Force::None || force == Force::Umma) && umma_grouped_supported(g))
+  static const bool grouping = []() {
+    const char *e = std::getenv("CAIFQ_GROUPED");   // "0": always loop over the experts
+    return e == nullptr || e[0] != '0';
+  }();
+  if (grouping && (force == Force::None || force == Force::Umma) && umma_grouped_supported(g))
   {
     set_path("umma-grouped");
     return launch_linear_umma_grouped(g, s);
