@@ -706,8 +706,24 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       for (int i = 0; i < PER_THREAD; ++i)
       {
         const int c = d + i * DEQ_THREADS;
-        c_row[i] = c / CHUNKS_PER_ROW;
-        c_part[i] = c % CHUNKS_PER_ROW;
+        if (BWD)
+        {
+          // A chunk expands to 64 (int4) or 32 (int8) bytes of one 128-byte operand row, whose 16-byte
+          // pieces sit at (piece ^ row % 8).  Eight consecutive threads (one shared-memory store phase)
+          // take RPQ neighbouring rows x PPQ neighbouring chunks: eight distinct bank groups, and the
+          // PPQ chunks of a row are contiguous in global memory.
+          constexpr int PPQ = 128 / (ELEMS * 2);
+          constexpr int RPQ = 8 / PPQ;
+          const int lo = c & 7;
+          const int hi = c >> 3;
+          c_row[i] = (hi % (BK / RPQ)) * RPQ + lo / PPQ;
+          c_part[i] = (hi / (BK / RPQ)) * PPQ + lo % PPQ;
+        }
+        else
+        {
+          c_row[i] = c / CHUNKS_PER_ROW;
+          c_part[i] = c % CHUNKS_PER_ROW;
+        }
       }
       auto load = [&](int kb, uint4 (&raw)[PER_THREAD], float (&sc)[PER_THREAD])
       {
