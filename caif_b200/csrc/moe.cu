@@ -349,6 +349,128 @@ __global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *
   }
 }
 
+// ---- 16-byte vector forms of the elementwise kernels (same arithmetic per element) ----
+template <typename T>
+struct Vec16
+{
+  static constexpr int N = 16 / static_cast<int>(sizeof(T));
+};
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T *p, float (&v)[Vec16<T>::N])
+{
+  const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p));
+  const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i)
+  {
+    v[i] = to_f<T>(e[i]);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_vec(T *p, const float (&v)[Vec16<T>::N])
+{
+  uint4 raw;
+  T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i)
+  {
+    e[i] = from_f<T>(v[i]);
+  }
+  *reinterpret_cast<uint4 *>(p) = raw;
+}
+
+template <typename T>
+__global__ void swiglu_fwd_vec_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ hidden,
+                                      int64_t n_vec)
+{
+  constexpr int N = Vec16<T>::N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride)
+  {
+    float g[N], u[N], h[N];
+    load_vec<T>(gate + i * N, g);
+    load_vec<T>(up + i * N, u);
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+    {
+      const T act = from_f<T>(g[j] / (1.0f + expf(-g[j])));
+      h[j] = to_f<T>(act) * u[j];
+    }
+    store_vec<T>(hidden + i * N, h);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_vec_kernel(const T *__restrict__ g_hidden, const T *__restrict__ gate,
+                                      const T *__restrict__ up, T *__restrict__ g_gate, T *__restrict__ g_up,
+                                      int64_t n_vec)
+{
+  constexpr int N = Vec16<T>::N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride)
+  {
+    float x[N], gh[N], u[N], gg[N], gu[N];
+    load_vec<T>(gate + i * N, x);
+    load_vec<T>(g_hidden + i * N, gh);
+    load_vec<T>(up + i * N, u);
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+    {
+      const T act = from_f<T>(x[j] / (1.0f + expf(-x[j])));
+      gu[j] = gh[j] * to_f<T>(act);
+      const float gv = to_f<T>(from_f<T>(gh[j] * u[j]));
+      const float sg = 1.0f / (1.0f + expf(-x[j]));
+      gg[j] = gv * sg * (1.0f + x[j] * (1.0f - sg));
+    }
+    store_vec<T>(g_up + i * N, gu);
+    store_vec<T>(g_gate + i * N, gg);
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_vec_kernel(const T *__restrict__ buffer, const int *__restrict__ expert_indices,
+                                       const T *__restrict__ expert_weights, const int *__restrict__ dispatch_map,
+                                       const int *__restrict__ expert_offsets, T *__restrict__ output,
+                                       int num_tokens, int dim, int top_k)
+{
+  constexpr int N = Vec16<T>::N;
+  const int dim_vec = dim / N;
+  const int64_t total = static_cast<int64_t>(num_tokens) * dim_vec;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    const int token = static_cast<int>(i / dim_vec);
+    const int d = static_cast<int>(i % dim_vec) * N;
+    float sum[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+    {
+      sum[j] = 0.0f;
+    }
+    for (int k = 0; k < top_k; ++k)
+    {
+      const int e = expert_indices[token * top_k + k];
+      const int pos = dispatch_map[token * top_k + k];
+      if (e >= 0 && pos >= 0)
+      {
+        const float w = to_f<T>(expert_weights[token * top_k + k]);
+        float v[N];
+        load_vec<T>(buffer + (static_cast<int64_t>(expert_offsets[e]) + pos) * dim + d, v);
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+        {
+          sum[j] = fmaf(w, v[j], sum[j]);
+        }
+      }
+    }
+    store_vec<T>(output + static_cast<int64_t>(token) * dim + d, sum);
+  }
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 inline int ew_grid(int64_t n)
 {
   int64_t g = (n + 255) / 256;
@@ -468,10 +590,15 @@ int launch_moe_combine(const void *buffer, int dtype, const int *expert_indices,
   {
     return CAIFQ_OK;
   }
-  CAIFQ_DISPATCH_FLOAT(dtype, (moe_combine_kernel<T><<<ew_grid(total), 256, 0, s>>>(
-                                  static_cast<const T *>(buffer), expert_indices,
-                                  static_cast<const T *>(expert_weights), dispatch_map, expert_offsets,
-                                  static_cast<T *>(output), num_tokens, dim, top_k)));
+  const bool vec = aligned16(buffer) && aligned16(output);
+  CAIFQ_DISPATCH_FLOAT(
+      dtype, (vec && (dim % Vec16<T>::N) == 0
+                  ? moe_combine_vec_kernel<T><<<ew_grid(total / Vec16<T>::N), 256, 0, s>>>(
+                        static_cast<const T *>(buffer), expert_indices, static_cast<const T *>(expert_weights),
+                        dispatch_map, expert_offsets, static_cast<T *>(output), num_tokens, dim, top_k)
+                  : moe_combine_kernel<T><<<ew_grid(total), 256, 0, s>>>(
+                        static_cast<const T *>(buffer), expert_indices, static_cast<const T *>(expert_weights),
+                        dispatch_map, expert_offsets, static_cast<T *>(output), num_tokens, dim, top_k)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
@@ -482,9 +609,15 @@ int launch_swiglu_fwd(const void *gate, const void *up, void *hidden, int dtype,
   {
     return CAIFQ_OK;
   }
-  CAIFQ_DISPATCH_FLOAT(dtype, (swiglu_fwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
-                                  static_cast<const T *>(gate), static_cast<const T *>(up), static_cast<T *>(hidden),
-                                  n)));
+  const bool vec = aligned16(gate) && aligned16(up) && aligned16(hidden);
+  CAIFQ_DISPATCH_FLOAT(
+      dtype, (vec && (n % Vec16<T>::N) == 0
+                  ? swiglu_fwd_vec_kernel<T><<<ew_grid(n / Vec16<T>::N), 256, 0, s>>>(
+                        static_cast<const T *>(gate), static_cast<const T *>(up), static_cast<T *>(hidden),
+                        n / Vec16<T>::N)
+                  : swiglu_fwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(static_cast<const T *>(gate),
+                                                                    static_cast<const T *>(up),
+                                                                    static_cast<T *>(hidden), n)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
@@ -496,9 +629,15 @@ int launch_swiglu_bwd(const void *g_hidden, const void *gate, const void *up, vo
   {
     return CAIFQ_OK;
   }
-  CAIFQ_DISPATCH_FLOAT(dtype, (swiglu_bwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
-                                  static_cast<const T *>(g_hidden), static_cast<const T *>(gate),
-                                  static_cast<const T *>(up), static_cast<T *>(g_gate), static_cast<T *>(g_up), n)));
+  const bool vec = aligned16(g_hidden) && aligned16(gate) && aligned16(up) && aligned16(g_gate) && aligned16(g_up);
+  CAIFQ_DISPATCH_FLOAT(
+      dtype, (vec && (n % Vec16<T>::N) == 0
+                  ? swiglu_bwd_vec_kernel<T><<<ew_grid(n / Vec16<T>::N), 256, 0, s>>>(
+                        static_cast<const T *>(g_hidden), static_cast<const T *>(gate), static_cast<const T *>(up),
+                        static_cast<T *>(g_gate), static_cast<T *>(g_up), n / Vec16<T>::N)
+                  : swiglu_bwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
+                        static_cast<const T *>(g_hidden), static_cast<const T *>(gate), static_cast<const T *>(up),
+                        static_cast<T *>(g_gate), static_cast<T *>(g_up), n)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
