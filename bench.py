@@ -396,7 +396,7 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel (see profiles/); None until captured
 NCU_TRAFFIC_C2 = 30.37e6  # bytes per launch, mean of the M=1,4,16 captures in profiles/linear_decode_int4_c2.md
-NCU_TRAFFIC_C3 = None
+NCU_TRAFFIC_C3 = 336.1e6  # bytes per launch of the forward tensor-core kernel (profiles/linear_umma_int8_c3.md)
 
 
 def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
@@ -480,7 +480,7 @@ def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
         "config": {"workload": "c3: 4096->4096 int8 per-tensor + LoRA r16 a32, M=8192 bf16, fwd + dX/dA/dB",
                    "l2": "two activation sets (268 MB) alternated between steps, larger than L2",
                    "parallelism": "1 GPU" if world == 1 else "column-parallel x%d, all-gather Y, all-reduce dX" % world},
-        "roofline": roofline, "e2e": e2e, "gpu_launches": None, "clocks": clocks,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": 11 * args.steps, "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         cb = cpu_reference_c3(steps=20, warmup=1, budget_s=20.0)
