@@ -11,12 +11,16 @@ library's own (reference bit-exact) int4 quantizer; activations seeded N(0,1).
 
 `--workload c3`: the training-shaped int8 frozen linear 4096->4096 with a
 rank-16 LoRA adapter, M=8192 bf16: forward + dX (+dA, dB); metric TFLOP/s.
+`--workload c5`: the frozen int4 experts of the MoE config (dispatch, grouped
+forward, combine, grouped dX); metric TFLOP/s.
 
 Contract: `python bench.py --gpus N --steps K --warmup W` prints ONE JSON line
-from rank 0.  With N > 1 (under torchrun) the weight is column-sharded by
-output features over the ranks and Y is all-gathered with NCCL (strong
-scaling).  `--impl reference` times the reference's CPU path (dequantize +
-OpenBLAS sgemm) on the host cores instead.
+from rank 0.  With N > 1 (under torchrun) the layer is N times as wide and
+column-sharded by output features: every rank holds a shard of the config's
+shape (weak scaling; `value` is the whole job over all ranks).  The decode
+workload gathers Y with the kernel's own stores into every rank's buffer over
+NVLink; the training workload all-gathers Y and all-reduces dX with NCCL.  `--impl reference` times the reference's CPU
+path (dequantize + OpenBLAS sgemm) on the host cores instead.
 """
 import argparse
 import json
@@ -271,34 +275,53 @@ def _keep_busy(torch, step, ms_per_step, target_ms=1600.0):
 
 
 def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
-    shard = C2_OUT // world
-    if shard * world != C2_OUT or shard % 8 != 0:
-        raise SystemExit("out=%d does not shard over %d ranks" % (C2_OUT, world))
+    # N > 1: a layer N times as wide, column-parallel: every rank holds a [14336, 4096] shard (its rows of
+    # the 1-GPU quantization of the wide weight), so per-GPU work is the config's and the job grows with N.
+    shard = C2_OUT
     gen = torch.Generator(device=dev).manual_seed(1235)
     weights = []
     for c in range(C2_COPIES):
-        # every rank draws the same full weight and keeps its rows: the codes are the 1-GPU codes
-        wf = torch.randn(C2_OUT * C2_IN, generator=gen, device=dev) * 0.02
-        packed, scales = nv.quantize_int4(wf, C2_GROUP)
-        del wf
-        full = nv.Weight(packed, nv.I4, C2_IN, C2_OUT, scales, group_size=C2_GROUP)
-        if world > 1:
-            sh = full.rows(rank * shard, (rank + 1) * shard)
-            weights.append(nv.Weight(sh.codes.clone(), nv.I4, C2_IN, shard, sh.scales.clone(), group_size=C2_GROUP))
-        else:
-            weights.append(full)
-    del full
+        for r in range(world):
+            # every rank makes the same draws and keeps its own rows; int4 groups never straddle rows
+            # here (4096 % 128 == 0), so quantizing a row block alone gives the wide weight's codes
+            wf = torch.randn(C2_OUT * C2_IN, generator=gen, device=dev) * 0.02
+            if r == rank:
+                packed, scales = nv.quantize_int4(wf, C2_GROUP)
+                weights.append(nv.Weight(packed, nv.I4, C2_IN, C2_OUT, scales, group_size=C2_GROUP))
+            del wf
     torch.cuda.empty_cache()
     xs = {m: torch.randn(m, C2_IN, generator=gen, device=dev).to(torch.bfloat16) for m in C2_MS}
-    ys = {m: torch.empty(m, shard, dtype=torch.float32, device=dev) for m in C2_MS}
-    gathered = {m: torch.empty(world * m, shard, dtype=torch.float32, device=dev) for m in C2_MS} if world > 1 else None
+    rows_all = sum(C2_MS)
+    # one output block per weight copy: the rows of M = 1, 4, 16 back to back, gathered in one collective
+    yblk = [torch.empty(rows_all, shard, dtype=torch.float32, device=dev) for _ in range(C2_COPIES)]
+    ys = []
+    for c in range(C2_COPIES):
+        views, r0 = {}, 0
+        for m in C2_MS:
+            views[m] = yblk[c][r0:r0 + m]
+            r0 += m
+        ys.append(views)
+    # N > 1: every rank owns a [copies, 21, N * 14336] result block mapped into all ranks; the kernel
+    # stores its slice into every rank's block (the all-gather is the kernel's own stores over NVLink)
+    peer = None
+    if world > 1:
+        from caif_b200.sharded import PeerBuffer
+        peer = PeerBuffer(C2_COPIES * rows_all * world * shard * 4, dev)
+    row0 = {}
+    r0 = 0
+    for m in C2_MS:
+        row0[m] = r0
+        r0 += m
 
     def step_eager():
-        for w in weights:
+        for c, w in enumerate(weights):
             for m in C2_MS:
-                nv.linear_fwd(w, xs[m], compute=nv.F32, out=ys[m])
                 if world > 1:
-                    dist.all_gather_into_tensor(gathered[m], ys[m])
+                    off = (c * rows_all + row0[m]) * world * shard * 4
+                    nv.linear_fwd_gather(w, xs[m], [q + off for q in peer.ptrs], world * shard, rank * shard,
+                                         nv.F32, nv.F32)
+                else:
+                    nv.linear_fwd(w, xs[m], compute=nv.F32, out=ys[c][m])
 
     launches_per_step = C2_COPIES * len(C2_MS)
     # warm-up (also sets the kernel's shared-memory attribute outside any capture)
@@ -338,7 +361,7 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
     _keep_busy(torch, step, ms / args.steps)
     clocks = sampler.stop() if rank == 0 else None
 
-    bytes_per_step = C2_COPIES * sum(c2_bytes(m) for m in C2_MS)   # whole job (all shards)
+    bytes_per_step = world * C2_COPIES * sum(c2_bytes(m) for m in C2_MS)   # whole job (all shards)
     ms_per_step = ms / args.steps
     value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
 
@@ -359,13 +382,11 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
         dx = {m: torch.empty_like(xs[m]) for m in C2_MS}
 
         def step_e2e():
-            for w in weights:
+            for c, w in enumerate(weights):
                 for m in C2_MS:
                     dx[m].copy_(hx[m], non_blocking=True)
-                    nv.linear_fwd(w, dx[m], compute=nv.F32, out=ys[m])
-                    if world > 1:
-                        dist.all_gather_into_tensor(gathered[m], ys[m])
-                    hy[m].copy_(ys[m], non_blocking=True)
+                    nv.linear_fwd(w, dx[m], compute=nv.F32, out=ys[c][m])
+                    hy[m].copy_(ys[c][m], non_blocking=True)
             torch.cuda.synchronize()
 
         for _ in range(3):
@@ -379,14 +400,19 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
     result = {
         "metric": "decode int4 frozen-linear forward, algorithmic HBM bytes per second", "value": value,
         "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 x int4 -> fp32", "data": "synthetic",
         "config": {"workload": "c2: in=4096 out=14336 int4 g128, M in {1,4,16}, forward; step = 8 weight copies x 3 M",
                    "l2": "8 weight copies = 242 MB > 126 MB L2, visited round-robin",
                    "launch": "CUDA graph replay" if graphed else "eager",
-                   "parallelism": "1 GPU" if world == 1 else "column-parallel x%d + NCCL all-gather of Y" % world},
+                   "parallelism": "1 GPU" if world == 1 else
+                   "column-parallel x%d: a layer of out=%d, one [14336, 4096] shard per GPU; every launch stores "
+                   "its slice of Y into all ranks' result buffers over NVLink (peer memory), no separate "
+                   "collective; e2e times the local slice only" % (world, world * C2_OUT)},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
     }
+    if peer is not None:
+        peer.close()
     if rank == 0 and world == 1 and not args.no_cpu:
         cb = cpu_reference_c2(steps=50, warmup=1, budget_s=15.0)
         result["cpu_baseline"] = {"value": cb["value"], "unit": "GB/s", "cores": cb["cores"], "kind": "port",
@@ -400,37 +426,46 @@ NCU_TRAFFIC_C3 = 336.1e6  # bytes per launch of the forward tensor-core kernel (
 
 
 def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
+    # N > 1: a projection 4096 -> 4096*N, column-parallel: every rank holds a [4096, 4096] int8 shard and
+    # the matching rows of LoRA B; Y is all-gathered, dX and dA are partial sums and all-reduced.
     dim, rank_r, m, alpha = 4096, 16, 8192, 32.0
-    shard = dim // world
     gen = torch.Generator(device=dev).manual_seed(1236)
-    wf = torch.randn(dim * dim, generator=gen, device=dev) * 0.02
-    q, s = nv.quantize_int8_per_tensor(wf)
-    del wf
-    qs = q.view(dim, dim)[rank * shard:(rank + 1) * shard].contiguous()
-    weight = nv.Weight(qs, nv.I8, dim, shard, s)
+    weight = None
+    for r in range(world):
+        wf = torch.randn(dim * dim, generator=gen, device=dev) * 0.02
+        if r == rank:
+            q, s = nv.quantize_int8_per_tensor(wf)   # one scale per shard: what a per-rank layer object holds
+            weight = nv.Weight(q.view(dim, dim), nv.I8, dim, dim, s)
+        del wf
     a = ((torch.rand(rank_r, dim, generator=gen, device=dev) * 2 - 1) / 64).to(torch.bfloat16)
-    b_full = (torch.randn(dim, rank_r, generator=gen, device=dev) * 1e-3).to(torch.bfloat16)
-    b = b_full[rank * shard:(rank + 1) * shard].contiguous()
+    b_full = (torch.randn(world * dim, rank_r, generator=gen, device=dev) * 1e-3).to(torch.bfloat16)
+    b = b_full[rank * dim:(rank + 1) * dim].contiguous()
     lora = nv.Lora(a, b, alpha)
     n_sets = 2  # 2 x (X + dY) = 268 MB of activations > L2, alternated between steps
     xs = [torch.randn(m, dim, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
     dys = [torch.randn(m, dim, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_sets)]
     state = {"i": 0}
-    gathered = torch.empty(world * m, shard, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    gathered = torch.empty(world * m, dim, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    comm = torch.cuda.Stream() if world > 1 else None
 
     def step():
         i = state["i"] % n_sets
         state["i"] += 1
+        main = torch.cuda.current_stream()
         y, hidden = nv.lora_linear_fwd(weight, lora, xs[i], compute=nv.F32)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, y)
-            dy = dys[i][:, rank * shard:(rank + 1) * shard].contiguous()
-        else:
-            dy = dys[i]
-        dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dy, xs[i], hidden, compute=nv.F32)
+            # the gather of Y runs beside the backward pass
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                dist.all_gather_into_tensor(gathered, y)
+        dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dys[i], xs[i], hidden, compute=nv.F32)
         if world > 1:
-            dist.all_reduce(dx)
-            dist.all_reduce(d_a)
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(dx)
+                dist.all_reduce(d_a)
+            main.wait_stream(comm)
+            y.record_stream(comm)
         return dx
 
     for _ in range(max(args.warmup, 3)):
@@ -445,7 +480,7 @@ def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
     _keep_busy(torch, step, ms / args.steps)
     clocks = sampler.stop() if rank == 0 else None
     ms_per_step = ms / args.steps
-    flops = c3_flops(m)
+    flops = c3_flops(m) * world
     value = flops / (ms_per_step * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": value / world / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_C3,
@@ -475,11 +510,13 @@ def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
     result = {
         "metric": "int8 frozen linear + LoRA r16, forward + dX/dA/dB, TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": "c3: 4096->4096 int8 per-tensor + LoRA r16 a32, M=8192 bf16, fwd + dX/dA/dB",
                    "l2": "two activation sets (268 MB) alternated between steps, larger than L2",
-                   "parallelism": "1 GPU" if world == 1 else "column-parallel x%d, all-gather Y, all-reduce dX" % world},
+                   "parallelism": "1 GPU" if world == 1 else
+                   "column-parallel x%d: a 4096 -> %d projection, one [4096, 4096] shard per GPU; all-gather of Y "
+                   "beside the backward pass, all-reduce of dX and dA" % (world, world * dim)},
         "roofline": roofline, "e2e": e2e, "gpu_launches": 11 * args.steps, "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu:

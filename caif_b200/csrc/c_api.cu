@@ -394,6 +394,51 @@ int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_dtype, int6
                     static_cast<cudaStream_t>(stream), "caifq_linear_fwd");
 }
 
+int caifq_linear_fwd_gather(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *const *y_peers,
+                            int32_t num_peers, int64_t y_ld, int64_t y_col0, int32_t y_dtype, int32_t compute_dtype,
+                            void *stream)
+{
+  const char *who = "caifq_linear_fwd_gather";
+  const int rc = check_weight(w, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(m >= 0, "%s: negative m", who);
+  CAIFQ_CHECK_ARG(is_float_dtype(x_dtype) && is_float_dtype(y_dtype) && is_float_dtype(compute_dtype),
+                  "%s: activation/output/compute dtypes must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(y_peers != nullptr && num_peers >= 1 && num_peers <= kMaxPeers, "%s: 1 to %d result buffers", who,
+                  kMaxPeers);
+  CAIFQ_CHECK_ARG(y_col0 >= 0 && y_ld >= y_col0 + w->out_dim, "%s: the slice does not fit the row pitch", who);
+  if (m == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(x != nullptr, "%s: null activation pointer", who);
+  LinearArgs args{};
+  args.w = *w;
+  args.backward = false;
+  args.a = x;
+  args.a_dtype = x_dtype;
+  args.a_prescale = 1.0f;
+  args.m = m;
+  args.c = y_peers[0];
+  args.c_dtype = y_dtype;
+  args.accumulate = false;
+  args.compute_dtype = compute_dtype;
+  args.c_peers = y_peers;
+  args.num_peers = num_peers;
+  args.c_ld = y_ld;
+  args.c_col0 = y_col0;
+  if (!decode_supported(args))
+  {
+    set_error("%s: only few-token calls the decode kernel takes (m <= 16, bf16 x, int4 or per-tensor int8)", who);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  set_path("decode");
+  return launch_linear_decode(args, static_cast<cudaStream_t>(stream));
+}
+
 int caifq_linear_dx(const caifq_weight *w, const void *dy, int32_t dy_dtype, int64_t m, void *dx, int32_t dx_dtype,
                     int32_t compute_dtype, void *stream)
 {

@@ -198,7 +198,16 @@ struct LinearArgs
   // for backward.  Both already carry every scale so that acc_total * epilogue scale is right.
   const void *lora_lhs;
   const void *lora_rhs;
+  // Optional fused all-gather of a column-parallel forward (few-token kernel only): when
+  // num_peers > 0 every output element goes to c_peers[r] for all r (this GPU's own buffer
+  // included, `c` is ignored) at row pitch c_ld and column offset c_col0.
+  void *const *c_peers;
+  int num_peers;
+  int64_t c_ld;
+  int64_t c_col0;
 };
+
+constexpr int kMaxPeers = 8;
 
 // generic tiled fp32-FMA GEMM over every (storage, compute) cell
 int launch_linear_generic(const LinearArgs &args, cudaStream_t s);

@@ -176,7 +176,10 @@ struct DecodeParams
   const uint8_t *codes;   // [out, in] packed
   const void *scales;     // int4: fp16 per group; int8: fp32[1] or null
   const __nv_bfloat16 *x; // [m, in]
-  void *y;                // [m, out]
+  void *y[kMaxPeers];     // [m, y_ld] on every GPU that receives the result (own buffer included)
+  int num_y;
+  int64_t y_ld;           // row pitch of the result, in elements
+  int64_t y_col0;         // first column this launch writes
   int y_dtype;
   int m;
   int in_dim;
@@ -557,7 +560,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
     const int row = row_begin + item * kItemRows + r;
     if (token < p.m && row < row_end)
     {
-      store_from_float(p.y, static_cast<int64_t>(token) * p.out_dim + row, p.y_dtype, sum);
+      // plain stores; with peers they travel over NVLink and are complete when the kernel is
+      const int64_t idx = static_cast<int64_t>(token) * p.y_ld + p.y_col0 + row;
+      for (int r = 0; r < p.num_y; ++r)
+      {
+        store_from_float(p.y[r], idx, p.y_dtype, sum);
+      }
     }
   }
 }
@@ -573,6 +581,17 @@ int sm_count()
     if (cached <= 0)
     {
       cached = 148;
+    }
+    // A host that runs a collective beside this kernel (column-parallel decode) can leave it a few
+    // SMs: the kernel keeps one CTA per SM, and a CTA that finds its SM taken waits for the whole
+    // collective.  CAIFQ_DECODE_CTAS caps the grid.
+    if (const char *e = std::getenv("CAIFQ_DECODE_CTAS"))
+    {
+      const int v = std::atoi(e);
+      if (v >= 1 && v < cached)
+      {
+        cached = v;
+      }
     }
   }
   return cached;
@@ -729,7 +748,33 @@ int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
   p.codes = static_cast<const uint8_t *>(w.codes);
   p.scales = w.scales;
   p.x = static_cast<const __nv_bfloat16 *>(x);
-  p.y = y;
+  if (args.num_peers > 0)
+  {
+    if (args.num_peers > kMaxPeers || args.c_peers == nullptr)
+    {
+      set_error("frozen linear (decode): at most %d peers", kMaxPeers);
+      return CAIFQ_ERR_INVALID;
+    }
+    for (int r = 0; r < args.num_peers; ++r)
+    {
+      if (args.c_peers[r] == nullptr)
+      {
+        set_error("frozen linear (decode): null peer buffer %d", r);
+        return CAIFQ_ERR_INVALID;
+      }
+      p.y[r] = args.c_peers[r];
+    }
+    p.num_y = args.num_peers;
+    p.y_ld = args.c_ld;
+    p.y_col0 = args.c_col0;
+  }
+  else
+  {
+    p.y[0] = y;
+    p.num_y = 1;
+    p.y_ld = w.out_dim;
+    p.y_col0 = 0;
+  }
   p.y_dtype = y_dtype;
   p.m = static_cast<int>(m);
   p.in_dim = w.in_dim;

@@ -66,6 +66,8 @@ _SIGNATURES = {
     "caifq_cast": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _vp]),
     "caifq_weight_materialize": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _vp]),
     "caifq_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_linear_fwd_gather": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, ctypes.POINTER(_vp), _i32,
+                                               _i64, _i64, _i32, _i32, _vp]),
     "caifq_linear_dx": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_lora_fwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
@@ -255,6 +257,16 @@ def linear_fwd(w, x, out_dtype=torch.float32, compute=F32, out=None):
     _check(lib().caifq_linear_fwd(w.ref(), _ptr(x), dtype_code(x), m, _ptr(out), dtype_code(out), compute, _stream()),
            "linear_fwd")
     return out
+
+
+def linear_fwd_gather(w, x, peer_ptrs, y_ld, y_col0, y_dtype=F32, compute=F32):
+    """Few-token forward whose result goes straight into every buffer of `peer_ptrs` (raw device
+    pointers: this GPU's own buffer and the peers' buffers mapped into this process)."""
+    _need_cuda(x)
+    m = x.shape[0]
+    arr = (_vp * len(peer_ptrs))(*[_vp(int(q)) for q in peer_ptrs])
+    _check(lib().caifq_linear_fwd_gather(w.ref(), _ptr(x), dtype_code(x), m, arr, len(peer_ptrs), int(y_ld),
+                                         int(y_col0), y_dtype, compute, _stream()), "linear_fwd_gather")
 
 
 def linear_dx(w, dy, out_dtype=torch.float32, compute=F32, out=None):

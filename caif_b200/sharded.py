@@ -15,10 +15,113 @@ The reference is single-device (no collective anywhere), so the contract is
 The compute itself is injected (`ops`): on a GPU box it is caif_b200.native (the CUDA
 library); the CPU tests of the collectives' bookkeeping pass the numpy oracle instead.
 No kernel of this package reads another GPU's memory: remote data always lands in local
-memory through the collective first.
+memory through the collective first.  One kernel WRITES to it: the few-token forward can store
+its slice of Y straight into every rank's result buffer (PeerBuffer below maps the buffers with
+CUDA IPC), which replaces the all-gather for decode-sized calls.
 """
+import ctypes
+import ctypes.util
+
 import torch
 import torch.distributed as dist
+
+
+class _IpcMemHandle(ctypes.Structure):
+    """cudaIpcMemHandle_t: 64 opaque bytes, passed to the runtime BY VALUE."""
+    _fields_ = [("reserved", ctypes.c_ubyte * 64)]
+
+
+class PeerBuffer:
+    """One device buffer per rank, each mapped into every process of the group (CUDA IPC with lazy
+    peer access).  `ptrs[r]` is rank r's buffer as seen from this process; `local()` views this
+    rank's own buffer as a tensor.  Collective constructor: every rank of the group calls it."""
+
+    _IPC_LAZY_PEER_ACCESS = 1
+    _cudart = None
+
+    @classmethod
+    def cudart(cls):
+        if cls._cudart is None:
+            last = None
+            for name in ("libcudart.so.12", "libcudart.so", ctypes.util.find_library("cudart")):
+                if not name:
+                    continue
+                try:
+                    rt = ctypes.CDLL(name)
+                    rt.cudaIpcGetMemHandle.argtypes = [ctypes.POINTER(_IpcMemHandle), ctypes.c_void_p]
+                    rt.cudaIpcOpenMemHandle.argtypes = [ctypes.POINTER(ctypes.c_void_p), _IpcMemHandle, ctypes.c_uint]
+                    rt.cudaIpcCloseMemHandle.argtypes = [ctypes.c_void_p]
+                    rt.cudaMalloc.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_size_t]
+                    rt.cudaMemset.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t]
+                    rt.cudaFree.argtypes = [ctypes.c_void_p]
+                    rt.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int,
+                                                   ctypes.c_void_p]
+                    cls._cudart = rt
+                    break
+                except OSError as e:
+                    last = e
+            if cls._cudart is None:
+                raise RuntimeError("the CUDA runtime library is needed for peer buffers: %s" % last)
+        return cls._cudart
+
+    def __init__(self, nbytes, device, group=None):
+        rt = self.cudart()
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.nbytes = int(nbytes)
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        base = ctypes.c_void_p()
+        self._check(rt.cudaMalloc(ctypes.byref(base), self.nbytes), "cudaMalloc")
+        self._check(rt.cudaMemset(base, 0, self.nbytes), "cudaMemset")
+        handle = _IpcMemHandle()
+        self._check(rt.cudaIpcGetMemHandle(ctypes.byref(handle), base), "cudaIpcGetMemHandle")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.reserved), group=group)
+        self.ptrs = []
+        self._opened = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(base.value)
+                continue
+            peer = ctypes.c_void_p()
+            h = _IpcMemHandle()
+            ctypes.memmove(h.reserved, raw, 64)
+            self._check(rt.cudaIpcOpenMemHandle(ctypes.byref(peer), h, self._IPC_LAZY_PEER_ACCESS),
+                        "cudaIpcOpenMemHandle")
+            self.ptrs.append(peer.value)
+            self._opened.append(peer)
+        self._base = base
+        dist.barrier(group=group)
+
+    @staticmethod
+    def _check(rc, what):
+        if rc != 0:
+            raise RuntimeError("%s failed with CUDA error %d" % (what, rc))
+
+    def read(self, dtype, shape):
+        """A copy of this rank's buffer as a tensor (device-to-device copy on the current stream)."""
+        out = torch.empty(shape, dtype=dtype, device=self.device)
+        nbytes = out.numel() * out.element_size()
+        if nbytes > self.nbytes:
+            raise ValueError("the buffer holds %d bytes, %d asked" % (self.nbytes, nbytes))
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        self._check(self.cudart().cudaMemcpyAsync(out.data_ptr(), self._base, nbytes, 3, stream),   # 3: device to device
+                    "cudaMemcpyAsync")
+        return out
+
+    def close(self):
+        """Collective: unmaps the peers' buffers, then frees this rank's."""
+        rt = self.cudart()
+        torch.cuda.synchronize(self.device)
+        for peer in self._opened:
+            rt.cudaIpcCloseMemHandle(peer)
+        self._opened = []
+        dist.barrier(group=self.group)
+        if self._base is not None:
+            rt.cudaFree(self._base)
+            self._base = None
 
 
 def shard_range(total, world, rank, quantum=1):
@@ -57,6 +160,15 @@ class ColumnParallelFrozenLinear:
         dist.all_gather_into_tensor(gathered, y_local.contiguous(), group=self.group)
         # [N, m, out/N] -> [m, N, out/N] -> [m, out]: rank r's features land at columns [r*out/N, ...)
         return gathered.view(self.world, m, shard).permute(1, 0, 2).reshape(m, self.out_dim)
+
+    def forward_gather(self, fwd_gather, x, peer_buffer, out_dtype=torch.float32):
+        """Few-token forward with the gather fused into the kernel: fwd_gather(x, ptrs, y_ld, y_col0)
+        stores this rank's [m, out/N] slice into every rank's [m, out] buffer.  Returns this rank's
+        full Y once all ranks' kernels are complete (a stream-ordered barrier collective)."""
+        m = x.shape[0]
+        fwd_gather(x, peer_buffer.ptrs, self.out_dim, self.begin)
+        dist.barrier(group=self.group)   # NCCL: a collective kernel behind this rank's stores on the stream
+        return peer_buffer.read(out_dtype, (m, self.out_dim))
 
     def backward(self, dy):
         part = self.dx(dy[:, self.begin:self.end].contiguous())  # partial sum over this rank's features

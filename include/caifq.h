@@ -148,6 +148,22 @@ CAIFQ_API int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_d
 CAIFQ_API int caifq_linear_dx(const caifq_weight *w, const void *dy, int32_t dy_dtype, int64_t m, void *dx, int32_t dx_dtype,
                     int32_t compute_dtype, void *stream);
 
+/*
+ * Column-parallel forward with the all-gather of Y fused into the kernel's stores: the design of
+ * BASELINE's north_star for layers sharded by output features (the reference itself has no
+ * multi-GPU linear; this replaces ForwardImpl followed by an NCCL all-gather of the slices).
+ * This rank holds rows [y_col0, y_col0 + w->out_dim) of a wider layer.  Every output element
+ * y[t, y_col0 + j] is written into y_peers[r] for r = 0 .. num_peers-1 (row pitch y_ld elements):
+ * this GPU's own result buffer and the peers' buffers mapped into this process (CUDA IPC or
+ * symmetric memory with peer access enabled).  Plain stores over NVLink, complete when the kernel
+ * is; the caller orders the consumers behind all ranks' kernels (stream-ordered barrier or event).
+ * Few-token calls only (m <= 16, bf16 x, int4 / per-tensor int8): other calls are refused with
+ * CAIFQ_ERR_UNSUPPORTED and should use caifq_linear_fwd plus a collective.
+ */
+CAIFQ_API int caifq_linear_fwd_gather(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m,
+                                      void *const *y_peers, int32_t num_peers, int64_t y_ld, int64_t y_col0,
+                                      int32_t y_dtype, int32_t compute_dtype, void *stream);
+
 /* Name of the kernel family the last caifq_linear_fwd / caifq_linear_dx call
  * on this thread chose ("decode", "umma", "generic"); for tests and reports. */
 CAIFQ_API const char *caifq_last_path(void);

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 from caif_b200 import native as nv  # noqa: E402
-from caif_b200.sharded import ColumnParallelFrozenLinear, ExpertParallelFrozenMoE, shard_range  # noqa: E402
+from caif_b200.sharded import ColumnParallelFrozenLinear, ExpertParallelFrozenMoE, PeerBuffer, shard_range  # noqa: E402
 
 
 def main():
@@ -49,6 +49,21 @@ def main():
         ok = ok and same and err <= 1e-5
         if rank == 0:
             print("column-parallel m=%d: forward identical=%s, dX rel err %.2e" % (m, same, err))
+
+    # ---- few-token forward with the all-gather fused into the kernel's stores (peer memory)
+    pb = PeerBuffer(16 * out_dim * 4, dev)
+    for m in (1, 5, 16):
+        x = torch.randn(m, in_dim, generator=g, device=dev).to(torch.bfloat16)
+        layer = ColumnParallelFrozenLinear(None, None, out_dim, in_dim)
+        y = layer.forward_gather(
+            lambda t, ptrs, ld, col0: nv.linear_fwd_gather(local, t, ptrs, ld, col0, nv.F32, nv.F32), x, pb)
+        y1 = nv.linear_fwd(full, x, torch.float32, nv.F32)
+        same = torch.equal(y, y1)
+        ok = ok and same
+        if rank == 0:
+            print("column-parallel m=%d, gather fused into the stores: identical=%s" % (m, same))
+        dist.barrier()   # nobody overwrites a buffer another rank is still reading
+    pb.close()
 
     # ---- expert-parallel frozen MoE
     experts, dim, hid, top_k, tokens = 8, 256, 384, 2, 300
