@@ -314,8 +314,10 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
         r0 += m
 
     def step_eager():
-        for c, w in enumerate(weights):
-            for m in C2_MS:
+        # M-major: consecutive launches use different weight copies, a copy comes back 8 launches
+        # (242 MB) later, so no launch finds its codes in L2
+        for m in C2_MS:
+            for c, w in enumerate(weights):
                 if world > 1:
                     off = (c * rows_all + row0[m]) * world * shard * 4
                     nv.linear_fwd_gather(w, xs[m], [q + off for q in peer.ptrs], world * shard, rank * shard,
@@ -382,8 +384,8 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
         dx = {m: torch.empty_like(xs[m]) for m in C2_MS}
 
         def step_e2e():
-            for c, w in enumerate(weights):
-                for m in C2_MS:
+            for m in C2_MS:
+                for c, w in enumerate(weights):
                     dx[m].copy_(hx[m], non_blocking=True)
                     nv.linear_fwd(w, dx[m], compute=nv.F32, out=ys[c][m])
                     hy[m].copy_(ys[c][m], non_blocking=True)
@@ -403,7 +405,7 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 x int4 -> fp32", "data": "synthetic",
         "config": {"workload": "c2: in=4096 out=14336 int4 g128, M in {1,4,16}, forward; step = 8 weight copies x 3 M",
-                   "l2": "8 weight copies = 242 MB > 126 MB L2, visited round-robin",
+                   "l2": "8 weight copies = 242 MB > 126 MB L2; consecutive launches use different copies, a copy returns 8 launches later",
                    "launch": "CUDA graph replay" if graphed else "eager",
                    "parallelism": "1 GPU" if world == 1 else
                    "column-parallel x%d: a layer of out=%d, one [14336, 4096] shard per GPU; every launch stores "

@@ -804,6 +804,14 @@ int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
   {
     stages = kMaxStages;
   }
+  if (const char *e = std::getenv("CAIFQ_DECODE_STAGES"))
+  {
+    const int v = std::atoi(e);
+    if (v >= 2 && v < stages)
+    {
+      stages = v;
+    }
+  }
   if (stages < 2)
   {
     set_error("frozen linear (decode): row too long for the shared-memory ring");

@@ -170,6 +170,32 @@ def test_decode_int8_without_scales_and_bf16_out():
     assert max_rel_err(y.float().cpu().numpy(), want) <= 1e-2  # bf16 output rounding
 
 
+def test_decode_forward_gather_into_several_buffers():
+    """The fused gather: two shards of a wider layer write their slices, at their column offsets,
+    into two result buffers each (on one GPU both 'ranks' are local buffers); every buffer ends up
+    holding the full-width result, equal to the plain forward of each shard bit for bit."""
+    rng = np.random.default_rng(2024)
+    in_dim, shard, m = 1024, 520, 5
+    shards = [make_weight(rng, shard, in_dim, orc.I4)[0] for _ in range(2)]
+    _, x = act(rng, m, in_dim, orc.BF16)
+    bufs = [torch.full((m, 2 * shard), float("nan"), device="cuda") for _ in range(2)]
+    ptrs = [b.data_ptr() for b in bufs]
+    for r, w in enumerate(shards):
+        nv.linear_fwd_gather(w, x, ptrs, 2 * shard, r * shard, orc.F32, orc.F32)
+        assert nv.last_path() == "decode"
+    torch.cuda.synchronize()
+    want = torch.cat([nv.linear_fwd(w, x, torch.float32, orc.F32) for w in shards], dim=1)
+    for b in bufs:
+        assert torch.equal(b, want)
+    # shapes the few-token kernel does not take are refused, not silently run elsewhere
+    _, x_many = act(rng, 64, in_dim, orc.BF16)
+    big = torch.empty((64, 2 * shard), device="cuda")
+    with pytest.raises(nv.CaifqError):
+        nv.linear_fwd_gather(shards[0], x_many, [big.data_ptr()], 2 * shard, 0, orc.F32, orc.F32)
+    with pytest.raises(nv.CaifqError):   # the slice must fit the row pitch
+        nv.linear_fwd_gather(shards[0], x, ptrs, shard, shard, orc.F32, orc.F32)
+
+
 # ------------------------------------------------------------ tensor-core path
 def _umma_case(storage, compute, m, in_dim, out_dim, seed, group=128):
     rng = np.random.default_rng(seed)
