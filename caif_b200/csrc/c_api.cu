@@ -39,6 +39,16 @@ int launch_moe_build_dispatch(const int *expert_indices, int num_tokens, int top
                               int *dispatch_map, int *expert_offsets, cudaStream_t s);
 int launch_moe_dispatch(const void *input, int dtype, const int *expert_indices, const int *dispatch_map,
                         const int *expert_offsets, void *buffer, int num_tokens, int dim, int top_k, cudaStream_t s);
+int launch_moe_combine_bwd_grad_expert(const void *grad_output, int dtype, const int *expert_indices,
+                                       const void *expert_weights, const int *dispatch_map, const int *expert_offsets,
+                                       void *grad_buffer, int num_tokens, int dim, int top_k, cudaStream_t s);
+int launch_moe_combine_bwd_grad_weights(const void *grad_output, const void *buffer, int dtype,
+                                        const int *expert_indices, const int *dispatch_map,
+                                        const int *expert_offsets, void *grad_weights, int num_tokens, int dim,
+                                        int top_k, cudaStream_t s);
+int launch_moe_dispatch_bwd(const void *grad_buffer, int dtype, const int *expert_indices, const int *dispatch_map,
+                            const int *expert_offsets, void *grad_input, int num_tokens, int dim, int top_k,
+                            cudaStream_t s);
 int launch_moe_combine(const void *buffer, int dtype, const int *expert_indices, const void *expert_weights,
                        const int *dispatch_map, const int *expert_offsets, void *output, int num_tokens, int dim,
                        int top_k, cudaStream_t s);
@@ -727,6 +737,46 @@ int caifq_moe_combine(const void *expert_buffer, int32_t dtype, const int32_t *e
                   "caifq_moe_combine: null pointer");
   return launch_moe_combine(expert_buffer, dtype, expert_indices, expert_weights, dispatch_map, expert_offsets,
                             output, num_tokens, dim, top_k, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_combine_bwd_grad_expert(const void *grad_output, int32_t dtype, const int32_t *expert_indices,
+                                      const void *expert_weights, const int32_t *dispatch_map,
+                                      const int32_t *expert_offsets, void *grad_expert_buffer, int32_t num_tokens,
+                                      int32_t dim, int32_t top_k, void *stream)
+{
+  CAIFQ_CHECK_ARG(num_tokens >= 0 && dim > 0 && top_k > 0, "caifq_moe_combine_bwd_grad_expert: bad shape");
+  CAIFQ_CHECK_ARG(num_tokens == 0 || (grad_output && expert_indices && expert_weights && dispatch_map &&
+                                      expert_offsets && grad_expert_buffer),
+                  "caifq_moe_combine_bwd_grad_expert: null pointer");
+  return launch_moe_combine_bwd_grad_expert(grad_output, dtype, expert_indices, expert_weights, dispatch_map,
+                                            expert_offsets, grad_expert_buffer, num_tokens, dim, top_k,
+                                            static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_combine_bwd_grad_weights(const void *grad_output, const void *expert_buffer, int32_t dtype,
+                                       const int32_t *expert_indices, const int32_t *dispatch_map,
+                                       const int32_t *expert_offsets, void *grad_weights, int32_t num_tokens,
+                                       int32_t dim, int32_t top_k, void *stream)
+{
+  CAIFQ_CHECK_ARG(num_tokens >= 0 && dim > 0 && top_k > 0, "caifq_moe_combine_bwd_grad_weights: bad shape");
+  CAIFQ_CHECK_ARG(num_tokens == 0 || (grad_output && expert_buffer && expert_indices && dispatch_map &&
+                                      expert_offsets && grad_weights),
+                  "caifq_moe_combine_bwd_grad_weights: null pointer");
+  return launch_moe_combine_bwd_grad_weights(grad_output, expert_buffer, dtype, expert_indices, dispatch_map,
+                                             expert_offsets, grad_weights, num_tokens, dim, top_k,
+                                             static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_dispatch_bwd(const void *grad_expert_buffer, int32_t dtype, const int32_t *expert_indices,
+                           const int32_t *dispatch_map, const int32_t *expert_offsets, void *grad_input,
+                           int32_t num_tokens, int32_t dim, int32_t top_k, void *stream)
+{
+  CAIFQ_CHECK_ARG(num_tokens >= 0 && dim > 0 && top_k > 0, "caifq_moe_dispatch_bwd: bad shape");
+  CAIFQ_CHECK_ARG(num_tokens == 0 ||
+                      (grad_expert_buffer && expert_indices && dispatch_map && expert_offsets && grad_input),
+                  "caifq_moe_dispatch_bwd: null pointer");
+  return launch_moe_dispatch_bwd(grad_expert_buffer, dtype, expert_indices, dispatch_map, expert_offsets, grad_input,
+                                 num_tokens, dim, top_k, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------------------ grouped experts

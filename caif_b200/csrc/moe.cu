@@ -469,6 +469,154 @@ __global__ void moe_combine_vec_kernel(const T *__restrict__ buffer, const int *
   }
 }
 
+// ---- backward of combine and dispatch (src/caif_cuda_kernels_moe.cu:816-1067) ----
+// grad_buffer[slot(t,k), d] = w[t,k] * grad_output[t,d]; one warp per (t,k), 16-byte pieces when possible
+template <typename T>
+__global__ void moe_combine_bwd_grad_expert_kernel(const T *__restrict__ grad_output,
+                                                   const int *__restrict__ expert_indices,
+                                                   const T *__restrict__ expert_weights,
+                                                   const int *__restrict__ dispatch_map,
+                                                   const int *__restrict__ expert_offsets,
+                                                   T *__restrict__ grad_buffer, int64_t assignments, int dim,
+                                                   int top_k, int vec_ok)
+{
+  constexpr int N = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int64_t a = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (a >= assignments)
+  {
+    return;
+  }
+  const int e = expert_indices[a];
+  const int pos = dispatch_map[a];
+  if (e < 0 || pos < 0)
+  {
+    return;
+  }
+  const float w = to_f<T>(expert_weights[a]);
+  const T *src = grad_output + (a / top_k) * dim;
+  T *dst = grad_buffer + (static_cast<int64_t>(expert_offsets[e]) + pos) * dim;
+  if (vec_ok)
+  {
+    for (int i = lane * N; i < dim; i += 32 * N)
+    {
+      float v[N];
+      load_vec<T>(src + i, v);
+#pragma unroll
+      for (int j = 0; j < N; ++j)
+      {
+        v[j] = __fmul_rn(w, v[j]);
+      }
+      store_vec<T>(dst + i, v);
+    }
+  }
+  else
+  {
+    for (int i = lane; i < dim; i += 32)
+    {
+      dst[i] = from_f<T>(__fmul_rn(w, to_f<T>(src[i])));
+    }
+  }
+}
+
+// grad_weights[t,k] = <grad_output[t,:], buffer[slot(t,k),:]>: the reference's summation order -
+// 256 threads, thread i takes d = i, i+256, ... with fused multiply-adds, then a halving tree
+constexpr int kGradWeightsThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kGradWeightsThreads)
+moe_combine_bwd_grad_weights_kernel(const T *__restrict__ grad_output, const T *__restrict__ buffer,
+                                    const int *__restrict__ expert_indices, const int *__restrict__ dispatch_map,
+                                    const int *__restrict__ expert_offsets, T *__restrict__ grad_weights, int dim,
+                                    int top_k)
+{
+  const int64_t a = blockIdx.x;
+  const int e = expert_indices[a];
+  const int pos = dispatch_map[a];
+  float partial = 0.0f;
+  if (e >= 0 && pos >= 0)
+  {
+    const T *src = buffer + (static_cast<int64_t>(expert_offsets[e]) + pos) * dim;
+    const T *g = grad_output + (a / top_k) * dim;
+    for (int d = threadIdx.x; d < dim; d += kGradWeightsThreads)
+    {
+      partial = fmaf(to_f<T>(g[d]), to_f<T>(src[d]), partial);
+    }
+  }
+  __shared__ float sdata[kGradWeightsThreads];
+  sdata[threadIdx.x] = partial;
+  __syncthreads();
+  for (int stride = kGradWeightsThreads / 2; stride > 0; stride >>= 1)
+  {
+    if (threadIdx.x < stride)
+    {
+      sdata[threadIdx.x] = __fadd_rn(sdata[threadIdx.x], sdata[threadIdx.x + stride]);
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0)
+  {
+    grad_weights[a] = from_f<T>(sdata[0]);
+  }
+}
+
+// grad_input[t,d] = sum over k (in order) of grad_buffer[slot(t,k), d]
+template <typename T>
+__global__ void moe_dispatch_bwd_kernel(const T *__restrict__ grad_buffer, const int *__restrict__ expert_indices,
+                                        const int *__restrict__ dispatch_map,
+                                        const int *__restrict__ expert_offsets, T *__restrict__ grad_input,
+                                        int num_tokens, int dim, int top_k, int vec_ok)
+{
+  constexpr int N = Vec16<T>::N;
+  const int step = vec_ok ? N : 1;
+  const int dim_steps = dim / step;
+  const int64_t total = static_cast<int64_t>(num_tokens) * dim_steps;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    const int token = static_cast<int>(i / dim_steps);
+    const int d = static_cast<int>(i % dim_steps) * step;
+    float sum[N];
+#pragma unroll
+    for (int j = 0; j < N; ++j)
+    {
+      sum[j] = 0.0f;
+    }
+    for (int k = 0; k < top_k; ++k)
+    {
+      const int e = expert_indices[token * top_k + k];
+      const int pos = dispatch_map[token * top_k + k];
+      if (e >= 0 && pos >= 0)
+      {
+        const T *src = grad_buffer + (static_cast<int64_t>(expert_offsets[e]) + pos) * dim + d;
+        if (vec_ok)
+        {
+          float v[N];
+          load_vec<T>(src, v);
+#pragma unroll
+          for (int j = 0; j < N; ++j)
+          {
+            sum[j] = __fadd_rn(sum[j], v[j]);
+          }
+        }
+        else
+        {
+          sum[0] = __fadd_rn(sum[0], to_f<T>(src[0]));
+        }
+      }
+    }
+    T *dst = grad_input + static_cast<int64_t>(token) * dim + d;
+    if (vec_ok)
+    {
+      store_vec<T>(dst, sum);
+    }
+    else
+    {
+      dst[0] = from_f<T>(sum[0]);
+    }
+  }
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int ew_grid(int64_t n)
@@ -599,6 +747,64 @@ int launch_moe_combine(const void *buffer, int dtype, const int *expert_indices,
                   : moe_combine_kernel<T><<<ew_grid(total), 256, 0, s>>>(
                         static_cast<const T *>(buffer), expert_indices, static_cast<const T *>(expert_weights),
                         dispatch_map, expert_offsets, static_cast<T *>(output), num_tokens, dim, top_k)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_combine_bwd_grad_expert(const void *grad_output, int dtype, const int *expert_indices,
+                                       const void *expert_weights, const int *dispatch_map, const int *expert_offsets,
+                                       void *grad_buffer, int num_tokens, int dim, int top_k, cudaStream_t s)
+{
+  const int64_t assignments = static_cast<int64_t>(num_tokens) * top_k;
+  if (assignments <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const int64_t threads = assignments * 32;
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  const bool al = aligned16(grad_output) && aligned16(grad_buffer);
+  CAIFQ_DISPATCH_FLOAT(dtype, (moe_combine_bwd_grad_expert_kernel<T><<<grid, 256, 0, s>>>(
+                                  static_cast<const T *>(grad_output), expert_indices,
+                                  static_cast<const T *>(expert_weights), dispatch_map, expert_offsets,
+                                  static_cast<T *>(grad_buffer), assignments, dim, top_k,
+                                  (al && (dim % Vec16<T>::N) == 0) ? 1 : 0)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_combine_bwd_grad_weights(const void *grad_output, const void *buffer, int dtype,
+                                        const int *expert_indices, const int *dispatch_map,
+                                        const int *expert_offsets, void *grad_weights, int num_tokens, int dim,
+                                        int top_k, cudaStream_t s)
+{
+  const int64_t assignments = static_cast<int64_t>(num_tokens) * top_k;
+  if (assignments <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (moe_combine_bwd_grad_weights_kernel<T>
+                               <<<static_cast<unsigned>(assignments), kGradWeightsThreads, 0, s>>>(
+                                   static_cast<const T *>(grad_output), static_cast<const T *>(buffer),
+                                   expert_indices, dispatch_map, expert_offsets, static_cast<T *>(grad_weights), dim,
+                                   top_k)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_dispatch_bwd(const void *grad_buffer, int dtype, const int *expert_indices, const int *dispatch_map,
+                            const int *expert_offsets, void *grad_input, int num_tokens, int dim, int top_k,
+                            cudaStream_t s)
+{
+  const int64_t total = static_cast<int64_t>(num_tokens) * dim;
+  if (total <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const bool al = aligned16(grad_buffer) && aligned16(grad_input);
+  CAIFQ_DISPATCH_FLOAT(dtype, (moe_dispatch_bwd_kernel<T><<<ew_grid(total / 4), 256, 0, s>>>(
+                                  static_cast<const T *>(grad_buffer), expert_indices, dispatch_map, expert_offsets,
+                                  static_cast<T *>(grad_input), num_tokens, dim, top_k,
+                                  (al && (dim % Vec16<T>::N) == 0) ? 1 : 0)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

@@ -83,6 +83,9 @@ _SIGNATURES = {
     "caifq_moe_build_dispatch": (ctypes.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "caifq_moe_dispatch": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_combine": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_combine_bwd_grad_expert": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_combine_bwd_grad_weights": (ctypes.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_dispatch_bwd": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_grouped_expert_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
                                                 ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp, _vp,
                                                 _vp, _vp, _i32, _i32, _vp]),
@@ -383,6 +386,41 @@ def moe_combine(buf, expert_indices, weights, dispatch_map, expert_offsets, num_
                                    _ptr(dispatch_map), _ptr(expert_offsets), _ptr(out), num_tokens, dim, top_k,
                                    _stream()), "moe_combine")
     return out
+
+
+def moe_combine_bwd_grad_expert(grad_output, expert_indices, weights, dispatch_map, expert_offsets, total_assigned):
+    _need_cuda(grad_output, expert_indices, weights, dispatch_map, expert_offsets)
+    tokens, dim = grad_output.shape
+    top_k = expert_indices.shape[1]
+    gbuf = torch.zeros((total_assigned, dim), dtype=grad_output.dtype, device=grad_output.device)
+    _check(lib().caifq_moe_combine_bwd_grad_expert(_ptr(grad_output), dtype_code(grad_output), _ptr(expert_indices),
+                                                   _ptr(weights), _ptr(dispatch_map), _ptr(expert_offsets),
+                                                   _ptr(gbuf), tokens, dim, top_k, _stream()),
+           "moe_combine_bwd_grad_expert")
+    return gbuf
+
+
+def moe_combine_bwd_grad_weights(grad_output, buf, expert_indices, dispatch_map, expert_offsets):
+    _need_cuda(grad_output, buf, expert_indices, dispatch_map, expert_offsets)
+    tokens, dim = grad_output.shape
+    top_k = expert_indices.shape[1]
+    gw = torch.empty((tokens, top_k), dtype=grad_output.dtype, device=grad_output.device)
+    _check(lib().caifq_moe_combine_bwd_grad_weights(_ptr(grad_output), _ptr(buf), dtype_code(grad_output),
+                                                    _ptr(expert_indices), _ptr(dispatch_map), _ptr(expert_offsets),
+                                                    _ptr(gw), tokens, dim, top_k, _stream()),
+           "moe_combine_bwd_grad_weights")
+    return gw
+
+
+def moe_dispatch_bwd(grad_buf, expert_indices, dispatch_map, expert_offsets, num_tokens):
+    _need_cuda(grad_buf, expert_indices, dispatch_map, expert_offsets)
+    dim = grad_buf.shape[1]
+    top_k = expert_indices.shape[1]
+    gin = torch.empty((num_tokens, dim), dtype=grad_buf.dtype, device=grad_buf.device)
+    _check(lib().caifq_moe_dispatch_bwd(_ptr(grad_buf), dtype_code(grad_buf), _ptr(expert_indices),
+                                        _ptr(dispatch_map), _ptr(expert_offsets), _ptr(gin), num_tokens, dim, top_k,
+                                        _stream()), "moe_dispatch_bwd")
+    return gin
 
 
 def _weight_array(ws):

@@ -260,6 +260,24 @@ CAIFQ_API int caifq_moe_combine(const void *expert_buffer, int32_t dtype, const 
                       const void *expert_weights, const int32_t *dispatch_map, const int32_t *expert_offsets,
                       void *output, int32_t num_tokens, int32_t dim, int32_t top_k, void *stream);
 
+/* launch_moe_combine_backward_grad_expert, src/caif_cuda_kernels_moe.cu:816-875:
+ * grad_expert_buffer[slot(t,k), :] = w[t,k] * grad_output[t, :] for every assigned (t,k);
+ * other rows of the buffer are left as they are. */
+CAIFQ_API int caifq_moe_combine_bwd_grad_expert(const void *grad_output, int32_t dtype, const int32_t *expert_indices,
+                      const void *expert_weights, const int32_t *dispatch_map, const int32_t *expert_offsets,
+                      void *grad_expert_buffer, int32_t num_tokens, int32_t dim, int32_t top_k, void *stream);
+/* launch_moe_combine_backward_grad_weights, src/caif_cuda_kernels_moe.cu:925-990:
+ * grad_weights[t,k] = <grad_output[t,:], expert_buffer[slot(t,k),:]> (0 for dropped picks), summed in
+ * the reference's order (256 strided partial sums, halving tree). */
+CAIFQ_API int caifq_moe_combine_bwd_grad_weights(const void *grad_output, const void *expert_buffer, int32_t dtype,
+                      const int32_t *expert_indices, const int32_t *dispatch_map, const int32_t *expert_offsets,
+                      void *grad_weights, int32_t num_tokens, int32_t dim, int32_t top_k, void *stream);
+/* launch_moe_dispatch_backward, src/caif_cuda_kernels_moe.cu:1040-1085:
+ * grad_input[t, :] = sum over k, in order, of grad_expert_buffer[slot(t,k), :]. */
+CAIFQ_API int caifq_moe_dispatch_bwd(const void *grad_expert_buffer, int32_t dtype, const int32_t *expert_indices,
+                      const int32_t *dispatch_map, const int32_t *expert_offsets, void *grad_input,
+                      int32_t num_tokens, int32_t dim, int32_t top_k, void *stream);
+
 /* ---- grouped frozen experts ---------------------------------------------- */
 
 /*

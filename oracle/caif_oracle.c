@@ -708,6 +708,100 @@ ORC_EXPORT void orc_moe_combine(const float *buffer, const int32_t *expert_indic
   }
 }
 
+/* Backward of the combine, packed-buffer gradient: src/caif_cuda_kernels_moe.cu:816-847.  */
+/* Every assigned slot gets w * g (one fp32 product, rounded to the storage dtype by the     */
+/* caller); unassigned slots of the buffer are not written.                                   */
+ORC_EXPORT void orc_moe_combine_bwd_grad_expert(const float *grad_output, const int32_t *expert_indices,
+                                                const float *weights, const int32_t *dispatch_map,
+                                                const int32_t *expert_offsets, int num_tokens, int dim, int top_k,
+                                                float *grad_buffer)
+{
+  for (int t = 0; t < num_tokens; ++t)
+  {
+    for (int k = 0; k < top_k; ++k)
+    {
+      const int32_t e = expert_indices[(int64_t)t * top_k + k];
+      const int32_t pos = dispatch_map[(int64_t)t * top_k + k];
+      if (e >= 0 && pos >= 0)
+      {
+        const float w = weights[(int64_t)t * top_k + k];
+        float *dst = grad_buffer + ((int64_t)expert_offsets[e] + pos) * dim;
+        for (int d = 0; d < dim; ++d)
+        {
+          dst[d] = w * grad_output[(int64_t)t * dim + d];
+        }
+      }
+    }
+  }
+}
+
+/* Backward of the combine, routing-weight gradient: src/caif_cuda_kernels_moe.cu:925-972.   */
+/* One 256-thread block per (token, k): thread i adds g*b for d = i, i+256, ... (the device    */
+/* compiler contracts the multiply-add to an FMA), then a halving tree over the 256 partials. */
+ORC_EXPORT void orc_moe_combine_bwd_grad_weights(const float *grad_output, const float *buffer,
+                                                 const int32_t *expert_indices, const int32_t *dispatch_map,
+                                                 const int32_t *expert_offsets, int num_tokens, int dim, int top_k,
+                                                 float *grad_weights)
+{
+#pragma omp parallel for schedule(static)
+  for (int a = 0; a < num_tokens * top_k; ++a)
+  {
+    const int t = a / top_k;
+    const int32_t e = expert_indices[a];
+    const int32_t pos = dispatch_map[a];
+    float part[256];
+    for (int i = 0; i < 256; ++i)
+    {
+      part[i] = 0.0f;
+    }
+    if (e >= 0 && pos >= 0)
+    {
+      const float *src = buffer + ((int64_t)expert_offsets[e] + pos) * dim;
+      const float *g = grad_output + (int64_t)t * dim;
+      for (int i = 0; i < 256; ++i)
+      {
+        for (int d = i; d < dim; d += 256)
+        {
+          part[i] = fmaf(g[d], src[d], part[i]);
+        }
+      }
+    }
+    for (int stride = 128; stride > 0; stride >>= 1)
+    {
+      for (int i = 0; i < stride; ++i)
+      {
+        part[i] += part[i + stride];
+      }
+    }
+    grad_weights[a] = part[0];
+  }
+}
+
+/* Backward of the dispatch: src/caif_cuda_kernels_moe.cu:1040-1067.  fp32 sum over k in order. */
+ORC_EXPORT void orc_moe_dispatch_bwd(const float *grad_buffer, const int32_t *expert_indices,
+                                     const int32_t *dispatch_map, const int32_t *expert_offsets, int num_tokens,
+                                     int dim, int top_k, float *grad_input)
+{
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < num_tokens; ++t)
+  {
+    for (int d = 0; d < dim; ++d)
+    {
+      float sum = 0.0f;
+      for (int k = 0; k < top_k; ++k)
+      {
+        const int32_t e = expert_indices[(int64_t)t * top_k + k];
+        const int32_t pos = dispatch_map[(int64_t)t * top_k + k];
+        if (e >= 0 && pos >= 0)
+        {
+          sum += grad_buffer[((int64_t)expert_offsets[e] + pos) * dim + d];
+        }
+      }
+      grad_input[(int64_t)t * dim + d] = sum;
+    }
+  }
+}
+
 /* SiLU and its derivative: src/caif_cuda_kernels_activations.cu:513-514,558-561. */
 ORC_EXPORT void orc_silu(const float *x, int64_t n, float *y)
 {

@@ -354,3 +354,37 @@ def moe_combine(buf, expert_indices, weights, dispatch_map, expert_offsets, num_
                           _p(_c(dispatch_map, np.int32)), _p(_c(expert_offsets, np.int32)),
                           ctypes.c_int(num_tokens), ctypes.c_int(dim), ctypes.c_int(top_k), _p(out))
     return out
+
+
+def moe_combine_bwd_grad_expert(grad_output, expert_indices, weights, dispatch_map, expert_offsets, total):
+    """fp32 values of the packed-buffer gradient (unassigned slots stay zero); round to storage outside."""
+    g = _c(grad_output, np.float32)
+    tokens, dim = g.shape
+    top_k = expert_indices.shape[1]
+    out = np.zeros((total, dim), np.float32)
+    lib().orc_moe_combine_bwd_grad_expert(_p(g), _p(_c(expert_indices, np.int32)), _p(_c(weights, np.float32)),
+                                          _p(_c(dispatch_map, np.int32)), _p(_c(expert_offsets, np.int32)),
+                                          ctypes.c_int(tokens), ctypes.c_int(dim), ctypes.c_int(top_k), _p(out))
+    return out
+
+
+def moe_combine_bwd_grad_weights(grad_output, buf, expert_indices, dispatch_map, expert_offsets):
+    g = _c(grad_output, np.float32)
+    tokens, dim = g.shape
+    top_k = expert_indices.shape[1]
+    out = np.empty((tokens, top_k), np.float32)
+    lib().orc_moe_combine_bwd_grad_weights(_p(g), _p(_c(buf, np.float32)), _p(_c(expert_indices, np.int32)),
+                                           _p(_c(dispatch_map, np.int32)), _p(_c(expert_offsets, np.int32)),
+                                           ctypes.c_int(tokens), ctypes.c_int(dim), ctypes.c_int(top_k), _p(out))
+    return out
+
+
+def moe_dispatch_bwd(grad_buf, expert_indices, dispatch_map, expert_offsets, num_tokens):
+    gb = _c(grad_buf, np.float32)
+    dim = gb.shape[1]
+    top_k = expert_indices.shape[1]
+    out = np.empty((num_tokens, dim), np.float32)
+    lib().orc_moe_dispatch_bwd(_p(gb), _p(_c(expert_indices, np.int32)), _p(_c(dispatch_map, np.int32)),
+                               _p(_c(expert_offsets, np.int32)), ctypes.c_int(num_tokens), ctypes.c_int(dim),
+                               ctypes.c_int(top_k), _p(out))
+    return out

@@ -83,4 +83,30 @@ void ref_moe_combine_f32(const float *buffer, float *output, int num_tokens, int
                             dim, top_k, static_cast<cudaStream_t>(stream));
 }
 
+void ref_moe_combine_bwd_grad_expert_f32(const float *grad_output, float *grad_buffer, int num_tokens, int dim,
+                                         int top_k, const int *expert_indices, const float *expert_weights,
+                                         const int *dispatch_map, const int *expert_offsets, void *stream)
+{
+  launch_moe_combine_backward_grad_expert<float>(grad_output, expert_indices, expert_weights, dispatch_map,
+                                                 expert_offsets, grad_buffer, num_tokens, dim, top_k,
+                                                 static_cast<cudaStream_t>(stream));
+}
+
+void ref_moe_combine_bwd_grad_weights_f32(const float *grad_output, const float *buffer, float *grad_weights,
+                                          int num_tokens, int dim, int top_k, const int *expert_indices,
+                                          const int *dispatch_map, const int *expert_offsets, void *stream)
+{
+  launch_moe_combine_backward_grad_weights<float>(grad_output, buffer, expert_indices, dispatch_map, expert_offsets,
+                                                  grad_weights, num_tokens, dim, top_k,
+                                                  static_cast<cudaStream_t>(stream));
+}
+
+void ref_moe_dispatch_bwd_f32(const float *grad_buffer, float *grad_input, int num_tokens, int dim, int top_k,
+                              const int *expert_indices, const int *dispatch_map, const int *expert_offsets,
+                              void *stream)
+{
+  launch_moe_dispatch_backward<float>(grad_buffer, expert_indices, dispatch_map, expert_offsets, grad_input, num_tokens,
+                                      dim, top_k, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

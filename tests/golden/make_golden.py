@@ -90,6 +90,17 @@ def main(out_dir):
     np.savez_compressed(os.path.join(out_dir, "dispatch_68x6.npz"), kind="dispatch", num_experts=68, x=xs.numpy(),
                         indices=idx.cpu().numpy(), weights=norm.cpu().numpy(), buffer=buf.cpu().numpy(),
                         combined=comb.cpu().numpy())
+    # backward of the pair: packed-buffer gradient, routing-weight gradient, token gradient
+    go = randn(256, 32)
+    dmap_d, off_d = torch.from_numpy(dmap).to(dev), torch.from_numpy(off).to(dev)
+    gbuf = ref.moe_combine_bwd_grad_expert(go.to(dev), idx_d, norm.contiguous(), dmap_d, off_d, total)
+    gw = ref.moe_combine_bwd_grad_weights(go.to(dev), buf, idx_d, dmap_d, off_d)
+    gin = ref.moe_dispatch_bwd(gbuf, idx_d, dmap_d, off_d, 256)
+    torch.cuda.synchronize()
+    np.savez_compressed(os.path.join(out_dir, "dispatch_backward_68x6.npz"), kind="dispatch_backward",
+                        num_experts=68, indices=idx.cpu().numpy(), weights=norm.cpu().numpy(),
+                        buffer=buf.cpu().numpy(), grad_output=go.numpy(), grad_buffer=gbuf.cpu().numpy(),
+                        grad_weights=gw.cpu().numpy(), grad_input=gin.cpu().numpy())
     print("wrote", sorted(os.listdir(out_dir)))
 
 

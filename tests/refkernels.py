@@ -103,3 +103,27 @@ def moe_combine(buf, idx, weights, dmap, off, tokens):
     lib().ref_moe_combine_f32(_p(buf), _p(out), ctypes.c_int(tokens), ctypes.c_int(dim), ctypes.c_int(idx.shape[1]),
                               _p(idx), _p(weights), _p(dmap), _p(off), _s())
     return out
+
+
+def moe_combine_bwd_grad_expert(grad_out, idx, weights, dmap, off, total):
+    tokens, dim = grad_out.shape
+    gbuf = torch.zeros((total, dim), dtype=torch.float32, device=grad_out.device)
+    lib().ref_moe_combine_bwd_grad_expert_f32(_p(grad_out), _p(gbuf), ctypes.c_int(tokens), ctypes.c_int(dim),
+                                              ctypes.c_int(idx.shape[1]), _p(idx), _p(weights), _p(dmap), _p(off), _s())
+    return gbuf
+
+
+def moe_combine_bwd_grad_weights(grad_out, buf, idx, dmap, off):
+    tokens, dim = grad_out.shape
+    gw = torch.empty((tokens, idx.shape[1]), dtype=torch.float32, device=grad_out.device)
+    lib().ref_moe_combine_bwd_grad_weights_f32(_p(grad_out), _p(buf), _p(gw), ctypes.c_int(tokens), ctypes.c_int(dim),
+                                               ctypes.c_int(idx.shape[1]), _p(idx), _p(dmap), _p(off), _s())
+    return gw
+
+
+def moe_dispatch_bwd(gbuf, idx, dmap, off, tokens):
+    dim = gbuf.shape[1]
+    gin = torch.empty((tokens, dim), dtype=torch.float32, device=gbuf.device)
+    lib().ref_moe_dispatch_bwd_f32(_p(gbuf), _p(gin), ctypes.c_int(tokens), ctypes.c_int(dim),
+                                   ctypes.c_int(idx.shape[1]), _p(idx), _p(dmap), _p(off), _s())
+    return gin

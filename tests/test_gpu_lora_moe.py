@@ -137,6 +137,41 @@ def test_dispatch_and_combine(dtype):
         assert torch.equal(ref.moe_combine(buf, d_idx, to_dev(w_np), d_map, d_off, tokens), out)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim", [96, 2048, 37])
+def test_combine_and_dispatch_backward(dtype, dim):
+    """The three backward kernels of the dispatch/combine pair, bit for bit against the oracle
+    (and the reference's kernels in fp32), with a capacity that drops some picks."""
+    rng = np.random.default_rng(23 + dim)
+    tokens, top_k, experts = 300, 6, 68
+    code = orc.F32 if dtype == torch.float32 else orc.BF16
+    g_np, g = act(rng, tokens, dim, code)
+    probs = rng.random((tokens, experts)).astype(np.float32)
+    idx, val = orc.topk(probs, top_k)
+    w_np = orc.round_through(orc.normalize_rows(val), code)
+    dmap, off, total = orc.build_dispatch_map(idx, experts, capacity=30)
+    buf_np = orc.round_through(rng.standard_normal((total, dim)).astype(np.float32), code)
+    d_idx, d_map, d_off = to_dev(idx), to_dev(dmap), to_dev(off)
+    w, buf = to_dev(w_np, dtype), to_dev(buf_np, dtype)
+
+    gbuf = nv.moe_combine_bwd_grad_expert(g, d_idx, w, d_map, d_off, total)
+    want = orc.round_through(orc.moe_combine_bwd_grad_expert(g_np, idx, w_np, dmap, off, total), code)
+    assert np.array_equal(gbuf.float().cpu().numpy(), want)
+
+    gw = nv.moe_combine_bwd_grad_weights(g, buf, d_idx, d_map, d_off)
+    want_gw = orc.round_through(orc.moe_combine_bwd_grad_weights(g_np, buf_np, idx, dmap, off), code)
+    assert np.array_equal(gw.float().cpu().numpy(), want_gw)
+
+    gin = nv.moe_dispatch_bwd(gbuf, d_idx, d_map, d_off, tokens)
+    want_gin = orc.round_through(orc.moe_dispatch_bwd(want, idx, dmap, off, tokens), code)
+    assert np.array_equal(gin.float().cpu().numpy(), want_gin)
+
+    if dtype == torch.float32 and ref.available():
+        assert torch.equal(ref.moe_combine_bwd_grad_expert(g, d_idx, w, d_map, d_off, total), gbuf)
+        assert torch.equal(ref.moe_combine_bwd_grad_weights(g, buf, d_idx, d_map, d_off), gw)
+        assert torch.equal(ref.moe_dispatch_bwd(gbuf, d_idx, d_map, d_off, tokens), gin)
+
+
 # ------------------------------------------------------------ grouped experts
 @pytest.mark.parametrize("storage,sd,compute", [(orc.I4, orc.BF16, orc.BF16), (orc.I8, orc.F32, orc.F32),
                                                 (orc.I4, orc.F32, orc.F32)])

@@ -309,5 +309,35 @@ def test_oracle_reproduces_reference_golden_vectors(path):
         assert np.array_equal(buf.view(np.uint32), g["buffer"].view(np.uint32))
         out = orc.moe_combine(buf, idx, g["weights"], dmap, off, g["x"].shape[0])
         assert np.array_equal(out.view(np.uint32), g["combined"].view(np.uint32))
+    elif kind == "dispatch_backward":
+        idx = g["indices"]
+        dmap, off, total = orc.build_dispatch_map(idx, int(g["num_experts"]))
+        gbuf = orc.moe_combine_bwd_grad_expert(g["grad_output"], idx, g["weights"], dmap, off, total)
+        assert np.array_equal(gbuf.view(np.uint32), g["grad_buffer"].view(np.uint32))
+        gw = orc.moe_combine_bwd_grad_weights(g["grad_output"], g["buffer"], idx, dmap, off)
+        assert np.array_equal(gw.view(np.uint32), g["grad_weights"].view(np.uint32))
+        gin = orc.moe_dispatch_bwd(gbuf, idx, dmap, off, g["grad_output"].shape[0])
+        assert np.array_equal(gin.view(np.uint32), g["grad_input"].view(np.uint32))
     else:
         raise AssertionError("unknown fixture kind %s" % kind)
+
+
+def test_dispatch_backward_is_the_adjoint_of_dispatch_and_combine():
+    """<combine(B), G> = <B, combine_bwd_expert(G)> and <dispatch(X), GB> = <X, dispatch_bwd(GB)> in
+    exact integer arithmetic (small integers keep every fp32 sum exact); the routing-weight gradient
+    of an all-ones buffer is the row sum of G."""
+    rng = np.random.default_rng(5)
+    tokens, dim, top_k, experts = 40, 24, 3, 7
+    idx = np.stack([rng.permutation(experts)[:top_k] for _ in range(tokens)]).astype(np.int32)
+    dmap, off, total = orc.build_dispatch_map(idx, experts, capacity=12)
+    w = rng.integers(-3, 4, (tokens, top_k)).astype(np.float32)
+    b = rng.integers(-4, 5, (total, dim)).astype(np.float32)
+    g = rng.integers(-4, 5, (tokens, dim)).astype(np.float32)
+    x = rng.integers(-4, 5, (tokens, dim)).astype(np.float32)
+    gb = orc.moe_combine_bwd_grad_expert(g, idx, w, dmap, off, total)
+    assert float((orc.moe_combine(b, idx, w, dmap, off, tokens) * g).sum()) == float((b * gb).sum())
+    assert float((orc.moe_dispatch(x, idx, dmap, off, total) * b).sum()) == \
+        float((x * orc.moe_dispatch_bwd(b, idx, dmap, off, tokens)).sum())
+    gw = orc.moe_combine_bwd_grad_weights(g, np.ones((total, dim), np.float32), idx, dmap, off)
+    want = np.where(dmap >= 0, g.sum(axis=1, keepdims=True), 0.0)
+    assert np.array_equal(gw, want.astype(np.float32))
