@@ -881,20 +881,48 @@ int caifq_grouped_expert_fwd(const caifq_weight *gate, const caifq_weight *up, c
   const size_t es = dtype_bytes(dtype);
   const int64_t in_dim = up[0].in_dim;
   const int64_t hid = up[0].out_dim;
-  int r = grouped_linear(up, num_experts, expert_offsets_host, false, x, up_out, dtype, false, compute_dtype, s, who);
-  if (r == CAIFQ_OK)
+  int r = CAIFQ_OK;
+  GroupedSwigluArgs fused{};
+  fused.gate = gate;
+  fused.up = up;
+  fused.num_experts = num_experts;
+  fused.offsets = expert_offsets_host;
+  fused.x = x;
+  fused.gate_out = gate_out;
+  fused.up_out = up_out;
+  fused.hidden = hidden_ws;
+  fused.dtype = dtype;
+  fused.compute_dtype = compute_dtype;
+  static const bool fuse_swiglu = []() {
+    const char *e = std::getenv("CAIFQ_FUSED_SWIGLU");   // "0": separate gate, up and SwiGLU launches
+    return e == nullptr || e[0] != '0';
+  }();
+  if (fuse_swiglu && forced_path() == Force::None && umma_swiglu_supported(fused))
   {
-    r = grouped_linear(gate, num_experts, expert_offsets_host, false, x, gate_out, dtype, false, compute_dtype, s,
-                       who);
+    // gate, up and the SwiGLU in one pass over the packed rows
+    r = launch_linear_umma_swiglu(fused, s);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
   }
-  if (r != CAIFQ_OK)
+  else
   {
-    return r;
-  }
-  r = launch_swiglu_fwd(gate_out, up_out, hidden_ws, dtype, total * hid, s);
-  if (r != CAIFQ_OK)
-  {
-    return r;
+    r = grouped_linear(up, num_experts, expert_offsets_host, false, x, up_out, dtype, false, compute_dtype, s, who);
+    if (r == CAIFQ_OK)
+    {
+      r = grouped_linear(gate, num_experts, expert_offsets_host, false, x, gate_out, dtype, false, compute_dtype, s,
+                         who);
+    }
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+    r = launch_swiglu_fwd(gate_out, up_out, hidden_ws, dtype, total * hid, s);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
   }
   return grouped_linear(down, num_experts, expert_offsets_host, false, hidden_ws, out, dtype, false, compute_dtype, s,
                         who);

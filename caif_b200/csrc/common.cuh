@@ -228,6 +228,24 @@ struct GroupedLinearArgs
   bool accumulate;
   int compute_dtype;
 };
+// gate(x), up(x) and silu(gate(x)) * up(x) of a run of frozen experts in one launch
+// (CAIF_DeviceMoEFrozenExpert::ForwardImpl up to the down projection,
+// src/caif_device_moe_frozen_expert.cpp:104-153).
+struct GroupedSwigluArgs
+{
+  const caifq_weight *gate;
+  const caifq_weight *up;
+  int num_experts;
+  const int32_t *offsets;
+  const void *x;
+  void *gate_out;
+  void *up_out;
+  void *hidden;
+  int dtype;
+  int compute_dtype;
+};
+bool umma_swiglu_supported(const GroupedSwigluArgs &args);
+int launch_linear_umma_swiglu(const GroupedSwigluArgs &args, cudaStream_t s);
 bool umma_grouped_supported(const GroupedLinearArgs &args);
 int launch_linear_umma_grouped(const GroupedLinearArgs &args, cudaStream_t s);
 bool decode_supported(const LinearArgs &args);

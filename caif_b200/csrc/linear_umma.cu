@@ -298,12 +298,21 @@ struct UmmaParams
   int num_m_tiles;
   int num_n_tiles;
   const uint8_t *lora_rhs;  // null = no LoRA k-block
+  // Fused gate/up/SwiGLU forward of a frozen expert (forward, 128-wide tiles, 16-bit outputs): a tile's
+  // columns 0..63 are features [64 j, 64 j + 64) of the gate projection, columns 64..127 the same
+  // features of the up projection.  c receives gate(x), c_up up(x), c_hidden silu(gate(x)) * up(x),
+  // each rounded to the storage dtype the way the separate kernels round them.
+  int swiglu;
+  const uint8_t *codes_up;
+  const void *scales_up;
+  void *c_up;
+  void *c_hidden;
 };
 
 // Grouped mode: one launch covers the same product for a run of experts whose activation rows lie
 // back to back in one packed buffer (rows offsets[e] .. offsets[e+1] belong to expert e).  The table
 // travels as a kernel parameter, so nothing is read back from or copied to the device to schedule it.
-constexpr int MAX_GROUPS = 128;
+constexpr int MAX_GROUPS = 80;   // the table must fit the 4 KB of kernel parameters
 
 struct GroupTable
 {
@@ -311,6 +320,8 @@ struct GroupTable
   int32_t mtile_start[MAX_GROUPS + 1];  // running count of 256-row tiles
   const uint8_t *codes[MAX_GROUPS];
   const void *scales[MAX_GROUPS];
+  const uint8_t *codes_up[MAX_GROUPS];   // fused gate/up mode only
+  const void *scales_up[MAX_GROUPS];
   int32_t num_groups;
 };
 
@@ -338,6 +349,8 @@ struct TileWork
   int64_t row_end;   // rows at or beyond this one belong to somebody else
   const uint8_t *codes;
   const void *scales;
+  const uint8_t *codes_up;
+  const void *scales_up;
 };
 
 template <bool GROUPED>
@@ -352,6 +365,8 @@ __device__ __forceinline__ TileWork locate_tile<false>(int tile, const UmmaParam
   t.row_end = p.m;
   t.codes = p.codes;
   t.scales = p.scales;
+  t.codes_up = p.codes_up;
+  t.scales_up = p.scales_up;
   return t;
 }
 
@@ -379,6 +394,8 @@ __device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams
   t.row_end = gt.offsets[lo + 1];
   t.codes = gt.codes[lo];
   t.scales = gt.scales[lo];
+  t.codes_up = gt.codes_up[lo];
+  t.scales_up = gt.scales_up[lo];
   return t;
 }
 
@@ -572,6 +589,65 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       mbar_wait(acc_full(acc), acc_par);
       tc_fence_after();
+      if (!BWD && BN == 128 && p.swiglu)
+      {
+        float up_scale = 1.0f;
+        if (WMODE == W_I8 && tw.scales_up != nullptr)
+        {
+          up_scale = __ldg(static_cast<const float *>(tw.scales_up));
+        }
+        const int hid = p.n_total / 2;   // features per projection
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+        {
+          const int64_t row = tw.row0 + mt * BM_SUB + quarter * 32 + lane;
+#pragma unroll
+          for (int cb = 0; cb < 2; ++cb)
+          {
+            uint32_t rg[32];
+            uint32_t ru[32];
+            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   static_cast<uint32_t>((acc * MT + mt) * BN);
+            tmem_ld32(tbase + cb * 32, rg);
+            tmem_ld32(tbase + 64 + cb * 32, ru);
+            tmem_ld_wait();
+            if (row < tw.row_end)
+            {
+              const int64_t off = row * hid + static_cast<int64_t>(n_tile) * 64 + cb * 32;
+              uint4 *dg = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c) + off);
+              uint4 *du = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c_up) + off);
+              uint4 *dh = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c_hidden) + off);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+              {
+                uint32_t pg[4], pu[4], ph[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                {
+                  float g2[2], u2[2], h2[2];
+#pragma unroll
+                  for (int z = 0; z < 2; ++z)
+                  {
+                    // the separate kernels' roundings: projection outputs to the storage dtype,
+                    // silu(gate) to the storage dtype, then the product
+                    g2[z] = round_through<CAIFQ_BF16>(__uint_as_float(rg[8 * q + 2 * e + z]) * out_scale);
+                    u2[z] = round_through<CAIFQ_BF16>(__uint_as_float(ru[8 * q + 2 * e + z]) * up_scale);
+                    const float act = round_through<CAIFQ_BF16>(g2[z] / (1.0f + expf(-g2[z])));
+                    h2[z] = act * u2[z];
+                  }
+                  pg[e] = pack_bf16x2(g2[0], g2[1]);
+                  pu[e] = pack_bf16x2(u2[0], u2[1]);
+                  ph[e] = pack_bf16x2(h2[0], h2[1]);
+                }
+                dg[q] = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                du[q] = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+                dh[q] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+              }
+            }
+          }
+        }
+      }
+      else
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
       {
@@ -732,14 +808,26 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         for (int i = 0; i < PER_THREAD; ++i)
         {
           // element coordinates of the chunk's first code in the [out, in] matrix
-          const int64_t o = BWD ? (k0 + c_row[i]) : (n0 + c_row[i]);
+          int64_t o = BWD ? (k0 + c_row[i]) : (n0 + c_row[i]);
+          const uint8_t *codes = tw.codes;
+          const void *scales = tw.scales;
+          if (!BWD && p.swiglu)
+          {
+            // tile rows 0..63: gate features 64 j + r; rows 64..127: up features 64 j + r - 64
+            o = static_cast<int64_t>(n_tile) * 64 + (c_row[i] & 63);
+            if (c_row[i] >= 64)
+            {
+              codes = tw.codes_up;
+              scales = tw.scales_up;
+            }
+          }
           const int64_t ii = BWD ? (n0 + c_part[i] * ELEMS) : (k0 + c_part[i] * ELEMS);
           const int64_t flat = o * p.in_dim + ii;
-          const uint8_t *src = tw.codes + ((WMODE == W_I8) ? flat : (flat >> 1));
+          const uint8_t *src = codes + ((WMODE == W_I8) ? flat : (flat >> 1));
           raw[i] = __ldg(reinterpret_cast<const uint4 *>(src));
           if (WMODE == W_I4)
           {
-            sc[i] = __half2float(static_cast<const __half *>(tw.scales)[flat / p.group_size]);
+            sc[i] = __half2float(static_cast<const __half *>(scales)[flat / p.group_size]);
           }
           else
           {
@@ -1207,6 +1295,107 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     CAIFQ_UMMA_GROUP_CASE(W_I8)
     CAIFQ_UMMA_GROUP_CASE(W_I4)
 #undef CAIFQ_UMMA_GROUP_CASE
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+  }
+  return CAIFQ_OK;
+}
+
+// ------------------------------------------------------------------ fused gate / up / SwiGLU
+bool umma_swiglu_supported(const GroupedSwigluArgs &g)
+{
+  if (g.num_experts < 1 || g.gate == nullptr || g.up == nullptr || g.offsets == nullptr || g.dtype != CAIFQ_BF16)
+  {
+    return false;
+  }
+  GroupedLinearArgs probe{};
+  probe.weights = g.gate;
+  probe.num_experts = g.num_experts;
+  probe.offsets = g.offsets;
+  probe.backward = false;
+  probe.a = g.x;
+  probe.a_dtype = g.dtype;
+  probe.c = g.gate_out;
+  probe.c_dtype = g.dtype;
+  probe.accumulate = false;
+  probe.compute_dtype = g.compute_dtype;
+  if (!umma_grouped_supported(probe))
+  {
+    return false;
+  }
+  probe.weights = g.up;
+  probe.c = g.up_out;
+  if (!umma_grouped_supported(probe))
+  {
+    return false;
+  }
+  const caifq_weight &w0 = g.gate[0];
+  const caifq_weight &u0 = g.up[0];
+  if (u0.storage != w0.storage || u0.scheme != w0.scheme || u0.group_size != w0.group_size ||
+      u0.in_dim != w0.in_dim || u0.out_dim != w0.out_dim || (w0.out_dim % 64) != 0)
+  {
+    return false;
+  }
+  return (reinterpret_cast<uintptr_t>(g.hidden) & 15u) == 0 && (reinterpret_cast<uintptr_t>(g.up_out) & 15u) == 0;
+}
+
+int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
+{
+  const caifq_weight &w0 = g.gate[0];
+  const int64_t total_rows = g.offsets[g.num_experts];
+  UmmaParams p{};
+  p.c = g.gate_out;
+  p.c_up = g.up_out;
+  p.c_hidden = g.hidden;
+  p.c_dtype = g.dtype;
+  p.accumulate = 0;
+  p.m = total_rows;
+  p.n_total = 2 * w0.out_dim;   // gate and up features side by side in every tile
+  p.k_total = w0.in_dim;
+  p.in_dim = w0.in_dim;
+  p.group_size = w0.group_size;
+  p.swiglu = 1;
+  p.num_n_tiles = w0.out_dim / 64;
+  CUtensorMap map_a;
+  int rc = make_map_bf16(&map_a, g.x, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(total_rows), BM_SUB);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  const int mode = wmode_of(w0);
+  for (int first = 0; first < g.num_experts; first += MAX_GROUPS)
+  {
+    const int count = (g.num_experts - first < MAX_GROUPS) ? (g.num_experts - first) : MAX_GROUPS;
+    GroupTable gt{};
+    int tiles = 0;
+    for (int e = 0; e < count; ++e)
+    {
+      gt.offsets[e] = g.offsets[first + e];
+      gt.mtile_start[e] = tiles;
+      tiles += (g.offsets[first + e + 1] - g.offsets[first + e] + BM - 1) / BM;
+      gt.codes[e] = static_cast<const uint8_t *>(g.gate[first + e].codes);
+      gt.scales[e] = g.gate[first + e].scales;
+      gt.codes_up[e] = static_cast<const uint8_t *>(g.up[first + e].codes);
+      gt.scales_up[e] = g.up[first + e].scales;
+    }
+    gt.offsets[count] = g.offsets[first + count];
+    gt.mtile_start[count] = tiles;
+    gt.num_groups = count;
+    if (tiles == 0)
+    {
+      continue;
+    }
+    p.num_m_tiles = tiles;
+    if (mode == W_I8)
+    {
+      rc = launch_inst<W_I8, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+    }
+    else
+    {
+      rc = launch_inst<W_I4, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+    }
     if (rc != CAIFQ_OK)
     {
       return rc;
