@@ -381,14 +381,55 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
     if rank == 0 or world > 1:
         hx = {m: xs[m].cpu().pin_memory() for m in C2_MS}
         hy = {m: torch.empty(m, shard, dtype=torch.float32).pin_memory() for m in C2_MS}
-        dx = {m: torch.empty_like(xs[m]) for m in C2_MS}
+        # one device copy of x per launch, so that the copy-in of a launch can run while the launch before
+        # it still reads its own; copies ride two side streams (one per direction) beside the kernels
+        dx = {m: [torch.empty_like(xs[m]) for _ in range(C2_COPIES)] for m in C2_MS}
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_in = {m: [torch.cuda.Event() for _ in range(C2_COPIES)] for m in C2_MS}
+        ev_k = {m: [torch.cuda.Event() for _ in range(C2_COPIES)] for m in C2_MS}
 
-        def step_e2e():
+        def e2e_body():
+            main = torch.cuda.current_stream()
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
             for m in C2_MS:
                 for c, w in enumerate(weights):
-                    dx[m].copy_(hx[m], non_blocking=True)
-                    nv.linear_fwd(w, dx[m], compute=nv.F32, out=ys[c][m])
-                    hy[m].copy_(ys[c][m], non_blocking=True)
+                    with torch.cuda.stream(s_in):
+                        dx[m][c].copy_(hx[m], non_blocking=True)
+                        ev_in[m][c].record(s_in)
+                    main.wait_event(ev_in[m][c])
+                    nv.linear_fwd(w, dx[m][c], compute=nv.F32, out=ys[c][m])
+                    ev_k[m][c].record(main)
+                    s_out.wait_event(ev_k[m][c])
+                    with torch.cuda.stream(s_out):
+                        hy[m].copy_(ys[c][m], non_blocking=True)
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+
+        e2e_graph = None
+        if graphed:
+            # the same calls, copies included, recorded once and replayed: what a serving loop does
+            try:
+                warm = torch.cuda.Stream()
+                warm.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(warm):
+                    e2e_body()
+                torch.cuda.current_stream().wait_stream(warm)
+                torch.cuda.synchronize()
+                e2e_graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(e2e_graph):
+                    e2e_body()
+            except Exception as e:
+                if rank == 0:
+                    sys.stderr.write("graph capture of the end-to-end step unavailable (%s)\n" % e)
+                e2e_graph = None
+                torch.cuda.synchronize()
+
+        def step_e2e():
+            if e2e_graph is not None:
+                e2e_graph.replay()
+            else:
+                e2e_body()
             torch.cuda.synchronize()
 
         for _ in range(3):

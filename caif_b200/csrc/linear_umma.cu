@@ -77,6 +77,13 @@ constexpr int NUM_WARPS = 14;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int DEQ_WARP0 = 6;
 constexpr int DEQ_THREADS = 8 * 32;
+// Teams of dequant warps (see the dequantization role): two where it measured faster (int4 dX,
+// 128-wide tiles), one where the per-thread state of two k-blocks in flight crowds the registers
+// (int8 with 256-wide tiles) or did not pay (int4 forward with 256-wide tiles).
+__host__ __device__ constexpr int deq_teams(int wmode, bool bwd, int bn)
+{
+  return (bn == 256 && (wmode == 0 || !bwd)) ? 1 : 2;
+}
 constexpr uint32_t kSpinLimit = 1u << 26;
 
 template <int BN>
@@ -409,6 +416,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   constexpr int STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
   constexpr int STAGES = TileCfg<BN>::STAGES;
   constexpr int ACC_BUFS = TileCfg<BN>::ACC_BUFS;
+  constexpr int DEQ_TEAMS = deq_teams(WMODE, BWD, BN);
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[MAX_STAGES * 3 + 4];
   __shared__ uint32_t tmem_base_slot;
@@ -431,7 +439,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int s = 0; s < STAGES; ++s)
     {
       mbar_init(a_full(s), 1);
-      mbar_init(b_full(s), (WMODE == W_BF16) ? 1 : 8);
+      mbar_init(b_full(s), (WMODE == W_BF16) ? 1 : 8 / DEQ_TEAMS);
       mbar_init(empty(s), 1);
     }
     for (int a = 0; a < ACC_BUFS; ++a)
@@ -758,19 +766,23 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   else if (WMODE != W_BF16)
   {
     // ------------------------------------------------------ weight dequantization
-    const int d = threadIdx.x - DEQ_WARP0 * 32;  // 0..255
+    // The eight warps work as DEQ_TEAMS teams; team t converts the k-blocks whose number is t modulo
+    // DEQ_TEAMS, so with two teams a k-block's conversion (loads, ~150 instructions per thread, stores,
+    // proxy fence, barrier arrive) has two k-blocks of MMA time to finish in.
+    constexpr int TEAM_THREADS = DEQ_THREADS / DEQ_TEAMS;
+    const int team = (threadIdx.x - DEQ_WARP0 * 32) / TEAM_THREADS;
+    const int d = (threadIdx.x - DEQ_WARP0 * 32) % TEAM_THREADS;
     // 16-byte chunks of codes per k-block and thread, and where they go:
     //   forward  (K-major B): tile rows are n, a chunk is 16 B of one row's k range
     //   backward (MN-major B): tile rows are k, a chunk is 16 B of one k-row's n range
     constexpr int ELEMS = (WMODE == W_I8) ? 16 : 32;                 // codes per chunk
     constexpr int CHUNKS = (BN * BK) / ELEMS;                        // per k-block
-    constexpr int PER_THREAD = CHUNKS / DEQ_THREADS;                 // 2 (int8) or 1 (int4)
+    constexpr int PER_THREAD = CHUNKS / TEAM_THREADS;
     constexpr int CHUNKS_PER_ROW = (BWD ? BN : BK) / ELEMS;          // chunks along the contiguous direction
     static_assert(PER_THREAD >= 1, "tile too small for the dequant warps");
 
-    int s = 0;
-    uint32_t par = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+    uint32_t gkb0 = 0;   // k-blocks (of all tiles so far) before this tile: the ring position of its first one
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, gkb0 += static_cast<uint32_t>(num_kb_all))
     {
       const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
       const int n_tile = tw.n_tile;
@@ -781,7 +793,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
       for (int i = 0; i < PER_THREAD; ++i)
       {
-        const int c = d + i * DEQ_THREADS;
+        const int c = d + i * TEAM_THREADS;
         if (BWD)
         {
           // A chunk expands to 64 (int4) or 32 (int8) bytes of one 128-byte operand row, whose 16-byte
@@ -836,17 +848,25 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
       };
 
+      // this team's first k-block of the tile
+      const int kb_first = static_cast<int>((static_cast<uint32_t>(team) + DEQ_TEAMS - (gkb0 % DEQ_TEAMS)) % DEQ_TEAMS);
       uint4 raw[PER_THREAD];
       float sc[PER_THREAD];
-      load(0, raw, sc);
-      for (int kb = 0; kb < num_kb; ++kb)
+      if (kb_first < num_kb)
+      {
+        load(kb_first, raw, sc);
+      }
+      for (int kb = kb_first; kb < num_kb; kb += DEQ_TEAMS)
       {
         uint4 nraw[PER_THREAD];
         float nsc[PER_THREAD];
-        if (kb + 1 < num_kb)
+        if (kb + DEQ_TEAMS < num_kb)
         {
-          load(kb + 1, nraw, nsc);  // in flight while this block is converted
+          load(kb + DEQ_TEAMS, nraw, nsc);  // in flight while this block is converted
         }
+        const uint32_t gkb = gkb0 + static_cast<uint32_t>(kb);
+        const int s = static_cast<int>(gkb % STAGES);
+        const uint32_t par = (gkb / STAGES) & 1u;
         mbar_wait(empty(s), par ^ 1u);
         const uint32_t bbase = b_addr(s);
 #pragma unroll
@@ -911,21 +931,20 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           raw[i] = nraw[i];
           sc[i] = nsc[i];
         }
-        if (++s == STAGES)
-        {
-          s = 0;
-          par ^= 1u;
-        }
       }
-      if (p.lora_rhs != nullptr)
+      if (p.lora_rhs != nullptr && ((gkb0 + static_cast<uint32_t>(num_kb)) % DEQ_TEAMS) == static_cast<uint32_t>(team))
       {
-        // LoRA k-block: the padded factor is bf16 already; copy its tile into the operand layout
+        // LoRA k-block (number num_kb, so one team's): the padded factor is bf16 already; copy its
+        // tile into the operand layout
+        const uint32_t gkb = gkb0 + static_cast<uint32_t>(num_kb);
+        const int s = static_cast<int>(gkb % STAGES);
+        const uint32_t par = (gkb / STAGES) & 1u;
         mbar_wait(empty(s), par ^ 1u);
         const uint32_t bbase = b_addr(s);
 #pragma unroll
-        for (int i = 0; i < (BN * BK * 2 / 16) / DEQ_THREADS; ++i)
+        for (int i = 0; i < (BN * BK * 2 / 16) / TEAM_THREADS; ++i)
         {
-          const int c = d + i * DEQ_THREADS;  // 16-byte chunk of the 128 x 64 bf16 tile
+          const int c = d + i * TEAM_THREADS;  // 16-byte chunk of the BN x 64 bf16 tile
           uint32_t dst;
           const uint8_t *src;
           if (BWD)
@@ -952,11 +971,6 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (lane == 0)
         {
           mbar_arrive(b_full(s));
-        }
-        if (++s == STAGES)
-        {
-          s = 0;
-          par ^= 1u;
         }
       }
     }
