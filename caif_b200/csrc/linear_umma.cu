@@ -77,12 +77,11 @@ constexpr int NUM_WARPS = 14;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int DEQ_WARP0 = 6;
 constexpr int DEQ_THREADS = 8 * 32;
-// Teams of dequant warps (see the dequantization role): two where it measured faster (int4 dX,
-// 128-wide tiles), one where the per-thread state of two k-blocks in flight crowds the registers
-// (int8 with 256-wide tiles) or did not pay (int4 forward with 256-wide tiles).
+// Teams of dequant warps (see the dequantization role): two, except for int4 forward with 256-wide
+// tiles where one measured faster (a tile width int4 is not given by default).
 __host__ __device__ constexpr int deq_teams(int wmode, bool bwd, int bn)
 {
-  return (bn == 256 && (wmode == 0 || !bwd)) ? 1 : 2;
+  return (bn == 256 && wmode != 0 && !bwd) ? 1 : 2;
 }
 constexpr uint32_t kSpinLimit = 1u << 26;
 
@@ -850,9 +849,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
       // this team's first k-block of the tile
       const int kb_first = static_cast<int>((static_cast<uint32_t>(team) + DEQ_TEAMS - (gkb0 % DEQ_TEAMS)) % DEQ_TEAMS);
+      // With eight chunks per thread the next block's codes are not kept in flight beside the current
+      // ones (registers); the other team's block covers the load instead.
+      constexpr bool PREFETCH = PER_THREAD <= 4;
       uint4 raw[PER_THREAD];
       float sc[PER_THREAD];
-      if (kb_first < num_kb)
+      if (PREFETCH && kb_first < num_kb)
       {
         load(kb_first, raw, sc);
       }
@@ -860,7 +862,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       {
         uint4 nraw[PER_THREAD];
         float nsc[PER_THREAD];
-        if (kb + DEQ_TEAMS < num_kb)
+        if (!PREFETCH)
+        {
+          load(kb, raw, sc);
+        }
+        else if (kb + DEQ_TEAMS < num_kb)
         {
           load(kb + DEQ_TEAMS, nraw, nsc);  // in flight while this block is converted
         }
@@ -925,11 +931,14 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         {
           mbar_arrive(b_full(s));
         }
-#pragma unroll
-        for (int i = 0; i < PER_THREAD; ++i)
+        if (PREFETCH)
         {
-          raw[i] = nraw[i];
-          sc[i] = nsc[i];
+#pragma unroll
+          for (int i = 0; i < PER_THREAD; ++i)
+          {
+            raw[i] = nraw[i];
+            sc[i] = nsc[i];
+          }
         }
       }
       if (p.lora_rhs != nullptr && ((gkb0 + static_cast<uint32_t>(num_kb)) % DEQ_TEAMS) == static_cast<uint32_t>(team))
@@ -1140,7 +1149,10 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
   // 256-wide tiles feed the tensor core better per shared-memory byte; 128-wide ones keep a
   // second accumulator set so the epilogue overlaps the next tile.  CAIFQ_UMMA_BN overrides.
-  int bn = ((p.n_total % 256) == 0 && static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
+  // a single int4 layer measured faster with 128-wide tiles (the conversion per k-block is shorter
+  // and two accumulator sets overlap the epilogue)
+  int bn = (w.storage != CAIFQ_I4 && (p.n_total % 256) == 0 &&
+            static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
                ? 256
                : 128;
   if (const char *e = std::getenv("CAIFQ_UMMA_BN"))
@@ -1292,6 +1304,7 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
       continue;
     }
     p.num_m_tiles = tiles;
+    // (for the experts' shapes the wide tile measured 3 % faster with int4 too, unlike the square case)
     const int bn =
         ((p.n_total % 256) == 0 && static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma()) ? 256 : 128;
     p.num_n_tiles = p.n_total / bn;
