@@ -149,9 +149,9 @@ CAIFQ_API int caifq_linear_dx(const caifq_weight *w, const void *dy, int32_t dy_
                     int32_t compute_dtype, void *stream);
 
 /*
- * Column-parallel forward with the all-gather of Y fused into the kernel's stores: the design of
- * BASELINE's north_star for layers sharded by output features (the reference itself has no
- * multi-GPU linear; this replaces ForwardImpl followed by an NCCL all-gather of the slices).
+ * Column-parallel forward with the all-gather of Y fused into the kernel's stores, for layers
+ * sharded by output features over the GPUs of one box (the reference itself has no multi-GPU
+ * linear; this replaces ForwardImpl followed by an NCCL all-gather of the slices).
  * This rank holds rows [y_col0, y_col0 + w->out_dim) of a wider layer.  Every output element
  * y[t, y_col0 + j] is written into y_peers[r] for r = 0 .. num_peers-1 (row pitch y_ld elements):
  * this GPU's own result buffer and the peers' buffers mapped into this process (CUDA IPC or

@@ -22,7 +22,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "_build", "libcaif_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libcaif_ref_kernels.so")
-REFERENCE_ROOT = os.environ.get("CAIF_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: CAIF_REFERENCE_ROOT, else a "reference" directory beside this repository
+REFERENCE_ROOT = os.environ.get("CAIF_REFERENCE_ROOT",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 
 
 def _newer(target, sources):
