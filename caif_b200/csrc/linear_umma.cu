@@ -85,12 +85,13 @@ __host__ __device__ constexpr int deq_teams(int wmode, bool bwd, int bn)
 }
 constexpr uint32_t kSpinLimit = 1u << 26;
 
-template <int BN>
+template <int BN, int PLANES = 1>
 struct TileCfg
 {
-  static constexpr int B_STAGE_BYTES = BN * BK * 2;               // 16 or 32 KB
+  static constexpr int B_PLANE_BYTES = BN * BK * 2;               // 16 or 32 KB
+  static constexpr int B_STAGE_BYTES = B_PLANE_BYTES * PLANES;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = (BN == 128) ? 4 : 3;              // 192 KB of operands either way
+  static constexpr int STAGES = (BN == 128 && PLANES == 1) ? 4 : 3;   // 192 KB of operands in every case
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the base to 1024
   static constexpr int ACC_BUFS = TMEM_COLS / (MT * BN);          // 2 (epilogue overlaps the next tile) or 1
 };
@@ -99,8 +100,13 @@ enum WMode
 {
   W_I8 = 0,
   W_I4 = 1,
-  W_BF16 = 2
+  W_BF16 = 2,
+  // int4 for fp32 compute: scale * code (exact in fp32) goes to the tensor core as two bf16 terms,
+  // hi = bf16(w) and lo = bf16(w - hi), in two operand planes; hi + lo equals w to 2^-17 relative
+  W_I4S = 3
 };
+
+__host__ __device__ constexpr int planes_of(int wmode) { return wmode == W_I4S ? 2 : 1; }
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -289,6 +295,23 @@ __device__ __forceinline__ void int4x8_to_bf16(uint32_t w, float scale, uint32_t
   }
 }
 
+// the same eight codes as two bf16 terms of scale * code: hi = bf16(w), lo = bf16(w - hi)
+__device__ __forceinline__ void int4x8_to_bf16_split(uint32_t w, float scale, uint32_t (&hi)[4], uint32_t (&lo)[4])
+{
+  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;
+  const uint32_t od = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+  const float base = 8388616.0f;   // 2^23 + 8
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+  {
+    const float a = __fmul_rn(__uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base, scale);
+    const float b = __fmul_rn(__uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base, scale);
+    const uint32_t h = pack_bf16x2(a, b);
+    hi[j] = h;
+    lo[j] = pack_bf16x2(a - __uint_as_float(h << 16), b - __uint_as_float(h & 0xFFFF0000u));
+  }
+}
+
 struct UmmaParams
 {
   const uint8_t *codes;
@@ -411,10 +434,13 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    const __grid_constant__ CUtensorMap map_h, const UmmaParams p,
                    const __grid_constant__ typename GroupSel<GROUPED>::type gt)
 {
-  constexpr int B_STAGE_BYTES = TileCfg<BN>::B_STAGE_BYTES;
-  constexpr int STAGE_BYTES = TileCfg<BN>::STAGE_BYTES;
-  constexpr int STAGES = TileCfg<BN>::STAGES;
-  constexpr int ACC_BUFS = TileCfg<BN>::ACC_BUFS;
+  constexpr int PLANES = planes_of(WMODE);
+  constexpr bool IS_I4 = (WMODE == W_I4 || WMODE == W_I4S);
+  constexpr int B_PLANE_BYTES = TileCfg<BN, PLANES>::B_PLANE_BYTES;
+  constexpr int B_STAGE_BYTES = TileCfg<BN, PLANES>::B_STAGE_BYTES;
+  constexpr int STAGE_BYTES = TileCfg<BN, PLANES>::STAGE_BYTES;
+  constexpr int STAGES = TileCfg<BN, PLANES>::STAGES;
+  constexpr int ACC_BUFS = TileCfg<BN, PLANES>::ACC_BUFS;
   constexpr int DEQ_TEAMS = deq_teams(WMODE, BWD, BN);
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[MAX_STAGES * 3 + 4];
@@ -555,6 +581,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 const uint64_t adesc = adesc0 + static_cast<uint64_t>((mt * A_SUB_BYTES + k16 * (UMMA_K * 2)) >> 4);
                 const uint64_t bdesc = bdesc0 + static_cast<uint64_t>((BWD ? k16 * 2048 : k16 * (UMMA_K * 2)) >> 4);
                 umma_bf16(d0 + static_cast<uint32_t>(mt * BN), adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+                if (PLANES == 2 && kb < num_kb)
+                {
+                  // the low-order term of the weights (the LoRA k-block has one plane only)
+                  umma_bf16(d0 + static_cast<uint32_t>(mt * BN), adesc,
+                            bdesc + static_cast<uint64_t>(B_PLANE_BYTES >> 4), idesc, 1u);
+                }
               }
             }
             umma_commit(empty(s));
@@ -836,7 +868,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const int64_t flat = o * p.in_dim + ii;
           const uint8_t *src = codes + ((WMODE == W_I8) ? flat : (flat >> 1));
           raw[i] = __ldg(reinterpret_cast<const uint4 *>(src));
-          if (WMODE == W_I4)
+          if (IS_I4)
           {
             sc[i] = __half2float(static_cast<const __half *>(scales)[flat / p.group_size]);
           }
@@ -881,12 +913,29 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t words[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
           // bf16 output: ELEMS values = ELEMS/8 chunks of 16 bytes
           uint32_t outw[ELEMS / 2];
+          uint32_t outl[(WMODE == W_I4S) ? ELEMS / 2 : 1];   // low-order plane (split mode)
           if (WMODE == W_I8)
           {
 #pragma unroll
             for (int w = 0; w < 4; ++w)
             {
               int8x4_to_bf16(words[w], outw[2 * w], outw[2 * w + 1]);
+            }
+          }
+          else if (WMODE == W_I4S)
+          {
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+              uint32_t h4[4];
+              uint32_t l4[4];
+              int4x8_to_bf16_split(words[w], sc[i], h4, l4);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+              {
+                outw[4 * w + q] = h4[q];
+                outl[(WMODE == W_I4S) ? (4 * w + q) : 0] = l4[q];
+              }
             }
           }
           else
@@ -923,6 +972,14 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(outw[4 * j + 0]),
                          "r"(outw[4 * j + 1]), "r"(outw[4 * j + 2]), "r"(outw[4 * j + 3])
                          : "memory");
+            if (WMODE == W_I4S)
+            {
+              constexpr int L = (WMODE == W_I4S) ? 1 : 0;
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + static_cast<uint32_t>(B_PLANE_BYTES)),
+                           "r"(outl[L * (4 * j + 0)]), "r"(outl[L * (4 * j + 1)]), "r"(outl[L * (4 * j + 2)]),
+                           "r"(outl[L * (4 * j + 3)])
+                           : "memory");
+            }
           }
         }
         fence_proxy_async();
@@ -1061,7 +1118,7 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtens
                 const typename GroupSel<GROUPED>::type &gt, cudaStream_t s)
 {
   auto kernel = linear_umma_kernel<WMODE, BWD, BN, GROUPED>;
-  constexpr int SMEM_BYTES = TileCfg<BN>::SMEM_BYTES;
+  constexpr int SMEM_BYTES = TileCfg<BN, planes_of(WMODE)>::SMEM_BYTES;
   static bool configured = false;
   if (!configured)
   {
@@ -1075,7 +1132,7 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtens
   return CAIFQ_OK;
 }
 
-int wmode_of(const caifq_weight &w)
+int wmode_of(const caifq_weight &w, int compute_dtype)
 {
   if (w.storage == CAIFQ_I8)
   {
@@ -1083,7 +1140,7 @@ int wmode_of(const caifq_weight &w)
   }
   if (w.storage == CAIFQ_I4)
   {
-    return W_I4;
+    return (compute_dtype == CAIFQ_F32) ? W_I4S : W_I4;
   }
   return W_BF16;
 }
@@ -1118,8 +1175,9 @@ bool umma_supported(const LinearArgs &g)
       }
       return g.compute_dtype == CAIFQ_BF16 || g.compute_dtype == CAIFQ_F32;
     case CAIFQ_I4:
-      // scale*code is rounded to bf16: the reference's bf16 compute cell only
-      if (g.compute_dtype != CAIFQ_BF16 || w.scales == nullptr)
+      // bf16 compute: scale*code rounded once to bf16, the reference's value; fp32 compute: scale*code
+      // as two bf16 terms (2^-17 relative), within the fp32 tolerance
+      if ((g.compute_dtype != CAIFQ_BF16 && g.compute_dtype != CAIFQ_F32) || w.scales == nullptr)
       {
         return false;
       }
@@ -1163,6 +1221,10 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
       bn = v;
     }
   }
+  if (w.storage == CAIFQ_I4 && g.compute_dtype == CAIFQ_F32)
+  {
+    bn = 128;   // the two-plane mode has 128-wide tiles only
+  }
   p.num_n_tiles = p.n_total / bn;
 
   CUtensorMap map_a;
@@ -1172,7 +1234,7 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   {
     return rc;
   }
-  const int mode = wmode_of(w);
+  const int mode = wmode_of(w, g.compute_dtype);
   if (mode == W_BF16)
   {
     // the [out, in] weight itself: forward boxes are 64 k x 128 n rows, backward 64 n x 64 k rows
@@ -1217,6 +1279,11 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   CAIFQ_UMMA_CASE(W_I4)
   CAIFQ_UMMA_CASE(W_BF16)
 #undef CAIFQ_UMMA_CASE
+  if (mode == W_I4S)   // two operand planes: 128-wide tiles only
+  {
+    return g.backward ? launch_inst<W_I4S, true, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s)
+                      : launch_inst<W_I4S, false, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s);
+  }
   set_error("frozen linear (umma): unsupported weight storage %d", w.storage);
   return CAIFQ_ERR_UNSUPPORTED;
 }
@@ -1282,7 +1349,7 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
   {
     return rc;
   }
-  const int mode = wmode_of(w0);
+  const int mode = wmode_of(w0, g.compute_dtype);
   for (int first = 0; first < g.num_experts; first += MAX_GROUPS)
   {
     const int count = (g.num_experts - first < MAX_GROUPS) ? (g.num_experts - first) : MAX_GROUPS;
@@ -1305,8 +1372,10 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     }
     p.num_m_tiles = tiles;
     // (for the experts' shapes the wide tile measured 3 % faster with int4 too, unlike the square case)
-    const int bn =
-        ((p.n_total % 256) == 0 && static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma()) ? 256 : 128;
+    const int bn = (mode != W_I4S && (p.n_total % 256) == 0 &&
+                    static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma())
+                       ? 256
+                       : 128;
     p.num_n_tiles = p.n_total / bn;
 #define CAIFQ_UMMA_GROUP_CASE(MODE)                                                              \
   if (mode == MODE && bn == 128)                                                                 \
@@ -1322,6 +1391,11 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     CAIFQ_UMMA_GROUP_CASE(W_I8)
     CAIFQ_UMMA_GROUP_CASE(W_I4)
 #undef CAIFQ_UMMA_GROUP_CASE
+    if (mode == W_I4S)
+    {
+      rc = g.backward ? launch_inst<W_I4S, true, 128, true>(map_a, map_a, map_a, p, gt, s)
+                      : launch_inst<W_I4S, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+    }
     if (rc != CAIFQ_OK)
     {
       return rc;
@@ -1391,7 +1465,7 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
   {
     return rc;
   }
-  const int mode = wmode_of(w0);
+  const int mode = wmode_of(w0, g.compute_dtype);
   for (int first = 0; first < g.num_experts; first += MAX_GROUPS)
   {
     const int count = (g.num_experts - first < MAX_GROUPS) ? (g.num_experts - first) : MAX_GROUPS;
@@ -1418,6 +1492,10 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
     if (mode == W_I8)
     {
       rc = launch_inst<W_I8, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+    }
+    else if (mode == W_I4S)
+    {
+      rc = launch_inst<W_I4S, false, 128, true>(map_a, map_a, map_a, p, gt, s);
     }
     else
     {

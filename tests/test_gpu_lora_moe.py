@@ -206,6 +206,7 @@ def test_grouped_frozen_experts(storage, sd, compute):
 
 @pytest.mark.parametrize("storage,compute,experts,in_dim,hid,mean_rows", [
     (orc.I4, orc.BF16, 6, 2048, 1408, 300),    # the MoE config's expert shape, ragged row counts
+    (orc.I4, orc.F32, 3, 512, 640, 200),       # fp32 compute: two-term int4 operand
     (orc.I8, orc.F32, 4, 256, 512, 700),
     (orc.I4, orc.BF16, 131, 128, 128, 5),      # more experts than one launch's table holds
 ])
@@ -247,7 +248,7 @@ def test_grouped_frozen_experts_single_launch(storage, compute, experts, in_dim,
         assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
 
 
-@pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I4, orc.BF16)])
+@pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I4, orc.BF16), (orc.I4, orc.F32)])
 @pytest.mark.parametrize("m,in_dim,out_dim,rank", [(300, 512, 384, 16), (1024, 1024, 1024, 8), (130, 256, 640, 64)])
 def test_lora_fused_tensor_core_path(storage, compute, m, in_dim, out_dim, rank):
     """bf16 adapter on a quantized base with enough tokens: the LoRA products ride in the tensor-core
