@@ -1150,7 +1150,9 @@ int wmode_of(const caifq_weight &w, int compute_dtype)
 bool umma_supported(const LinearArgs &g)
 {
   const caifq_weight &w = g.w;
-  if (g.a_dtype != CAIFQ_BF16 || g.a_prescale != 1.0f || g.m < 32)
+  // (calls of up to 16 tokens are the few-token kernel's; from 17 on one 256-row tile, mostly
+  // zero rows, still beats the fp32-FMA kernel by far)
+  if (g.a_dtype != CAIFQ_BF16 || g.a_prescale != 1.0f || g.m < 17)
   {
     return false;
   }

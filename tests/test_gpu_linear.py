@@ -213,7 +213,8 @@ def _umma_case(storage, compute, m, in_dim, out_dim, seed, group=128):
     (orc.I4, orc.F32, TOL_F32),     # scale*code as two bf16 terms: holds the fp32 bound
     (orc.BF16, orc.F32, TOL_F32),
 ])
-@pytest.mark.parametrize("m,in_dim,out_dim", [(300, 512, 384), (256, 128, 128), (77, 1408, 2048), (1000, 2048, 1408)])
+@pytest.mark.parametrize("m,in_dim,out_dim", [(300, 512, 384), (256, 128, 128), (77, 1408, 2048), (1000, 2048, 1408),
+                                             (17, 256, 384)])
 def test_umma_forward_and_dx(storage, compute, tol, m, in_dim, out_dim):
     weight, wc, x_np, x, dy_np, dy = _umma_case(storage, compute, m, in_dim, out_dim, 500 + storage + m)
     y = nv.linear_fwd(weight, x, torch.float32, compute)
