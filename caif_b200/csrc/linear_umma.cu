@@ -388,9 +388,11 @@ __device__ __forceinline__ TileWork locate_tile(int tile, const UmmaParams &p, c
 template <>
 __device__ __forceinline__ TileWork locate_tile<false>(int tile, const UmmaParams &p, const NoGroupTable &)
 {
+  // column tiles fastest: the CTAs running at one time share a few row tiles of the activations
+  // (read from memory once) and sweep the weight, which stays in L2
   TileWork t;
-  t.n_tile = tile / p.num_m_tiles;
-  t.row0 = static_cast<int64_t>(tile % p.num_m_tiles) * BM;
+  t.n_tile = tile % p.num_n_tiles;
+  t.row0 = static_cast<int64_t>(tile / p.num_n_tiles) * BM;
   t.row_end = p.m;
   t.codes = p.codes;
   t.scales = p.scales;
@@ -402,7 +404,7 @@ __device__ __forceinline__ TileWork locate_tile<false>(int tile, const UmmaParam
 template <>
 __device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams &p, const GroupTable &gt)
 {
-  const int mt = tile % p.num_m_tiles;   // num_m_tiles = all experts' row tiles
+  const int mt = tile / p.num_n_tiles;   // row tile among all experts' row tiles; column tiles fastest
   int lo = 0;
   int hi = gt.num_groups;                // mtile_start[lo] <= mt < mtile_start[hi]
   while (hi - lo > 1)
@@ -418,7 +420,7 @@ __device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams
     }
   }
   TileWork t;
-  t.n_tile = tile / p.num_m_tiles;
+  t.n_tile = tile % p.num_n_tiles;
   t.row0 = static_cast<int64_t>(gt.offsets[lo]) + static_cast<int64_t>(mt - gt.mtile_start[lo]) * BM;
   t.row_end = gt.offsets[lo + 1];
   t.codes = gt.codes[lo];
