@@ -465,7 +465,7 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode kernel (see profiles/); None until captured
 NCU_TRAFFIC_C2 = 30.37e6  # bytes per launch, mean of the M=1,4,16 captures in profiles/linear_decode_int4_c2.md
-NCU_TRAFFIC_C3 = 336.1e6  # bytes per launch of the forward tensor-core kernel (profiles/linear_umma_int8_c3.md)
+NCU_TRAFFIC_C3 = 116.6e6  # bytes per launch of the forward tensor-core kernel (profiles/linear_umma_int8_c3.md)
 
 
 def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):

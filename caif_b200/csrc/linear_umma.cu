@@ -1376,7 +1376,8 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     }
     p.num_m_tiles = tiles;
     // (for the experts' shapes the wide tile measured 3 % faster with int4 too, unlike the square case)
-    const int bn = (mode != W_I4S && (p.n_total % 256) == 0 &&
+    // (an accumulating epilogue reads the output first: with 128-wide tiles it overlaps the next tile)
+    const int bn = (mode != W_I4S && !g.accumulate && (p.n_total % 256) == 0 &&
                     static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma())
                        ? 256
                        : 128;
