@@ -304,9 +304,21 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
     # N > 1: every rank owns a [copies, 21, N * 14336] result block mapped into all ranks; the kernel
     # stores its slice into every rank's block (the all-gather is the kernel's own stores over NVLink)
     peer = None
+    gathered = None
     if world > 1:
         from caif_b200.sharded import PeerBuffer
-        peer = PeerBuffer(C2_COPIES * rows_all * world * shard * 4, dev)
+        ok = torch.ones(1, device=dev)
+        try:
+            peer = PeerBuffer(C2_COPIES * rows_all * world * shard * 4, dev)
+        except Exception as e:   # no peer mapping on this box: gather with NCCL instead
+            sys.stderr.write("rank %d: peer buffers unavailable (%s); gathering Y with NCCL\n" % (rank, e))
+            ok.zero_()
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            peer = None
+            gathered = [torch.empty(world * rows_all, shard, dtype=torch.float32, device=dev)
+                        for _ in range(C2_COPIES)]
+    comm = torch.cuda.Stream() if gathered is not None else None
     row0 = {}
     r0 = 0
     for m in C2_MS:
@@ -318,12 +330,19 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
         # (242 MB) later, so no launch finds its codes in L2
         for m in C2_MS:
             for c, w in enumerate(weights):
-                if world > 1:
+                if peer is not None:
                     off = (c * rows_all + row0[m]) * world * shard * 4
                     nv.linear_fwd_gather(w, xs[m], [q + off for q in peer.ptrs], world * shard, rank * shard,
                                          nv.F32, nv.F32)
                 else:
                     nv.linear_fwd(w, xs[m], compute=nv.F32, out=ys[c][m])
+        if gathered is not None:
+            main = torch.cuda.current_stream()
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                for c in range(C2_COPIES):
+                    dist.all_gather_into_tensor(gathered[c], yblk[c])
+            main.wait_stream(comm)
 
     launches_per_step = C2_COPIES * len(C2_MS)
     # warm-up (also sets the kernel's shared-memory attribute outside any capture)
@@ -449,9 +468,10 @@ def bench_c2(args, nv, torch, dist, dev, world, rank, peaks):
                    "l2": "8 weight copies = 242 MB > 126 MB L2; consecutive launches use different copies, a copy returns 8 launches later",
                    "launch": "CUDA graph replay" if graphed else "eager",
                    "parallelism": "1 GPU" if world == 1 else
-                   "column-parallel x%d: a layer of out=%d, one [14336, 4096] shard per GPU; every launch stores "
-                   "its slice of Y into all ranks' result buffers over NVLink (peer memory), no separate "
-                   "collective; e2e times the local slice only" % (world, world * C2_OUT)},
+                   ("column-parallel x%d: a layer of out=%d, one [14336, 4096] shard per GPU; " % (world, world * C2_OUT)) +
+                   ("every launch stores its slice of Y into all ranks' result buffers over NVLink (peer memory), "
+                    "no separate collective" if peer is not None else "NCCL all-gather of Y at the end of the step") +
+                   "; e2e times the local slice only"},
         "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
     }
     if peer is not None:
