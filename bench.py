@@ -211,6 +211,10 @@ def run_gpu(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and args.workload == "c3":
+        # the collectives run beside the persistent tensor-core kernels: give them SMs of their own
+        os.environ.setdefault("NCCL_MAX_NCHANNELS", "16")
+        os.environ.setdefault("CAIFQ_UMMA_CTAS", "132")
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("--gpus %d needs torchrun with that many ranks" % args.gpus)
@@ -510,25 +514,31 @@ def bench_c3(args, nv, torch, dist, dev, world, rank, peaks):
     state = {"i": 0}
     gathered = torch.empty(world * m, dim, dtype=torch.bfloat16, device=dev) if world > 1 else None
     comm = torch.cuda.Stream() if world > 1 else None
+    overlap = os.environ.get("BENCH_C3_OVERLAP", "1") != "0"
 
     def step():
         i = state["i"] % n_sets
         state["i"] += 1
         main = torch.cuda.current_stream()
         y, hidden = nv.lora_linear_fwd(weight, lora, xs[i], compute=nv.F32)
-        if world > 1:
+        if world > 1 and overlap:
             # the gather of Y runs beside the backward pass
             comm.wait_stream(main)
             with torch.cuda.stream(comm):
                 dist.all_gather_into_tensor(gathered, y)
+        elif world > 1:
+            dist.all_gather_into_tensor(gathered, y)
         dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dys[i], xs[i], hidden, compute=nv.F32)
-        if world > 1:
+        if world > 1 and overlap:
             comm.wait_stream(main)
             with torch.cuda.stream(comm):
                 dist.all_reduce(dx)
                 dist.all_reduce(d_a)
             main.wait_stream(comm)
             y.record_stream(comm)
+        elif world > 1:
+            dist.all_reduce(dx)
+            dist.all_reduce(d_a)
         return dx
 
     for _ in range(max(args.warmup, 3)):

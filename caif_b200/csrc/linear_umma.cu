@@ -1111,6 +1111,16 @@ int sm_count_umma()
     {
       cached = 148;
     }
+    // A host that runs a collective beside these persistent kernels leaves it some SMs: a CTA here
+    // takes a whole SM, and one that finds its SM taken waits for the collective to end.
+    if (const char *e = std::getenv("CAIFQ_UMMA_CTAS"))
+    {
+      const int v = std::atoi(e);
+      if (v >= 1 && v < cached)
+      {
+        cached = v;
+      }
+    }
   }
   return cached;
 }
