@@ -272,12 +272,13 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t addr, uint32_t &r0, u
 // staged in shared memory as they lie and the tensor-core fragments are read transposed
 // (ldmatrix.trans).  A CTA owns 64 columns of U, its 4 warps 16 each; gridDim.y slices the tokens.
 // With `transpose_out` the accumulator is indexed [R, big] (dA).
-constexpr int TN_COLS = 64;
+constexpr int TN_COLS = 128;   // 256 bytes of every row per CTA; one warp per 16 columns
+constexpr int STN_THREADS = (TN_COLS / 16) * 32;
 constexpr int TN_ROWS = 64;
 constexpr int TN_UPITCH = TN_COLS + 8;  // bf16 elements: 144-byte rows keep ldmatrix conflict-free
 
 template <int NT>  // R = 8 * NT
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(STN_THREADS)
 skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__restrict__ v, float *__restrict__ acc,
                  float u_prescale, int64_t m, int big, int transpose_out)
 {
@@ -303,10 +304,10 @@ skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__res
   for (int64_t mb = m_begin; mb < m_end; mb += TN_ROWS)
   {
     // stage 64 tokens x 64 columns of U (16-byte chunks, coalesced) and 64 x R of V
-    for (int e = tid; e < TN_ROWS * (TN_COLS / 8); e += 128)
+    for (int e = tid; e < TN_ROWS * (TN_COLS / 8); e += STN_THREADS)
     {
-      const int rr = e >> 3;
-      const int ch = e & 7;
+      const int rr = e / (TN_COLS / 8);
+      const int ch = e % (TN_COLS / 8);
       uint4 val = make_uint4(0u, 0u, 0u, 0u);
       if (mb + rr < m_end && c0 + ch * 8 < big)
       {
@@ -319,7 +320,7 @@ skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__res
       }
       *reinterpret_cast<uint4 *>(&su[rr][ch * 8]) = val;
     }
-    for (int e = tid; e < TN_ROWS * NT; e += 128)
+    for (int e = tid; e < TN_ROWS * NT; e += STN_THREADS)
     {
       const int rr = e / NT;
       const int ch = e % NT;
@@ -521,16 +522,16 @@ int launch_skinny_tn(const void *u, const void *v, void *c, float *scratch, floa
     switch (rank)
     {
       case 8:
-        skinny_tn_kernel<1><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<1><<<grid, STN_THREADS, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       case 16:
-        skinny_tn_kernel<2><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<2><<<grid, STN_THREADS, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       case 32:
-        skinny_tn_kernel<4><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<4><<<grid, STN_THREADS, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       case 64:
-        skinny_tn_kernel<8><<<grid, 128, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
+        skinny_tn_kernel<8><<<grid, STN_THREADS, 0, s>>>(up, vp, scratch, u_prescale, m, big, tr);
         break;
       default:
         set_error("LoRA fast path: unsupported rank %d", rank);
