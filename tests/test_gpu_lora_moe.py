@@ -248,6 +248,53 @@ def test_grouped_frozen_experts_single_launch(storage, compute, experts, in_dim,
         assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
 
 
+def test_grouped_experts_at_the_moe_config_size_equal_single_expert_calls():
+    """64 int4 experts 2048 -> 1408 -> 2048, 16384 tokens routed top-6 (98,304 packed rows): the grouped
+    launches must give every expert's rows exactly what a call with that expert alone gives (an
+    expert's tiles never mix rows or codes of its neighbours), forward and dX; one expert is also
+    checked against the oracle."""
+    g = torch.Generator(device="cuda").manual_seed(77)
+    hidden, ffn, n_exp, tokens, top_k = 2048, 1408, 64, 16384, 6
+    gate, up, down = [], [], []
+    for _ in range(n_exp):
+        for lst, (o, i) in ((gate, (ffn, hidden)), (up, (ffn, hidden)), (down, (hidden, ffn))):
+            wf = torch.randn(o * i, generator=g, device="cuda") * 0.02
+            pk, sc = nv.quantize_int4(wf, 128)
+            lst.append(nv.Weight(pk, nv.I4, i, o, sc, group_size=128))
+    probs = torch.softmax(torch.randn(tokens, n_exp, generator=g, device="cuda"), dim=-1)
+    idx, _ = nv.moe_topk(probs, top_k)
+    dmap, off = nv.moe_build_dispatch(idx, n_exp)
+    offs = off.cpu().tolist()
+    total = offs[-1]
+    assert total == tokens * top_k
+    x = torch.randn(tokens, hidden, generator=g, device="cuda").to(torch.bfloat16)
+    buf = nv.moe_dispatch(x, idx, dmap, off, total)
+    dy = torch.randn(total, hidden, generator=g, device="cuda").to(torch.bfloat16)
+    out, g_out, u_out = nv.grouped_expert_fwd(gate, up, down, offs, buf, orc.BF16)
+    assert nv.last_path() == "umma-grouped"
+    dx = nv.grouped_expert_bwd(gate, up, down, offs, dy, g_out, u_out, orc.BF16)
+    assert nv.lib().caifq_device_status() == 0
+    for e in (0, 17, 63):
+        lo, hi = offs[e], offs[e + 1]
+        o1, g1, u1 = nv.grouped_expert_fwd([gate[e]], [up[e]], [down[e]], [0, hi - lo], buf[lo:hi].contiguous(),
+                                           orc.BF16)
+        d1 = nv.grouped_expert_bwd([gate[e]], [up[e]], [down[e]], [0, hi - lo], dy[lo:hi].contiguous(), g1, u1,
+                                   orc.BF16)
+        assert torch.equal(o1, out[lo:hi]) and torch.equal(g1, g_out[lo:hi]) and torch.equal(u1, u_out[lo:hi])
+        assert torch.equal(d1, dx[lo:hi])
+    # expert 17 against the oracle on its first 64 rows
+    e = 17
+    lo = offs[e]
+    ws = []
+    for w in (gate[e], up[e], down[e]):
+        codes = w.codes.cpu().numpy()
+        scales = w.scales.cpu().view(torch.int16).numpy().view(np.uint16)
+        ws.append(orc.weight_to_compute(codes, scales, orc.I4, w.in_dim, w.out_dim, orc.BF16, 0, 128))
+    want, _, _ = orc.frozen_expert_forward(buf[lo:lo + 64].float().cpu().numpy(), ws[0], ws[1], ws[2], orc.BF16,
+                                           orc.BF16)
+    assert max_rel_err(out[lo:lo + 64].float().cpu().numpy(), want) <= 2e-2
+
+
 @pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I4, orc.BF16), (orc.I4, orc.F32)])
 @pytest.mark.parametrize("m,in_dim,out_dim,rank", [(300, 512, 384, 16), (1024, 1024, 1024, 8), (130, 256, 640, 64)])
 def test_lora_fused_tensor_core_path(storage, compute, m, in_dim, out_dim, rank):
