@@ -324,6 +324,7 @@ struct UmmaParams
   int k_total;       // reduction length
   int in_dim;        // row length of the code matrix
   int group_size;    // int4
+  int groups_per_row;  // int4: in_dim / group_size
   int num_m_tiles;
   int num_n_tiles;
   const uint8_t *lora_rhs;  // null = no LoRA k-block
@@ -872,7 +873,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           raw[i] = __ldg(reinterpret_cast<const uint4 *>(src));
           if (IS_I4)
           {
-            sc[i] = __half2float(static_cast<const __half *>(scales)[flat / p.group_size]);
+            // in_dim is a multiple of the group size here, so the flat group index splits into a row
+            // part and a 32-bit division inside the row (a 64-bit division costs as much as the conversion)
+            const int64_t grp = o * p.groups_per_row + static_cast<int>(ii) / p.group_size;
+            sc[i] = __half2float(static_cast<const __half *>(scales)[grp]);
           }
           else
           {
@@ -1218,6 +1222,7 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   p.k_total = g.backward ? w.out_dim : w.in_dim;
   p.in_dim = w.in_dim;
   p.group_size = w.group_size;
+  p.groups_per_row = (w.group_size > 0) ? w.in_dim / w.group_size : 0;
   p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
   // 256-wide tiles feed the tensor core better per shared-memory byte; 128-wide ones keep a
   // second accumulator set so the epilogue overlaps the next tile.  CAIFQ_UMMA_BN overrides.
@@ -1357,6 +1362,7 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
   p.k_total = g.backward ? w0.out_dim : w0.in_dim;
   p.in_dim = w0.in_dim;
   p.group_size = w0.group_size;
+  p.groups_per_row = (w0.group_size > 0) ? w0.in_dim / w0.group_size : 0;
   CUtensorMap map_a;
   int rc = make_map_bf16(&map_a, g.a, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(total_rows), BM_SUB);
   if (rc != CAIFQ_OK)
@@ -1472,6 +1478,7 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
   p.k_total = w0.in_dim;
   p.in_dim = w0.in_dim;
   p.group_size = w0.group_size;
+  p.groups_per_row = (w0.group_size > 0) ? w0.in_dim / w0.group_size : 0;
   p.swiglu = 1;
   p.num_n_tiles = w0.out_dim / 64;
   CUtensorMap map_a;
