@@ -1226,9 +1226,9 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
   // 256-wide tiles feed the tensor core better per shared-memory byte; 128-wide ones keep a
   // second accumulator set so the epilogue overlaps the next tile.  CAIFQ_UMMA_BN overrides.
-  // a single int4 layer measured faster with 128-wide tiles (the conversion per k-block is shorter
-  // and two accumulator sets overlap the epilogue)
-  int bn = (w.storage != CAIFQ_I4 && (p.n_total % 256) == 0 &&
+  // the forward pass of a single int4 layer measured faster with 128-wide tiles (923-968 vs 827-877
+  // TFLOP/s at 4096 x 4096), its dX with 256-wide ones (992-1040 vs 905-920)
+  int bn = ((w.storage != CAIFQ_I4 || g.backward) && (p.n_total % 256) == 0 &&
             static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
                ? 256
                : 128;
