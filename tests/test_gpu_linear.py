@@ -229,6 +229,15 @@ def test_umma_forward_and_dx(storage, compute, tol, m, in_dim, out_dim):
         assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, compute)) <= 1e-4
 
 
+def test_umma_int4_group_size_that_is_not_a_power_of_two():
+    weight, wc, x_np, x, dy_np, dy = _umma_case(orc.I4, orc.BF16, 64, 384, 256, 4321, group=96)
+    y = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    assert nv.last_path() == "umma"
+    dx = nv.linear_dx(weight, dy, torch.float32, orc.BF16)
+    assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, orc.BF16)) <= 1e-4
+    assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, orc.BF16)) <= 1e-4
+
+
 def test_umma_bf16_output_and_accumulate_epilogue():
     weight, wc, x_np, x, dy_np, dy = _umma_case(orc.I8, orc.F32, 200, 256, 256, 42)
     yb = nv.linear_fwd(weight, x, torch.bfloat16, orc.F32)
