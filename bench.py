@@ -197,6 +197,52 @@ def cpu_reference_c3(steps, warmup, budget_s=25.0):
                       % (done, m)}
 
 
+def cpu_reference_c5(steps, warmup, budget_s=25.0):
+    """Reference Host_e path for the frozen experts on a bounded sample: 4 of the 64 experts with 256
+    rows each (1024 of the 98,304 packed rows): cached fp32 weights (dequantized once), the expert
+    loop of the layer with sgemm for the six products and the elementwise steps in numpy."""
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import caif_oracle as orc
+
+    rng = np.random.default_rng(1238)
+    hidden, ffn, n_exp, rows = 2048, 1408, 4, 256
+    ws = []
+    for _ in range(n_exp):
+        trio = []
+        for (o, i) in ((ffn, hidden), (ffn, hidden), (hidden, ffn)):
+            w = (rng.standard_normal((o, i)) * 0.02).astype(np.float32)
+            pk, sc = orc.quantize_int4(w, 128)
+            trio.append(orc.dequantize_int4(pk, sc, o * i, 128).reshape(o, i))
+        ws.append(trio)
+    x = orc.round_through(rng.standard_normal((n_exp * rows, hidden)).astype(np.float32), orc.BF16)
+    dy = orc.round_through(rng.standard_normal((n_exp * rows, hidden)).astype(np.float32), orc.BF16)
+
+    def step():
+        for e in range(n_exp):
+            xe = x[e * rows:(e + 1) * rows]
+            _, g, u = orc.frozen_expert_forward(xe, ws[e][0], ws[e][1], ws[e][2], orc.F32, orc.BF16, exact=False)
+            orc.frozen_expert_backward(dy[e * rows:(e + 1) * rows], g, u, ws[e][0], ws[e][1], ws[e][2], orc.F32,
+                                       orc.BF16, exact=False)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(steps):
+        step()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    flops = c5_flops(n_exp * rows)
+    return {"value": flops * done / dt / 1e12, "ms_per_step": dt / done * 1e3, "steps": done,
+            "cores": orc.num_threads(),
+            "sample": "%d steps over %d experts x %d rows (1/96 of the packed rows): per-expert loop, sgemm on cached "
+                      "fp32 weights, forward + dX" % (done, n_exp, rows)}
+
+
 def c3_flops(m, dim=4096, rank=16):
     return 2 * (2 * m * dim * dim) + 6 * (2 * m * dim * rank)
 
@@ -693,6 +739,10 @@ def bench_c5(args, nv, torch, dist, dev, world, rank, peaks):
                      "note": "whole step incl. dispatch, SwiGLU and combine kernels over its duration"},
         "e2e": e2e, "gpu_launches": 11 * args.steps, "clocks": clocks,
     }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cb = cpu_reference_c5(steps=20, warmup=1, budget_s=20.0)
+        result["cpu_baseline"] = {"value": cb["value"], "unit": "TFLOP/s", "cores": cb["cores"], "kind": "port",
+                                  "sample": cb["sample"]}
     return result
 
 
@@ -704,14 +754,20 @@ def run_reference(args):
         cb = cpu_reference_c2(steps=args.steps, warmup=min(args.warmup, 2), budget_s=120.0)
         unit, metric = "GB/s", "decode int4 frozen-linear forward, algorithmic HBM bytes per second"
         workload = "c2: in=4096 out=14336 int4 g128, M in {1,4,16}, forward; step = 8 weight copies x 3 M"
-    else:
+    elif args.workload == "c3":
         cb = cpu_reference_c3(steps=args.steps, warmup=min(args.warmup, 1), budget_s=120.0)
         unit, metric = "TFLOP/s", "int8 frozen linear + LoRA r16, forward + dX/dA/dB, TFLOP/s"
         workload = "c3: 4096->4096 int8 per-tensor + LoRA r16 a32, M=8192 bf16, fwd + dX/dA/dB"
+    else:
+        cb = cpu_reference_c5(steps=args.steps, warmup=min(args.warmup, 1), budget_s=120.0)
+        unit, metric = "TFLOP/s", "frozen int4 experts, grouped forward + dX, TFLOP/s"
+        workload = ("c5: 64 frozen int4 experts 2048->1408->2048 (SwiGLU), 16384 tokens top-6, "
+                    "dispatch + grouped fwd + combine + grouped dX")
     line = {
         "impl": "reference", "metric": metric, "value": cb["value"], "unit": unit, "n_gpus": args.gpus,
         "steps": cb["steps"], "warmup": min(args.warmup, 2), "ms_per_step": cb["ms_per_step"],
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (host sgemm)",
+        "higher_is_better": True, "scaling": "strong" if args.workload == "c5" else "weak", "vs_baseline": None,
+        "dtype": "fp32 (host sgemm)",
         "data": "synthetic", "config": {"workload": workload},
         "cpu_baseline": {"value": cb["value"], "unit": unit, "cores": cb["cores"], "kind": "port",
                          "sample": cb["sample"]},
