@@ -137,6 +137,11 @@ CAIFQ_API int caifq_weight_materialize(const caifq_weight *w, void *dst, int32_t
  * returns), or F16/BF16 for callers that cast straight after.
  * The weight is dequantized on the fly inside the kernel: no [out,in] float
  * copy is ever written to memory.
+ * Few-token calls (m <= 16) are launched with the programmatic-dependent-launch attribute: the
+ * kernel starts copying codes and scales as soon as the previous kernel in the stream lets go of
+ * the SMs, and waits for that kernel only before it touches x and y.  Codes and scales are frozen:
+ * they must have been written by work that is complete (not merely enqueued just ahead in the same
+ * stream) - or set CAIFQ_PDL=0.
  */
 CAIFQ_API int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *y, int32_t y_dtype,
                      int32_t compute_dtype, void *stream);
