@@ -334,6 +334,7 @@ int caifq_device_ok(void)
 
 int caifq_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int64_t n, void *stream)
 {
+  note_codes_written();
   CAIFQ_CHECK_ARG(n >= 0, "quantize_int8_per_tensor: negative n");
   CAIFQ_CHECK_ARG(n == 0 || (x && q && scale), "quantize_int8_per_tensor: null pointer");
   return launch_quantize_int8_per_tensor(x, q, scale, n, static_cast<cudaStream_t>(stream));
@@ -341,6 +342,7 @@ int caifq_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int6
 
 int caifq_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, int32_t rows, int32_t cols, void *stream)
 {
+  note_codes_written();
   CAIFQ_CHECK_ARG(rows >= 0 && cols >= 0, "quantize_int8_per_channel: negative shape");
   CAIFQ_CHECK_ARG(rows == 0 || cols == 0 || (x && q && scales), "quantize_int8_per_channel: null pointer");
   return launch_quantize_int8_per_channel(x, q, scales, rows, cols, static_cast<cudaStream_t>(stream));
@@ -349,6 +351,7 @@ int caifq_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, in
 int caifq_quantize_int4_per_group(const float *x, uint8_t *packed, uint16_t *scales_f16, int64_t n, int32_t group_size,
                                   void *stream)
 {
+  note_codes_written();
   CAIFQ_CHECK_ARG(n >= 0, "quantize_int4_per_group: negative n");
   CAIFQ_CHECK_ARG(group_size > 0, "quantize_int4_per_group: group_size must be positive");
   CAIFQ_CHECK_ARG(n == 0 || (x && packed && scales_f16), "quantize_int4_per_group: null pointer");

@@ -25,6 +25,8 @@
 // Codes and activations are exact in bf16 and products accumulate in fp32, so
 // the result matches an fp32 GEMM on the dequantized weight up to summation
 // order.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace caifq
@@ -597,6 +599,20 @@ int sm_count()
   return cached;
 }
 
+}  // namespace
+
+namespace
+{
+std::atomic<bool> g_codes_written{false};
+}
+
+void note_codes_written() { g_codes_written.store(true, std::memory_order_relaxed); }
+
+bool take_codes_written() { return g_codes_written.exchange(false, std::memory_order_relaxed); }
+
+namespace
+{
+
 template <int BITS, int MT, int NCH>
 int launch_decode_inst(const DecodeParams &p, cudaStream_t s)
 {
@@ -626,7 +642,7 @@ int launch_decode_inst(const DecodeParams &p, cudaStream_t s)
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = (pdl && !take_codes_written()) ? 1 : 0;
   CAIFQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;

@@ -140,8 +140,9 @@ CAIFQ_API int caifq_weight_materialize(const caifq_weight *w, void *dst, int32_t
  * Few-token calls (m <= 16) are launched with the programmatic-dependent-launch attribute: the
  * kernel starts copying codes and scales as soon as the previous kernel in the stream lets go of
  * the SMs, and waits for that kernel only before it touches x and y.  Codes and scales are frozen:
- * they must have been written by work that is complete (not merely enqueued just ahead in the same
- * stream) - or set CAIFQ_PDL=0.
+ * a kernel of another library that writes them must not be the one enqueued directly ahead of this
+ * call in the same stream (the first few-token call after one of this library's own quantize calls
+ * is a plain launch and needs no care); CAIFQ_PDL=0 turns the attribute off.
  */
 CAIFQ_API int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *y, int32_t y_dtype,
                      int32_t compute_dtype, void *stream);
