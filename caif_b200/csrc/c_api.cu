@@ -315,6 +315,8 @@ int caifq_device_status(void)
   return (decode_flag ? 1 : 0) | (umma_flag ? 2 : 0);
 }
 
+void caifq_selftest_stall_next_decode(void) { decode_stall_next_launch(); }
+
 int caifq_device_ok(void)
 {
   int dev = 0;
@@ -334,7 +336,7 @@ int caifq_device_ok(void)
 
 int caifq_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int64_t n, void *stream)
 {
-  note_codes_written();
+  note_codes_written(static_cast<cudaStream_t>(stream));
   CAIFQ_CHECK_ARG(n >= 0, "quantize_int8_per_tensor: negative n");
   CAIFQ_CHECK_ARG(n == 0 || (x && q && scale), "quantize_int8_per_tensor: null pointer");
   return launch_quantize_int8_per_tensor(x, q, scale, n, static_cast<cudaStream_t>(stream));
@@ -342,7 +344,7 @@ int caifq_quantize_int8_per_tensor(const float *x, int8_t *q, float *scale, int6
 
 int caifq_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, int32_t rows, int32_t cols, void *stream)
 {
-  note_codes_written();
+  note_codes_written(static_cast<cudaStream_t>(stream));
   CAIFQ_CHECK_ARG(rows >= 0 && cols >= 0, "quantize_int8_per_channel: negative shape");
   CAIFQ_CHECK_ARG(rows == 0 || cols == 0 || (x && q && scales), "quantize_int8_per_channel: null pointer");
   return launch_quantize_int8_per_channel(x, q, scales, rows, cols, static_cast<cudaStream_t>(stream));
@@ -351,7 +353,7 @@ int caifq_quantize_int8_per_channel(const float *x, int8_t *q, float *scales, in
 int caifq_quantize_int4_per_group(const float *x, uint8_t *packed, uint16_t *scales_f16, int64_t n, int32_t group_size,
                                   void *stream)
 {
-  note_codes_written();
+  note_codes_written(static_cast<cudaStream_t>(stream));
   CAIFQ_CHECK_ARG(n >= 0, "quantize_int4_per_group: negative n");
   CAIFQ_CHECK_ARG(group_size > 0, "quantize_int4_per_group: group_size must be positive");
   CAIFQ_CHECK_ARG(n == 0 || (x && packed && scales_f16), "quantize_int4_per_group: null pointer");
@@ -386,6 +388,10 @@ int caifq_cast(const void *src, int32_t src_dtype, void *dst, int32_t dst_dtype,
 {
   CAIFQ_CHECK_ARG(n >= 0, "cast: negative n");
   CAIFQ_CHECK_ARG(n == 0 || (src && dst), "cast: null pointer");
+  if (dst_dtype == CAIFQ_I8)
+  {
+    note_codes_written(static_cast<cudaStream_t>(stream));  // int8 codes without scales are a valid weight
+  }
   return launch_cast(src, src_dtype, dst, dst_dtype, n, static_cast<cudaStream_t>(stream));
 }
 

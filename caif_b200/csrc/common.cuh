@@ -249,10 +249,13 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &args, cudaStream_t s);
 bool umma_grouped_supported(const GroupedLinearArgs &args);
 int launch_linear_umma_grouped(const GroupedLinearArgs &args, cudaStream_t s);
 // The few-token kernel reads codes and scales ahead of the previous kernel's completion (dependent
-// launch).  The library's own quantize kernels produce codes: the first few-token launch after one
-// of them is a plain launch, which orders it (and everything after it) behind that kernel.
-void note_codes_written();
-bool take_codes_written();
+// launch).  The library's own quantize and cast kernels produce codes: the first few-token launch
+// on the same device and stream after one of them is a plain launch, which orders it (and
+// everything after it) behind that kernel.
+void note_codes_written(cudaStream_t s);
+bool take_codes_written(cudaStream_t s);
+// self-test hook: the next few-token launch of this thread waits for bytes that never arrive
+void decode_stall_next_launch();
 bool decode_supported(const LinearArgs &args);
 int launch_linear_decode(const LinearArgs &args, cudaStream_t s);
 

@@ -9,9 +9,10 @@
 //   * one persistent CTA per SM owns a contiguous range of rows of the
 //     [out, in] code matrix, i.e. one contiguous slab of HBM, cut into items of
 //     16 rows (the M of the tensor-core instruction);
-//   * warp 0 streams that slab through a shared-memory ring with bulk async
-//     copies (cp.async.bulk + mbarrier transaction counts): 100+ KB in flight
-//     per SM regardless of register pressure;
+//   * the slab streams through a shared-memory ring of three items with bulk
+//     async copies (cp.async.bulk + mbarrier transaction counts), started before
+//     the kernel waits for the previous kernel in the stream (programmatic
+//     dependent launch): the frozen codes never depend on earlier work;
 //   * 16 warps split the reduction dimension; each lane pulls 16 bytes of codes
 //     of rows g and g+8 from the ring, turns nibbles/bytes into exact bf16
 //     integers with logic ops (no int->float converts), and feeds them as the A
@@ -20,12 +21,20 @@
 //   * int4 group scales multiply the fp32 partial sum once per 128-element
 //     chunk; the int8 per-tensor scale multiplies the final sum;
 //   * the warps never synchronise with each other in the main loop: each parks
-//     its partial sums of every item in shared memory, and one pass at the end
-//     adds the 16 partials of each output.
+//     its partial sums of every item (live tokens only) in shared memory, and
+//     one pass at the end adds the 16 partials of each output in a fixed order
+//     and stores four rows (or, for 9 to 16 tokens, one row of four tokens) per
+//     thread.
+// After the previous kernel has completed the launch is bound by the logic ops
+// of the dequantization (two cycles per warp instruction on this GPU, seven of
+// them per eight int4 weights), not by HBM: see the design notes of the package.
 // Codes and activations are exact in bf16 and products accumulate in fp32, so
 // the result matches an fp32 GEMM on the dequantized weight up to summation
-// order.
+// order.  The summation order of an output does not depend on which CTA owns
+// its row, so a row slice of a layer gives the same bits as the whole layer.
 #include <atomic>
+#include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -53,13 +62,16 @@ int take_decode_timeout_flag()
 namespace
 {
 
-constexpr int kComputeWarps = 16;                // 4 per scheduler: the 128-register budget holds
-constexpr int kThreads = kComputeWarps * 32;
 constexpr int kItemRows = 16;                    // weight rows per work item (the MMA's M)
 constexpr int kRowQuantum = 8;                   // CTA row ranges start on multiples of this
 constexpr int kMaxStages = 8;
-constexpr uint32_t kSmemBudget = 220u * 1024u;
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kWarps = 16;                       // 4 per scheduler: the 128-register budget holds
+constexpr int kThreads = kWarps * 32;
+constexpr int kRingDepth = 3;                    // items in flight per SM
+constexpr uint32_t kSmemBudget = 220u * 1024u;   // dynamic shared memory of the one CTA per SM
+constexpr uint32_t kSpinLimit = 1u << 22;        // polls of one wait before it gives up (tens of ms)
+constexpr uint32_t kSpinLimitTest = 1u << 12;    // the same for the self-test of the give-up path
+constexpr int kMaxDevices = 64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -82,33 +94,49 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar)
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Bounded wait: gives up after kSpinLimit polls and records it, so a copy that
-// never lands turns into wrong numbers plus a flag instead of a hung GPU.
-__device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_try(uint32_t addr, uint32_t parity)
 {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
-  {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done)
-    {
-      return;
-    }
-  }
-  atomicExch(&g_decode_timeout_flag, 1u);
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return done != 0;
 }
 
-__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar)
+// Bounded wait, called by all lanes of a warp.  Gives up after `limit` polls, or as soon as
+// another warp of the CTA has given up, and says so: a copy that never lands turns into a
+// flag and missing outputs instead of a hung GPU.  The answer is the same in every lane.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit, volatile uint32_t *abort_word)
 {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst)),
+  const uint32_t addr = smem_u32(bar);
+  bool done = mbar_try(addr, parity);
+  if (!done)
+  {
+    for (uint32_t spin = 0; spin < limit && !done; ++spin)
+    {
+      done = mbar_try(addr, parity);
+      if (!done && (spin & 255u) == 255u && *abort_word != 0u)
+      {
+        break;
+      }
+    }
+  }
+  done = __all_sync(0xFFFFFFFFu, done);
+  if (!done)
+  {
+    *abort_word = 1u;
+    atomicExch(&g_decode_timeout_flag, 1u);
+  }
+  return done;
+}
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar)
+{
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
@@ -168,10 +196,11 @@ __device__ __forceinline__ float lds_f32(uint32_t addr)
   return v;
 }
 
-__device__ __forceinline__ void sts_f32(uint32_t addr, float a)
+__device__ __forceinline__ void sts_f32x2(uint32_t addr, float a, float b)
 {
-  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+  asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
+
 
 struct DecodeParams
 {
@@ -190,11 +219,14 @@ struct DecodeParams
   int chunks_per_group;   // int4: group_size / 128
   int num_quanta;         // ceil(out / 8)
   int stages;
-  uint32_t smem_bytes;     // dynamic shared memory of the launch
-  uint32_t partial_offset; // byte offset of the partial sums in dynamic shared memory
+  int vec4;               // fp32 results may be stored four rows at a time (16-byte aligned on every buffer)
+  int tokp;               // tokens per parked row: m rounded up to 2, 4, 8 or 16
+  uint32_t partial_offset; // byte offset of the parked partial sums in dynamic shared memory
   uint32_t row_bytes;      // packed bytes per weight row
-  uint32_t row_stride;     // padded row pitch in the ring
+  uint32_t row_stride;     // row pitch in the ring
   uint32_t stage_bytes;    // ring stage pitch
+  uint32_t spin_limit;     // polls of one wait before it gives up
+  uint32_t stall_bytes;    // self-test only: bytes the first item announces but never receives
 };
 
 // int4 codes are turned into the bf16 integers 136 + q (q in [-8,7]): the
@@ -206,18 +238,18 @@ constexpr float kInt4Offset = 136.0f;
 // BITS: 4 or 8.  MT: token tiles of 8 (1 -> m <= 8, 2 -> m <= 16).
 // NCH: chunks (64 bytes of one row: a quad of lanes x 16 bytes) per warp.
 template <int BITS, int MT, int NCH>
-__global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const DecodeParams p)
+__global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid_constant__ DecodeParams p)
 {
   constexpr int ELEMS = 128 / BITS;      // codes per 16-byte load: 32 or 16
   constexpr int CHUNK_K = 4 * ELEMS;     // k covered by a quad of lanes: 128 or 64
   constexpr int XR = ELEMS / 2;          // bf16x2 registers of x per chunk and token tile: 16 or 8
-  constexpr int TOK = 8 * MT;
-  constexpr uint32_t kPartWarpBytes = kItemRows * TOK * 4;            // one warp's sums of one item
-  constexpr uint32_t kPartItemBytes = kComputeWarps * kPartWarpBytes;  // all warps' sums of one item
+  constexpr int WARPS = kWarps;
+  constexpr int CHAINS = (MT == 1) ? 2 : 1;   // accumulation chains per token tile
 
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ uint64_t full_bar[kMaxStages];   // a stage's copies have landed
-  __shared__ uint64_t empty_bar[kMaxStages];  // all 16 warps are done reading a stage
+  __shared__ uint64_t empty_bar[kMaxStages];  // all warps are done reading a stage
+  __shared__ uint32_t cta_abort;              // a wait of this CTA has run out
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -234,52 +266,52 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
   const int stages = p.stages;
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t part_base = smem_base + p.partial_offset;
+  volatile uint32_t *abort_word = &cta_abort;
 
-  if (tid == 0)
-  {
-    for (int s = 0; s < stages; ++s)
-    {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kComputeWarps);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  __syncthreads();
-
-  // Producer: the item's rows are contiguous in memory, so one bulk copy brings
-  // the codes and a second one the scales (two lanes of warp 0).
+  // One thread starts the copies of an item: its rows are contiguous in memory, so one bulk copy
+  // brings the codes and a second one the scales.
   auto issue = [&](int item, int s)
   {
     const int row0 = row_begin + item * kItemRows;
     const int rows = min(kItemRows, row_end - row0);
-    uint8_t *stage = smem + static_cast<size_t>(s) * p.stage_bytes;
+    const uint32_t stage = smem_base + static_cast<uint32_t>(s) * p.stage_bytes;
     const uint32_t code_bytes = static_cast<uint32_t>(rows) * p.row_bytes;
     const uint32_t scale_bytes = (BITS == 4) ? static_cast<uint32_t>(rows * p.groups_per_row * 2) : 0u;
-    if (lane == 0)
-    {
-      mbar_expect_tx(&full_bar[s], code_bytes + scale_bytes);
-      bulk_g2s(stage, p.codes + static_cast<size_t>(row0) * p.row_bytes, code_bytes, &full_bar[s]);
-    }
-    if (BITS == 4 && lane == 1)
+    mbar_expect_tx(&full_bar[s], code_bytes + scale_bytes + (item == 0 ? p.stall_bytes : 0u));
+    bulk_g2s(stage, p.codes + static_cast<size_t>(row0) * p.row_bytes, code_bytes, &full_bar[s]);
+    if (BITS == 4)
     {
       const uint8_t *src = static_cast<const uint8_t *>(p.scales) + static_cast<size_t>(row0) * p.groups_per_row * 2;
-      bulk_g2s(stage + static_cast<size_t>(kItemRows) * p.row_stride, src, scale_bytes, &full_bar[s]);
+      bulk_g2s(stage + static_cast<uint32_t>(kItemRows) * p.row_stride, src, scale_bytes, &full_bar[s]);
     }
   };
-  if (warp == 0)
+
+  if (tid == 0)
   {
-    const int pre = min(stages, my_items);
-    for (int i = 0; i < pre; ++i)
+    cta_abort = 0u;
+    for (int s = 0; s < stages; ++s)
+    {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], WARPS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // The frozen codes and scales never depend on earlier work in the stream: the ring starts before
+  // the wait on the previous kernel.  The next kernel in the stream may place its CTAs as soon as
+  // this grid's CTAs have all come this far (programmatic dependent launch).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Warp 0 is the only producer; it knows how many items it has started (needed if it gives up).
+  int issued_items = min(stages, my_items);
+  if (tid == 0)
+  {
+    for (int i = 0; i < issued_items; ++i)
     {
       issue(i, i);
     }
   }
 
-  // Programmatic dependent launch: the frozen codes and scales never depend on earlier work in
-  // the stream, so their copies above may start while the previous kernel is still draining.
-  // Activations and the output are touched only after that kernel has completed.  The next
-  // kernel in the stream may begin its own weight copies as soon as this CTA's resources free up.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Activations and the output are touched only after the previous kernel has completed.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // Token fragments (B operand), resident for the whole kernel.  For the 16
@@ -294,7 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
 #pragma unroll
   for (int ch = 0; ch < NCH; ++ch)
   {
-    const int cidx = warp + ch * kComputeWarps;
+    const int cidx = warp + ch * WARPS;
     code_off[ch] = static_cast<uint32_t>(g) * p.row_stride + static_cast<uint32_t>(cidx) * 64u + static_cast<uint32_t>(t) * 16u;
     scale_off[ch] = static_cast<uint32_t>(kItemRows) * p.row_stride +
                     static_cast<uint32_t>(g * p.groups_per_row + cidx / p.chunks_per_group) * 2u;
@@ -328,17 +360,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
       }
       if (BITS == 4)
       {
-        float lane_sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < XR; ++i)
-        {
-          lane_sum += __uint_as_float(raw[i] << 16) + __uint_as_float(raw[i] & 0xFFFF0000u);
-        }
-        lane_sum += __shfl_xor_sync(0xFFFFFFFFu, lane_sum, 1);
-        lane_sum += __shfl_xor_sync(0xFFFFFFFFu, lane_sum, 2);
-        // every lane of quad g now holds the sum for token g (+8 mt); fetch tokens 2t, 2t+1
-        sx[ch][mt][0] = -kInt4Offset * __shfl_sync(0xFFFFFFFFu, lane_sum, (2 * t) * 4);
-        sx[ch][mt][1] = -kInt4Offset * __shfl_sync(0xFFFFFFFFu, lane_sum, (2 * t + 1) * 4);
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi)
         {
@@ -346,6 +367,18 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
           xf[ch][mt][4 * wi + 1] = __byte_perm(raw[4 * wi + 1], raw[4 * wi + 3], 0x5410);
           xf[ch][mt][4 * wi + 2] = __byte_perm(raw[4 * wi + 0], raw[4 * wi + 2], 0x7632);
           xf[ch][mt][4 * wi + 3] = __byte_perm(raw[4 * wi + 1], raw[4 * wi + 3], 0x7632);
+        }
+        {
+          float lane_sum = 0.0f;
+#pragma unroll
+          for (int i = 0; i < XR; ++i)
+          {
+            lane_sum += __uint_as_float(raw[i] << 16) + __uint_as_float(raw[i] & 0xFFFF0000u);
+          }
+          lane_sum += __shfl_xor_sync(0xFFFFFFFFu, lane_sum, 1);
+          lane_sum += __shfl_xor_sync(0xFFFFFFFFu, lane_sum, 2);
+          sx[ch][mt][0] = -kInt4Offset * __shfl_sync(0xFFFFFFFFu, lane_sum, (2 * t) * 4);
+          sx[ch][mt][1] = -kInt4Offset * __shfl_sync(0xFFFFFFFFu, lane_sum, (2 * t + 1) * 4);
         }
       }
       else
@@ -363,51 +396,44 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
   }
   const uint32_t row8_off = 8u * p.row_stride;
   const uint32_t scale8_off = static_cast<uint32_t>(8 * p.groups_per_row) * 2u;
-  // parked partial sums: [item][warp][token][row], rows fastest
-  const uint32_t part_write_off =
-      static_cast<uint32_t>(warp) * kPartWarpBytes + static_cast<uint32_t>(2 * t * kItemRows + g) * 4u;
-
-  int s = 0;           // ring stage of the current item
-  uint32_t s_par = 0;  // its phase parity
+  // parked partial sums: [item][warp][row][token], tokens fastest and only the live ones (tokp of
+  // them): a lane's two tokens of a row are one 8-byte store.  With 16 tokens the groups of four
+  // tokens of a row are stored in an order that depends on the row (quad ^ ((row >> 1) & 3)), so that
+  // the 16-byte reads of the final reduction, eight rows at a time, fall into different banks.
+  const uint32_t part_warp_bytes = static_cast<uint32_t>(kItemRows * p.tokp) * 4u;
+  const uint32_t part_item_bytes = WARPS * part_warp_bytes;
+  uint32_t part_write_off[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+  {
+    if (MT == 2)
+    {
+      const int quad = ((t >> 1) + 2 * mt) ^ ((g >> 1) & 3);
+      part_write_off[mt] = static_cast<uint32_t>(warp) * part_warp_bytes +
+                           static_cast<uint32_t>(g * 16 + 4 * quad + 2 * (t & 1)) * 4u;
+    }
+    else
+    {
+      part_write_off[mt] =
+          static_cast<uint32_t>(warp) * part_warp_bytes + static_cast<uint32_t>(g * p.tokp + 2 * t) * 4u;
+    }
+  }
+  float tensor_scale = 1.0f;
+  if (BITS == 8 && p.scales != nullptr)
+  {
+    tensor_scale = static_cast<const float *>(p.scales)[0];
+  }
+  int s = 0;             // ring stage of the current item
+  uint32_t s_par = 0;    // its phase parity
+  bool ok = true;
   for (int it = 0; it < my_items; ++it)
   {
-    mbar_wait(&full_bar[s], s_par);
+    ok = mbar_wait(&full_bar[s], s_par, p.spin_limit, abort_word);
+    if (!ok)
+    {
+      break;
+    }
     const uint32_t stage_addr = smem_base + static_cast<uint32_t>(s) * p.stage_bytes;
-
-    // all shared-memory reads of the item first, so the stage can be released
-    // early and the MMAs of different chunks overlap
-    uint32_t wlo[NCH][4];
-    uint32_t whi[NCH][4];
-    float s_lo[NCH];
-    float s_hi[NCH];
-#pragma unroll
-    for (int ch = 0; ch < NCH; ++ch)
-    {
-      if (warp + ch * kComputeWarps < num_chunks)
-      {
-        const uint4 lo = lds128(stage_addr + code_off[ch]);
-        const uint4 hi = lds128(stage_addr + code_off[ch] + row8_off);
-        wlo[ch][0] = lo.x;
-        wlo[ch][1] = lo.y;
-        wlo[ch][2] = lo.z;
-        wlo[ch][3] = lo.w;
-        whi[ch][0] = hi.x;
-        whi[ch][1] = hi.y;
-        whi[ch][2] = hi.z;
-        whi[ch][3] = hi.w;
-        if (BITS == 4)
-        {
-          s_lo[ch] = lds_half(stage_addr + scale_off[ch]);
-          s_hi[ch] = lds_half(stage_addr + scale_off[ch] + scale8_off);
-        }
-      }
-    }
-    __syncwarp();
-    if (lane == 0)
-    {
-      mbar_arrive(&empty_bar[s]);
-    }
-
     // yacc[mt][0..1]: row g, tokens 2t, 2t+1 of tile mt;  [2..3]: row g+8
     float yacc[MT][4];
 #pragma unroll
@@ -415,19 +441,62 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
     {
       yacc[mt][0] = yacc[mt][1] = yacc[mt][2] = yacc[mt][3] = 0.0f;
     }
+
+    // all shared-memory reads of the item first, so the stage can be released early and the
+    // MMAs of different chunks overlap
+    uint32_t wlo_all[NCH][4];
+    uint32_t whi_all[NCH][4];
+    float s_lo_all[NCH];
+    float s_hi_all[NCH];
 #pragma unroll
     for (int ch = 0; ch < NCH; ++ch)
     {
-      if (warp + ch * kComputeWarps < num_chunks)
+      s_lo_all[ch] = 0.0f;
+      s_hi_all[ch] = 0.0f;
+      if (warp + ch * WARPS < num_chunks)
       {
-        // two accumulation chains per token tile (even / odd words)
-        float c[2][MT][4];
+        const uint4 lo = lds128(stage_addr + code_off[ch]);
+        const uint4 hi = lds128(stage_addr + code_off[ch] + row8_off);
+        wlo_all[ch][0] = lo.x;
+        wlo_all[ch][1] = lo.y;
+        wlo_all[ch][2] = lo.z;
+        wlo_all[ch][3] = lo.w;
+        whi_all[ch][0] = hi.x;
+        whi_all[ch][1] = hi.y;
+        whi_all[ch][2] = hi.z;
+        whi_all[ch][3] = hi.w;
+        if (BITS == 4)
+        {
+          s_lo_all[ch] = lds_half(stage_addr + scale_off[ch]);
+          s_hi_all[ch] = lds_half(stage_addr + scale_off[ch] + scale8_off);
+        }
+      }
+    }
+    // every read of the stage has been issued: count this warp out
+    __syncwarp();
+    if (lane == 0)
+    {
+      mbar_arrive(&empty_bar[s]);
+    }
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch)
+    {
+      const uint32_t(&wlo)[4] = wlo_all[ch];
+      const uint32_t(&whi)[4] = whi_all[ch];
+      const float s_lo = s_lo_all[ch];
+      const float s_hi = s_hi_all[ch];
+      if (warp + ch * WARPS < num_chunks)
+      {
+        float c[CHAINS][MT][4];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
         {
           c[0][mt][0] = c[0][mt][2] = (BITS == 4) ? sx[ch][mt][0] : 0.0f;  // -136 * sum(x): ends as sum(x * q)
           c[0][mt][1] = c[0][mt][3] = (BITS == 4) ? sx[ch][mt][1] : 0.0f;
-          c[1][mt][0] = c[1][mt][1] = c[1][mt][2] = c[1][mt][3] = 0.0f;
+          if (CHAINS == 2)
+          {
+            c[CHAINS - 1][mt][0] = c[CHAINS - 1][mt][1] = c[CHAINS - 1][mt][2] = c[CHAINS - 1][mt][3] = 0.0f;
+          }
         }
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi)
@@ -437,16 +506,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
             uint32_t a_lo[4];
             uint32_t a_hi[4];
             {
-              const uint32_t ev = lop3_and_xor(wlo[ch][wi], 0x0F0F0F0Fu, 0x08080808u);
-              const uint32_t od = lop3_and_xor(wlo[ch][wi] >> 4, 0x0F0F0F0Fu, 0x08080808u);
+              const uint32_t ev = lop3_and_xor(wlo[wi], 0x0F0F0F0Fu, 0x08080808u);
+              const uint32_t od = lop3_and_xor(wlo[wi] >> 4, 0x0F0F0F0Fu, 0x08080808u);
               a_lo[0] = __byte_perm(ev, 0x43434343u, 0x4240);
               a_lo[1] = __byte_perm(ev, 0x43434343u, 0x4341);
               a_lo[2] = __byte_perm(od, 0x43434343u, 0x4240);
               a_lo[3] = __byte_perm(od, 0x43434343u, 0x4341);
             }
             {
-              const uint32_t ev = lop3_and_xor(whi[ch][wi], 0x0F0F0F0Fu, 0x08080808u);
-              const uint32_t od = lop3_and_xor(whi[ch][wi] >> 4, 0x0F0F0F0Fu, 0x08080808u);
+              const uint32_t ev = lop3_and_xor(whi[wi], 0x0F0F0F0Fu, 0x08080808u);
+              const uint32_t od = lop3_and_xor(whi[wi] >> 4, 0x0F0F0F0Fu, 0x08080808u);
               a_hi[0] = __byte_perm(ev, 0x43434343u, 0x4240);
               a_hi[1] = __byte_perm(ev, 0x43434343u, 0x4341);
               a_hi[2] = __byte_perm(od, 0x43434343u, 0x4240);
@@ -459,7 +528,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
 #pragma unroll
               for (int mt = 0; mt < MT; ++mt)
               {
-                mma_bf16_16816(c[h][mt], a_lo[2 * h], a_hi[2 * h], a_lo[2 * h + 1], a_hi[2 * h + 1],
+                mma_bf16_16816(c[h % CHAINS][mt], a_lo[2 * h], a_hi[2 * h], a_lo[2 * h + 1], a_hi[2 * h + 1],
                                xf[ch][mt][2 * j], xf[ch][mt][2 * j + 1]);
               }
             }
@@ -472,15 +541,15 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
             for (int sh = 0; sh < 2; ++sh)
             {
               const uint32_t sel = sh ? 0x4341u : 0x4240u;
-              const uint32_t pl = __byte_perm(wlo[ch][wi], 0u, sel);
-              const uint32_t ph = __byte_perm(whi[ch][wi], 0u, sel);
+              const uint32_t pl = __byte_perm(wlo[wi], 0u, sel);
+              const uint32_t ph = __byte_perm(whi[wi], 0u, sel);
               a_lo[sh] = sub_bf16x2(lop3_and_or(pl, 0x007F007Fu, 0x43004300u), lop3_and_or(pl, 0x00800080u, 0x43004300u));
               a_hi[sh] = sub_bf16x2(lop3_and_or(ph, 0x007F007Fu, 0x43004300u), lop3_and_or(ph, 0x00800080u, 0x43004300u));
             }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
             {
-              mma_bf16_16816(c[wi & 1][mt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], xf[ch][mt][2 * wi],
+              mma_bf16_16816(c[wi % CHAINS][mt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], xf[ch][mt][2 * wi],
                              xf[ch][mt][2 * wi + 1]);
             }
           }
@@ -488,141 +557,289 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const Decode
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
         {
+          float sum[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+          {
+            sum[i] = (CHAINS == 2) ? (c[0][mt][i] + c[CHAINS - 1][mt][i]) : c[0][mt][i];
+          }
           if (BITS == 4)
           {
             // the chunk lies inside one scale group of rows g and g+8; scaling per
             // 128-element chunk equals scaling per group up to rounding order
-            yacc[mt][0] = fmaf(s_lo[ch], c[0][mt][0] + c[1][mt][0], yacc[mt][0]);
-            yacc[mt][1] = fmaf(s_lo[ch], c[0][mt][1] + c[1][mt][1], yacc[mt][1]);
-            yacc[mt][2] = fmaf(s_hi[ch], c[0][mt][2] + c[1][mt][2], yacc[mt][2]);
-            yacc[mt][3] = fmaf(s_hi[ch], c[0][mt][3] + c[1][mt][3], yacc[mt][3]);
+            yacc[mt][0] = fmaf(s_lo, sum[0], yacc[mt][0]);
+            yacc[mt][1] = fmaf(s_lo, sum[1], yacc[mt][1]);
+            yacc[mt][2] = fmaf(s_hi, sum[2], yacc[mt][2]);
+            yacc[mt][3] = fmaf(s_hi, sum[3], yacc[mt][3]);
           }
           else
           {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
             {
-              yacc[mt][i] += c[0][mt][i] + c[1][mt][i];
+              yacc[mt][i] += sum[i];
             }
           }
         }
       }
     }
-    // park this warp's partial sums of the item; nobody reads them before the end
-    const uint32_t dst = part_base + static_cast<uint32_t>(it) * kPartItemBytes + part_write_off;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    // park this warp's partial sums of the item; nobody reads them before the end of the kernel
     {
-      const uint32_t d = dst + static_cast<uint32_t>(8 * mt * kItemRows) * 4u;
-      sts_f32(d, yacc[mt][0]);                         // token 2t,   row g
-      sts_f32(d + kItemRows * 4u, yacc[mt][1]);        // token 2t+1, row g
-      sts_f32(d + 8u * 4u, yacc[mt][2]);               // token 2t,   row g+8
-      sts_f32(d + (kItemRows + 8u) * 4u, yacc[mt][3]); // token 2t+1, row g+8
+      const uint32_t d0 = part_base + static_cast<uint32_t>(it) * part_item_bytes;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+      {
+        if (MT == 2 || 2 * t < p.tokp)
+        {
+          const uint32_t d = d0 + part_write_off[mt];
+          sts_f32x2(d, yacc[mt][0], yacc[mt][1]);                                        // row g,   tokens 2t, 2t+1
+          sts_f32x2(d + static_cast<uint32_t>(8 * p.tokp) * 4u, yacc[mt][2], yacc[mt][3]);  // row g+8
+        }
+      }
     }
-    // warp 0 refills this item's stage once all warps have read it (they read
-    // it at the top of the iteration, so by now this rarely waits)
+    // warp 0 refills this item's stage once all warps have read it (they read it at the top of the
+    // iteration, so by now this rarely waits)
     if (warp == 0 && it + stages < my_items)
     {
-      mbar_wait(&empty_bar[s], s_par);
-      issue(it + stages, s);
+      ok = mbar_wait(&empty_bar[s], s_par, p.spin_limit, abort_word);
+      if (!ok)
+      {
+        break;
+      }
+      if (lane == 0)
+      {
+        issue(it + stages, s);
+      }
+      issued_items = it + stages + 1;
     }
+
     if (++s == stages)
     {
       s = 0;
       s_par ^= 1u;
     }
   }
-  __syncthreads();
-
-  // Cross-warp reduction: output (item, token, row) = sum over the 16 warps.
-  float tensor_scale = 1.0f;
-  if (BITS == 8 && p.scales != nullptr)
+  if (!ok && warp == 0)
   {
-    tensor_scale = static_cast<const float *>(p.scales)[0];
+    // A wait ran out.  Before the CTA gives its shared memory back, every copy that was started
+    // into the ring must have landed (a copy must not arrive in memory that already belongs to
+    // another CTA).  Warp 0 started them all and waits for those it has not consumed; these waits
+    // are bounded too.  (A warp that leaves the loop normally has consumed every item.)
+    for (int st = 0; st < stages && st < issued_items; ++st)
+    {
+      // the last item started into this stage; once it has landed the earlier ones have too
+      const int j = issued_items - 1 - ((issued_items - 1 - st) % stages);
+      const uint32_t addr = smem_u32(&full_bar[st]);
+      const uint32_t parity = static_cast<uint32_t>(j / stages) & 1u;
+      bool done = false;
+      for (uint32_t spin = 0; spin < p.spin_limit && !done; ++spin)
+      {
+        done = mbar_try(addr, parity);
+      }
+    }
   }
-  const int outputs = my_items * kItemRows * TOK;
-  for (int o = tid; o < outputs; o += kThreads)
+  __syncthreads();
+  if (*abort_word != 0u)
   {
-    const int r = o % kItemRows;
-    const int token = (o / kItemRows) % TOK;
-    const int item = o / (kItemRows * TOK);
-    const uint32_t src =
-        part_base + static_cast<uint32_t>(item) * kPartItemBytes + static_cast<uint32_t>(token * kItemRows + r) * 4u;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    return;   // outputs stay unwritten; the host sees the flag
+  }
+
+  // Cross-warp reduction: an output is the sum of its WARPS partial sums in warp order.
+  if (MT == 2)
+  {
+    // a thread takes four tokens of one row; consecutive lanes take consecutive rows, so the stores
+    // of a token are contiguous across the warp
+    const int n = my_items * 64;
+    for (int o = tid; o < n; o += WARPS * 32)
+    {
+      const int r16 = o & 15;
+      const int tq = (o >> 4) & 3;
+      const int item = o >> 6;
+      const int quad = tq ^ ((r16 >> 1) & 3);
+      const uint32_t src = part_base + static_cast<uint32_t>(item) * part_item_bytes +
+                           static_cast<uint32_t>(r16 * 16 + 4 * quad) * 4u;
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int w = 0; w < kComputeWarps; ++w)
-    {
-      acc[w & 3] += lds_f32(src + static_cast<uint32_t>(w) * kPartWarpBytes);
+      for (int w = 0; w < WARPS; ++w)
+      {
+        const uint4 v = lds128(src + static_cast<uint32_t>(w) * part_warp_bytes);
+        acc[0] += __uint_as_float(v.x);
+        acc[1] += __uint_as_float(v.y);
+        acc[2] += __uint_as_float(v.z);
+        acc[3] += __uint_as_float(v.w);
+      }
+      const int row = row_begin + item * kItemRows + r16;
+      if (row < row_end)
+      {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+          const int token = 4 * tq + i;
+          if (token < p.m)
+          {
+            const float v = (BITS == 8) ? acc[i] * tensor_scale : acc[i];
+            const int64_t idx = static_cast<int64_t>(token) * p.y_ld + p.y_col0 + row;
+            for (int r = 0; r < p.num_y; ++r)
+            {
+              store_from_float(p.y[r], idx, p.y_dtype, v);
+            }
+          }
+        }
+      }
     }
-    float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    if (BITS == 8)
+  }
+  else
+  {
+    // a thread takes four consecutive rows of one live token
+    const int quads = my_items * 4 * p.m;
+    for (int o = tid; o < quads; o += WARPS * 32)
     {
-      sum *= tensor_scale;
-    }
-    const int row = row_begin + item * kItemRows + r;
-    if (token < p.m && row < row_end)
-    {
+      const int rq = o & 3;
+      const int token = (o >> 2) % p.m;
+      const int item = (o >> 2) / p.m;
+      const uint32_t src = part_base + static_cast<uint32_t>(item) * part_item_bytes +
+                           static_cast<uint32_t>((4 * rq) * p.tokp + token) * 4u;
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w)
+      {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+          acc[i] += lds_f32(src + static_cast<uint32_t>(w) * part_warp_bytes + static_cast<uint32_t>(i * p.tokp) * 4u);
+        }
+      }
+      if (BITS == 8)
+      {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+          acc[i] *= tensor_scale;
+        }
+      }
+      const int row = row_begin + item * kItemRows + 4 * rq;
       // plain stores; with peers they travel over NVLink and are complete when the kernel is
       const int64_t idx = static_cast<int64_t>(token) * p.y_ld + p.y_col0 + row;
-      for (int r = 0; r < p.num_y; ++r)
+      if (p.vec4 && row + 3 < row_end)
       {
-        store_from_float(p.y[r], idx, p.y_dtype, sum);
+        const float4 v = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        for (int r = 0; r < p.num_y; ++r)
+        {
+          *reinterpret_cast<float4 *>(static_cast<float *>(p.y[r]) + idx) = v;
+        }
+      }
+      else
+      {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+        {
+          if (row + i < row_end)
+          {
+            for (int r = 0; r < p.num_y; ++r)
+            {
+              store_from_float(p.y[r], idx + i, p.y_dtype, acc[i]);
+            }
+          }
+        }
       }
     }
   }
 }
 
+// Per device: the SM count (CAIFQ_DECODE_CTAS caps the grid for a host that runs a collective
+// beside this kernel and wants to leave it a few SMs).
 int sm_count()
 {
-  static int cached = 0;
-  if (cached == 0)
+  static std::atomic<int> cached[kMaxDevices];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices)
   {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
-    if (cached <= 0)
+    dev = 0;
+  }
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v == 0)
+  {
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    if (v <= 0)
     {
-      cached = 148;
+      v = 148;
     }
-    // A host that runs a collective beside this kernel (column-parallel decode) can leave it a few
-    // SMs: the kernel keeps one CTA per SM, and a CTA that finds its SM taken waits for the whole
-    // collective.  CAIFQ_DECODE_CTAS caps the grid.
     if (const char *e = std::getenv("CAIFQ_DECODE_CTAS"))
     {
-      const int v = std::atoi(e);
-      if (v >= 1 && v < cached)
+      const int cap = std::atoi(e);
+      if (cap >= 1 && cap < v)
       {
-        cached = v;
+        v = cap;
       }
     }
+    cached[dev].store(v, std::memory_order_relaxed);
   }
-  return cached;
+  return v;
 }
+
+// Streams (per device) on which one of this library's calls has just written codes or scales.
+std::mutex g_written_mutex;
+std::vector<std::pair<int, cudaStream_t>> g_written;
+
+thread_local bool t_stall_next = false;
 
 }  // namespace
 
-namespace
+void note_codes_written(cudaStream_t s)
 {
-std::atomic<bool> g_codes_written{false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_written_mutex);
+  for (const auto &e : g_written)
+  {
+    if (e.first == dev && e.second == s)
+    {
+      return;
+    }
+  }
+  g_written.emplace_back(dev, s);
 }
 
-void note_codes_written() { g_codes_written.store(true, std::memory_order_relaxed); }
+bool take_codes_written(cudaStream_t s)
+{
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(g_written_mutex);
+  for (size_t i = 0; i < g_written.size(); ++i)
+  {
+    if (g_written[i].first == dev && g_written[i].second == s)
+    {
+      g_written.erase(g_written.begin() + static_cast<std::ptrdiff_t>(i));
+      return true;
+    }
+  }
+  return false;
+}
 
-bool take_codes_written() { return g_codes_written.exchange(false, std::memory_order_relaxed); }
+void decode_stall_next_launch() { t_stall_next = true; }
+
 
 namespace
 {
 
 template <int BITS, int MT, int NCH>
-int launch_decode_inst(const DecodeParams &p, cudaStream_t s)
+int launch_decode_inst(const DecodeParams &p, uint32_t smem, cudaStream_t s)
 {
   auto kernel = linear_decode_kernel<BITS, MT, NCH>;
-  const size_t smem = p.smem_bytes;
-  static bool configured = false;
-  if (!configured)
+  static std::atomic<bool> configured[kMaxDevices];
+  int dev = 0;
+  CAIFQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
   {
-    CAIFQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
-    configured = true;
+    set_error("frozen linear (decode): device ordinal %d out of range", dev);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  if (!configured[dev].load(std::memory_order_acquire))
+  {
+    CAIFQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(kSmemBudget)));
+    configured[dev].store(true, std::memory_order_release);
   }
   int grid = sm_count();
   if (grid > p.num_quanta)
@@ -642,16 +859,39 @@ int launch_decode_inst(const DecodeParams &p, cudaStream_t s)
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = (pdl && !take_codes_written()) ? 1 : 0;
+  // codes written just ahead in this stream by one of the library's own calls: a plain launch
+  // orders the early copies behind that kernel
+  cfg.numAttrs = (pdl && !take_codes_written(s)) ? 1 : 0;
   CAIFQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
 
-// Shared memory for the parked partial sums: the largest number of items any CTA gets.
-uint32_t partial_bytes_for(int out_dim, int mt)
+int chunks_per_warp(const caifq_weight &w)
 {
-  const int quanta = (out_dim + kRowQuantum - 1) / kRowQuantum;
+  const int chunk_k = (w.storage == CAIFQ_I4) ? 128 : 64;
+  const int chunks = w.in_dim / chunk_k;
+  return (chunks + kWarps - 1) / kWarps;
+}
+
+int tokp_for(int64_t m) { return m <= 2 ? 2 : (m <= 4 ? 4 : (m <= 8 ? 8 : 16)); }
+
+struct Layout
+{
+  uint32_t stage_bytes;
+  uint32_t partial_bytes;
+  int stages;
+};
+
+Layout layout_for(const caifq_weight &w, int64_t m)
+{
+  Layout l{};
+  const bool i4 = (w.storage == CAIFQ_I4);
+  const uint32_t row_bytes = i4 ? static_cast<uint32_t>(w.in_dim / 2) : static_cast<uint32_t>(w.in_dim);
+  const uint32_t scale_bytes = i4 ? static_cast<uint32_t>(kItemRows * (w.in_dim / w.group_size) * 2) : 0u;
+  l.stage_bytes = ((kItemRows * row_bytes + scale_bytes) + 127u) & ~127u;
+  // parked partial sums of every item a CTA can get: [item][warp][16 rows][tokp]
+  const int quanta = (w.out_dim + kRowQuantum - 1) / kRowQuantum;
   int grid = sm_count();
   if (grid > quanta)
   {
@@ -659,14 +899,19 @@ uint32_t partial_bytes_for(int out_dim, int mt)
   }
   const int max_quanta = (quanta + grid - 1) / grid;
   const int max_items = (max_quanta * kRowQuantum + kItemRows - 1) / kItemRows;
-  return static_cast<uint32_t>(max_items * kComputeWarps * kItemRows * 8 * mt * sizeof(float));
-}
-
-int chunks_per_warp(const caifq_weight &w)
-{
-  const int chunk_k = (w.storage == CAIFQ_I4) ? 128 : 64;
-  const int chunks = w.in_dim / chunk_k;
-  return (chunks + kComputeWarps - 1) / kComputeWarps;
+  l.partial_bytes = static_cast<uint32_t>(max_items * kWarps * kItemRows * tokp_for(m) * sizeof(float));
+  int stages =
+      (kSmemBudget > l.partial_bytes) ? static_cast<int>((kSmemBudget - l.partial_bytes) / l.stage_bytes) : 0;
+  // Three items in flight per SM are enough to cover the latency of HBM.  More of them make the
+  // launch slower, not faster (measured on B200: 10.8 us per launch with three, 11.3 with four,
+  // 12.8 with six at in=4096, out=14336): every SM then asks for its whole share at once and the
+  // first item of each lands later.
+  if (stages > kRingDepth)
+  {
+    stages = kRingDepth;
+  }
+  l.stages = stages;
+  return l;
 }
 
 }  // namespace
@@ -722,26 +967,24 @@ bool decode_supported(const LinearArgs &args)
   {
     return false;
   }
-  const int nch = chunks_per_warp(w);
-  const int xr = (w.storage == CAIFQ_I4) ? 16 : 8;
-  const int mt = (m > 8) ? 2 : 1;
-  if (nch * xr * mt > 64 || nch > 8)
   {
-    return false;
-  }
-  // at least two ring stages must fit beside the partial-sum buffers
-  {
-    const uint32_t row_bytes = (w.storage == CAIFQ_I4) ? static_cast<uint32_t>(w.in_dim / 2) : static_cast<uint32_t>(w.in_dim);
-    const uint32_t row_stride = row_bytes;
-    const uint32_t scale_bytes =
-        (w.storage == CAIFQ_I4) ? static_cast<uint32_t>(kItemRows * (w.in_dim / w.group_size) * 2) : 0u;
-    const uint32_t stage_bytes = ((kItemRows * row_stride + scale_bytes) + 127u) & ~127u;
-    if (2u * stage_bytes + partial_bytes_for(w.out_dim, mt) > kSmemBudget)
+    // the token fragments of a warp's chunks must fit 64 registers
+    const int nch = chunks_per_warp(w);
+    const int xr = (w.storage == CAIFQ_I4) ? 16 : 8;
+    const int mt = (m > 8) ? 2 : 1;
+    if (nch * xr * mt > 64 || nch > 8)
     {
       return false;
     }
   }
-  if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(w.scales) & 15u) != 0)
+  // at least two ring stages must fit beside the parked partial sums
+  if (layout_for(w, m).stages < 2)
+  {
+    return false;
+  }
+  // bulk copies and 16-byte loads need aligned operands; a misaligned call goes to another kernel
+  if ((reinterpret_cast<uintptr_t>(w.codes) & 15u) != 0 || (reinterpret_cast<uintptr_t>(w.scales) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(args.a) & 15u) != 0)
   {
     return false;
   }
@@ -751,19 +994,12 @@ bool decode_supported(const LinearArgs &args)
 int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
 {
   const caifq_weight &w = args.w;
-  const void *x = args.a;
   const int64_t m = args.m;
-  void *y = args.c;
   const int y_dtype = args.c_dtype;
-  if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0)
-  {
-    set_error("frozen linear (decode): x must be 16-byte aligned");
-    return CAIFQ_ERR_INVALID;
-  }
   DecodeParams p{};
   p.codes = static_cast<const uint8_t *>(w.codes);
   p.scales = w.scales;
-  p.x = static_cast<const __nv_bfloat16 *>(x);
+  p.x = static_cast<const __nv_bfloat16 *>(args.a);
   if (args.num_peers > 0)
   {
     if (args.num_peers > kMaxPeers || args.c_peers == nullptr)
@@ -786,13 +1022,23 @@ int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
   }
   else
   {
-    p.y[0] = y;
+    p.y[0] = args.c;
     p.num_y = 1;
     p.y_ld = w.out_dim;
     p.y_col0 = 0;
   }
   p.y_dtype = y_dtype;
+  // four rows of one token as one 16-byte store: fp32 results whose rows of four start aligned
+  p.vec4 = (y_dtype == CAIFQ_F32 && (p.y_ld % 4) == 0 && (p.y_col0 % 4) == 0) ? 1 : 0;
+  for (int r = 0; r < p.num_y; ++r)
+  {
+    if ((reinterpret_cast<uintptr_t>(p.y[r]) & 15u) != 0)
+    {
+      p.vec4 = 0;
+    }
+  }
   p.m = static_cast<int>(m);
+  p.tokp = tokp_for(m);
   p.in_dim = w.in_dim;
   p.out_dim = w.out_dim;
   p.num_quanta = (w.out_dim + kRowQuantum - 1) / kRowQuantum;
@@ -801,25 +1047,18 @@ int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
   // rows lie unpadded, as in memory, so one bulk copy fills a stage; the 2-way
   // bank conflict on the four 16-byte reads per item is noise
   p.row_stride = p.row_bytes;
-  uint32_t scale_bytes = 0;
   if (i4)
   {
     p.groups_per_row = w.in_dim / w.group_size;
     p.chunks_per_group = w.group_size / 128;
-    scale_bytes = static_cast<uint32_t>(kItemRows * p.groups_per_row * 2);
   }
   else
   {
     p.groups_per_row = 0;
     p.chunks_per_group = 1;
   }
-  p.stage_bytes = ((kItemRows * p.row_stride + scale_bytes) + 127u) & ~127u;
-  const uint32_t partial_bytes = partial_bytes_for(w.out_dim, (m > 8) ? 2 : 1);
-  int stages = static_cast<int>((kSmemBudget - partial_bytes) / p.stage_bytes);
-  if (stages > kMaxStages)
-  {
-    stages = kMaxStages;
-  }
+  const Layout lay = layout_for(w, m);
+  int stages = lay.stages;
   if (const char *e = std::getenv("CAIFQ_DECODE_STAGES"))
   {
     const int v = std::atoi(e);
@@ -833,16 +1072,26 @@ int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
     set_error("frozen linear (decode): row too long for the shared-memory ring");
     return CAIFQ_ERR_UNSUPPORTED;
   }
+  p.stage_bytes = lay.stage_bytes;
   p.stages = stages;
   p.partial_offset = static_cast<uint32_t>(stages) * p.stage_bytes;
-  p.smem_bytes = p.partial_offset + partial_bytes;
+  const uint32_t smem_bytes = p.partial_offset + lay.partial_bytes;
+  p.spin_limit = kSpinLimit;
+  p.stall_bytes = 0;
+  if (t_stall_next)
+  {
+    // self-test of the give-up path: the first item announces 16 bytes that never arrive
+    t_stall_next = false;
+    p.spin_limit = kSpinLimitTest;
+    p.stall_bytes = 16;
+  }
 
   const int nch = chunks_per_warp(w);
   const int mt = (m > 8) ? 2 : 1;
-#define CAIFQ_DECODE_CASE(B, M, N)        \
-  if (nch <= N && mt == M)                \
-  {                                       \
-    return launch_decode_inst<B, M, N>(p, s); \
+#define CAIFQ_DECODE_CASE(B, M, N)                          \
+  if (nch <= N && mt == M)                                  \
+  {                                                         \
+    return launch_decode_inst<B, M, N>(p, smem_bytes, s);   \
   }
   if (i4)
   {

@@ -99,6 +99,14 @@ CAIFQ_API const char *caifq_version(void);
  * itself failed) and clears them.
  */
 CAIFQ_API int caifq_device_status(void);
+/*
+ * Self-test of that give-up path (no counterpart in the reference): the next few-token
+ * caifq_linear_fwd / caifq_linear_fwd_gather call of the calling thread is launched with a short
+ * wait limit and announces 16 bytes for its first copy that never arrive.  The kernel returns
+ * within milliseconds without writing its outputs, the GPU context stays usable, and
+ * caifq_device_status() then reports bit 0.  Nothing faults and nothing hangs.
+ */
+CAIFQ_API void caifq_selftest_stall_next_decode(void);
 
 /* ---- quantize / dequantize (bit-exact with the reference kernels) -------- */
 

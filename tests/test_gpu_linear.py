@@ -272,3 +272,44 @@ def test_umma_config3_shape_matches_generic_and_oracle_rows(monkeypatch):
     assert max_rel_err(y[rows].cpu().numpy(), want) <= TOL_F32
     want_dx = orc.gemm_nn(dy[rows].float().cpu().numpy(), wc)
     assert max_rel_err(dx[rows].cpu().numpy(), want_dx) <= TOL_F32
+
+
+def test_decode_misaligned_activations_fall_back():
+    """bf16 activations that do not start on a 16-byte boundary (a row slice of a larger tensor)
+    are a legal call: the few-token kernel declines them and another kernel family answers."""
+    rng = np.random.default_rng(77)
+    weight, codes, scales = make_weight(rng, 136, 1024, orc.I8)
+    x_np, x = act(rng, 4, 1024, orc.BF16)
+    big = torch.zeros(4 * 1024 + 8, dtype=torch.bfloat16, device="cuda")
+    shifted = big[1:1 + 4 * 1024].view(4, 1024)     # starts 2 bytes past an aligned address
+    shifted.copy_(x)
+    assert shifted.data_ptr() % 16 == 2
+    y = nv.linear_fwd(weight, shifted, torch.float32, orc.F32)
+    assert nv.last_path() != "decode"
+    wc = _oracle_w(weight, codes, scales, orc.F32)
+    assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc)) <= TOL_F32
+
+
+def test_decode_wait_that_runs_out_raises_the_flag_and_returns():
+    """The library's self-test of its bounded waits: the next few-token launch announces bytes that
+    never arrive, with a short wait limit.  The kernel must return (no hang, no fault), the status
+    word must report the few-token kernel (bit 0), and the next call must be healthy again."""
+    import time
+
+    rng = np.random.default_rng(78)
+    weight, codes, scales = make_weight(rng, 1024, 4096, orc.I4)
+    x_np, x = act(rng, 4, 4096, orc.BF16)
+    wc = _oracle_w(weight, codes, scales, orc.F32)
+    want = orc.frozen_linear_forward(x_np, wc)
+    y = nv.linear_fwd(weight, x, torch.float32, orc.F32)
+    assert nv.last_path() == "decode"
+    assert nv.lib().caifq_device_status() == 0
+    nv.lib().caifq_selftest_stall_next_decode()
+    t0 = time.time()
+    nv.linear_fwd(weight, x, torch.float32, orc.F32)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0
+    assert nv.lib().caifq_device_status() & 1
+    y = nv.linear_fwd(weight, x, torch.float32, orc.F32)
+    assert nv.lib().caifq_device_status() == 0
+    assert max_rel_err(y.cpu().numpy(), want) <= TOL_F32
