@@ -35,6 +35,8 @@ void set_path(const char *name) { t_path = name; }
 int launch_moe_topk(const void *probs, int dtype, int *indices, void *values, int batch, int dim, int k,
                     cudaStream_t s);
 int launch_moe_normalize_rows(const void *input, void *output, int dtype, int batch, int dim, cudaStream_t s);
+int launch_moe_router_softmax(const void *logits, const void *bias, void *probs, int dtype, int rows, int cols,
+                              cudaStream_t s);
 int launch_moe_build_dispatch(const int *expert_indices, int num_tokens, int top_k, int num_experts, int capacity,
                               int *dispatch_map, int *expert_offsets, cudaStream_t s);
 int launch_moe_dispatch(const void *input, int dtype, const int *expert_indices, const int *dispatch_map,
@@ -713,6 +715,27 @@ int caifq_moe_normalize_rows(const void *input, void *output, int32_t dtype, int
   CAIFQ_CHECK_ARG(batch >= 0 && dim > 0, "caifq_moe_normalize_rows: bad shape");
   CAIFQ_CHECK_ARG(batch == 0 || (input && output), "caifq_moe_normalize_rows: null pointer");
   return launch_moe_normalize_rows(input, output, dtype, batch, dim, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_router_softmax(const void *logits, const void *bias, void *probs, int32_t dtype, int32_t rows,
+                             int32_t cols, void *stream)
+{
+  CAIFQ_CHECK_ARG(rows >= 0 && cols > 0, "caifq_moe_router_softmax: bad shape");
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "caifq_moe_router_softmax: dtype must be F32, F16 or BF16");
+  CAIFQ_CHECK_ARG(rows == 0 || (logits && probs), "caifq_moe_router_softmax: null pointer");
+  return launch_moe_router_softmax(logits, bias, probs, dtype, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_scale(const void *src, void *dst, int32_t dtype, float factor, int64_t n, void *stream)
+{
+  CAIFQ_CHECK_ARG(n >= 0, "caifq_scale: negative n");
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "caifq_scale: dtype must be F32, F16 or BF16");
+  CAIFQ_CHECK_ARG(n == 0 || (src && dst), "caifq_scale: null pointer");
+  if (n == 0)
+  {
+    return CAIFQ_OK;
+  }
+  return launch_scale(src, dst, dtype, factor, n, static_cast<cudaStream_t>(stream));
 }
 
 int caifq_moe_build_dispatch(const int32_t *expert_indices, int32_t num_tokens, int32_t top_k, int32_t num_experts,

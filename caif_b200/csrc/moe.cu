@@ -147,6 +147,95 @@ __global__ void normalize_rows_kernel(const T *__restrict__ input, T *__restrict
   }
 }
 
+// ---------------------------------------------------------------- router softmax
+// CAIF_DeviceMoERouter::Route turns logits into probabilities with the attention softmax kernel
+// (src/caif_cuda_kernels_attention_support.cu:350-460) after an optional AddBias
+// (src/caif_cuda_kernels_elementwise.cu:124-137, which stores T(float(x) + float(bias))).  The routing
+// indices depend on the exact probabilities, so the order of every operation is kept: the reference
+// runs 128 threads per row, thread t scanning columns t, t+128, ... with the online (max, sum)
+// update, then an xor butterfly inside each warp, then the four warp results combined in lanes 0-3
+// with offsets 2 and 1.  Here one warp owns a row: lane l plays threads l, l+32, l+64, l+96 (one
+// per warp of the reference), runs the same butterfly on each of the four values, and combines them
+// in the reference's order.  Far fewer idle threads for rows of 64-256 experts, identical bits.
+__device__ __forceinline__ void softmax_absorb(float &m, float &s, float m_other, float s_other)
+{
+  if (m_other > m)
+  {
+    s = s * expf(m - m_other) + s_other;
+    m = m_other;
+  }
+  else
+  {
+    s += s_other * expf(m_other - m);
+  }
+}
+
+template <typename T>
+__global__ void router_softmax_kernel(const T *__restrict__ logits, const T *__restrict__ bias,
+                                      T *__restrict__ probs, int rows, int cols)
+{
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (row >= rows)
+  {
+    return;
+  }
+  const T *x = logits + static_cast<size_t>(row) * cols;
+  T *y = probs + static_cast<size_t>(row) * cols;
+  // the value the softmax sees: the logit, or the biased logit rounded to T as the separate
+  // AddBias kernel would have stored it
+  auto value = [&](int col) -> float
+  {
+    float v = to_f<T>(x[col]);
+    if (bias != nullptr)
+    {
+      v = to_f<T>(from_f<T>(v + to_f<T>(bias[col])));
+    }
+    return v;
+  };
+  float m[4];
+  float sum[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w)
+  {
+    // thread 32 w + lane of the reference's 128-thread block
+    m[w] = kNegSentinel;
+    sum[w] = 0.0f;
+    for (int col = 32 * w + lane; col < cols; col += 128)
+    {
+      const float v = value(col);
+      if (v > m[w])
+      {
+        sum[w] = sum[w] * expf(m[w] - v) + 1.0f;
+        m[w] = v;
+      }
+      else
+      {
+        sum[w] += expf(v - m[w]);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+    {
+      const float m_other = __shfl_xor_sync(0xFFFFFFFFu, m[w], off);
+      const float s_other = __shfl_xor_sync(0xFFFFFFFFu, sum[w], off);
+      softmax_absorb(m[w], sum[w], m_other, s_other);
+    }
+  }
+  // lanes 0..3 of the reference's warp 0 hold the four warp results; lane 0 ends with
+  // absorb(absorb(v0, v2), absorb(v1, v3))
+  softmax_absorb(m[0], sum[0], m[2], sum[2]);
+  softmax_absorb(m[1], sum[1], m[3], sum[3]);
+  softmax_absorb(m[0], sum[0], m[1], sum[1]);
+  const float row_max = m[0];
+  const float inv_sum = __fdiv_rn(1.0f, sum[0]);
+  for (int col = lane; col < cols; col += 32)
+  {
+    y[col] = from_f<T>(__fmul_rn(expf(value(col) - row_max), inv_sum));
+  }
+}
+
 // ------------------------------------------------------------------ dispatch map
 // Stable counting rank on the device.  One CTA walks the [T*k] index list in
 // chunks of blockDim entries; inside a chunk, warps rank equal experts with
@@ -692,6 +781,22 @@ int launch_moe_normalize_rows(const void *input, void *output, int dtype, int ba
   const int grid = (batch + warps - 1) / warps;
   CAIFQ_DISPATCH_FLOAT(dtype, (normalize_rows_kernel<T><<<grid, warps * 32, 0, s>>>(
                                   static_cast<const T *>(input), static_cast<T *>(output), batch, dim)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_router_softmax(const void *logits, const void *bias, void *probs, int dtype, int rows, int cols,
+                              cudaStream_t s)
+{
+  if (rows <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const int warps = 8;
+  const int grid = (rows + warps - 1) / warps;
+  CAIFQ_DISPATCH_FLOAT(dtype, (router_softmax_kernel<T><<<grid, warps * 32, 0, s>>>(
+                                  static_cast<const T *>(logits), static_cast<const T *>(bias),
+                                  static_cast<T *>(probs), rows, cols)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

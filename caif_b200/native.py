@@ -81,6 +81,8 @@ _SIGNATURES = {
                                                      _i64, _vp, _vp, _vp, _i32, _vp]),
     "caifq_moe_topk": (ctypes.c_int, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_normalize_rows": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_moe_router_softmax": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_scale": (ctypes.c_int, [_vp, _vp, _i32, ctypes.c_float, _i64, _vp]),
     "caifq_moe_build_dispatch": (ctypes.c_int, [_vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "caifq_moe_dispatch": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_combine": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
@@ -298,28 +300,40 @@ class Lora:
         return ctypes.byref(self.c)
 
 
-def lora_linear_fwd(w, lora, x, compute=F32):
+def lora_linear_fwd(w, lora, x, compute=F32, out=None, hidden=None, workspace=None):
+    """y = W-path(x) + (alpha/r) . (x . A^T) . B^T.  `out`, `hidden` and `workspace` (a uint8 tensor of at
+    least caifq_lora_fwd_workspace_bytes) may be passed in to keep the call free of allocations."""
     _need_cuda(x)
     m = x.numel() // w.in_dim
-    y = torch.empty(tuple(x.shape[:-1]) + (w.out_dim,), dtype=x.dtype, device=x.device)
-    hidden = torch.empty((m, lora.rank), dtype=x.dtype, device=x.device)
-    ws_bytes = lib().caifq_lora_fwd_workspace_bytes(w.ref(), lora.ref(), m)
-    ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=x.device)
-    _check(lib().caifq_lora_linear_fwd(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), _ptr(ws), compute,
-                                       _stream()), "lora_linear_fwd")
+    y = out if out is not None else torch.empty(tuple(x.shape[:-1]) + (w.out_dim,), dtype=x.dtype, device=x.device)
+    if hidden is None:
+        hidden = torch.empty((m, lora.rank), dtype=x.dtype, device=x.device)
+    ws_bytes = int(lib().caifq_lora_fwd_workspace_bytes(w.ref(), lora.ref(), m))
+    if workspace is None:
+        workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
+    elif workspace.numel() < ws_bytes:
+        raise CaifqError("lora_linear_fwd: workspace of %d bytes, %d needed" % (workspace.numel(), ws_bytes))
+    _check(lib().caifq_lora_linear_fwd(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), _ptr(workspace),
+                                       compute, _stream()), "lora_linear_fwd")
     return y, hidden
 
 
-def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32):
+def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32, dx=None, d_a=None, d_b=None, workspace=None):
     _need_cuda(dy, x, hidden)
     m = dy.numel() // w.out_dim
-    dx = torch.empty(tuple(dy.shape[:-1]) + (w.in_dim,), dtype=dy.dtype, device=dy.device)
-    d_a = torch.empty_like(lora.a)
-    d_b = torch.empty_like(lora.b)
-    ws_bytes = lib().caifq_lora_bwd_workspace_bytes(w.ref(), lora.ref(), m)
-    ws = torch.empty(max(int(ws_bytes), 1), dtype=torch.uint8, device=dy.device)
+    if dx is None:
+        dx = torch.empty(tuple(dy.shape[:-1]) + (w.in_dim,), dtype=dy.dtype, device=dy.device)
+    if d_a is None:
+        d_a = torch.empty_like(lora.a)
+    if d_b is None:
+        d_b = torch.empty_like(lora.b)
+    ws_bytes = int(lib().caifq_lora_bwd_workspace_bytes(w.ref(), lora.ref(), m))
+    if workspace is None:
+        workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dy.device)
+    elif workspace.numel() < ws_bytes:
+        raise CaifqError("lora_linear_bwd: workspace of %d bytes, %d needed" % (workspace.numel(), ws_bytes))
     _check(lib().caifq_lora_linear_bwd(w.ref(), lora.ref(), _ptr(dy), _ptr(x), _ptr(hidden), m, _ptr(dx), _ptr(d_a),
-                                       _ptr(d_b), _ptr(ws), compute, _stream()), "lora_linear_bwd")
+                                       _ptr(d_b), _ptr(workspace), compute, _stream()), "lora_linear_bwd")
     return dx, d_a, d_b
 
 
@@ -355,6 +369,24 @@ def moe_normalize_rows(x):
     out = torch.empty_like(x)
     _check(lib().caifq_moe_normalize_rows(_ptr(x), _ptr(out), dtype_code(x), batch, dim, _stream()),
            "moe_normalize_rows")
+    return out
+
+
+def moe_softmax(logits, bias=None):
+    """Router probabilities: softmax over the experts of each row, optional bias added first."""
+    _need_cuda(logits, bias)
+    rows, cols = logits.shape
+    probs = torch.empty_like(logits)
+    _check(lib().caifq_moe_router_softmax(_ptr(logits), _ptr(bias), _ptr(probs), dtype_code(logits), rows, cols,
+                                          _stream()), "moe_router_softmax")
+    return probs
+
+
+def scale(x, factor, out=None):
+    _need_cuda(x)
+    if out is None:
+        out = torch.empty_like(x)
+    _check(lib().caifq_scale(_ptr(x), _ptr(out), dtype_code(x), float(factor), x.numel(), _stream()), "scale")
     return out
 
 

@@ -100,14 +100,16 @@ class PeerBuffer:
         if rc != 0:
             raise RuntimeError("%s failed with CUDA error %d" % (what, rc))
 
-    def read(self, dtype, shape):
-        """A copy of this rank's buffer as a tensor (device-to-device copy on the current stream)."""
+    def read(self, dtype, shape, offset=0):
+        """A copy of this rank's buffer (from byte `offset`) as a tensor: a device-to-device copy on the
+        current stream."""
         out = torch.empty(shape, dtype=dtype, device=self.device)
         nbytes = out.numel() * out.element_size()
-        if nbytes > self.nbytes:
-            raise ValueError("the buffer holds %d bytes, %d asked" % (self.nbytes, nbytes))
+        if offset + nbytes > self.nbytes:
+            raise ValueError("the buffer holds %d bytes, %d asked at offset %d" % (self.nbytes, nbytes, offset))
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        self._check(self.cudart().cudaMemcpyAsync(out.data_ptr(), self._base, nbytes, 3, stream),   # 3: device to device
+        src = ctypes.c_void_p(self._base.value + offset)
+        self._check(self.cudart().cudaMemcpyAsync(out.data_ptr(), src, nbytes, 3, stream),   # 3: device to device
                     "cudaMemcpyAsync")
         return out
 
@@ -150,6 +152,7 @@ class ColumnParallelFrozenLinear:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.begin, self.end = shard_range(out_dim, self.world, self.rank)
+        self._gather_calls = 0
 
     def forward(self, x):
         y_local = self.fwd(x)                                    # [m, out/N]
@@ -164,11 +167,26 @@ class ColumnParallelFrozenLinear:
     def forward_gather(self, fwd_gather, x, peer_buffer, out_dtype=torch.float32):
         """Few-token forward with the gather fused into the kernel: fwd_gather(x, ptrs, y_ld, y_col0)
         stores this rank's [m, out/N] slice into every rank's [m, out] buffer.  Returns this rank's
-        full Y once all ranks' kernels are complete (a stream-ordered barrier collective)."""
+        full Y once all ranks' kernels are complete (a stream-ordered barrier collective).
+
+        Buffer reuse: the peer buffer is used as two halves, alternating per call.  A rank can only
+        start call n+2 (which writes the half that call n used) after it has passed the barrier of
+        call n+1, and that barrier completes on it only after every rank has enqueued its own barrier of
+        call n+1, which is ordered behind that rank's read of call n on its stream.  So a fast rank
+        never overwrites a result a slower rank is still reading, without a second barrier per call.
+        The buffer must hold 2 * m * out elements of `out_dtype`."""
         m = x.shape[0]
-        fwd_gather(x, peer_buffer.ptrs, self.out_dim, self.begin)
+        elem = torch.empty((), dtype=out_dtype).element_size()
+        half_bytes = m * self.out_dim * elem
+        if 2 * half_bytes > peer_buffer.nbytes:
+            raise ValueError("the peer buffer holds %d bytes; two results of %d bytes are needed"
+                             % (peer_buffer.nbytes, half_bytes))
+        half = self._gather_calls & 1
+        self._gather_calls += 1
+        off = half * half_bytes
+        fwd_gather(x, [q + off for q in peer_buffer.ptrs], self.out_dim, self.begin)
         dist.barrier(group=self.group)   # NCCL: a collective kernel behind this rank's stores on the stream
-        return peer_buffer.read(out_dtype, (m, self.out_dim))
+        return peer_buffer.read(out_dtype, (m, self.out_dim), offset=off)
 
     def backward(self, dy):
         part = self.dx(dy[:, self.begin:self.end].contiguous())  # partial sum over this rank's features
@@ -181,7 +199,9 @@ class ExpertParallelFrozenMoE:
     C ABI entry points of the same names: build_dispatch(indices) -> (dispatch_map, offsets),
     dispatch(x, indices, dmap, offsets, total) -> packed rows, experts(packed, offsets_local)
     -> packed outputs for the experts this rank owns, combine(buf, indices, weights, dmap,
-    offsets, tokens) -> [tokens, dim]."""
+    offsets, tokens) -> [tokens, dim]; for backward() also combine_bwd(dy, indices, weights, dmap,
+    offsets, total) -> packed gradients, experts_bwd(packed_dy, offsets_local) -> packed dX of the
+    owned experts, dispatch_bwd(grad_buf, indices, dmap, offsets, tokens) -> [tokens, dim]."""
 
     def __init__(self, ops, num_experts, group=None):
         self.ops = ops
@@ -228,22 +248,67 @@ class ExpertParallelFrozenMoE:
         local_offsets[1:] = torch.cumsum(incoming.sum(dim=0), 0).to(torch.int32)
         return perm, local_offsets
 
-    def forward(self, x, expert_indices, expert_weights):
-        tokens = x.shape[0]
+    def route(self, expert_indices):
+        """Everything about a routing decision that the exchange needs, computed once: dispatch map and
+        offsets of this rank's tokens, rows per destination and per source, the permutation that groups
+        arriving rows by expert.  Reusable as long as `expert_indices` does not change."""
         dmap, offsets = self.ops.build_dispatch(expert_indices)
         total = int(offsets[-1])
-        packed = self.ops.dispatch(x, expert_indices, dmap, offsets, total)          # ordered by expert
         send_counts, recv_counts, incoming = self.plan(offsets)
-        received = torch.empty((int(recv_counts.sum()), x.shape[1]), dtype=x.dtype, device=x.device)
-        dist.all_to_all_single(received, packed, output_split_sizes=recv_counts.tolist(),
-                               input_split_sizes=send_counts.tolist(), group=self.group)
         perm, local_offsets = self.regroup_index(incoming)
-        perm_dev = perm.to(x.device)
-        grouped = received.index_select(0, perm_dev)
-        out_grouped = self.ops.experts(grouped, local_offsets)
-        out_received = torch.empty_like(out_grouped)
-        out_received.index_copy_(0, perm_dev, out_grouped)                             # back to arrival order
-        returned = torch.empty_like(packed)
-        dist.all_to_all_single(returned, out_received, output_split_sizes=send_counts.tolist(),
-                               input_split_sizes=recv_counts.tolist(), group=self.group)
-        return self.ops.combine(returned, expert_indices, expert_weights, dmap, offsets, tokens)
+        return {"indices": expert_indices, "dmap": dmap, "offsets": offsets, "total": total,
+                "send": send_counts.tolist(), "recv": recv_counts.tolist(), "perm": perm.to(dmap.device),
+                "local_offsets": local_offsets, "received_rows": int(recv_counts.sum())}
+
+    def _to_owners(self, packed, routing):
+        """Rows packed by (global) expert -> rows grouped by local expert on the experts' owners."""
+        received = torch.empty((routing["received_rows"], packed.shape[1]), dtype=packed.dtype, device=packed.device)
+        dist.all_to_all_single(received, packed, output_split_sizes=routing["recv"],
+                               input_split_sizes=routing["send"], group=self.group)
+        return received.index_select(0, routing["perm"])
+
+    def _from_owners(self, grouped, routing):
+        """The mirror exchange: rows grouped by local expert -> the senders' packed order."""
+        arrival = torch.empty_like(grouped)
+        arrival.index_copy_(0, routing["perm"], grouped)                              # back to arrival order
+        returned = torch.empty((routing["total"], grouped.shape[1]), dtype=grouped.dtype, device=grouped.device)
+        dist.all_to_all_single(returned, arrival, output_split_sizes=routing["send"],
+                               input_split_sizes=routing["recv"], group=self.group)
+        return returned
+
+    def forward(self, x, expert_indices, expert_weights, routing=None):
+        """The frozen experts' part of the layer forward (src/caif_device_moe_layer.cpp:534-557) with the
+        experts on their owners.  Keeps what backward() needs."""
+        tokens = x.shape[0]
+        if routing is None:
+            routing = self.route(expert_indices)
+        packed = self.ops.dispatch(x, expert_indices, routing["dmap"], routing["offsets"], routing["total"])
+        grouped = self._to_owners(packed, routing)
+        out_grouped = self.ops.experts(grouped, routing["local_offsets"])
+        returned = self._from_owners(out_grouped, routing)
+        self._saved = (routing, expert_weights, tokens)
+        return self.ops.combine(returned, expert_indices, expert_weights, routing["dmap"], routing["offsets"], tokens)
+
+    def backward(self, dy):
+        """The mirror of the layer backward over frozen experts (src/caif_device_moe_layer.cpp:754-778):
+        the gradient of every (token, k) pick goes to the expert's owner, which runs the experts' dX on the
+        rows it owns (`ops.experts_bwd`, using what its forward saved); the rows come back and are summed
+        over k per token.  dX only: frozen experts have no weight gradient."""
+        routing, expert_weights, tokens = self._saved
+        idx = routing["indices"]
+        gbuf = self.ops.combine_bwd(dy, idx, expert_weights, routing["dmap"], routing["offsets"], routing["total"])
+        grouped = self._to_owners(gbuf, routing)
+        gx_grouped = self.ops.experts_bwd(grouped, routing["local_offsets"])
+        returned = self._from_owners(gx_grouped, routing)
+        return self.ops.dispatch_bwd(returned, idx, routing["dmap"], routing["offsets"], tokens)
+
+    def round_trip_check(self, x, expert_indices, routing=None):
+        """Sends every packed row to its expert's owner and straight back: the largest absolute
+        difference between what was sent and what returned (0.0 when the exchange is exact)."""
+        if routing is None:
+            routing = self.route(expert_indices)
+        packed = self.ops.dispatch(x, expert_indices, routing["dmap"], routing["offsets"], routing["total"])
+        back = self._from_owners(self._to_owners(packed, routing), routing)
+        if packed.numel() == 0:
+            return 0.0
+        return float((back.float() - packed.float()).abs().max())

@@ -257,6 +257,21 @@ CAIFQ_API int caifq_moe_topk(const void *probs, int32_t dtype, int32_t *indices,
 CAIFQ_API int caifq_moe_normalize_rows(const void *input, void *output, int32_t dtype, int32_t batch, int32_t dim,
                              void *stream);
 /*
+ * The score function of CAIF_DeviceMoERouter::Route for SoftmaxTopK gating,
+ * src/caif_device_moe_router.cpp:233-303: probs = softmax(logits [+ bias]) over the experts of each
+ * row, with the operation order of launch_attention_softmax
+ * (src/caif_cuda_kernels_attention_support.cu:350-460, 866-884) so that the probabilities, and with
+ * them the top-k indices, come out bit-identical.  `bias` [cols] may be NULL; when given it is added
+ * first and the sum rounded to `dtype`, as the reference's separate AddBias kernel stores it
+ * (src/caif_cuda_kernels_elementwise.cu:124-137).  In place (probs == logits) is allowed.
+ */
+CAIFQ_API int caifq_moe_router_softmax(const void *logits, const void *bias, void *probs, int32_t dtype, int32_t rows,
+                             int32_t cols, void *stream);
+/* CAIF_Ops::Scale, src/caif_ops_device.cpp:3142-3160 (the router's routed_scaling_factor on the top-k
+ * weights, src/caif_device_moe_router.cpp:394-407; LoRA's alpha/r): dst = T(float(src) * factor).
+ * In place is allowed. */
+CAIFQ_API int caifq_scale(const void *src, void *dst, int32_t dtype, float factor, int64_t n, void *stream);
+/*
  * CAIF_Ops::MoEBuildDispatchMap, src/caif_ops_device.cpp:4876-4950, computed on
  * the device with the identical result: expert_offsets[E+1] (exclusive prefix
  * sum of the capacity-clamped counts) and dispatch_map[T,k] (arrival order

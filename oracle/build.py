@@ -6,9 +6,10 @@ script produces.
 
   oracle/_build/libcaif_oracle.so       gcc, from oracle/caif_oracle.c
   oracle/_ref/libcaif_ref_kernels.so    nvcc, from the reference's unmodified
-                                        src/caif_cuda_kernels_quant.cu and
-                                        src/caif_cuda_kernels_moe.cu compiled
-                                        where they lie, plus oracle/ref_shim.cu
+                                        src/caif_cuda_kernels_quant.cu, _moe.cu,
+                                        _attention_support.cu (router softmax) and
+                                        _elementwise.cu compiled where they lie,
+                                        plus oracle/ref_shim.cu
 
 Both outputs are binaries kept out of version control.  The second one is only
 built where the reference sources exist; elsewhere a previously built copy is
@@ -49,7 +50,9 @@ def build_reference_kernels(force=False):
     """Returns the path of the library, or None when it cannot be had."""
     ref_src = os.path.join(REFERENCE_ROOT, "src")
     sources = [os.path.join(ref_src, "caif_cuda_kernels_quant.cu"),
-               os.path.join(ref_src, "caif_cuda_kernels_moe.cu")]
+               os.path.join(ref_src, "caif_cuda_kernels_moe.cu"),
+               os.path.join(ref_src, "caif_cuda_kernels_attention_support.cu"),
+               os.path.join(ref_src, "caif_cuda_kernels_elementwise.cu")]
     shim = os.path.join(HERE, "ref_shim.cu")
     if not all(os.path.exists(s) for s in sources):
         return REF_SO if os.path.exists(REF_SO) else None

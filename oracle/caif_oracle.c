@@ -614,6 +614,100 @@ ORC_EXPORT void orc_normalize_rows(const float *input, int batch, int dim, float
   }
 }
 
+/* Router softmax: launch_attention_softmax,                                   */
+/* src/caif_cuda_kernels_attention_support.cu:350-460, 866-884 (128 threads  */
+/* per row on every architecture the selection table knows, :53-83).  Thread */
+/* t scans columns t, t+128, ... with the online (max, sum) update; each     */
+/* warp of 32 threads folds its values with an xor butterfly (offsets 16..1);*/
+/* the four warp results are folded in lanes 0..3 with offsets 2 and 1; then */
+/* y = expf(x - max) * (1 / sum).  With a bias (CAIF_Ops::AddBias,           */
+/* src/caif_cuda_kernels_elementwise.cu:124-137, ahead of the softmax in     */
+/* src/caif_device_moe_router.cpp:233-243) the value seen is the sum rounded */
+/* through `dtype`.  expf here is the host libm's: the order of operations   */
+/* is the kernel's, the last bits of expf need not be.                       */
+static void orc_softmax_absorb(float *m, float *s, float m_other, float s_other)
+{
+  if (m_other > *m)
+  {
+    *s = *s * expf(*m - m_other) + s_other;
+    *m = m_other;
+  }
+  else
+  {
+    *s += s_other * expf(m_other - *m);
+  }
+}
+
+ORC_EXPORT void orc_router_softmax(const float *logits, const float *bias, int rows, int cols, int dtype, float *probs)
+{
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r)
+  {
+    const float *x = logits + (int64_t)r * cols;
+    float m[128];
+    float s[128];
+    float *v = (float *)malloc((size_t)cols * sizeof(float));
+    for (int c = 0; c < cols; ++c)
+    {
+      v[c] = x[c];
+      if (bias != NULL)
+      {
+        v[c] = x[c] + bias[c];
+        orc_round_through(&v[c], 1, dtype);
+      }
+    }
+    for (int t = 0; t < 128; ++t)
+    {
+      m[t] = -1e30f;
+      s[t] = 0.0f;
+      for (int c = t; c < cols; c += 128)
+      {
+        if (v[c] > m[t])
+        {
+          s[t] = s[t] * expf(m[t] - v[c]) + 1.0f;
+          m[t] = v[c];
+        }
+        else
+        {
+          s[t] += expf(v[c] - m[t]);
+        }
+      }
+    }
+    for (int w = 0; w < 4; ++w)
+    {
+      for (int off = 16; off > 0; off >>= 1)
+      {
+        float nm[32];
+        float ns[32];
+        for (int l = 0; l < 32; ++l)
+        {
+          nm[l] = m[32 * w + l];
+          ns[l] = s[32 * w + l];
+          orc_softmax_absorb(&nm[l], &ns[l], m[32 * w + (l ^ off)], s[32 * w + (l ^ off)]);
+        }
+        for (int l = 0; l < 32; ++l)
+        {
+          m[32 * w + l] = nm[l];
+          s[32 * w + l] = ns[l];
+        }
+      }
+    }
+    {
+      float fm[4] = {m[0], m[32], m[64], m[96]};
+      float fs[4] = {s[0], s[32], s[64], s[96]};
+      orc_softmax_absorb(&fm[0], &fs[0], fm[2], fs[2]);
+      orc_softmax_absorb(&fm[1], &fs[1], fm[3], fs[3]);
+      orc_softmax_absorb(&fm[0], &fs[0], fm[1], fs[1]);
+      const float inv = 1.0f / fs[0];
+      for (int c = 0; c < cols; ++c)
+      {
+        probs[(int64_t)r * cols + c] = expf(v[c] - fm[0]) * inv;
+      }
+    }
+    free(v);
+  }
+}
+
 /* Dispatch map: CAIF_Ops::MoEBuildDispatchMapDevice,                        */
 /* src/caif_ops_device.cpp:4876-4950.  counts per expert (indices outside    */
 /* [0,E) ignored) -> capacity clamp -> exclusive prefix sum -> position of   */

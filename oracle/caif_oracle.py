@@ -324,6 +324,20 @@ def normalize_rows(x):
     return out
 
 
+def router_softmax(logits, bias=None, dtype=F32):
+    """Probabilities of CAIF_DeviceMoERouter::Route for SoftmaxTopK gating
+    (src/caif_device_moe_router.cpp:233-303): optional AddBias (sum rounded through
+    `dtype`), then the attention softmax kernel's operation order.  fp32 in, fp32 out
+    (round the result through `dtype` for 16-bit storage)."""
+    x = _c(logits, np.float32)
+    rows, cols = x.shape
+    out = np.empty_like(x)
+    b = None if bias is None else _c(bias, np.float32)
+    lib().orc_router_softmax(_p(x), None if b is None else _p(b), ctypes.c_int(rows), ctypes.c_int(cols),
+                             ctypes.c_int(dtype), _p(out))
+    return out
+
+
 def build_dispatch_map(expert_indices, num_experts, capacity=0):
     idx = _c(expert_indices, np.int32)
     tokens, top_k = idx.shape

@@ -1,8 +1,9 @@
 // C-linkage doorway onto the reference's own device kernels.
 //
 // TEST INFRASTRUCTURE ONLY.  oracle/build.py compiles this file together with
-// the reference's unmodified src/caif_cuda_kernels_quant.cu and
-// src/caif_cuda_kernels_moe.cu (read in place from the reference checkout,
+// the reference's unmodified src/caif_cuda_kernels_quant.cu, src/caif_cuda_kernels_moe.cu,
+// src/caif_cuda_kernels_attention_support.cu (the router's softmax) and
+// src/caif_cuda_kernels_elementwise.cu (read in place from the reference checkout,
 // never copied) into oracle/_ref/libcaif_ref_kernels.so.  The GPU tests load
 // that library to check the CPU oracle and the product kernels bit for bit
 // against what the reference itself computes.  Every pointer is a device
@@ -15,6 +16,8 @@
 
 #include "caif_cuda_kernels_quant.cuh"
 #include "caif_cuda_kernels_moe.cuh"
+#include "caif_cuda_kernels_attention_support.cuh"
+#include "caif_cuda_kernels_elementwise.cuh"
 
 extern "C" {
 
@@ -107,6 +110,38 @@ void ref_moe_dispatch_bwd_f32(const float *grad_buffer, float *grad_input, int n
 {
   launch_moe_dispatch_backward<float>(grad_buffer, expert_indices, dispatch_map, expert_offsets, grad_input, num_tokens,
                                       dim, top_k, static_cast<cudaStream_t>(stream));
+}
+
+// the router's score path: AddBias, Softmax, Scale
+void ref_softmax_f32(const float *input, float *output, int rows, int cols, void *stream)
+{
+  launch_attention_softmax<float>(input, output, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+void ref_softmax_bf16(const void *input, void *output, int rows, int cols, void *stream)
+{
+  launch_attention_softmax<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input),
+                                          static_cast<__nv_bfloat16 *>(output), rows, cols,
+                                          static_cast<cudaStream_t>(stream));
+}
+
+void ref_bias_add_f32(const float *input, const float *bias, float *output, int batch, int units, void *stream)
+{
+  launch_bias_add_2d<float>(input, bias, output, batch, units, static_cast<cudaStream_t>(stream));
+}
+
+void ref_bias_add_bf16(const void *input, const void *bias, void *output, int batch, int units, void *stream)
+{
+  launch_bias_add_2d<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input),
+                                    static_cast<const __nv_bfloat16 *>(bias), static_cast<__nv_bfloat16 *>(output),
+                                    batch, units, static_cast<cudaStream_t>(stream));
+}
+
+void ref_scale_bf16(const void *input, void *output, float factor, int64_t n, void *stream)
+{
+  launch_elementwise_mul_scalar<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input), factor,
+                                               static_cast<__nv_bfloat16 *>(output), n,
+                                               static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

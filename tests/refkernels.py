@@ -127,3 +127,26 @@ def moe_dispatch_bwd(gbuf, idx, dmap, off, tokens):
     lib().ref_moe_dispatch_bwd_f32(_p(gbuf), _p(gin), ctypes.c_int(tokens), ctypes.c_int(dim),
                                    ctypes.c_int(idx.shape[1]), _p(idx), _p(dmap), _p(off), _s())
     return gin
+
+
+def softmax(x):
+    """launch_attention_softmax on fp32 or bf16 rows (the router's score function)."""
+    rows, cols = x.shape
+    out = torch.empty_like(x)
+    fn = lib().ref_softmax_f32 if x.dtype == torch.float32 else lib().ref_softmax_bf16
+    fn(_p(x), _p(out), ctypes.c_int(rows), ctypes.c_int(cols), _s())
+    return out
+
+
+def bias_add(x, bias):
+    rows, cols = x.shape
+    out = torch.empty_like(x)
+    fn = lib().ref_bias_add_f32 if x.dtype == torch.float32 else lib().ref_bias_add_bf16
+    fn(_p(x), _p(bias), _p(out), ctypes.c_int(rows), ctypes.c_int(cols), _s())
+    return out
+
+
+def scale_bf16(x, factor):
+    out = torch.empty_like(x)
+    lib().ref_scale_bf16(_p(x), _p(out), ctypes.c_float(factor), ctypes.c_int64(x.numel()), _s())
+    return out

@@ -84,6 +84,55 @@ def test_topk_and_normalize_bit_exact(dtype):
         assert torch.equal(ref.normalize_rows(val), norm)
 
 
+@pytest.mark.parametrize("dtype,rows,cols,with_bias", [
+    (torch.float32, 16384, 68, False),     # the MoE config's router
+    (torch.float32, 777, 64, True),
+    (torch.bfloat16, 1000, 68, True),
+    (torch.bfloat16, 300, 256, False),
+    (torch.float32, 50, 300, True),        # more than 128 columns: the strided per-thread scan
+    (torch.float32, 9, 1, False),
+])
+def test_router_softmax_bit_exact_with_the_reference_kernel(dtype, rows, cols, with_bias):
+    """Router probabilities: bit-identical to the reference's softmax kernel run on the same GPU
+    (so the top-k indices that follow are identical too), and within a few ulp of the CPU oracle,
+    whose expf is the host's."""
+    g = torch.Generator().manual_seed(rows + cols)
+    logits = (torch.randn(rows, cols, generator=g) * 2.0).to(dtype)
+    bias = (torch.randn(cols, generator=g) * 0.5).to(dtype) if with_bias else None
+    ld = logits.to(dev()).contiguous()
+    bd = bias.to(dev()).contiguous() if with_bias else None
+    probs = nv.moe_softmax(ld, bd)
+    code = orc.F32 if dtype == torch.float32 else orc.BF16
+    want = orc.round_through(orc.router_softmax(logits.float().numpy(), None if bias is None else bias.float().numpy(),
+                                                code), code)
+    got = probs.float().cpu().numpy()
+    assert np.max(np.abs(got - want)) <= (2e-7 if dtype == torch.float32 else 1e-2) * max(1.0, float(np.max(want)))
+    if ref.available():
+        biased = ref.bias_add(ld, bd) if with_bias else ld
+        assert torch.equal(ref.softmax(biased), probs)
+        k = min(6, cols)
+        ridx, _ = ref.topk(ref.softmax(biased).float().contiguous(), k)
+        idx, _ = nv.moe_topk(probs.float().contiguous(), k)
+        assert torch.equal(ridx, idx)
+    # in place
+    again = ld.clone()
+    nv._check(nv.lib().caifq_moe_router_softmax(nv._ptr(again), nv._ptr(bd), nv._ptr(again), nv.dtype_code(again),
+                                                rows, cols, nv._stream()), "softmax in place")
+    assert torch.equal(again, probs)
+
+
+def test_scale_matches_the_reference_kernel():
+    g = torch.Generator().manual_seed(5)
+    w = torch.rand(1000, 6, generator=g).to(torch.bfloat16).to(dev())
+    got = nv.scale(w, 16.0)
+    want = orc.round_through(w.float().cpu().numpy() * np.float32(16.0), orc.BF16)
+    assert np.array_equal(got.float().cpu().numpy(), want)
+    if ref.available():
+        assert torch.equal(ref.scale_bf16(w, 16.0), got)
+    odd = nv.scale(w, 2.5)
+    assert np.array_equal(odd.float().cpu().numpy(), orc.round_through(w.float().cpu().numpy() * np.float32(2.5), orc.BF16))
+
+
 def test_topk_edge_cases():
     p = torch.tensor([[0.25, 0.25, 0.25, 0.25], [-2e30, -2e30, -2e30, -2e30], [0.0, 1.0, float("nan"), 1.0]])
     idx, val = nv.moe_topk(p.to(dev()), 2)

@@ -341,3 +341,30 @@ def test_dispatch_backward_is_the_adjoint_of_dispatch_and_combine():
     gw = orc.moe_combine_bwd_grad_weights(g, np.ones((total, dim), np.float32), idx, dmap, off)
     want = np.where(dmap >= 0, g.sum(axis=1, keepdims=True), 0.0)
     assert np.array_equal(gw, want.astype(np.float32))
+
+
+def test_router_softmax_restatement():
+    """The oracle's router softmax keeps the kernel's operation order; against a float64 softmax it is
+    exact to a few fp32 ulp, rows sum to one, and a bias is added before the score function."""
+    rng = np.random.default_rng(41)
+    for rows, cols in ((33, 68), (5, 300), (4, 1), (7, 128)):
+        x = (rng.standard_normal((rows, cols)) * 3).astype(np.float32)
+        b = rng.standard_normal(cols).astype(np.float32)
+        for bias in (None, b):
+            p = orc.router_softmax(x, bias)
+            z = x.astype(np.float64) + (0 if bias is None else bias.astype(np.float32).astype(np.float64))
+            e = np.exp(z - z.max(axis=1, keepdims=True))
+            want = e / e.sum(axis=1, keepdims=True)
+            assert np.max(np.abs(p - want)) <= 3e-7
+            assert np.allclose(p.sum(axis=1), 1.0, atol=1e-6)
+    # the biased logit is rounded through the storage dtype before the softmax, as AddBias stores it
+    x = np.array([[1.0, 1.0]], np.float32)
+    b = np.array([2 ** -10, 0.0], np.float32)
+    p = orc.router_softmax(x, b, orc.BF16)
+    assert p[0, 0] == p[0, 1]          # 1 + 2^-10 rounds to 1 in bf16
+    p = orc.router_softmax(x, b, orc.F32)
+    assert p[0, 0] > p[0, 1]
+    # a row of equal logits gives the uniform distribution; -inf-like entries vanish
+    assert np.array_equal(orc.router_softmax(np.zeros((1, 4), np.float32)), np.full((1, 4), 0.25, np.float32))
+    p = orc.router_softmax(np.array([[0.0, -1e30, 0.0]], np.float32))
+    assert p[0, 1] == 0.0 and p[0, 0] == 0.5

@@ -70,14 +70,27 @@ def _expert_parallel_worker(rank, world, port, out_q):
     idx_all, val_all = orc.topk(probs, top_k)
     w_all = orc.normalize_rows(val_all)
 
-    def run_experts(packed, offsets, first_expert):
+    def run_experts(packed, offsets, first_expert, saved=None):
         out = np.zeros_like(packed)
         for e in range(len(offsets) - 1):
             lo, hi = int(offsets[e]), int(offsets[e + 1])
             if hi > lo:
                 g, u, d = experts[first_expert + e]
-                out[lo:hi] = orc.frozen_expert_forward(packed[lo:hi], g, u, d)[0]
+                o, gate, up = orc.frozen_expert_forward(packed[lo:hi], g, u, d)
+                out[lo:hi] = o
+                if saved is not None:
+                    saved[e] = (gate, up)
         return out
+
+    def run_experts_bwd(packed_dy, offsets, first_expert, saved):
+        dx = np.zeros_like(packed_dy)
+        for e in range(len(offsets) - 1):
+            lo, hi = int(offsets[e]), int(offsets[e + 1])
+            if hi > lo:
+                g, u, d = experts[first_expert + e]
+                gate, up = saved[e]
+                dx[lo:hi] = orc.frozen_expert_backward(packed_dy[lo:hi], gate, up, g, u, d)
+        return dx
 
     class Ops:
         def build_dispatch(self, indices):
@@ -89,7 +102,20 @@ def _expert_parallel_worker(rank, world, port, out_q):
 
         def experts(self, packed, local_offsets):
             first = rank * (num_experts // world)
-            return torch.from_numpy(run_experts(packed.numpy(), local_offsets.numpy(), first))
+            self.saved = {}
+            return torch.from_numpy(run_experts(packed.numpy(), local_offsets.numpy(), first, self.saved))
+
+        def experts_bwd(self, packed_dy, local_offsets):
+            first = rank * (num_experts // world)
+            return torch.from_numpy(run_experts_bwd(packed_dy.numpy(), local_offsets.numpy(), first, self.saved))
+
+        def combine_bwd(self, dy, indices, weights, dmap, off, total):
+            return torch.from_numpy(orc.moe_combine_bwd_grad_expert(dy.numpy(), indices.numpy(), weights.numpy(),
+                                                                    dmap.numpy(), off.numpy(), total))
+
+        def dispatch_bwd(self, gbuf, indices, dmap, off, tokens):
+            return torch.from_numpy(orc.moe_dispatch_bwd(gbuf.numpy(), indices.numpy(), dmap.numpy(), off.numpy(),
+                                                         tokens))
 
         def combine(self, buf, indices, weights, dmap, off, tokens):
             return torch.from_numpy(orc.moe_combine(buf.numpy(), indices.numpy(), weights.numpy(), dmap.numpy(),
@@ -101,8 +127,21 @@ def _expert_parallel_worker(rank, world, port, out_q):
     # single-process reference on this rank's tokens with all experts local
     dmap, off, total = orc.build_dispatch_map(idx_all[sl], num_experts)
     packed = orc.moe_dispatch(x_all[sl], idx_all[sl], dmap, off, total)
-    want = orc.moe_combine(run_experts(packed, off, 0), idx_all[sl], w_all[sl], dmap, off, tokens_per_rank)
-    out_q.put((rank, bool(np.array_equal(got.numpy(), want)), True))
+    saved = {}
+    want = orc.moe_combine(run_experts(packed, off, 0, saved), idx_all[sl], w_all[sl], dmap, off, tokens_per_rank)
+    ok_fwd = bool(np.array_equal(got.numpy(), want))
+    # backward: the gradient of this rank's tokens through combine, the experts' dX and dispatch
+    dy = np.random.default_rng(31 + rank).standard_normal((tokens_per_rank, dim)).astype(np.float32)
+    got_dx = moe.backward(torch.from_numpy(dy))
+    gbuf = orc.moe_combine_bwd_grad_expert(dy, idx_all[sl], w_all[sl], dmap, off, total)
+    want_dx = orc.moe_dispatch_bwd(run_experts_bwd(gbuf, off, 0, saved), idx_all[sl], dmap, off, tokens_per_rank)
+    ok_bwd = bool(np.array_equal(got_dx.numpy(), want_dx))
+    # a cached routing gives the same result, and the exchange alone returns every row unchanged
+    routing = moe.route(torch.from_numpy(idx_all[sl]))
+    again = moe.forward(torch.from_numpy(x_all[sl]), torch.from_numpy(idx_all[sl]), torch.from_numpy(w_all[sl]), routing)
+    ok_fwd = ok_fwd and bool(np.array_equal(again.numpy(), want))
+    ok_fwd = ok_fwd and moe.round_trip_check(torch.from_numpy(x_all[sl]), torch.from_numpy(idx_all[sl]), routing) == 0.0
+    out_q.put((rank, ok_fwd, ok_bwd))
     dist.destroy_process_group()
 
 
@@ -145,5 +184,7 @@ def test_column_parallel_world2_gloo():
 
 
 def test_expert_parallel_world2_gloo():
-    for rank, ok, _ in _spawn(_expert_parallel_worker):
-        assert ok, rank
+    """Forward and backward of the expert-parallel frozen experts equal the one-process dataflow bit for bit."""
+    for rank, ok_fwd, ok_bwd in _spawn(_expert_parallel_worker):
+        assert ok_fwd, rank
+        assert ok_bwd, rank
