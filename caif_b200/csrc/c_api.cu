@@ -1,6 +1,7 @@
 // The extern "C" surface declared in include/caifq.h: argument checks, kernel
 // family selection, and the compositions (LoRA, grouped experts) that are
 // several launches.  No entry point allocates device memory or synchronises.
+#include <atomic>
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
@@ -30,6 +31,52 @@ void set_error(const char *fmt, ...)
 }
 
 void set_path(const char *name) { t_path = name; }
+
+namespace
+{
+std::atomic<int> g_cta_limit{0};   // 0 = no limit set through the API
+}
+
+int device_sm_count()
+{
+  static std::atomic<int> cached[kMaxDevices];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices)
+  {
+    dev = 0;
+  }
+  int v = cached[dev].load(std::memory_order_relaxed);
+  if (v == 0)
+  {
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    if (v <= 0)
+    {
+      v = 148;
+    }
+    cached[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+int persistent_ctas(const char *env_name)
+{
+  int n = device_sm_count();
+  const int api = g_cta_limit.load(std::memory_order_relaxed);
+  if (api >= 1 && api < n)
+  {
+    return api;
+  }
+  if (const char *e = std::getenv(env_name))
+  {
+    const int v = std::atoi(e);
+    if (v >= 1 && v < n)
+    {
+      n = v;
+    }
+  }
+  return n;
+}
 
 // moe.cu
 int launch_moe_topk(const void *probs, int dtype, int *indices, void *values, int batch, int dim, int k,
@@ -318,6 +365,8 @@ int caifq_device_status(void)
 }
 
 void caifq_selftest_stall_next_decode(void) { decode_stall_next_launch(); }
+
+void caifq_set_cta_limit(int32_t max_ctas) { g_cta_limit.store(max_ctas > 0 ? max_ctas : 0, std::memory_order_relaxed); }
 
 int caifq_device_ok(void)
 {
@@ -652,7 +701,6 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[CAIFQ_NOALLOC_S
 
 namespace
 {
-constexpr int kMaxDevices = 64;
 void *g_noalloc_ptr[kMaxDevices] = {};
 std::mutex g_noalloc_mutex;
 }  // namespace

@@ -40,6 +40,13 @@ void set_path(const char *name);
 
 #define CAIFQ_CHECK_LAUNCH() CAIFQ_CHECK_CUDA(cudaGetLastError())
 
+// SMs of the current device (cached per device ordinal) and the number of CTAs a persistent kernel
+// may launch: one per SM unless the host has asked for fewer (caifq_set_cta_limit, or the
+// CAIFQ_DECODE_CTAS / CAIFQ_UMMA_CTAS environment variables read at the first launch).
+constexpr int kMaxDevices = 64;
+int device_sm_count();
+int persistent_ctas(const char *env_name);
+
 inline bool is_float_dtype(int d) { return d == CAIFQ_F32 || d == CAIFQ_F16 || d == CAIFQ_BF16; }
 
 inline size_t dtype_bytes(int d)

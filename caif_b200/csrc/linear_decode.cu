@@ -71,7 +71,6 @@ constexpr int kRingDepth = 3;                    // items in flight per SM
 constexpr uint32_t kSmemBudget = 220u * 1024u;   // dynamic shared memory of the one CTA per SM
 constexpr uint32_t kSpinLimit = 1u << 22;        // polls of one wait before it gives up (tens of ms)
 constexpr uint32_t kSpinLimitTest = 1u << 12;    // the same for the self-test of the give-up path
-constexpr int kMaxDevices = 64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -221,6 +220,7 @@ struct DecodeParams
   int stages;
   int vec4;               // fp32 results may be stored four rows at a time (16-byte aligned on every buffer)
   int tokp;               // tokens per parked row: m rounded up to 2, 4, 8 or 16
+  int park_items;         // items whose partial sums fit the parking area: the CTA reduces and stores that often
   uint32_t partial_offset; // byte offset of the parked partial sums in dynamic shared memory
   uint32_t row_bytes;      // packed bytes per weight row
   uint32_t row_stride;     // row pitch in the ring
@@ -426,7 +426,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
   int s = 0;             // ring stage of the current item
   uint32_t s_par = 0;    // its phase parity
   bool ok = true;
-  for (int it = 0; it < my_items; ++it)
+  // Rounds: the parking area holds the partial sums of park_items items (all of a CTA's items for the
+  // usual layer sizes, so one round); after each round the CTA adds them up and stores the outputs.
+  for (int round_begin = 0; round_begin < my_items; round_begin += p.park_items)
+  {
+  const int round_end = min(round_begin + p.park_items, my_items);
+  for (int it = round_begin; it < round_end; ++it)
   {
     ok = mbar_wait(&full_bar[s], s_par, p.spin_limit, abort_word);
     if (!ok)
@@ -585,7 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     }
     // park this warp's partial sums of the item; nobody reads them before the end of the kernel
     {
-      const uint32_t d0 = part_base + static_cast<uint32_t>(it) * part_item_bytes;
+      const uint32_t d0 = part_base + static_cast<uint32_t>(it - round_begin) * part_item_bytes;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
       {
@@ -619,29 +624,29 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
       s_par ^= 1u;
     }
   }
-  if (!ok && warp == 0)
-  {
-    // A wait ran out.  Before the CTA gives its shared memory back, every copy that was started
-    // into the ring must have landed (a copy must not arrive in memory that already belongs to
-    // another CTA).  Warp 0 started them all and waits for those it has not consumed; these waits
-    // are bounded too.  (A warp that leaves the loop normally has consumed every item.)
-    for (int st = 0; st < stages && st < issued_items; ++st)
-    {
-      // the last item started into this stage; once it has landed the earlier ones have too
-      const int j = issued_items - 1 - ((issued_items - 1 - st) % stages);
-      const uint32_t addr = smem_u32(&full_bar[st]);
-      const uint32_t parity = static_cast<uint32_t>(j / stages) & 1u;
-      bool done = false;
-      for (uint32_t spin = 0; spin < p.spin_limit && !done; ++spin)
-      {
-        done = mbar_try(addr, parity);
-      }
-    }
-  }
   __syncthreads();
   if (*abort_word != 0u)
   {
-    return;   // outputs stay unwritten; the host sees the flag
+    // A wait ran out somewhere in the CTA; the outputs stay unwritten and the host sees the flag.
+    // Before the CTA gives its shared memory back, every copy that was started into the ring must
+    // have landed (a copy must not arrive in memory that already belongs to another CTA).  Warp 0
+    // started them all and waits for them; these waits are bounded too.
+    if (warp == 0)
+    {
+      for (int st = 0; st < stages && st < issued_items; ++st)
+      {
+        // the last item started into this stage; once it has landed the earlier ones have too
+        const int j = issued_items - 1 - ((issued_items - 1 - st) % stages);
+        const uint32_t addr = smem_u32(&full_bar[st]);
+        const uint32_t parity = static_cast<uint32_t>(j / stages) & 1u;
+        bool done = false;
+        for (uint32_t spin = 0; spin < p.spin_limit && !done; ++spin)
+        {
+          done = mbar_try(addr, parity);
+        }
+      }
+    }
+    return;
   }
 
   // Cross-warp reduction: an output is the sum of its WARPS partial sums in warp order.
@@ -649,7 +654,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
   {
     // a thread takes four tokens of one row; consecutive lanes take consecutive rows, so the stores
     // of a token are contiguous across the warp
-    const int n = my_items * 64;
+    const int n = (round_end - round_begin) * 64;
     for (int o = tid; o < n; o += WARPS * 32)
     {
       const int r16 = o & 15;
@@ -668,7 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
         acc[2] += __uint_as_float(v.z);
         acc[3] += __uint_as_float(v.w);
       }
-      const int row = row_begin + item * kItemRows + r16;
+      const int row = row_begin + (round_begin + item) * kItemRows + r16;
       if (row < row_end)
       {
 #pragma unroll
@@ -691,7 +696,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
   else
   {
     // a thread takes four consecutive rows of one live token
-    const int quads = my_items * 4 * p.m;
+    const int quads = (round_end - round_begin) * 4 * p.m;
     for (int o = tid; o < quads; o += WARPS * 32)
     {
       const int rq = o & 3;
@@ -717,7 +722,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
           acc[i] *= tensor_scale;
         }
       }
-      const int row = row_begin + item * kItemRows + 4 * rq;
+      const int row = row_begin + (round_begin + item) * kItemRows + 4 * rq;
       // plain stores; with peers they travel over NVLink and are complete when the kernel is
       const int64_t idx = static_cast<int64_t>(token) * p.y_ld + p.y_col0 + row;
       if (p.vec4 && row + 3 < row_end)
@@ -744,39 +749,15 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
       }
     }
   }
+  if (round_end < my_items)
+  {
+    __syncthreads();   // the parking area is free for the next round
+  }
+  }  // rounds
 }
 
-// Per device: the SM count (CAIFQ_DECODE_CTAS caps the grid for a host that runs a collective
-// beside this kernel and wants to leave it a few SMs).
-int sm_count()
-{
-  static std::atomic<int> cached[kMaxDevices];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= kMaxDevices)
-  {
-    dev = 0;
-  }
-  int v = cached[dev].load(std::memory_order_relaxed);
-  if (v == 0)
-  {
-    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    if (v <= 0)
-    {
-      v = 148;
-    }
-    if (const char *e = std::getenv("CAIFQ_DECODE_CTAS"))
-    {
-      const int cap = std::atoi(e);
-      if (cap >= 1 && cap < v)
-      {
-        v = cap;
-      }
-    }
-    cached[dev].store(v, std::memory_order_relaxed);
-  }
-  return v;
-}
+// One CTA per SM, fewer when the host runs a collective beside this kernel and wants to leave it SMs.
+int sm_count() { return persistent_ctas("CAIFQ_DECODE_CTAS"); }
 
 // Streams (per device) on which one of this library's calls has just written codes or scales.
 std::mutex g_written_mutex;
@@ -881,6 +862,7 @@ struct Layout
   uint32_t stage_bytes;
   uint32_t partial_bytes;
   int stages;
+  int park_items;
 };
 
 Layout layout_for(const caifq_weight &w, int64_t m)
@@ -890,7 +872,8 @@ Layout layout_for(const caifq_weight &w, int64_t m)
   const uint32_t row_bytes = i4 ? static_cast<uint32_t>(w.in_dim / 2) : static_cast<uint32_t>(w.in_dim);
   const uint32_t scale_bytes = i4 ? static_cast<uint32_t>(kItemRows * (w.in_dim / w.group_size) * 2) : 0u;
   l.stage_bytes = ((kItemRows * row_bytes + scale_bytes) + 127u) & ~127u;
-  // parked partial sums of every item a CTA can get: [item][warp][16 rows][tokp]
+  // parked partial sums: [item][warp][16 rows][tokp] for as many of a CTA's items as fit beside
+  // the ring (all of them for the usual layer sizes)
   const int quanta = (w.out_dim + kRowQuantum - 1) / kRowQuantum;
   int grid = sm_count();
   if (grid > quanta)
@@ -899,17 +882,31 @@ Layout layout_for(const caifq_weight &w, int64_t m)
   }
   const int max_quanta = (quanta + grid - 1) / grid;
   const int max_items = (max_quanta * kRowQuantum + kItemRows - 1) / kItemRows;
-  l.partial_bytes = static_cast<uint32_t>(max_items * kWarps * kItemRows * tokp_for(m) * sizeof(float));
-  int stages =
-      (kSmemBudget > l.partial_bytes) ? static_cast<int>((kSmemBudget - l.partial_bytes) / l.stage_bytes) : 0;
+  const uint32_t per_item = static_cast<uint32_t>(kWarps * kItemRows * tokp_for(m) * sizeof(float));
+  int stages = kRingDepth;
   // Three items in flight per SM are enough to cover the latency of HBM.  More of them make the
   // launch slower, not faster (measured on B200: 10.8 us per launch with three, 11.3 with four,
   // 12.8 with six at in=4096, out=14336): every SM then asks for its whole share at once and the
   // first item of each lands later.
-  if (stages > kRingDepth)
+  while (stages > 2 && static_cast<uint32_t>(stages) * l.stage_bytes + per_item > kSmemBudget)
   {
-    stages = kRingDepth;
+    --stages;
   }
+  if (static_cast<uint32_t>(stages) * l.stage_bytes + per_item > kSmemBudget)
+  {
+    stages = 0;   // a row too long for two stages and one parked item
+  }
+  int park = max_items;
+  if (stages > 0)
+  {
+    const int fit = static_cast<int>((kSmemBudget - static_cast<uint32_t>(stages) * l.stage_bytes) / per_item);
+    if (park > fit)
+    {
+      park = fit;
+    }
+  }
+  l.park_items = park;
+  l.partial_bytes = static_cast<uint32_t>(park) * per_item;
   l.stages = stages;
   return l;
 }
@@ -1074,6 +1071,7 @@ int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
   }
   p.stage_bytes = lay.stage_bytes;
   p.stages = stages;
+  p.park_items = lay.park_items;
   p.partial_offset = static_cast<uint32_t>(stages) * p.stage_bytes;
   const uint32_t smem_bytes = p.partial_offset + lay.partial_bytes;
   p.spin_limit = kSpinLimit;

@@ -37,6 +37,8 @@
 
 #include <cstdlib>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace caifq
@@ -1103,31 +1105,9 @@ int make_map_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t o
   return CAIFQ_OK;
 }
 
-int sm_count_umma()
-{
-  static int cached = 0;
-  if (cached == 0)
-  {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
-    if (cached <= 0)
-    {
-      cached = 148;
-    }
-    // A host that runs a collective beside these persistent kernels leaves it some SMs: a CTA here
-    // takes a whole SM, and one that finds its SM taken waits for the collective to end.
-    if (const char *e = std::getenv("CAIFQ_UMMA_CTAS"))
-    {
-      const int v = std::atoi(e);
-      if (v >= 1 && v < cached)
-      {
-        cached = v;
-      }
-    }
-  }
-  return cached;
-}
+// A host that runs a collective beside these persistent kernels leaves it some SMs: a CTA here takes
+// a whole SM, and one that finds its SM taken waits for the collective to end.
+int sm_count_umma() { return persistent_ctas("CAIFQ_UMMA_CTAS"); }
 
 template <int WMODE, bool BWD, int BN, bool GROUPED>
 int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const UmmaParams &p,
@@ -1135,11 +1115,18 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtens
 {
   auto kernel = linear_umma_kernel<WMODE, BWD, BN, GROUPED>;
   constexpr int SMEM_BYTES = TileCfg<BN, planes_of(WMODE)>::SMEM_BYTES;
-  static bool configured = false;
-  if (!configured)
+  static std::atomic<bool> configured[kMaxDevices];
+  int dev = 0;
+  CAIFQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+  {
+    set_error("frozen linear (umma): device ordinal %d out of range", dev);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  if (!configured[dev].load(std::memory_order_acquire))
   {
     CAIFQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
   const int grid = tiles < sm_count_umma() ? static_cast<int>(tiles) : sm_count_umma();

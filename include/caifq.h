@@ -107,6 +107,14 @@ CAIFQ_API int caifq_device_status(void);
  * caifq_device_status() then reports bit 0.  Nothing faults and nothing hangs.
  */
 CAIFQ_API void caifq_selftest_stall_next_decode(void);
+/*
+ * The weight-streaming and tensor-core kernels are persistent: one CTA per SM.  A host that runs
+ * collectives (NCCL) beside them on another stream caps their grids with this call so that the
+ * collective's CTAs find SMs of their own; a persistent CTA that finds its SM taken would wait for
+ * the whole collective.  max_ctas <= 0 restores one CTA per SM.  Process-wide; applies to launches
+ * made after the call.  (No counterpart in the reference, which is single-device.)
+ */
+CAIFQ_API void caifq_set_cta_limit(int32_t max_ctas);
 
 /* ---- quantize / dequantize (bit-exact with the reference kernels) -------- */
 

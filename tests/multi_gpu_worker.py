@@ -1,11 +1,9 @@
-"""Multi-GPU parity, run under torchrun on a box with N GPUs (not collected by pytest):
-
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29533 tests/run_multi_gpu_parity.py
+"""One rank of the multi-GPU parity test (tests/test_gpu_multi.py launches it under torchrun, one
+process per GPU).
 
 Column-parallel forward must equal the 1-GPU forward bit for bit (each output element runs the
-same K loop), dX within 1e-5 (the reduce changes the summation order); the expert-parallel MoE
-layer must equal the same layer with all experts local."""
+same K loop), dX within 1e-5 (the reduce changes the summation order); the expert-parallel frozen
+experts, forward and backward, must equal the same layer with all experts local."""
 import os
 import sys
 
@@ -51,10 +49,10 @@ def main():
             print("column-parallel m=%d: forward identical=%s, dX rel err %.2e" % (m, same, err))
 
     # ---- few-token forward with the all-gather fused into the kernel's stores (peer memory)
-    pb = PeerBuffer(16 * out_dim * 4, dev)
-    for m in (1, 5, 16):
+    pb = PeerBuffer(2 * 16 * out_dim * 4, dev)     # two halves: forward_gather alternates them
+    layer = ColumnParallelFrozenLinear(None, None, out_dim, in_dim)
+    for m in (1, 5, 16, 16, 3):
         x = torch.randn(m, in_dim, generator=g, device=dev).to(torch.bfloat16)
-        layer = ColumnParallelFrozenLinear(None, None, out_dim, in_dim)
         y = layer.forward_gather(
             lambda t, ptrs, ld, col0: nv.linear_fwd_gather(local, t, ptrs, ld, col0, nv.F32, nv.F32), x, pb)
         y1 = nv.linear_fwd(full, x, torch.float32, nv.F32)
@@ -62,7 +60,6 @@ def main():
         ok = ok and same
         if rank == 0:
             print("column-parallel m=%d, gather fused into the stores: identical=%s" % (m, same))
-        dist.barrier()   # nobody overwrites a buffer another rank is still reading
     pb.close()
 
     # ---- expert-parallel frozen MoE
@@ -88,24 +85,45 @@ def main():
             return nv.moe_dispatch(xx, indices, dmap, off, total)
 
         def experts(self, packed, local_offsets):
-            return nv.grouped_expert_fwd(gate[eb:ee], up[eb:ee], down[eb:ee], local_offsets.tolist(), packed,
-                                         nv.BF16)[0]
+            self.offs = local_offsets.tolist()
+            out, self.g_out, self.u_out = nv.grouped_expert_fwd(gate[eb:ee], up[eb:ee], down[eb:ee], self.offs, packed,
+                                                                nv.BF16)
+            return out
+
+        def experts_bwd(self, packed_dy, local_offsets):
+            return nv.grouped_expert_bwd(gate[eb:ee], up[eb:ee], down[eb:ee], self.offs, packed_dy, self.g_out,
+                                         self.u_out, nv.BF16)
 
         def combine(self, buf, indices, weights, dmap, off, n):
             return nv.moe_combine(buf, indices, weights, dmap, off, n)
 
-    got = ExpertParallelFrozenMoE(Ops(), experts).forward(x, idx, wts)
+        def combine_bwd(self, dy, indices, weights, dmap, off, total):
+            return nv.moe_combine_bwd_grad_expert(dy, indices, weights, dmap, off, total)
+
+        def dispatch_bwd(self, gbuf, indices, dmap, off, n):
+            return nv.moe_dispatch_bwd(gbuf, indices, dmap, off, n)
+
+    moe = ExpertParallelFrozenMoE(Ops(), experts)
+    got = moe.forward(x, idx, wts)
+    dy = torch.randn(tokens, dim, generator=gr, device=dev).to(torch.bfloat16)
+    got_dx = moe.backward(dy)
+    rt = moe.round_trip_check(x, idx)
     dmap, off = nv.moe_build_dispatch(idx, experts)
     total = int(off[-1])
     packed = nv.moe_dispatch(x, idx, dmap, off, total)
-    want = nv.moe_combine(nv.grouped_expert_fwd(gate, up, down, off.tolist(), packed, nv.BF16)[0], idx, wts, dmap,
-                          off, tokens)
+    out1, g1, u1 = nv.grouped_expert_fwd(gate, up, down, off.tolist(), packed, nv.BF16)
+    want = nv.moe_combine(out1, idx, wts, dmap, off, tokens)
+    gbuf = nv.moe_combine_bwd_grad_expert(dy, idx, wts, dmap, off, total)
+    want_dx = nv.moe_dispatch_bwd(nv.grouped_expert_bwd(gate, up, down, off.tolist(), gbuf, g1, u1, nv.BF16), idx,
+                                  dmap, off, tokens)
     moe_err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
+    dx_err = float((got_dx.float() - want_dx.float()).abs().max() / want_dx.float().abs().max())
     # per-expert row counts differ between the sharded and local runs, which may pick another
     # kernel family per expert; bf16 bound
-    ok = ok and moe_err <= 2e-2
+    ok = ok and moe_err <= 2e-2 and dx_err <= 2e-2 and rt == 0.0
     if rank == 0:
-        print("expert-parallel MoE rel err %.2e" % moe_err)
+        print("expert-parallel frozen experts: forward rel err %.2e, dX rel err %.2e, exchange round trip %.1e"
+              % (moe_err, dx_err, rt))
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

@@ -149,6 +149,9 @@ def test_decode_int4_config2(m):
     (orc.I8, 1024, 136, 12, 0),
     (orc.I8, 5120, 64, 7, 0),       # five chunks per warp
     (orc.I8, 320, 72, 1, 0),
+    (orc.I4, 1024, 40000, 16, 128),  # more items per CTA than partial sums can be parked: several rounds
+    (orc.I4, 1024, 40000, 3, 128),
+    (orc.I8, 512, 33000, 9, 0),
 ])
 def test_decode_shapes(storage, in_dim, out_dim, m, group):
     rng = np.random.default_rng(in_dim + out_dim + m)
