@@ -366,6 +366,8 @@ int caifq_device_status(void)
 
 void caifq_selftest_stall_next_decode(void) { decode_stall_next_launch(); }
 
+void caifq_selftest_stall_next_umma(void) { umma_stall_next_launch(); }
+
 void caifq_set_cta_limit(int32_t max_ctas) { g_cta_limit.store(max_ctas > 0 ? max_ctas : 0, std::memory_order_relaxed); }
 
 int caifq_device_ok(void)

@@ -46,6 +46,14 @@ namespace caifq
 
 __device__ unsigned int g_umma_timeout_flag = 0;
 
+namespace
+{
+thread_local bool t_umma_stall_next = false;
+}
+
+// self-test hook: the next single-layer tensor-core launch of this thread waits for bytes that never arrive
+void umma_stall_next_launch() { t_umma_stall_next = true; }
+
 // Reads and clears the flag (1 = some bounded wait ran out since the last call; -1 = query failed).
 int take_umma_timeout_flag()
 {
@@ -85,7 +93,8 @@ __host__ __device__ constexpr int deq_teams(int wmode, bool bwd, int bn)
 {
   return (bn == 256 && wmode != 0 && !bwd) ? 1 : 2;
 }
-constexpr uint32_t kSpinLimit = 1u << 26;
+constexpr uint32_t kSpinLimit = 1u << 22;       // polls of one wait before it gives up (tens of ms)
+constexpr uint32_t kSpinLimitTest = 1u << 12;   // the same for the self-test of the give-up path
 
 template <int BN, int PLANES = 1>
 struct TileCfg
@@ -131,9 +140,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+// Bounded wait.  A wait that runs out raises the CTA's abort word and the device flag; from then on
+// every wait of the CTA returns at once, so the roles run through the rest of their loops without
+// spinning (on garbage: the results are wrong and the host sees the flag) and the kernel ends within
+// about one limit, TMEM released.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_word, uint32_t limit)
 {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+  if (*abort_word != 0u)
+  {
+    return false;
+  }
+  for (uint32_t spin = 0; spin < limit; ++spin)
   {
     uint32_t done;
     asm volatile(
@@ -147,7 +164,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
     {
       return true;
     }
+    if ((spin & 1023u) == 1023u && *abort_word != 0u)
+    {
+      return false;
+    }
   }
+  *abort_word = 1u;
   atomicExch(&g_umma_timeout_flag, 1u);
   return false;
 }
@@ -334,6 +356,8 @@ struct UmmaParams
   // columns 0..63 are features [64 j, 64 j + 64) of the gate projection, columns 64..127 the same
   // features of the up projection.  c receives gate(x), c_up up(x), c_hidden silu(gate(x)) * up(x),
   // each rounded to the storage dtype the way the separate kernels round them.
+  uint32_t spin_limit;   // polls of one wait before it gives up
+  uint32_t stall_bytes;  // self-test only: bytes the first activation tile announces but never receives
   int swiglu;
   const uint8_t *codes_up;
   const void *scales_up;
@@ -449,7 +473,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   constexpr int DEQ_TEAMS = deq_teams(WMODE, BWD, BN);
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[MAX_STAGES * 3 + 4];
+  __shared__ uint64_t drain_bar;   // give-up path only: the MMAs issued so far have completed
   __shared__ uint32_t tmem_base_slot;
+  __shared__ uint32_t cta_abort;   // a wait of this CTA has run out
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -464,8 +490,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   auto acc_full = [&](int a) { return bar0 + static_cast<uint32_t>(3 * STAGES + a) * 8u; };
   auto acc_empty = [&](int a) { return bar0 + static_cast<uint32_t>(3 * STAGES + 2 + a) * 8u; };
 
+  volatile uint32_t *abort_word = &cta_abort;
+  auto wait = [&](uint32_t bar, uint32_t parity) { return mbar_wait(bar, parity, abort_word, p.spin_limit); };
   if (threadIdx.x == 0)
   {
+    cta_abort = 0u;
+    mbar_init(smem_u32(&drain_bar), 1);
     for (int s = 0; s < STAGES; ++s)
     {
       mbar_init(a_full(s), 1);
@@ -510,8 +540,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int row_tile = static_cast<int>(tw.row0);
         for (int kb = 0; kb < num_kb_all; ++kb)
         {
-          mbar_wait(empty(s), par ^ 1u);
-          mbar_expect_tx(a_full(s), A_STAGE_BYTES);
+          if (!wait(empty(s), par ^ 1u))
+          {
+            tile = num_tiles;   // nothing new is started once a wait has run out
+            break;
+          }
+          mbar_expect_tx(a_full(s), A_STAGE_BYTES + ((tile == static_cast<int>(blockIdx.x) && kb == 0) ? p.stall_bytes : 0u));
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
           {
@@ -564,12 +598,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       uint32_t acc_par = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
       {
-        mbar_wait(acc_empty(acc), acc_par ^ 1u);
+        wait(acc_empty(acc), acc_par ^ 1u);
         tc_fence_after();
         for (int kb = 0; kb < num_kb_all; ++kb)
         {
-          mbar_wait(a_full(s), par);
-          mbar_wait(b_full(s), par);
+          wait(a_full(s), par);
+          wait(b_full(s), par);
           tc_fence_after();
           const uint64_t adesc0 = make_desc(a_addr(s, 0), 16, 1024);
           const uint64_t bdesc0 = BWD ? make_desc(b_addr(s), 8192, 1024) : make_desc(b_addr(s), 16, 1024);
@@ -631,7 +665,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       {
         out_scale = __ldg(static_cast<const float *>(tw.scales));
       }
-      mbar_wait(acc_full(acc), acc_par);
+      wait(acc_full(acc), acc_par);
       tc_fence_after();
       if (!BWD && BN == 128 && p.swiglu)
       {
@@ -913,7 +947,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const uint32_t gkb = gkb0 + static_cast<uint32_t>(kb);
         const int s = static_cast<int>(gkb % STAGES);
         const uint32_t par = (gkb / STAGES) & 1u;
-        mbar_wait(empty(s), par ^ 1u);
+        wait(empty(s), par ^ 1u);
         const uint32_t bbase = b_addr(s);
 #pragma unroll
         for (int i = 0; i < PER_THREAD; ++i)
@@ -1013,7 +1047,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const uint32_t gkb = gkb0 + static_cast<uint32_t>(num_kb);
         const int s = static_cast<int>(gkb % STAGES);
         const uint32_t par = (gkb / STAGES) & 1u;
-        mbar_wait(empty(s), par ^ 1u);
+        wait(empty(s), par ^ 1u);
         const uint32_t bbase = b_addr(s);
 #pragma unroll
         for (int i = 0; i < (BN * BK * 2 / 16) / TEAM_THREADS; ++i)
@@ -1051,6 +1085,39 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
 
   // ------------------------------------------------------------------ teardown
+  if (*abort_word != 0u && warp == 0 && lane == 0)
+  {
+    // activation tiles that were started may still be on their way: give them time to land before the
+    // CTA's shared memory goes back (a copy must not arrive in memory that belongs to another CTA)
+    for (int i = 0; i < 64; ++i)
+    {
+      __nanosleep(2000);
+    }
+  }
+  if (*abort_word != 0u && warp == 1)
+  {
+    // MMAs issued after the give-up may still run: tensor memory is released only after they have
+    // completed (a commit tracks every MMA issued before it); bounded like every other wait
+    if (elect_one())
+    {
+      umma_commit(smem_u32(&drain_bar));
+    }
+    __syncwarp();
+    const uint32_t addr = smem_u32(&drain_bar);
+    bool done = false;
+    for (uint32_t spin = 0; spin < p.spin_limit && !done; ++spin)
+    {
+      uint32_t ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(addr), "r"(0u)
+          : "memory");
+      done = ok != 0;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 1)
@@ -1199,6 +1266,15 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
 {
   const caifq_weight &w = g.w;
   UmmaParams p{};
+  p.spin_limit = kSpinLimit;
+  p.stall_bytes = 0;
+  if (t_umma_stall_next)
+  {
+    // self-test of the give-up path: the first activation tile announces 16 bytes that never arrive
+    t_umma_stall_next = false;
+    p.spin_limit = kSpinLimitTest;
+    p.stall_bytes = 16;
+  }
   p.codes = static_cast<const uint8_t *>(w.codes);
   p.scales = w.scales;
   p.c = g.c;
@@ -1339,6 +1415,8 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
   const caifq_weight &w0 = g.weights[0];
   const int64_t total_rows = g.offsets[g.num_experts];
   UmmaParams p{};
+  p.spin_limit = kSpinLimit;
+  p.stall_bytes = 0;
   p.codes = nullptr;
   p.scales = nullptr;
   p.c = g.c;
@@ -1455,6 +1533,8 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
   const caifq_weight &w0 = g.gate[0];
   const int64_t total_rows = g.offsets[g.num_experts];
   UmmaParams p{};
+  p.spin_limit = kSpinLimit;
+  p.stall_bytes = 0;
   p.c = g.gate_out;
   p.c_up = g.up_out;
   p.c_hidden = g.hidden;

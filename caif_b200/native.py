@@ -58,6 +58,7 @@ _SIGNATURES = {
     "caifq_device_ok": (ctypes.c_int, []),
     "caifq_device_status": (ctypes.c_int, []),
     "caifq_selftest_stall_next_decode": (None, []),
+    "caifq_selftest_stall_next_umma": (None, []),
     "caifq_set_cta_limit": (None, [_i32]),
     "caifq_quantize_int8_per_tensor": (ctypes.c_int, [_vp, _vp, _vp, _i64, _vp]),
     "caifq_quantize_int8_per_channel": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _vp]),

@@ -107,6 +107,10 @@ CAIFQ_API int caifq_device_status(void);
  * caifq_device_status() then reports bit 0.  Nothing faults and nothing hangs.
  */
 CAIFQ_API void caifq_selftest_stall_next_decode(void);
+/* The same for the tensor-core kernel: the next many-token caifq_linear_fwd / caifq_linear_dx call of the
+ * calling thread announces 16 bytes for its first activation tile that never arrive.  The kernel returns
+ * (its output is garbage), its tensor memory is released, caifq_device_status() reports bit 1. */
+CAIFQ_API void caifq_selftest_stall_next_umma(void);
 /*
  * The weight-streaming and tensor-core kernels are persistent: one CTA per SM.  A host that runs
  * collectives (NCCL) beside them on another stream caps their grids with this call so that the

@@ -105,4 +105,6 @@ def main(out_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "gpurun_out/golden")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py OUTPUT_DIR   (run on a box with a GPU)")
+    main(sys.argv[1])

@@ -316,3 +316,27 @@ def test_decode_wait_that_runs_out_raises_the_flag_and_returns():
     y = nv.linear_fwd(weight, x, torch.float32, orc.F32)
     assert nv.lib().caifq_device_status() == 0
     assert max_rel_err(y.cpu().numpy(), want) <= TOL_F32
+
+
+def test_umma_wait_that_runs_out_raises_the_flag_and_returns():
+    """The tensor-core kernel's give-up path: one activation tile announces bytes that never arrive.  The
+    first wait that runs out makes every later wait of the CTA return at once, so the kernel ends within
+    about one (short, self-test) limit instead of one limit per remaining wait; its tensor memory is
+    released (the next launch can allocate it) and the status word reports bit 1."""
+    import time
+
+    weight, wc, x_np, x, dy_np, dy = _umma_case(orc.I8, orc.BF16, 512, 1024, 1024, 4242)
+    y = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    assert nv.last_path() == "umma"
+    assert nv.lib().caifq_device_status() == 0
+    nv.lib().caifq_selftest_stall_next_umma()
+    t0 = time.time()
+    nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0
+    assert nv.lib().caifq_device_status() & 2
+    y2 = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    dx = nv.linear_dx(weight, dy, torch.float32, orc.BF16)
+    assert nv.lib().caifq_device_status() == 0
+    assert torch.equal(y, y2)
+    assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, orc.BF16)) <= TOL_16

@@ -331,17 +331,24 @@ def test_grouped_experts_at_the_moe_config_size_equal_single_expert_calls():
                                    orc.BF16)
         assert torch.equal(o1, out[lo:hi]) and torch.equal(g1, g_out[lo:hi]) and torch.equal(u1, u_out[lo:hi])
         assert torch.equal(d1, dx[lo:hi])
-    # expert 17 against the oracle on its first 64 rows
-    e = 17
-    lo = offs[e]
-    ws = []
-    for w in (gate[e], up[e], down[e]):
-        codes = w.codes.cpu().numpy()
-        scales = w.scales.cpu().view(torch.int16).numpy().view(np.uint16)
-        ws.append(orc.weight_to_compute(codes, scales, orc.I4, w.in_dim, w.out_dim, orc.BF16, 0, 128))
-    want, _, _ = orc.frozen_expert_forward(buf[lo:lo + 64].float().cpu().numpy(), ws[0], ws[1], ws[2], orc.BF16,
-                                           orc.BF16)
-    assert max_rel_err(out[lo:lo + 64].float().cpu().numpy(), want) <= 2e-2
+    # three experts (first, middle, last) against the oracle on 64 of their rows each, forward and dX
+    for e in (0, 17, 63):
+        lo = offs[e] + 5
+        ws = []
+        for w in (gate[e], up[e], down[e]):
+            codes = w.codes.cpu().numpy()
+            scales = w.scales.cpu().view(torch.int16).numpy().view(np.uint16)
+            ws.append(orc.weight_to_compute(codes, scales, orc.I4, w.in_dim, w.out_dim, orc.BF16, 0, 128))
+        xe = buf[lo:lo + 64].float().cpu().numpy()
+        want, og, ou = orc.frozen_expert_forward(xe, ws[0], ws[1], ws[2], orc.BF16, orc.BF16, exact=False)
+        assert max_rel_err(out[lo:lo + 64].float().cpu().numpy(), want) <= 2e-2
+        assert max_rel_err(g_out[lo:lo + 64].float().cpu().numpy(), og) <= 2e-2
+        # the backward from the kernel's own saved gate/up values, as the layer does it
+        want_dx = orc.frozen_expert_backward(dy[lo:lo + 64].float().cpu().numpy(),
+                                             g_out[lo:lo + 64].float().cpu().numpy(),
+                                             u_out[lo:lo + 64].float().cpu().numpy(), ws[0], ws[1], ws[2], orc.BF16,
+                                             orc.BF16, exact=False)
+        assert max_rel_err(dx[lo:lo + 64].float().cpu().numpy(), want_dx) <= 2e-2
 
 
 @pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I4, orc.BF16), (orc.I4, orc.F32)])
@@ -373,3 +380,62 @@ def test_lora_fused_tensor_core_path(storage, compute, m, in_dim, out_dim, rank)
     want_big, _ = orc.lora_forward(x_np, orc.frozen_linear_forward(x_np, wc, compute), a,
                                    orc.round_through(b * 100, sd), alpha, sd)
     assert max_rel_err(y_big.float().cpu().numpy(), want_big) <= TOL[sd]
+
+
+def test_lora_at_the_training_config_size():
+    """4096 -> 4096 int8 per-tensor base, LoRA r16 a32, M = 8192 bf16 tokens, fp32 compute (config 3): Y and dX
+    on 64 sampled rows and the whole dA and dB against the oracle (host sgemm for the big products)."""
+    g = torch.Generator(device="cuda").manual_seed(1236)
+    dim, m, rank, alpha = 4096, 8192, 16, 32.0
+    wf = torch.randn(dim * dim, generator=g, device="cuda") * 0.02
+    q, s = nv.quantize_int8_per_tensor(wf)
+    weight = nv.Weight(q.view(dim, dim), nv.I8, dim, dim, s)
+    a = ((torch.rand(rank, dim, generator=g, device="cuda") * 2 - 1) / 64).to(torch.bfloat16)
+    b = (torch.randn(dim, rank, generator=g, device="cuda") * 1e-3).to(torch.bfloat16)
+    lora = nv.Lora(a, b, alpha)
+    x = torch.randn(m, dim, generator=g, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(m, dim, generator=g, device="cuda").to(torch.bfloat16)
+    y, hidden = nv.lora_linear_fwd(weight, lora, x, nv.F32)
+    assert nv.last_path() == "umma"
+    dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dy, x, hidden, nv.F32)
+    assert nv.lib().caifq_device_status() == 0
+    wc = orc.dequantize_int8_per_tensor(q.cpu().numpy().reshape(dim, dim), s.cpu().numpy())
+    a_np, b_np = a.float().cpu().numpy(), b.float().cpu().numpy()
+    x_np, dy_np = x.float().cpu().numpy(), dy.float().cpu().numpy()
+    rows = np.arange(0, m, m // 64)
+    base = orc.frozen_linear_forward(x_np[rows], wc, orc.F32, exact=False)
+    want_y, want_h = orc.lora_forward(x_np[rows], base, a_np, b_np, alpha, orc.BF16, exact=False)
+    assert max_rel_err(hidden[rows].float().cpu().numpy(), want_h) <= 2e-2
+    assert max_rel_err(y[rows].float().cpu().numpy(), want_y) <= 2e-2
+    # backward over ALL tokens (dA and dB reduce over them); hidden is the kernel's own, as the layer caches it
+    dx_base = orc.frozen_linear_backward(dy_np, wc, orc.F32, exact=False)
+    want_dx, want_da, want_db = orc.lora_backward(dy_np, x_np, hidden.float().cpu().numpy(), dx_base, a_np, b_np, alpha,
+                                                  orc.BF16, exact=False)
+    assert max_rel_err(dx[rows].float().cpu().numpy(), want_dx[rows]) <= 2e-2
+    assert max_rel_err(d_a.float().cpu().numpy(), want_da) <= 2e-2
+    assert max_rel_err(d_b.float().cpu().numpy(), want_db) <= 2e-2
+
+
+def test_lora_unfused_path_accumulates_into_the_tensor_core_epilogue():
+    """A rank the fused path does not take (12): the base product then ADDS into the LoRA term that is already
+    in y / dx (the reference's cast-then-Add, src/caif_device_lora_adapter.cpp:170-203), through the
+    tensor-core kernel's accumulate epilogue."""
+    rng = np.random.default_rng(812)
+    in_dim, out_dim, m, rank, alpha, sd = 1024, 768, 512, 12, 24.0, orc.BF16
+    weight, codes, scales, a, b, x_np, x, dy_np, dy, lora = _lora_case(rng, orc.I8, sd, in_dim, out_dim, m, rank, alpha)
+    big_b = orc.round_through(b * 300, sd)     # a LoRA term of the base's magnitude: a lost Add would show
+    lora = nv.Lora(lora.a, to_dev(big_b, torch.bfloat16), alpha)
+    wc = orc.weight_to_compute(codes, scales, orc.I8, in_dim, out_dim, orc.BF16, weight.scheme, weight.group_size)
+    y, hidden = nv.lora_linear_fwd(weight, lora, x, orc.BF16)
+    assert nv.last_path() == "umma"
+    want_y, want_h = orc.lora_forward(x_np, orc.frozen_linear_forward(x_np, wc, orc.BF16), a, big_b, alpha, sd)
+    assert max_rel_err(y.float().cpu().numpy(), want_y) <= 2e-2
+    lora_only = want_y - orc.round_through(orc.frozen_linear_forward(x_np, wc, orc.BF16), sd)
+    assert np.max(np.abs(lora_only)) > 0.1 * np.max(np.abs(want_y))       # the Add matters in this case
+    dx, d_a, d_b = nv.lora_linear_bwd(weight, lora, dy, x, hidden, orc.BF16)
+    assert nv.last_path() == "umma"
+    want_dx, want_da, want_db = orc.lora_backward(dy_np, x_np, want_h, orc.frozen_linear_backward(dy_np, wc, orc.BF16),
+                                                  a, big_b, alpha, sd)
+    assert max_rel_err(dx.float().cpu().numpy(), want_dx) <= 2e-2
+    assert max_rel_err(d_a.float().cpu().numpy(), want_da) <= 2e-2
+    assert max_rel_err(d_b.float().cpu().numpy(), want_db) <= 2e-2
