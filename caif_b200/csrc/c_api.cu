@@ -105,6 +105,8 @@ int launch_swiglu_fwd(const void *gate, const void *up, void *hidden, int dtype,
 int launch_swiglu_bwd(const void *g_hidden, const void *gate, const void *up, void *g_gate, void *g_up, int dtype,
                       int64_t n, cudaStream_t s);
 int launch_add(const void *a, const void *b, void *out, int dtype, int64_t n, cudaStream_t s);
+int launch_silu_fwd(const void *x, void *out, int dtype, int64_t n, cudaStream_t s);
+int launch_silu_bwd(const void *x, const void *grad, void *out, int dtype, int64_t n, cudaStream_t s);
 // lora.cu
 size_t gemm_tn_scratch_bytes(int p, int q);
 int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
@@ -866,13 +868,14 @@ int caifq_moe_dispatch_bwd(const void *grad_expert_buffer, int32_t dtype, const 
 static int check_experts(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
                          int32_t num_experts, const int32_t *offsets, const char *who)
 {
-  CAIFQ_CHECK_ARG(gate && up && down && offsets, "%s: null expert table", who);
+  // gate == nullptr: experts without a gate projection (the reference's UseGated() == false)
+  CAIFQ_CHECK_ARG(up && down && offsets, "%s: null expert table", who);
   CAIFQ_CHECK_ARG(num_experts > 0, "%s: num_experts must be positive", who);
   const int in_dim = up[0].in_dim;
   const int hidden = up[0].out_dim;
   for (int e = 0; e < num_experts; ++e)
   {
-    int rc = check_weight(&gate[e], who);
+    int rc = (gate != nullptr) ? check_weight(&gate[e], who) : CAIFQ_OK;
     if (rc == CAIFQ_OK)
     {
       rc = check_weight(&up[e], who);
@@ -885,8 +888,9 @@ static int check_experts(const caifq_weight *gate, const caifq_weight *up, const
     {
       return rc;
     }
-    CAIFQ_CHECK_ARG(gate[e].in_dim == in_dim && up[e].in_dim == in_dim && down[e].out_dim == in_dim &&
-                        gate[e].out_dim == hidden && up[e].out_dim == hidden && down[e].in_dim == hidden,
+    CAIFQ_CHECK_ARG(up[e].in_dim == in_dim && down[e].out_dim == in_dim && up[e].out_dim == hidden &&
+                        down[e].in_dim == hidden &&
+                        (gate == nullptr || (gate[e].in_dim == in_dim && gate[e].out_dim == hidden)),
                     "%s: expert %d has inconsistent dims", who, e);
     CAIFQ_CHECK_ARG(offsets[e + 1] >= offsets[e], "%s: expert offsets must be non-decreasing", who);
   }
@@ -958,12 +962,25 @@ int caifq_grouped_expert_fwd(const caifq_weight *gate, const caifq_weight *up, c
   {
     return CAIFQ_OK;
   }
-  CAIFQ_CHECK_ARG(x && out && gate_out && up_out && hidden_ws, "%s: null pointer", who);
+  CAIFQ_CHECK_ARG(x && out && up_out && hidden_ws && (gate == nullptr || gate_out), "%s: null pointer", who);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t es = dtype_bytes(dtype);
-  const int64_t in_dim = up[0].in_dim;
   const int64_t hid = up[0].out_dim;
   int r = CAIFQ_OK;
+  if (gate == nullptr)
+  {
+    // hidden = SiLU(up(x)), src/caif_device_moe_frozen_expert.cpp:158-162
+    r = grouped_linear(up, num_experts, expert_offsets_host, false, x, up_out, dtype, false, compute_dtype, s, who);
+    if (r == CAIFQ_OK)
+    {
+      r = launch_silu_fwd(up_out, hidden_ws, dtype, total * hid, s);
+    }
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+    return grouped_linear(down, num_experts, expert_offsets_host, false, hidden_ws, out, dtype, false, compute_dtype,
+                          s, who);
+  }
   GroupedSwigluArgs fused{};
   fused.gate = gate;
   fused.up = up;
@@ -1027,10 +1044,9 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
   {
     return CAIFQ_OK;
   }
-  CAIFQ_CHECK_ARG(dy && gate_out && up_out && dx && ws, "%s: null pointer", who);
+  CAIFQ_CHECK_ARG(dy && up_out && dx && ws && (gate == nullptr || gate_out), "%s: null pointer", who);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t es = dtype_bytes(dtype);
-  const int64_t in_dim = up[0].in_dim;
   const int64_t hid = up[0].out_dim;
   char *g_hidden = static_cast<char *>(ws);
   char *g_gate = g_hidden + total * hid * es;
@@ -1040,6 +1056,16 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
   if (r != CAIFQ_OK)
   {
     return r;
+  }
+  if (gate == nullptr)
+  {
+    // g_up = SiLUBackward(up_out, g_hidden); dx = up.Bwd(g_up), src/caif_device_moe_frozen_expert.cpp:318-331
+    r = launch_silu_bwd(up_out, g_hidden, g_up, dtype, total * hid, s);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
+    return grouped_linear(up, num_experts, expert_offsets_host, true, g_up, dx, dtype, false, compute_dtype, s, who);
   }
   r = launch_swiglu_bwd(g_hidden, gate_out, up_out, g_gate, g_up, dtype, total * hid, s);
   if (r != CAIFQ_OK)

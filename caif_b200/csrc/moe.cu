@@ -428,6 +428,32 @@ __global__ void swiglu_bwd_kernel(const T *__restrict__ g_hidden, const T *__res
   }
 }
 
+// Non-gated experts (CAIF_DeviceMoEFrozenExpert with UseGated() == false,
+// src/caif_device_moe_frozen_expert.cpp:158-162, 318-331): hidden = SiLU(up), g_up = SiLUBackward(up, g_hidden)
+// with the reference's formulas (src/caif_cuda_kernels_activations.cu:513-514, 558-561).
+template <typename T>
+__global__ void silu_fwd_kernel(const T *__restrict__ x_in, T *__restrict__ out, int64_t n)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+  {
+    const float x = to_f<T>(x_in[i]);
+    out[i] = from_f<T>(x / (1.0f + expf(-x)));
+  }
+}
+
+template <typename T>
+__global__ void silu_bwd_kernel(const T *__restrict__ x_in, const T *__restrict__ grad, T *__restrict__ out, int64_t n)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+  {
+    const float x = to_f<T>(x_in[i]);
+    const float s = 1.0f / (1.0f + expf(-x));
+    out[i] = from_f<T>(to_f<T>(grad[i]) * s * (1.0f + x * (1.0f - s)));
+  }
+}
+
 template <typename T>
 __global__ void add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ out, int64_t n)
 {
@@ -949,6 +975,30 @@ int launch_swiglu_bwd(const void *g_hidden, const void *gate, const void *up, vo
                   : swiglu_bwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
                         static_cast<const T *>(g_hidden), static_cast<const T *>(gate), static_cast<const T *>(up),
                         static_cast<T *>(g_gate), static_cast<T *>(g_up), n)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_silu_fwd(const void *x, void *out, int dtype, int64_t n, cudaStream_t s)
+{
+  if (n <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (silu_fwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(static_cast<const T *>(x),
+                                                                             static_cast<T *>(out), n)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_silu_bwd(const void *x, const void *grad, void *out, int dtype, int64_t n, cudaStream_t s)
+{
+  if (n <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (silu_bwd_kernel<T><<<ew_grid(n), 256, 0, s>>>(
+                                  static_cast<const T *>(x), static_cast<const T *>(grad), static_cast<T *>(out), n)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

@@ -202,7 +202,9 @@ class CAIF_DeviceTensor
       const size_t bytes = t.SizeBytes();
       if (bytes > 0)
       {
-        CAIF_CheckCuda(cudaMalloc(&t._data, bytes), "CAIF_DeviceTensor: cudaMalloc");
+        // stream-ordered allocation from the device's pool: no device-wide synchronisation, and a
+        // temporary can be released while the kernels that use it are still queued on the stream
+        CAIF_CheckCuda(cudaMallocAsync(&t._data, bytes, t._stream), "CAIF_DeviceTensor: cudaMallocAsync");
       }
       return t;
     }
@@ -292,7 +294,7 @@ class CAIF_DeviceTensor
     {
       if (_owns && _data != nullptr)
       {
-        cudaFree(_data);
+        cudaFreeAsync(_data, _stream);   // ordered behind everything queued on the tensor's stream
       }
       _data = nullptr;
     }
@@ -1022,10 +1024,6 @@ class CAIF_DeviceMoEFrozenExpert : public CAIF_DeviceLayerTyped<ComputeT, Storag
       {
         THROW_CAIFE("MoEFrozenExpert: sub-layers must not be null");
       }
-      if (!config.UseGated())
-      {
-        THROW_CAIFE("MoEFrozenExpert: only the gated form is built");
-      }
     }
 
     CAIF_DeviceTensor ForwardImpl(const CAIF_DeviceTensor &input, CAIF_RunContext &ctx) override
@@ -1051,14 +1049,23 @@ class CAIF_DeviceMoEFrozenExpert : public CAIF_DeviceLayerTyped<ComputeT, Storag
       {
         THROW_CAIFE("MoEFrozenExpert::ForwardInto: tensors must be in the expert's storage dtype");
       }
-      CAIF_DeviceTensor gate_out = CAIF_DeviceTensor::Uninitialized({n, _config.HiddenDim()}, Stream(), sd);
+      const bool gated = _config.UseGated();
+      CAIF_DeviceTensor gate_out;
+      if (gated)
+      {
+        gate_out = CAIF_DeviceTensor::Uninitialized({n, _config.HiddenDim()}, Stream(), sd);
+      }
       CAIF_DeviceTensor up_out = CAIF_DeviceTensor::Uninitialized({n, _config.HiddenDim()}, Stream(), sd);
       CAIF_DeviceTensor hidden = CAIF_DeviceTensor::Uninitialized({n, _config.HiddenDim()}, Stream(), sd);
-      const caifq_weight g = _sub.gate->AsCaifqWeight();
+      caifq_weight g{};
+      if (gated)
+      {
+        g = _sub.gate->AsCaifqWeight();
+      }
       const caifq_weight u = _sub.up->AsCaifqWeight();
       const caifq_weight d = _sub.down->AsCaifqWeight();
       const int32_t offsets[2] = {0, static_cast<int32_t>(n)};
-      CAIF_CheckCaifq(caifq_grouped_expert_fwd(&g, &u, &d, 1, offsets, input.DeviceDataRaw(),
+      CAIF_CheckCaifq(caifq_grouped_expert_fwd(gated ? &g : nullptr, &u, &d, 1, offsets, input.DeviceDataRaw(),
                                                output_view.DeviceDataRaw(), gate_out.DeviceDataRaw(),
                                                up_out.DeviceDataRaw(), hidden.DeviceDataRaw(),
                                                static_cast<int32_t>(sd), static_cast<int32_t>(Base_t::ComputeDtype()),
@@ -1070,30 +1077,34 @@ class CAIF_DeviceMoEFrozenExpert : public CAIF_DeviceLayerTyped<ComputeT, Storag
         _cached_up_out = std::move(up_out);
         _cached_rows = n;
       }
-      CAIF_CheckCuda(cudaStreamSynchronize(Stream().Handle()), "MoEFrozenExpert::Forward");  // temporaries die here
+      // the temporaries are released in stream order when they go out of scope: no synchronisation
     }
 
     CAIF_DeviceTensor BackwardImpl(const CAIF_DeviceTensor &grad_output, CAIF_RunContext &) override
     {
-      if (_cached_gate_out.IsEmpty())
+      if (_cached_up_out.IsEmpty())
       {
         THROW_CAIFE("MoEFrozenExpert::Backward: must call Forward(training=true) first");
       }
+      const bool gated = _config.UseGated();
       const uint32_t n = _cached_rows;
       constexpr Dtype_e sd = Base_t::StorageDtype();
       CAIF_DeviceTensor grad_input = CAIF_DeviceTensor::Uninitialized({n, _config.InputDim()}, Stream(), sd);
       CAIF_DeviceTensor ws = CAIF_DeviceTensor::Uninitialized({3u, n, _config.HiddenDim()}, Stream(), sd);
-      const caifq_weight g = _sub.gate->AsCaifqWeight();
+      caifq_weight g{};
+      if (gated)
+      {
+        g = _sub.gate->AsCaifqWeight();
+      }
       const caifq_weight u = _sub.up->AsCaifqWeight();
       const caifq_weight d = _sub.down->AsCaifqWeight();
       const int32_t offsets[2] = {0, static_cast<int32_t>(n)};
-      CAIF_CheckCaifq(caifq_grouped_expert_bwd(&g, &u, &d, 1, offsets, grad_output.DeviceDataRaw(),
+      CAIF_CheckCaifq(caifq_grouped_expert_bwd(gated ? &g : nullptr, &u, &d, 1, offsets, grad_output.DeviceDataRaw(),
                                                _cached_gate_out.DeviceDataRaw(), _cached_up_out.DeviceDataRaw(),
                                                grad_input.DeviceDataRaw(), ws.DeviceDataRaw(),
                                                static_cast<int32_t>(sd), static_cast<int32_t>(Base_t::ComputeDtype()),
                                                Stream().Handle()),
                       "MoEFrozenExpert::Backward");
-      CAIF_CheckCuda(cudaStreamSynchronize(Stream().Handle()), "MoEFrozenExpert::Backward");
       return grad_input;
     }
 

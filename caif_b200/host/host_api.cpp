@@ -70,6 +70,60 @@ std::unique_ptr<CAIF_DeviceLayer> make_lora(Dtype_e sd, const CAIF_DeviceLoRAAda
   THROW_CAIFE("LoRAAdapter: storage dtype must be fp32, fp16 or bf16");
 }
 
+// Moves the frozen linear out of a handle's box (the box is destroyed); the expert owns it afterwards.
+std::unique_ptr<CAIF_DeviceFrozenLinearBase> take_frozen(void *handle)
+{
+  auto *box = static_cast<LayerBox *>(handle);
+  if (box == nullptr)
+  {
+    return nullptr;
+  }
+  auto *f = dynamic_cast<CAIF_DeviceFrozenLinearBase *>(box->layer.get());
+  if (f == nullptr)
+  {
+    THROW_CAIFE("handle is not a frozen linear layer");
+  }
+  box->layer.release();
+  delete box;
+  return std::unique_ptr<CAIF_DeviceFrozenLinearBase>(f);
+}
+
+template <typename ComputeT>
+std::unique_ptr<CAIF_DeviceLayer> make_expert(Dtype_e sd, const CAIF_DeviceMoEFrozenExpertConfig &cfg, void *gate,
+                                              void *up, void *down, CAIF_CudaStream &stream)
+{
+  switch (sd)
+  {
+    case Dtype_e::Float32:
+    {
+      typename CAIF_DeviceMoEFrozenExpert<ComputeT, float>::FrozenSubLayers_t sub;
+      sub.gate = take_frozen(gate);
+      sub.up = take_frozen(up);
+      sub.down = take_frozen(down);
+      return std::make_unique<CAIF_DeviceMoEFrozenExpert<ComputeT, float>>(cfg, std::move(sub), stream);
+    }
+    case Dtype_e::Float16:
+    {
+      typename CAIF_DeviceMoEFrozenExpert<ComputeT, caif_half_t>::FrozenSubLayers_t sub;
+      sub.gate = take_frozen(gate);
+      sub.up = take_frozen(up);
+      sub.down = take_frozen(down);
+      return std::make_unique<CAIF_DeviceMoEFrozenExpert<ComputeT, caif_half_t>>(cfg, std::move(sub), stream);
+    }
+    case Dtype_e::BFloat16:
+    {
+      typename CAIF_DeviceMoEFrozenExpert<ComputeT, caif_bfloat16_t>::FrozenSubLayers_t sub;
+      sub.gate = take_frozen(gate);
+      sub.up = take_frozen(up);
+      sub.down = take_frozen(down);
+      return std::make_unique<CAIF_DeviceMoEFrozenExpert<ComputeT, caif_bfloat16_t>>(cfg, std::move(sub), stream);
+    }
+    default:
+      break;
+  }
+  THROW_CAIFE("MoEFrozenExpert: storage dtype must be fp32, fp16 or bf16");
+}
+
 void copy_string(const std::string &s, char *buf, size_t cap)
 {
   if (cap == 0)
@@ -145,6 +199,36 @@ CAIFH_API int caifh_lora_wrap(void *base_handle, uint32_t rank, float alpha, int
     box->storage = sd;
     box->out_dtype = sd;
     delete base;  // its layer and stream moved into the adapter
+    *handle = box.release();
+  });
+}
+
+// A frozen expert over three frozen-linear handles (gate may be null for the non-gated form).  The
+// expert takes ownership of the three layers: their handles must not be used or destroyed afterwards.
+CAIFH_API int caifh_moe_frozen_expert_create(void *gate, void *up, void *down, uint32_t input_dim, uint32_t hidden_dim,
+                                             int use_gated, int storage, int compute, void *stream, void **handle)
+{
+  return guarded([&] {
+    const CAIF_DeviceMoEFrozenExpertConfig cfg(input_dim, hidden_dim, use_gated != 0);
+    auto box = std::make_unique<LayerBox>();
+    box->stream = std::make_unique<CAIF_CudaStream>(static_cast<cudaStream_t>(stream));
+    const Dtype_e sd = static_cast<Dtype_e>(storage);
+    switch (static_cast<Dtype_e>(compute))
+    {
+      case Dtype_e::Float32:
+        box->layer = make_expert<float>(sd, cfg, gate, up, down, *box->stream);
+        break;
+      case Dtype_e::Float16:
+        box->layer = make_expert<caif_half_t>(sd, cfg, gate, up, down, *box->stream);
+        break;
+      case Dtype_e::BFloat16:
+        box->layer = make_expert<caif_bfloat16_t>(sd, cfg, gate, up, down, *box->stream);
+        break;
+      default:
+        THROW_CAIFE("MoEFrozenExpert: compute dtype must be fp32, fp16 or bf16");
+    }
+    box->storage = sd;
+    box->out_dtype = sd;
     *handle = box.release();
   });
 }

@@ -15,7 +15,7 @@ _lib = None
 EXPORTS = ["caifh_last_error", "caifh_frozen_linear_create", "caifh_load_weight_from_device",
            "caifh_load_scales_from_host", "caifh_lora_wrap", "caifh_forward", "caifh_backward", "caifh_description",
            "caifh_parameter_names", "caifh_counts", "caifh_parameter_copy", "caifh_frozen_tensor_fp32",
-           "caifh_destroy"]
+           "caifh_moe_frozen_expert_create", "caifh_destroy"]
 
 
 class HostLayerError(RuntimeError):
@@ -120,3 +120,21 @@ class Layer:
         if self.h:
             lib().caifh_destroy(self.h)
             self.h = ctypes.c_void_p()
+
+
+class FrozenExpert(Layer):
+    """CAIF_DeviceMoEFrozenExpert over three frozen linears (gate may be None: the non-gated form).
+    The expert takes the three layers over: their Python objects are emptied."""
+
+    def __init__(self, gate, up, down, input_dim, hidden_dim, storage, compute=native.F32):
+        self.in_dim, self.out_dim = input_dim, input_dim
+        self.out_code = storage
+        self.h = ctypes.c_void_p()
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream) if torch.cuda.is_available() else None
+        _check(lib().caifh_moe_frozen_expert_create(gate.h if gate is not None else None, up.h, down.h,
+                                                    ctypes.c_uint32(input_dim), ctypes.c_uint32(hidden_dim),
+                                                    int(gate is not None), int(storage), int(compute), stream,
+                                                    ctypes.byref(self.h)))
+        for layer in (gate, up, down):
+            if layer is not None:
+                layer.h = ctypes.c_void_p()

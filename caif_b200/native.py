@@ -466,17 +466,19 @@ def _weight_array(ws):
 
 
 def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32):
-    """gate/up/down: lists of Weight; offsets_host: list of E+1 ints; x: packed [total, in]."""
+    """gate/up/down: lists of Weight (gate=None: experts without a gate projection; the gate output
+    returned is then None); offsets_host: list of E+1 ints; x: packed [total, in]."""
     _need_cuda(x)
-    n_exp = len(gate)
+    n_exp = len(up)
     total = int(offsets_host[-1])
     hid = up[0].out_dim
     out = torch.empty((total, up[0].in_dim), dtype=x.dtype, device=x.device)
-    gate_out = torch.empty((total, hid), dtype=x.dtype, device=x.device)
+    gate_out = torch.empty((total, hid), dtype=x.dtype, device=x.device) if gate is not None else None
     up_out = torch.empty((total, hid), dtype=x.dtype, device=x.device)
     hidden = torch.empty((total, hid), dtype=x.dtype, device=x.device)
     offs = (ctypes.c_int32 * (n_exp + 1))(*[int(v) for v in offsets_host])
-    _check(lib().caifq_grouped_expert_fwd(_weight_array(gate), _weight_array(up), _weight_array(down), n_exp, offs,
+    _check(lib().caifq_grouped_expert_fwd(_weight_array(gate) if gate is not None else None, _weight_array(up),
+                                          _weight_array(down), n_exp, offs,
                                           _ptr(x), _ptr(out), _ptr(gate_out), _ptr(up_out), _ptr(hidden),
                                           dtype_code(x), compute, _stream()), "grouped_expert_fwd")
     return out, gate_out, up_out
@@ -484,13 +486,14 @@ def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32):
 
 def grouped_expert_bwd(gate, up, down, offsets_host, dy, gate_out, up_out, compute=F32):
     _need_cuda(dy, gate_out, up_out)
-    n_exp = len(gate)
+    n_exp = len(up)
     total = int(offsets_host[-1])
     hid = up[0].out_dim
     dx = torch.empty((total, up[0].in_dim), dtype=dy.dtype, device=dy.device)
     ws = torch.empty((3, max(total, 1), hid), dtype=dy.dtype, device=dy.device)
     offs = (ctypes.c_int32 * (n_exp + 1))(*[int(v) for v in offsets_host])
-    _check(lib().caifq_grouped_expert_bwd(_weight_array(gate), _weight_array(up), _weight_array(down), n_exp, offs,
+    _check(lib().caifq_grouped_expert_bwd(_weight_array(gate) if gate is not None else None, _weight_array(up),
+                                          _weight_array(down), n_exp, offs,
                                           _ptr(dy), _ptr(gate_out), _ptr(up_out), _ptr(dx), _ptr(ws),
                                           dtype_code(dy), compute, _stream()), "grouped_expert_bwd")
     return dx

@@ -328,7 +328,9 @@ CAIFQ_API int caifq_moe_dispatch_bwd(const void *grad_expert_buffer, int32_t dty
  * for every expert e, rows [offsets[e], offsets[e+1]) of the packed buffer go
  * through  down_e( silu(gate_e(x)) * up_e(x) ).
  * gate/up/down are arrays of num_experts weights (host array of structs whose
- * pointers are device pointers).  x, out, and the saved gate_out / up_out
+ * pointers are device pointers).  gate == NULL selects experts without a gate
+ * projection (the reference's UseGated() == false, :158-162, 318-331):
+ * down_e( silu(up_e(x)) ); gate_out is then unused and may be NULL.  x, out, and the saved gate_out / up_out
  * (each [total, hidden], may be NULL when not training) are in `dtype`.
  * expert_offsets_host is the host copy of the offsets (E+1 ints).
  */

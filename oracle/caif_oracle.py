@@ -284,9 +284,14 @@ def silu_backward(grad, x):
 
 def frozen_expert_forward(x, wg, wu, wd, compute=F32, sd=F32, exact=True):
     """down( silu(gate(x)) * up(x) ); each frozen-linear output (fp32) is cast
-    to the storage dtype before the elementwise step (:113-126)."""
-    gate = round_through(frozen_linear_forward(x, wg, compute, exact), sd)
+    to the storage dtype before the elementwise step (:113-126).  wg=None is the
+    non-gated form down( silu(up(x)) ) (:158-162); gate is then returned as None."""
     up = round_through(frozen_linear_forward(x, wu, compute, exact), sd)
+    if wg is None:
+        hid = round_through(silu(up), sd)
+        out = round_through(frozen_linear_forward(hid, wd, compute, exact), sd)
+        return out, None, up
+    gate = round_through(frozen_linear_forward(x, wg, compute, exact), sd)
     act = round_through(silu(gate), sd)
     hid = round_through(act * up, sd)
     out = round_through(frozen_linear_forward(hid, wd, compute, exact), sd)
@@ -295,6 +300,10 @@ def frozen_expert_forward(x, wg, wu, wd, compute=F32, sd=F32, exact=True):
 
 def frozen_expert_backward(dy, gate, up, wg, wu, wd, compute=F32, sd=F32, exact=True):
     g_hidden = round_through(frozen_linear_backward(dy, wd, compute, exact), sd)
+    if wg is None:
+        # src/caif_device_moe_frozen_expert.cpp:318-331
+        g_up = round_through(silu_backward(g_hidden, up), sd)
+        return round_through(frozen_linear_backward(g_up, wu, compute, exact), sd)
     act = round_through(silu(gate), sd)
     g_up = round_through(g_hidden * act, sd)
     g_act = round_through(g_hidden * up, sd)

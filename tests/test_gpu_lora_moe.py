@@ -253,6 +253,41 @@ def test_grouped_frozen_experts(storage, sd, compute):
         assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
 
 
+@pytest.mark.parametrize("storage,sd,compute,rows", [
+    (orc.I8, orc.F32, orc.F32, [13, 0, 40]),            # per-expert calls of the generic kernel
+    (orc.I4, orc.BF16, orc.BF16, [300, 0, 700, 1]),     # grouped tensor-core launches
+])
+def test_frozen_experts_without_a_gate_projection(storage, sd, compute, rows):
+    """UseGated() == false: down( silu(up(x)) ), dX = up.Bwd( SiLUBackward(up_out, down.Bwd(dy)) )
+    (src/caif_device_moe_frozen_expert.cpp:158-162, 318-331), selected by gate == NULL."""
+    rng = np.random.default_rng(450 + storage)
+    in_dim, hid = 256, 384
+    offsets = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    total = int(offsets[-1])
+    up, down, o_up, o_down = [], [], [], []
+    for _ in rows:
+        for lst, olst, (o, i) in ((up, o_up, (hid, in_dim)), (down, o_down, (in_dim, hid))):
+            w, codes, scales = make_weight(rng, o, i, storage, std=0.05)
+            lst.append(w)
+            olst.append(orc.weight_to_compute(codes, scales, storage, i, o, compute, w.scheme, w.group_size))
+    x_np, x = act(rng, total, in_dim, sd)
+    dy_np, dy = act(rng, total, in_dim, sd)
+    out, gate_out, up_out = nv.grouped_expert_fwd(None, up, down, offsets.tolist(), x, compute)
+    assert gate_out is None
+    dx = nv.grouped_expert_bwd(None, up, down, offsets.tolist(), dy, None, up_out, compute)
+    assert nv.lib().caifq_device_status() == 0
+    tol = max(TOL[sd], TOL[compute])
+    for e in range(len(rows)):
+        lo, hi = offsets[e], offsets[e + 1]
+        if lo == hi:
+            continue
+        want, _, u = orc.frozen_expert_forward(x_np[lo:hi], None, o_up[e], o_down[e], compute, sd)
+        assert max_rel_err(out[lo:hi].float().cpu().numpy(), want) <= tol
+        assert max_rel_err(up_out[lo:hi].float().cpu().numpy(), u) <= tol
+        want_dx = orc.frozen_expert_backward(dy_np[lo:hi], None, u, None, o_up[e], o_down[e], compute, sd)
+        assert max_rel_err(dx[lo:hi].float().cpu().numpy(), want_dx) <= tol
+
+
 @pytest.mark.parametrize("storage,compute,experts,in_dim,hid,mean_rows", [
     (orc.I4, orc.BF16, 6, 2048, 1408, 300),    # the MoE config's expert shape, ragged row counts
     (orc.I4, orc.F32, 3, 512, 640, 200),       # fp32 compute: two-term int4 operand

@@ -123,3 +123,47 @@ def test_lora_adapter_layer():
     assert max_rel_err(layer.parameter(0, a, gradient=True).cpu().numpy(), want_da) <= 1e-4
     assert max_rel_err(layer.parameter(1, b, gradient=True).cpu().numpy(), want_db) <= 1e-4
     layer.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("gated", [True, False])
+@pytest.mark.parametrize("storage,sd,compute", [(orc.I4, orc.BF16, orc.BF16), (orc.I8, orc.F32, orc.F32)])
+def test_moe_frozen_expert_layer(gated, storage, sd, compute):
+    """CAIF_DeviceMoEFrozenExpert over three frozen linears, gated and not
+    (src/caif_device_moe_frozen_expert.cpp:91-332): forward, backward after a training forward,
+    no trainable parameters, backward before forward refused."""
+    from gpu_util import TORCH_DTYPE, act, make_weight, max_rel_err
+
+    rng = np.random.default_rng(60 + storage + int(gated))
+    in_dim, hid, m = 256, 384, 70
+    subs, oracle_w = [], []
+    for (o, i) in ((hid, in_dim), (hid, in_dim), (in_dim, hid)):
+        weight, codes, scales = make_weight(rng, o, i, storage, std=0.05)
+        layer = hl.Layer(i, o, storage, compute)
+        layer.load_weight(weight.codes, storage)
+        layer.load_scales_from_host(np.ascontiguousarray(scales).tobytes())
+        subs.append(layer)
+        oracle_w.append(orc.weight_to_compute(codes, scales, storage, i, o, compute, weight.scheme, weight.group_size))
+    gate, up, down = subs
+    wg, wu, wd = oracle_w
+    if not gated:
+        gate.close()
+        gate, wg = None, None
+    expert = hl.FrozenExpert(gate, up, down, in_dim, hid, sd, compute)
+    assert expert.counts()[:2] == (0, 0)
+    assert expert.description() == "MoEFrozenExpert(%d,%d)" % (in_dim, hid)
+    x_np, x = act(rng, m, in_dim, sd)
+    dy_np, dy = act(rng, m, in_dim, sd)
+    with pytest.raises(hl.HostLayerError, match="Forward"):
+        expert.backward(dy)
+    y = expert.forward(x, training=True)
+    assert y.dtype == TORCH_DTYPE[sd] and tuple(y.shape) == (m, in_dim)
+    want, g, u = orc.frozen_expert_forward(x_np, wg, wu, wd, compute, sd)
+    tol = 2e-2 if sd == orc.BF16 else 1e-4
+    assert max_rel_err(y.float().cpu().numpy(), want) <= tol
+    dx = expert.backward(dy)
+    want_dx = orc.frozen_expert_backward(dy_np, g, u, wg, wu, wd, compute, sd)
+    assert max_rel_err(dx.float().cpu().numpy(), want_dx) <= tol
+    with pytest.raises(hl.HostLayerError, match="input_dim"):
+        expert.forward(torch.zeros(m, in_dim + 1, dtype=TORCH_DTYPE[sd], device="cuda"))
+    expert.close()
