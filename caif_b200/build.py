@@ -58,7 +58,7 @@ def build(verbose=False, force=False):
     changed = any(c for _, c in results)
     if changed or not os.path.exists(LIB):
         # hidden visibility by default; the extern "C" entry points carry default visibility
-        cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs
+        cmd = ["nvcc", "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + objs + ["-ldl"]
         subprocess.check_call(cmd)
     return LIB
 

@@ -91,6 +91,10 @@ _SIGNATURES = {
     "caifq_moe_combine_bwd_grad_expert": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_combine_bwd_grad_weights": (ctypes.c_int, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_dispatch_bwd": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
+    "caifq_linear_fwd_sharded": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _vp, _i32, _i32, _vp, _vp]),
+    "caifq_linear_dx_sharded": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _vp, _i32, _i32, _i32,
+                                               _vp, _vp]),
+    "caifq_rows_all_to_all": (ctypes.c_int, [_vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _i64, _vp, _vp]),
     "caifq_grouped_expert_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
                                                 ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp, _vp,
                                                 _vp, _vp, _i32, _i32, _vp]),

@@ -346,6 +346,37 @@ CAIFQ_API int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_wei
                              const void *gate_out, const void *up_out, void *dx, void *ws, int32_t dtype,
                              int32_t compute_dtype, void *stream);
 
+/* ---- sharded over the GPUs of one box ------------------------------------- */
+/*
+ * The reference is single-device; these entry points have no counterpart in it.  They run the
+ * entry point named in each comment and enqueue the NCCL collective a sharded layer needs behind it
+ * on the same stream.  `nccl_comm` is the host's ncclComm_t (passed as void*); NCCL is not linked into
+ * the library: its functions are looked up among the libraries loaded into the process (the host's
+ * own NCCL), then in libnccl.so.2.  One process per GPU; every rank of the communicator makes the
+ * same call.  No kernel of the library reads peer memory here: remote data lands in local buffers
+ * through the collective.
+ */
+
+/* Column-parallel forward: this rank holds output features [r*out/N, (r+1)*out/N) (a contiguous
+ * slice of codes and scales, w_shard->out_dim = out/N).  caifq_linear_fwd into y_local [m, out/N],
+ * then ncclAllGather into y_gathered [N, m, out/N] (rank r's slice at index r). */
+CAIFQ_API int caifq_linear_fwd_sharded(const caifq_weight *w_shard, const void *x, int32_t x_dtype, int64_t m,
+                             void *y_local, void *y_gathered, int32_t y_dtype, int32_t compute_dtype,
+                             void *nccl_comm, void *stream);
+/* Column-parallel dX: caifq_linear_dx on this rank's slice of dY [m, out/N] gives a partial sum
+ * dx_partial [m, in]; reduce_scatter != 0: ncclReduceScatter into dx_out [m/N, in] (rank r keeps rows
+ * [r*m/N, (r+1)*m/N)); reduce_scatter == 0: ncclAllReduce into dx_out [m, in] (may equal dx_partial). */
+CAIFQ_API int caifq_linear_dx_sharded(const caifq_weight *w_shard, const void *dy_local, int32_t dy_dtype, int64_t m,
+                            void *dx_partial, void *dx_out, int32_t reduce_scatter, int32_t dx_dtype,
+                            int32_t compute_dtype, void *nccl_comm, void *stream);
+/* The exchange of expert-parallel frozen experts: rows of `row_bytes` bytes, send_rows_host[r] of them
+ * for rank r lying back to back in `send` (rank order), recv_rows_host[r] arriving from rank r back to
+ * back in `recv`: an all-to-all with per-pair counts as one group of ncclSend / ncclRecv; a rank's own
+ * rows are copied.  With the packed buffer of caifq_moe_dispatch (ordered by expert, experts owned in
+ * rank order) this delivers every row to its expert's owner; the mirror call returns the results. */
+CAIFQ_API int caifq_rows_all_to_all(const void *send, const int64_t *send_rows_host, void *recv,
+                          const int64_t *recv_rows_host, int64_t row_bytes, void *nccl_comm, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,6 +4,7 @@ process per GPU).
 Column-parallel forward must equal the 1-GPU forward bit for bit (each output element runs the
 same K loop), dX within 1e-5 (the reduce changes the summation order); the expert-parallel frozen
 experts, forward and backward, must equal the same layer with all experts local."""
+import ctypes
 import os
 import sys
 
@@ -15,6 +16,70 @@ sys.path.insert(0, ROOT)
 
 from caif_b200 import native as nv  # noqa: E402
 from caif_b200.sharded import ColumnParallelFrozenLinear, ExpertParallelFrozenMoE, PeerBuffer, shard_range  # noqa: E402
+
+
+class _NcclUniqueId(ctypes.Structure):
+    """ncclUniqueId: 128 opaque bytes, passed to ncclCommInitRank BY VALUE."""
+    _fields_ = [("internal", ctypes.c_byte * 128)]
+
+
+def _sharded_c_abi(rank, world, dev, full, local, in_dim, out_dim, g):
+    """caifq_linear_fwd_sharded / caifq_linear_dx_sharded / caifq_rows_all_to_all: a host that is not
+    Python would create its ncclComm_t itself; so does this test (the NCCL library already in the
+    process), and hands the raw pointer to the library."""
+    nccl = ctypes.CDLL("libnccl.so.2")
+    uid = _NcclUniqueId()
+    if rank == 0:
+        assert nccl.ncclGetUniqueId(ctypes.byref(uid)) == 0
+    raw = torch.tensor(list(bytes(uid.internal)), dtype=torch.uint8, device=dev)
+    dist.broadcast(raw, 0)
+    ctypes.memmove(uid.internal, bytes(raw.cpu().tolist()), 128)
+    comm = ctypes.c_void_p()
+    nccl.ncclCommInitRank.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, _NcclUniqueId, ctypes.c_int]
+    assert nccl.ncclCommInitRank(ctypes.byref(comm), world, uid, rank) == 0
+    stream = nv._stream()
+    ok = True
+    m = 256
+    x = torch.randn(m, in_dim, generator=g, device=dev).to(torch.bfloat16)
+    dy = torch.randn(m, out_dim, generator=g, device=dev).to(torch.bfloat16)
+    shard = out_dim // world
+    y_local = torch.empty(m, shard, dtype=torch.float32, device=dev)
+    y_all = torch.empty(world, m, shard, dtype=torch.float32, device=dev)
+    nv._check(nv.lib().caifq_linear_fwd_sharded(local.ref(), nv._ptr(x), nv.BF16, m, nv._ptr(y_local), nv._ptr(y_all),
+                                                nv.F32, nv.BF16, comm, stream), "linear_fwd_sharded")
+    y1 = nv.linear_fwd(full, x, torch.float32, nv.BF16)
+    same = torch.equal(y_all.permute(1, 0, 2).reshape(m, out_dim), y1)
+    dy_local = dy[:, rank * shard:(rank + 1) * shard].contiguous()
+    dx_part = torch.empty(m, in_dim, dtype=torch.float32, device=dev)
+    dx_rs = torch.empty(m // world, in_dim, dtype=torch.float32, device=dev)
+    nv._check(nv.lib().caifq_linear_dx_sharded(local.ref(), nv._ptr(dy_local), nv.BF16, m, nv._ptr(dx_part),
+                                               nv._ptr(dx_rs), 1, nv.F32, nv.BF16, comm, stream), "linear_dx_sharded")
+    dx_ar = torch.empty(m, in_dim, dtype=torch.float32, device=dev)
+    nv._check(nv.lib().caifq_linear_dx_sharded(local.ref(), nv._ptr(dy_local), nv.BF16, m, nv._ptr(dx_part),
+                                               nv._ptr(dx_ar), 0, nv.F32, nv.BF16, comm, stream), "linear_dx_sharded")
+    dx1 = nv.linear_dx(full, dy, torch.float32, nv.BF16)
+    err_ar = float((dx_ar - dx1).abs().max() / dx1.abs().max())
+    rows = slice(rank * (m // world), (rank + 1) * (m // world))
+    err_rs = float((dx_rs - dx1[rows]).abs().max() / dx1.abs().max())
+    # rows all-to-all: rank r sends (r + 1) * (d + 1) rows to rank d, each row tagged with (source, dest)
+    send_rows = [(rank + 1) * (d + 1) for d in range(world)]
+    recv_rows = [(s + 1) * (rank + 1) for s in range(world)]
+    width = 64
+    send = torch.cat([torch.full((n, width), 100.0 * rank + d, device=dev) for d, n in enumerate(send_rows)])
+    recv = torch.zeros(sum(recv_rows), width, device=dev)
+    sr = (ctypes.c_int64 * world)(*send_rows)
+    rr = (ctypes.c_int64 * world)(*recv_rows)
+    nv._check(nv.lib().caifq_rows_all_to_all(nv._ptr(send), sr, nv._ptr(recv), rr, width * 4, comm, stream),
+              "rows_all_to_all")
+    want = torch.cat([torch.full((n, width), 100.0 * s + rank, device=dev) for s, n in enumerate(recv_rows)])
+    a2a = torch.equal(recv, want)
+    torch.cuda.synchronize()
+    nccl.ncclCommDestroy(comm)
+    ok = same and err_ar <= 1e-5 and err_rs <= 1e-5 and a2a
+    if rank == 0:
+        print("sharded C ABI: forward identical=%s, dX all-reduce %.1e, reduce-scatter %.1e, rows all-to-all exact=%s"
+              % (same, err_ar, err_rs, a2a))
+    return ok
 
 
 def main():
@@ -61,6 +126,9 @@ def main():
         if rank == 0:
             print("column-parallel m=%d, gather fused into the stores: identical=%s" % (m, same))
     pb.close()
+
+    # ---- the sharded C-ABI entry points with a communicator made through NCCL's own C API
+    ok = ok and _sharded_c_abi(rank, world, dev, full, local, in_dim, out_dim, g)
 
     # ---- expert-parallel frozen MoE
     experts, dim, hid, top_k, tokens = 8, 256, 384, 2, 300
