@@ -1,0 +1,152 @@
+"""ctypes binding of oracle/_ref/libcaif_ref_layers.so: the reference's own layer classes
+(CAIF_DeviceFrozenLinear, CAIF_DeviceLoRAAdapter, CAIF_DeviceMoEFrozenExpert), every translation unit
+compiled unmodified by oracle/build_ref_layers.py.  Test infrastructure: used to capture golden vectors
+from the executing reference and to time its device path as a comparator.  All buffers are numpy arrays
+on the host; the reference uploads and downloads them itself."""
+import ctypes
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PATH = os.path.join(ROOT, "oracle", "_ref", "libcaif_ref_layers.so")
+
+# CAIF_DataType_e
+F32, F16, BF16, I4, I8, U8 = 0, 2, 3, 4, 5, 9
+
+_lib = None
+
+
+def available():
+    return os.path.exists(PATH)
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(PATH)
+        _lib.refl_last_error.restype = ctypes.c_char_p
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise RuntimeError("reference layer call failed: %s" % lib().refl_last_error().decode())
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+
+def set_accuracy(on=True):
+    _check(lib().refl_set_accuracy(int(on)))
+
+
+def u8_code():
+    """CAIF_DataType_e::UInt8, read from the enum's order in include/caif/caif_data_type.h."""
+    return U8
+
+
+_ELEM = {F32: 4, F16: 2, BF16: 2}
+
+
+class Layer:
+    def __init__(self, handle, in_dim, out_dim):
+        self.h = handle
+        self.in_dim, self.out_dim = in_dim, out_dim
+
+    def _run(self, fn, x, dtype, last_dim, out_dim, *extra):
+        x = np.ascontiguousarray(x)
+        rows = x.size * x.itemsize // (_ELEM[dtype] * last_dim)
+        cap = rows * out_dim * 4
+        out = np.empty(cap, np.uint8)
+        out_dtype, out_bytes = ctypes.c_int(), ctypes.c_size_t()
+        _check(fn(self.h, _p(x), dtype, ctypes.c_uint32(rows), ctypes.c_uint32(last_dim), *extra, _p(out),
+                  ctypes.c_size_t(cap), ctypes.byref(out_dtype), ctypes.byref(out_bytes)))
+        raw = out[:out_bytes.value]
+        return _to_f32(raw, out_dtype.value).reshape(rows, out_dim), out_dtype.value
+
+    def forward(self, x, dtype, training=True):
+        return self._run(lib().refl_forward, x, dtype, self.in_dim, self.out_dim, int(training))
+
+    def backward(self, dy, dtype):
+        return self._run(lib().refl_backward, dy, dtype, self.out_dim, self.in_dim)
+
+    def gradient(self, index_from_end, shape, dtype):
+        cap = int(np.prod(shape)) * 4
+        out = np.empty(cap, np.uint8)
+        nbytes = ctypes.c_size_t()
+        _check(lib().refl_gradient(self.h, ctypes.c_uint32(index_from_end), _p(out), ctypes.c_size_t(cap),
+                                   ctypes.byref(nbytes)))
+        return _to_f32(out[:nbytes.value], dtype).reshape(shape)
+
+    def time(self, x, x_dtype, dy, dy_dtype, backward, warm, iters):
+        x = np.ascontiguousarray(x)
+        rows = x.size * x.itemsize // (_ELEM[x_dtype] * self.in_dim)
+        ms = ctypes.c_float()
+        _check(lib().refl_time(self.h, _p(x), x_dtype, _p(np.ascontiguousarray(dy)) if dy is not None else None,
+                               dy_dtype, ctypes.c_uint32(rows), ctypes.c_uint32(self.in_dim),
+                               ctypes.c_uint32(self.out_dim), int(backward), int(warm), int(iters), ctypes.byref(ms)))
+        return ms.value
+
+    def close(self):
+        if self.h:
+            lib().refl_destroy(self.h)
+            self.h = None
+
+
+def _to_f32(raw, dtype):
+    if dtype == F32:
+        return raw.view(np.float32).copy()
+    bits = raw.view(np.uint16)
+    if dtype == BF16:
+        return (bits.astype(np.uint32) << 16).view(np.float32)
+    return bits.view(np.float16).astype(np.float32)
+
+
+def to_raw(x_f32, dtype):
+    """fp32 values (already representable in `dtype`) as the raw array the reference uploads."""
+    x = np.ascontiguousarray(x_f32, np.float32)
+    if dtype == F32:
+        return x
+    if dtype == BF16:
+        return (x.view(np.uint32) >> 16).astype(np.uint16)
+    return x.astype(np.float16).view(np.uint16)
+
+
+def frozen_linear(in_dim, out_dim, storage, compute, codes, scales, group=128, cache_fp32=True, scheme=0):
+    """codes: packed uint8 (int4), int8, or raw float array; scales: fp16 bits (uint16) / fp32 / None."""
+    codes = np.ascontiguousarray(codes)
+    if storage == I4:
+        codes_dtype = U8
+    elif storage == I8:
+        codes_dtype = I8
+    else:
+        codes_dtype = storage
+    h = ctypes.c_void_p()
+    sc = np.ascontiguousarray(scales) if scales is not None else None
+    _check(lib().refl_frozen_create(ctypes.c_uint32(in_dim), ctypes.c_uint32(out_dim), storage, compute,
+                                    ctypes.c_uint32(group), int(cache_fp32), scheme, _p(codes), codes_dtype,
+                                    ctypes.c_uint32(codes.size), _p(sc),
+                                    ctypes.c_size_t(sc.nbytes if sc is not None else 0), ctypes.byref(h)))
+    return Layer(h, in_dim, out_dim)
+
+
+def lora_wrap(base, rank, alpha, storage, compute, a_raw, b_raw):
+    h = ctypes.c_void_p()
+    _check(lib().refl_lora_wrap(base.h, ctypes.c_uint32(rank), ctypes.c_float(alpha), ctypes.c_uint32(base.in_dim),
+                                ctypes.c_uint32(base.out_dim), storage, compute, _p(np.ascontiguousarray(a_raw)),
+                                _p(np.ascontiguousarray(b_raw)), ctypes.byref(h)))
+    base.h = None
+    return Layer(h, base.in_dim, base.out_dim)
+
+
+def frozen_expert(gate, up, down, input_dim, hidden_dim, storage, compute):
+    h = ctypes.c_void_p()
+    _check(lib().refl_expert_create(gate.h if gate is not None else None, up.h, down.h, ctypes.c_uint32(input_dim),
+                                    ctypes.c_uint32(hidden_dim), int(gate is not None), storage, compute,
+                                    ctypes.byref(h)))
+    for layer in (gate, up, down):
+        if layer is not None:
+            layer.h = None
+    return Layer(h, input_dim, input_dim)
