@@ -232,36 +232,83 @@ def _cpu_loop(step, steps, warmup, budget_s):
     return time.perf_counter() - t0, done
 
 
+class _RefHostOps:
+    """The reference's own Host_e matmul (CAIF_Ops::MatMulTransposeB on host tensors ->
+    src/caif_host_gemm.cpp -> cblas_sgemm), from the reference's unmodified sources compiled into
+    oracle/_ref/libcaif_ref_layers.so.  Raises when that library cannot be loaded."""
+
+    def __init__(self):
+        import ctypes
+
+        import numpy as np
+
+        self.ct, self.np = ctypes, np
+        self.lib = ctypes.CDLL(os.path.join(ROOT, "oracle", "_ref", "libcaif_ref_layers.so"))
+        self.lib.refl_last_error.restype = ctypes.c_char_p
+
+    def tensor(self, rows, cols, init=None):
+        ct = self.ct
+        h, d = ct.c_void_p(), ct.POINTER(ct.c_float)()
+        if self.lib.refl_host_tensor(ct.c_uint32(rows), ct.c_uint32(cols), ct.byref(h), ct.byref(d)) != 0:
+            raise RuntimeError(self.lib.refl_last_error().decode())
+        view = self.np.ctypeslib.as_array(d, shape=(rows, cols))
+        if init is not None:
+            view[:] = init
+        return h, view
+
+    def matmul_nt(self, a, b, out):
+        if self.lib.refl_host_matmul(2, a, b, out) != 0:
+            raise RuntimeError(self.lib.refl_last_error().decode())
+
+
 def cpu_reference_c2(steps, warmup, budget_s=20.0):
     """The reference's Host_e path for this layer with its default cache_fp32=true: the int4 weights are
     dequantized to fp32 once (restated kernel, OpenMP, outside the timed loop, as the reference's cache does
-    after the first call), then every forward is CAIF_Ops::MatMulTransposeB = OpenBLAS sgemm (numpy).
-    One sample step = one of the 32 layer passes: a forward at each M in {1,4,16} on each of the 8 copies."""
+    after the first call), then every forward is CAIF_Ops::MatMulTransposeB on host tensors (OpenBLAS sgemm):
+    the reference's own code where its library is available (kind "reference"), numpy's sgemm otherwise
+    (kind "port").  One sample step = one of the 32 layer passes: a forward at each M in {1,4,16} on each
+    of the 8 copies."""
     cores = _cpu_threads()
     import numpy as np
 
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import caif_oracle as orc
 
+    try:
+        ref = _RefHostOps()
+    except Exception:
+        ref = None
     rng = np.random.default_rng(1235)
     wds = []
     for _ in range(C2_COPIES):
         w = (rng.standard_normal((C2_OUT, C2_IN)) * 0.02).astype(np.float32)
         packed, scales = orc.quantize_int4(w, C2_GROUP)
         del w
-        wds.append(orc.dequantize_int4(packed, scales, C2_OUT * C2_IN, C2_GROUP).reshape(C2_OUT, C2_IN))
+        wd = orc.dequantize_int4(packed, scales, C2_OUT * C2_IN, C2_GROUP).reshape(C2_OUT, C2_IN)
+        wds.append(ref.tensor(C2_OUT, C2_IN, wd)[0] if ref is not None else wd)
     xs = [orc.round_through(rng.standard_normal((m, C2_IN)).astype(np.float32), orc.BF16) for m in C2_MS]
+    if ref is not None:
+        xt = [ref.tensor(x.shape[0], C2_IN, x)[0] for x in xs]
+        yt = [ref.tensor(x.shape[0], C2_OUT)[0] for x in xs]
 
-    def step():
-        for x in xs:
-            for wd in wds:
-                orc.gemm_nt(x, wd, exact=False)
+        def step():
+            for x, y in zip(xt, yt):
+                for wd in wds:
+                    ref.matmul_nt(x, wd, y)
+    else:
+        def step():
+            for x in xs:
+                for wd in wds:
+                    orc.gemm_nt(x, wd, exact=False)
 
     dt, done = _cpu_loop(step, steps, warmup, budget_s)
     bytes_per_step = C2_COPIES * sum(c2_bytes(m) for m in C2_MS)
+    how = ("the reference's CAIF_Ops::MatMulTransposeB on host tensors (its own sources, OpenBLAS sgemm)"
+           if ref is not None else "numpy sgemm (OpenBLAS)")
     return {"value": bytes_per_step * done / dt / 1e9, "ms_per_step": dt / done * 1e3, "steps": done, "cores": cores,
-            "sample": "%d sample steps, each ONE of the 32 layer passes of the step: sgemm at M=1,4,16 on 8 cached "
-                      "fp32 14336x4096 weights (dequantized once)" % done}
+            "kind": "reference" if ref is not None else "port",
+            "sample": "%d sample steps, each ONE of the 32 layer passes of the step: %s at M=1,4,16 on 8 cached fp32 "
+                      "14336x4096 weights (dequantized once)" % (done, how)}
 
 
 def cpu_reference_c3(steps, warmup, budget_s=25.0):
@@ -379,7 +426,8 @@ CPU_ARM = {"c2": cpu_reference_c2, "c3": cpu_reference_c3, "c5": cpu_reference_c
 
 def _cpu_baseline(workload, unit, budget_s=15.0):
     cb = CPU_ARM[workload](steps=50, warmup=1, budget_s=budget_s)
-    return {"value": cb["value"], "unit": unit, "cores": cb["cores"], "kind": "port", "sample": cb["sample"]}
+    return {"value": cb["value"], "unit": unit, "cores": cb["cores"], "kind": cb.get("kind", "port"),
+            "sample": cb["sample"]}
 
 
 # ----------------------------------------------------------------------- GPU arm
@@ -1191,7 +1239,7 @@ def run_reference(args):
             "steps": cb["steps"], "warmup": args.warmup if i == 0 else 1, "ms_per_step": cb["ms_per_step"],
             "higher_is_better": True, "scaling": SCALING[w], "vs_baseline": None, "dtype": "fp32 (host sgemm)",
             "data": "synthetic", "config": config_for(w, world),
-            "cpu_baseline": {"value": cb["value"], "unit": unit, "cores": cb["cores"], "kind": "port",
+            "cpu_baseline": {"value": cb["value"], "unit": unit, "cores": cb["cores"], "kind": cb.get("kind", "port"),
                              "sample": cb["sample"]},
             "e2e": {"value": cb["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }

@@ -27,6 +27,7 @@
 #include "caif_device_moe_frozen_expert.h"
 #include "caif_device_moe_frozen_expert_config.h"
 #include "caif_device_tensor.h"
+#include "caif_ops.h"
 #include "caif_run_context.h"
 #include "caif_settings.h"
 
@@ -338,6 +339,47 @@ __attribute__((visibility("default"))) int refl_time(void *handle, const void *x
     cudaEventDestroy(e0);
     cudaEventDestroy(e1);
     *ms_per_iter = ms / static_cast<float>(iters);
+  });
+}
+
+// ---- the reference's Host_e path: CAIF_Ops::MatMul / MatMulTransposeA / MatMulTransposeB on host tensors
+// (src/caif_ops_host.cpp:54-139 -> src/caif_host_gemm.cpp -> cblas_sgemm).  No GPU is touched.
+
+// An fp32 [rows, cols] tensor in the reference's host memory; *data points at its storage.
+__attribute__((visibility("default"))) int refl_host_tensor(uint32_t rows, uint32_t cols, void **handle, float **data)
+{
+  return guarded([&] {
+    auto *t = new CAIF_DeviceTensor(CAIF_DeviceTensor::UninitializedHost({rows, cols}));
+    *handle = t;
+    *data = static_cast<float *>(t->DeviceDataRaw());
+  });
+}
+
+__attribute__((visibility("default"))) int refl_host_tensor_free(void *handle)
+{
+  return guarded([&] { delete static_cast<CAIF_DeviceTensor *>(handle); });
+}
+
+// kind 0: out = a . b;  1: out = a^T . b;  2: out = a . b^T
+__attribute__((visibility("default"))) int refl_host_matmul(int kind, void *a, void *b, void *out)
+{
+  return guarded([&] {
+    CAIF_RunContext ctx;
+    const CAIF_DeviceTensor &ta = *static_cast<CAIF_DeviceTensor *>(a);
+    const CAIF_DeviceTensor &tb = *static_cast<CAIF_DeviceTensor *>(b);
+    CAIF_DeviceTensor &to = *static_cast<CAIF_DeviceTensor *>(out);
+    if (kind == 0)
+    {
+      CAIF_Ops::MatMul(ta, tb, to, ctx);
+    }
+    else if (kind == 1)
+    {
+      CAIF_Ops::MatMulTransposeA(ta, tb, to, ctx);
+    }
+    else
+    {
+      CAIF_Ops::MatMulTransposeB(ta, tb, to, ctx);
+    }
   });
 }
 
