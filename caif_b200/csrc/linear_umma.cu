@@ -87,12 +87,9 @@ constexpr int NUM_WARPS = 14;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int DEQ_WARP0 = 6;
 constexpr int DEQ_THREADS = 8 * 32;
-// Teams of dequant warps (see the dequantization role): two, except for int4 forward with 256-wide
-// tiles where one measured faster (a tile width int4 is not given by default).
-__host__ __device__ constexpr int deq_teams(int wmode, bool bwd, int bn)
-{
-  return (bn == 256 && wmode != 0 && !bwd) ? 1 : 2;
-}
+// Teams of dequant warps (see the dequantization role): two in every configuration (one team measured
+// 10-15 % slower for 256-wide int4 forward tiles, the only case where it was ever ahead).
+__host__ __device__ constexpr int deq_teams(int /*wmode*/, bool /*bwd*/, int /*bn*/) { return 2; }
 constexpr uint32_t kSpinLimit = 1u << 22;       // polls of one wait before it gives up (tens of ms)
 constexpr uint32_t kSpinLimitTest = 1u << 12;   // the same for the self-test of the give-up path
 
@@ -301,22 +298,32 @@ __device__ __forceinline__ void int8x4_to_bf16(uint32_t w, uint32_t &p01, uint32
   p23 = sub_bf16x2(lop3_and_or(b, 0x007F007Fu, 0x43004300u), lop3_and_or(b, 0x00800080u, 0x43004300u));
 }
 
-// eight int4 codes (one 32-bit word, memory order) times a scale -> four bf16x2
-// registers; each product is formed in fp32 and rounded once to bf16, the value
-// the reference's dequantize-then-cast yields
-__device__ __forceinline__ void int4x8_to_bf16(uint32_t w, float scale, uint32_t (&out)[4])
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b)
 {
-  // offset-binary nibbles u = q + 8 as the low byte of 2^23 + u, exact in fp32
-  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;         // u0 u2 u4 u6
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Eight int4 codes (one 32-bit word, memory order) times a scale -> four bf16x2 registers, for bf16
+// compute.  The codes become exact bf16 integers with logic ops (the offset-binary nibble dropped into
+// the mantissa of 128.0, then 136 subtracted: exact) and are multiplied by the group scale rounded to
+// bf16, one rounding.  The reference's dequantize-then-cast forms scale * code in fp32 and rounds once;
+// the two differ by the bf16 rounding of the fp16 scale (2^-9 relative), far inside the bf16 bound, and
+// the conversion takes 17 instructions per eight weights instead of 31: the int4 launches are bound by
+// this conversion, not by the tensor core.
+__device__ __forceinline__ void int4x8_to_bf16(uint32_t w, uint32_t scale2, uint32_t (&out)[4])
+{
+  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;         // u0 u2 u4 u6   (u = q + 8)
   const uint32_t od = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;  // u1 u3 u5 u7
-  const float base = 8388616.0f;                               // 2^23 + 8
-#pragma unroll
-  for (int j = 0; j < 4; ++j)
-  {
-    const float lo = __uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base;
-    const float hi = __uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base;
-    out[j] = pack_bf16x2(__fmul_rn(lo, scale), __fmul_rn(hi, scale));
-  }
+  const uint32_t t0 = __byte_perm(ev, od, 0x5140);             // u0 u1 u2 u3
+  const uint32_t t1 = __byte_perm(ev, od, 0x7362);             // u4 u5 u6 u7
+  constexpr uint32_t kExp = 0x43434343u;                       // high byte of bf16 128.0 .. 143.0
+  constexpr uint32_t k136 = 0x43084308u;
+  out[0] = mul_bf16x2(sub_bf16x2(__byte_perm(t0, kExp, 0x4140), k136), scale2);
+  out[1] = mul_bf16x2(sub_bf16x2(__byte_perm(t0, kExp, 0x4342), k136), scale2);
+  out[2] = mul_bf16x2(sub_bf16x2(__byte_perm(t1, kExp, 0x4140), k136), scale2);
+  out[3] = mul_bf16x2(sub_bf16x2(__byte_perm(t1, kExp, 0x4342), k136), scale2);
 }
 
 // the same eight codes as two bf16 terms of scale * code: hi = bf16(w), lo = bf16(w - hi)
@@ -986,7 +993,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             for (int w = 0; w < 4; ++w)
             {
               uint32_t o4[4];
-              int4x8_to_bf16(words[w], sc[i], o4);
+              int4x8_to_bf16(words[w], pack_bf16x2(sc[i], sc[i]), o4);
               outw[4 * w + 0] = o4[0];
               outw[4 * w + 1] = o4[1];
               outw[4 * w + 2] = o4[2];
@@ -1289,10 +1296,7 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
   // 256-wide tiles feed the tensor core better per shared-memory byte; 128-wide ones keep a
   // second accumulator set so the epilogue overlaps the next tile.  CAIFQ_UMMA_BN overrides.
-  // the forward pass of a single int4 layer measured faster with 128-wide tiles (923-968 vs 827-877
-  // TFLOP/s at 4096 x 4096), its dX with 256-wide ones (992-1040 vs 905-920)
-  int bn = ((w.storage != CAIFQ_I4 || g.backward) && (p.n_total % 256) == 0 &&
-            static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
+  int bn = ((p.n_total % 256) == 0 && static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
                ? 256
                : 128;
   if (const char *e = std::getenv("CAIFQ_UMMA_BN"))

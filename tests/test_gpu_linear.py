@@ -228,8 +228,9 @@ def test_umma_forward_and_dx(storage, compute, tol, m, in_dim, out_dim):
     assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, compute)) <= tol
     assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, compute)) <= tol
     if storage == orc.I4 and compute == orc.BF16:
-        # the operand is the reference's own (scale*code rounded to bf16): far inside the bound
-        assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, compute)) <= 1e-4
+        # the operand is code * bf16(scale), the reference's is bf16(code * scale): they differ by the bf16
+        # rounding of the fp16 scale, a small fraction of the bound
+        assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, compute)) <= 4e-3
 
 
 def test_umma_int4_group_size_that_is_not_a_power_of_two():
@@ -237,8 +238,8 @@ def test_umma_int4_group_size_that_is_not_a_power_of_two():
     y = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
     assert nv.last_path() == "umma"
     dx = nv.linear_dx(weight, dy, torch.float32, orc.BF16)
-    assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, orc.BF16)) <= 1e-4
-    assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, orc.BF16)) <= 1e-4
+    assert max_rel_err(y.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, orc.BF16)) <= 4e-3
+    assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, orc.BF16)) <= 4e-3
 
 
 def test_umma_bf16_output_and_accumulate_epilogue():
