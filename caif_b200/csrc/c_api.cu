@@ -370,6 +370,8 @@ void caifq_selftest_stall_next_decode(void) { decode_stall_next_launch(); }
 
 void caifq_selftest_stall_next_umma(void) { umma_stall_next_launch(); }
 
+int32_t caifq_umma_pair_capacity(void) { return umma_pair_capacity(); }
+
 void caifq_set_cta_limit(int32_t max_ctas) { g_cta_limit.store(max_ctas > 0 ? max_ctas : 0, std::memory_order_relaxed); }
 
 int caifq_device_ok(void)

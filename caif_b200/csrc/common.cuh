@@ -263,6 +263,7 @@ void note_codes_written(cudaStream_t s);
 bool take_codes_written(cudaStream_t s);
 // self-test hook: the next few-token launch of this thread waits for bytes that never arrive
 void decode_stall_next_launch();
+int umma_pair_capacity();   // resident CTA pairs of the tensor-core kernel seen on the current device (0: none launched yet)
 void umma_stall_next_launch();
 bool decode_supported(const LinearArgs &args);
 int launch_linear_decode(const LinearArgs &args, cudaStream_t s);

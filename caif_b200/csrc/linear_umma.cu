@@ -80,28 +80,40 @@ constexpr int BM = BM_SUB * MT;      // 256
 constexpr int BK = 64;               // one 128-byte swizzle span of bf16
 constexpr int UMMA_K = 16;
 constexpr int A_SUB_BYTES = BM_SUB * BK * 2;       // 16 KB
-constexpr int A_STAGE_BYTES = A_SUB_BYTES * MT;    // 32 KB
-constexpr int MAX_STAGES = 4;
+
+constexpr int MAX_STAGES = 6;
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_WARPS = 14;
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int DEQ_WARP0 = 6;
 constexpr int DEQ_THREADS = 8 * 32;
-// Teams of dequant warps (see the dequantization role): two in every configuration (one team measured
-// 10-15 % slower for 256-wide int4 forward tiles, the only case where it was ever ahead).
-__host__ __device__ constexpr int deq_teams(int /*wmode*/, bool /*bwd*/, int /*bn*/) { return 2; }
+// Teams of dequant warps (see the dequantization role): two for a single CTA's tile; four for a CTA pair,
+// whose k-blocks take half as long while a conversion's latency chain (wait, loads, ~150 instructions,
+// stores, proxy fence, arrive) stays the same (two teams: 750-830 TFLOP/s on 4096 x 4096 int8, four: 980-1150).
+__host__ __device__ constexpr int deq_teams(bool pair) { return pair ? 4 : 2; }
 constexpr uint32_t kSpinLimit = 1u << 22;       // polls of one wait before it gives up (tens of ms)
 constexpr uint32_t kSpinLimitTest = 1u << 12;   // the same for the self-test of the give-up path
 
-template <int BN, int PLANES = 1>
+// A weight tile (BM = 256 activation rows x BN output columns) is worked on by one CTA, as two 128-row MMAs that
+// share the staged weights, or -- PAIR -- by the two CTAs of a cluster with one `cta_group::2` MMA of 256 rows:
+// each CTA stages its own 128 activation rows and its own half of the weight rows, so an SM moves half the
+// operand bytes through its shared memory per flop and the 256 accumulator columns leave room for a second
+// accumulator set (the epilogue overlaps the next tile).
+template <int BN, int PLANES = 1, bool PAIR = false>
 struct TileCfg
 {
-  static constexpr int B_PLANE_BYTES = BN * BK * 2;               // 16 or 32 KB
+  static constexpr int MTK = PAIR ? 1 : MT;                       // 128-row sub-tiles of a CTA
+  static constexpr int BNC = PAIR ? BN / 2 : BN;                  // weight-tile rows a CTA stages
+  static constexpr int A_BYTES = A_SUB_BYTES * MTK;               // 16 or 32 KB
+  static constexpr int B_PLANE_BYTES = BNC * BK * 2;              // 16 or 32 KB
   static constexpr int B_STAGE_BYTES = B_PLANE_BYTES * PLANES;
-  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-  static constexpr int STAGES = (BN == 128 && PLANES == 1) ? 4 : 3;   // 192 KB of operands in every case
+  static constexpr int STAGE_BYTES = A_BYTES + B_STAGE_BYTES;
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;       // 192 KB of operands in every case: 3, 4 or 6
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the base to 1024
-  static constexpr int ACC_BUFS = TMEM_COLS / (MT * BN);          // 2 (epilogue overlaps the next tile) or 1
+  static constexpr int ACC_COLS = PAIR ? BN : MT * BN;            // accumulator columns of a CTA per tile
+  static constexpr int ACC_BUFS = TMEM_COLS / ACC_COLS;           // 2 (epilogue overlaps the next tile) or 1
+  static_assert(!PAIR || BN == 256, "tile pairs are 256 columns wide");
+  static_assert(STAGES >= 3 && STAGES <= MAX_STAGES, "operand ring depth");
 };
 
 enum WMode
@@ -180,6 +192,51 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       : "memory");
 }
 
+// ---- two-CTA (cluster) forms
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// the shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_shared_cluster(uint32_t cluster_addr)
+{
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// A tile load of this CTA's own shared memory whose bytes are counted on a barrier of the pair's leader CTA
+// (`cluster_bar`, a shared::cluster address).  No multicast: every CTA fetches its own tile.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 uint32_t cluster_bar)
+{
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
+      "[%4];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(cluster_bar)
+      : "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async()
 {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -206,6 +263,19 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
       : "memory");
 }
 
+// one MMA of 256 rows over the CTA pair: each CTA's shared memory holds its 128 rows of A and its half of B
+// at the same offsets, the accumulator rows land in each CTA's own tensor memory
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate)
+{
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ bool elect_one()
 {
   uint32_t pred;
@@ -221,6 +291,21 @@ __device__ __forceinline__ bool elect_one()
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// the same for the pair's MMAs; the arrival goes to the barrier at this offset in both CTAs
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
+
+// the same, arriving on a barrier of the issuing CTA only
+__device__ __forceinline__ void umma_commit_pair_local(uint32_t bar)
+{
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
@@ -257,14 +342,14 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
 
 // Instruction descriptor, kind::f16: fp32 accumulate, bf16 x bf16, A K-major,
 // B K-major (forward) or MN-major (backward), N = 128, M = 128.
-__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int BN)
+__host__ __device__ constexpr uint32_t make_idesc(bool b_mn_major, int BN, int M = BM_SUB)
 {
   return (1u << 4)                          // D format f32
          | (1u << 7)                        // A format bf16
          | (1u << 10)                       // B format bf16
          | (0u << 15)                       // A major: K
          | ((b_mn_major ? 1u : 0u) << 16)   // B major
-         | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(BM_SUB >> 4) << 24);
+         | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c)
@@ -464,7 +549,7 @@ __device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams
   return t;
 }
 
-template <int WMODE, bool BWD, int BN, bool GROUPED>
+template <int WMODE, bool BWD, int BN, bool GROUPED, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_h, const UmmaParams p,
@@ -472,12 +557,18 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 {
   constexpr int PLANES = planes_of(WMODE);
   constexpr bool IS_I4 = (WMODE == W_I4 || WMODE == W_I4S);
-  constexpr int B_PLANE_BYTES = TileCfg<BN, PLANES>::B_PLANE_BYTES;
-  constexpr int B_STAGE_BYTES = TileCfg<BN, PLANES>::B_STAGE_BYTES;
-  constexpr int STAGE_BYTES = TileCfg<BN, PLANES>::STAGE_BYTES;
-  constexpr int STAGES = TileCfg<BN, PLANES>::STAGES;
-  constexpr int ACC_BUFS = TileCfg<BN, PLANES>::ACC_BUFS;
-  constexpr int DEQ_TEAMS = deq_teams(WMODE, BWD, BN);
+  typedef TileCfg<BN, PLANES, PAIR> Cfg;
+  constexpr int MTK = Cfg::MTK;
+  constexpr int BNC = Cfg::BNC;
+  constexpr int A_STAGE = Cfg::A_BYTES;
+  constexpr int B_PLANE_BYTES = Cfg::B_PLANE_BYTES;
+  constexpr int B_STAGE_BYTES = Cfg::B_STAGE_BYTES;
+  constexpr int STAGE_BYTES = Cfg::STAGE_BYTES;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int ACC_COLS = Cfg::ACC_COLS;
+  constexpr int ACC_BUFS = Cfg::ACC_BUFS;
+  constexpr uint32_t CTAS = PAIR ? 2u : 1u;   // CTAs that work on one tile
+    constexpr int DEQ_TEAMS = deq_teams(PAIR);
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[MAX_STAGES * 3 + 4];
   __shared__ uint64_t drain_bar;   // give-up path only: the MMAs issued so far have completed
@@ -489,7 +580,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   auto a_addr = [&](int s, int mt) { return smem_base + static_cast<uint32_t>(s) * STAGE_BYTES + mt * A_SUB_BYTES; };
-  auto b_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * STAGE_BYTES + A_STAGE_BYTES; };
+  auto b_addr = [&](int s) { return smem_base + static_cast<uint32_t>(s) * STAGE_BYTES + A_STAGE; };
   const uint32_t bar0 = smem_u32(bars);
   auto a_full = [&](int s) { return bar0 + static_cast<uint32_t>(s) * 8u; };
   auto b_full = [&](int s) { return bar0 + static_cast<uint32_t>(STAGES + s) * 8u; };
@@ -497,6 +588,25 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   auto acc_full = [&](int a) { return bar0 + static_cast<uint32_t>(3 * STAGES + a) * 8u; };
   auto acc_empty = [&](int a) { return bar0 + static_cast<uint32_t>(3 * STAGES + 2 + a) * 8u; };
 
+  // Pair mode: rank 0 of the cluster (the leader) issues the MMAs; the barriers that gate them (operands
+  // landed, accumulator drained) are the leader's, and the other CTA's copies and warps arrive on them
+  // through the cluster's shared address space.  The barriers that the MMAs' completion signals (stage free,
+  // accumulator ready) exist in both CTAs and get a multicast commit.
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int workers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  auto lead = [&](uint32_t bar) { return PAIR ? map_to_cta(bar, 0u) : bar; };
+  auto arrive_lead = [&](uint32_t bar)
+  {
+    if (PAIR)
+    {
+      mbar_arrive_cluster(map_to_cta(bar, 0u));
+    }
+    else
+    {
+      mbar_arrive(bar);
+    }
+  };
   volatile uint32_t *abort_word = &cta_abort;
   auto wait = [&](uint32_t bar, uint32_t parity) { return mbar_wait(bar, parity, abort_word, p.spin_limit); };
   if (threadIdx.x == 0)
@@ -506,25 +616,40 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int s = 0; s < STAGES; ++s)
     {
       mbar_init(a_full(s), 1);
-      mbar_init(b_full(s), (WMODE == W_BF16) ? 1 : 8 / DEQ_TEAMS);
+      mbar_init(b_full(s), (WMODE == W_BF16) ? 1 : (8 / DEQ_TEAMS) * CTAS);
       mbar_init(empty(s), 1);
     }
     for (int a = 0; a < ACC_BUFS; ++a)
     {
       mbar_init(acc_full(a), 1);
-      mbar_init(acc_empty(a), 4);
+      mbar_init(acc_empty(a), 4 * CTAS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1)
   {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR)
+    {
+      // both CTAs of the pair run this, from the same warp number
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    else
+    {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR)
+  {
+    cluster_sync_all();   // the other CTA's barriers are initialised before anything arrives on them
+  }
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
@@ -540,11 +665,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     {
       int s = 0;
       uint32_t par = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+      for (int tile = worker; tile < num_tiles; tile += workers)
       {
         const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
         const int n_tile = tw.n_tile;
-        const int row_tile = static_cast<int>(tw.row0);
+        const int row_tile = static_cast<int>(tw.row0) + static_cast<int>(rank) * BM_SUB;   // pair: this CTA's half
         for (int kb = 0; kb < num_kb_all; ++kb)
         {
           if (!wait(empty(s), par ^ 1u))
@@ -552,35 +677,54 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             tile = num_tiles;   // nothing new is started once a wait has run out
             break;
           }
-          mbar_expect_tx(a_full(s), A_STAGE_BYTES + ((tile == static_cast<int>(blockIdx.x) && kb == 0) ? p.stall_bytes : 0u));
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
+          // (pair: the leader announces both CTAs' bytes; the other CTA's copies may complete first, the
+          // phase cannot end before the leader's arrival)
+          auto load = [&](uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
           {
-            if (kb < num_kb)
+            if (PAIR)
             {
-              tma_load_2d(a_addr(s, mt), &map_a, kb * BK, row_tile + mt * BM_SUB, a_full(s));
+              tma_load_2d_pair(dst, map, c0, c1, lead(bar));
             }
             else
             {
-              tma_load_2d(a_addr(s, mt), &map_h, 0, row_tile + mt * BM_SUB, a_full(s));
+              tma_load_2d(dst, map, c0, c1, bar);
+            }
+          };
+          if (rank == 0)
+          {
+            mbar_expect_tx(a_full(s), A_STAGE * CTAS + ((tile == worker && kb == 0) ? p.stall_bytes : 0u));
+          }
+#pragma unroll
+          for (int mt = 0; mt < MTK; ++mt)
+          {
+            if (kb < num_kb)
+            {
+              load(a_addr(s, mt), &map_a, kb * BK, row_tile + mt * BM_SUB, a_full(s));
+            }
+            else
+            {
+              load(a_addr(s, mt), &map_h, 0, row_tile + mt * BM_SUB, a_full(s));
             }
           }
           if (WMODE == W_BF16)
           {
-            mbar_expect_tx(b_full(s), B_STAGE_BYTES);
+            const int nc0 = n_tile * BN + static_cast<int>(rank) * BNC;   // this CTA's weight rows
+            if (rank == 0)
+            {
+              mbar_expect_tx(b_full(s), B_STAGE_BYTES * CTAS);
+            }
             if (BWD)
             {
-              // [k rows][n cols]: two boxes of 64 n x 64 k land as the two MN-major blocks
+              // [k rows][n cols]: boxes of 64 n x 64 k land as the MN-major blocks
 #pragma unroll
-              for (int nb = 0; nb < BN / 64; ++nb)
+              for (int nb = 0; nb < BNC / 64; ++nb)
               {
-                tma_load_2d(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, &map_b, n_tile * BN + nb * 64, kb * BK,
-                            b_full(s));
+                load(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, &map_b, nc0 + nb * 64, kb * BK, b_full(s));
               }
             }
             else
             {
-              tma_load_2d(b_addr(s), &map_b, kb * BK, n_tile * BN, b_full(s));
+              load(b_addr(s), &map_b, kb * BK, nc0, b_full(s));
             }
           }
           if (++s == STAGES)
@@ -596,14 +740,37 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   {
     // -------------------------------------------------------------- MMA issuer
     // The whole warp runs the loop, so addresses and descriptors are warp-uniform values;
-    // one elected lane issues the MMAs and the commits.
+    // one elected lane issues the MMAs and the commits.  (Pair: the leader CTA's warp only.)
+    if (rank == 0)
     {
-      constexpr uint32_t idesc = make_idesc(BWD, BN);
+      constexpr uint32_t idesc = make_idesc(BWD, BN, PAIR ? 2 * BM_SUB : BM_SUB);
+      auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t accumulate)
+      {
+        if (PAIR)
+        {
+          umma_bf16_pair(d, a, b, idesc, accumulate);
+        }
+        else
+        {
+          umma_bf16(d, a, b, idesc, accumulate);
+        }
+      };
+      auto commit = [&](uint32_t bar)
+      {
+        if (PAIR)
+        {
+          umma_commit_pair(bar);
+        }
+        else
+        {
+          umma_commit(bar);
+        }
+      };
       int s = 0;
       uint32_t par = 0;
       int acc = 0;
       uint32_t acc_par = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+      for (int tile = worker; tile < num_tiles; tile += workers)
       {
         wait(acc_empty(acc), acc_par ^ 1u);
         tc_fence_after();
@@ -614,11 +781,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           tc_fence_after();
           const uint64_t adesc0 = make_desc(a_addr(s, 0), 16, 1024);
           const uint64_t bdesc0 = BWD ? make_desc(b_addr(s), 8192, 1024) : make_desc(b_addr(s), 16, 1024);
-          const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc * MT * BN);
+          const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc * ACC_COLS);
           if (elect_one())
           {
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+            for (int mt = 0; mt < MTK; ++mt)
             {
 #pragma unroll
               for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
@@ -626,16 +793,15 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 // descriptor address fields count 16-byte units
                 const uint64_t adesc = adesc0 + static_cast<uint64_t>((mt * A_SUB_BYTES + k16 * (UMMA_K * 2)) >> 4);
                 const uint64_t bdesc = bdesc0 + static_cast<uint64_t>((BWD ? k16 * 2048 : k16 * (UMMA_K * 2)) >> 4);
-                umma_bf16(d0 + static_cast<uint32_t>(mt * BN), adesc, bdesc, idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+                mma(d0 + static_cast<uint32_t>(mt * BN), adesc, bdesc, (kb > 0 || k16 > 0) ? 1u : 0u);
                 if (PLANES == 2 && kb < num_kb)
                 {
                   // the low-order term of the weights (the LoRA k-block has one plane only)
-                  umma_bf16(d0 + static_cast<uint32_t>(mt * BN), adesc,
-                            bdesc + static_cast<uint64_t>(B_PLANE_BYTES >> 4), idesc, 1u);
+                  mma(d0 + static_cast<uint32_t>(mt * BN), adesc, bdesc + static_cast<uint64_t>(B_PLANE_BYTES >> 4), 1u);
                 }
               }
             }
-            umma_commit(empty(s));
+            commit(empty(s));
           }
           __syncwarp();
           if (++s == STAGES)
@@ -646,7 +812,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         if (elect_one())
         {
-          umma_commit(acc_full(acc));
+          commit(acc_full(acc));
         }
         __syncwarp();
         if (++acc == ACC_BUFS)
@@ -663,7 +829,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     int acc = 0;
     uint32_t acc_par = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+    for (int tile = worker; tile < num_tiles; tile += workers)
     {
       const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
       const int n_tile = tw.n_tile;
@@ -674,8 +840,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       wait(acc_full(acc), acc_par);
       tc_fence_after();
-      if (!BWD && BN == 128 && p.swiglu)
+      if (!BWD && (BN == 128 || PAIR) && p.swiglu)
       {
+        constexpr int HALF = BN / 2;   // features of each projection in a tile
         float up_scale = 1.0f;
         if (WMODE == W_I8 && tw.scales_up != nullptr)
         {
@@ -683,22 +850,22 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         const int hid = p.n_total / 2;   // features per projection
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int mt = 0; mt < MTK; ++mt)
         {
-          const int64_t row = tw.row0 + mt * BM_SUB + quarter * 32 + lane;
+          const int64_t row = tw.row0 + static_cast<int64_t>(rank) * BM_SUB + mt * BM_SUB + quarter * 32 + lane;
 #pragma unroll
-          for (int cb = 0; cb < 2; ++cb)
+          for (int cb = 0; cb < HALF / 32; ++cb)
           {
             uint32_t rg[32];
             uint32_t ru[32];
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   static_cast<uint32_t>((acc * MT + mt) * BN);
+                                   static_cast<uint32_t>(acc * ACC_COLS + mt * BN);
             tmem_ld32(tbase + cb * 32, rg);
-            tmem_ld32(tbase + 64 + cb * 32, ru);
+            tmem_ld32(tbase + HALF + cb * 32, ru);
             tmem_ld_wait();
             if (row < tw.row_end)
             {
-              const int64_t off = row * hid + static_cast<int64_t>(n_tile) * 64 + cb * 32;
+              const int64_t off = row * hid + static_cast<int64_t>(n_tile) * HALF + cb * 32;
               uint4 *dg = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c) + off);
               uint4 *du = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c_up) + off);
               uint4 *dh = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c_hidden) + off);
@@ -734,15 +901,15 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
       else
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+      for (int mt = 0; mt < MTK; ++mt)
       {
-        const int64_t row = tw.row0 + mt * BM_SUB + quarter * 32 + lane;
+        const int64_t row = tw.row0 + static_cast<int64_t>(rank) * BM_SUB + mt * BM_SUB + quarter * 32 + lane;
 #pragma unroll
         for (int cb = 0; cb < BN / 32; ++cb)
         {
           uint32_t r[32];
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                 static_cast<uint32_t>((acc * MT + mt) * BN + cb * 32);
+                                 static_cast<uint32_t>(acc * ACC_COLS + mt * BN + cb * 32);
           tmem_ld32(taddr, r);
           tmem_ld_wait();
           if (row < tw.row_end)
@@ -831,7 +998,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       __syncwarp();
       if (lane == 0)
       {
-        mbar_arrive(acc_empty(acc));
+        arrive_lead(acc_empty(acc));
       }
       if (++acc == ACC_BUFS)
       {
@@ -853,17 +1020,17 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     //   forward  (K-major B): tile rows are n, a chunk is 16 B of one row's k range
     //   backward (MN-major B): tile rows are k, a chunk is 16 B of one k-row's n range
     constexpr int ELEMS = (WMODE == W_I8) ? 16 : 32;                 // codes per chunk
-    constexpr int CHUNKS = (BN * BK) / ELEMS;                        // per k-block
+    constexpr int CHUNKS = (BNC * BK) / ELEMS;                       // per k-block (of this CTA's weight rows)
     constexpr int PER_THREAD = CHUNKS / TEAM_THREADS;
-    constexpr int CHUNKS_PER_ROW = (BWD ? BN : BK) / ELEMS;          // chunks along the contiguous direction
+    constexpr int CHUNKS_PER_ROW = (BWD ? BNC : BK) / ELEMS;         // chunks along the contiguous direction
     static_assert(PER_THREAD >= 1, "tile too small for the dequant warps");
 
     uint32_t gkb0 = 0;   // k-blocks (of all tiles so far) before this tile: the ring position of its first one
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, gkb0 += static_cast<uint32_t>(num_kb_all))
+    for (int tile = worker; tile < num_tiles; tile += workers, gkb0 += static_cast<uint32_t>(num_kb_all))
     {
       const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
       const int n_tile = tw.n_tile;
-      const int n0 = n_tile * BN;
+      const int n0 = n_tile * BN + static_cast<int>(rank) * BNC;   // first of this CTA's weight rows / columns
       // chunk -> (row inside the tile, part along the contiguous direction)
       int c_row[PER_THREAD];
       int c_part[PER_THREAD];
@@ -902,9 +1069,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const void *scales = tw.scales;
           if (!BWD && p.swiglu)
           {
-            // tile rows 0..63: gate features 64 j + r; rows 64..127: up features 64 j + r - 64
-            o = static_cast<int64_t>(n_tile) * 64 + (c_row[i] & 63);
-            if (c_row[i] >= 64)
+            // first half of the tile's rows: gate features HALF j + r; second half: the same up features
+            constexpr int HALF = BN / 2;
+            const int t = static_cast<int>(rank) * BNC + c_row[i];
+            o = static_cast<int64_t>(n_tile) * HALF + (t % HALF);
+            if (t >= HALF)
             {
               codes = tw.codes_up;
               scales = tw.scales_up;
@@ -1035,7 +1204,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         __syncwarp();
         if (lane == 0)
         {
-          mbar_arrive(b_full(s));
+          arrive_lead(b_full(s));
         }
         if (PREFETCH)
         {
@@ -1057,15 +1226,15 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         wait(empty(s), par ^ 1u);
         const uint32_t bbase = b_addr(s);
 #pragma unroll
-        for (int i = 0; i < (BN * BK * 2 / 16) / TEAM_THREADS; ++i)
+        for (int i = 0; i < (BNC * BK * 2 / 16) / TEAM_THREADS; ++i)
         {
-          const int c = d + i * TEAM_THREADS;  // 16-byte chunk of the BN x 64 bf16 tile
+          const int c = d + i * TEAM_THREADS;  // 16-byte chunk of the BNC x 64 bf16 tile
           uint32_t dst;
           const uint8_t *src;
           if (BWD)
           {
-            const int r = c / (BN / 8);   // k row (0..63) of the [64, N] factor
-            const int cb = c % (BN / 8);  // 16-byte chunk along n
+            const int r = c / (BNC / 8);   // k row (0..63) of the [64, N] factor
+            const int cb = c % (BNC / 8);  // 16-byte chunk along n
             src = p.lora_rhs + (static_cast<int64_t>(r) * p.n_total + n0 + cb * 8) * 2;
             dst = bbase + static_cast<uint32_t>((cb >> 3) * 8192 + (r >> 3) * 1024 + (r & 7) * 128 +
                                                 (((cb & 7) ^ (r & 7)) << 4));
@@ -1085,14 +1254,21 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         __syncwarp();
         if (lane == 0)
         {
-          mbar_arrive(b_full(s));
+          arrive_lead(b_full(s));
         }
       }
     }
   }
 
   // ------------------------------------------------------------------ teardown
-  if (*abort_word != 0u && warp == 0 && lane == 0)
+  uint32_t gave_up = *abort_word;
+  if (PAIR)
+  {
+    // every role of both CTAs has left its loops; a give-up in either CTA is handled by both
+    cluster_sync_all();
+    gave_up |= ld_shared_cluster(map_to_cta(smem_u32(&cta_abort), rank ^ 1u));
+  }
+  if (gave_up != 0u && warp == 0 && lane == 0)
   {
     // activation tiles that were started may still be on their way: give them time to land before the
     // CTA's shared memory goes back (a copy must not arrive in memory that belongs to another CTA)
@@ -1101,13 +1277,20 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       __nanosleep(2000);
     }
   }
-  if (*abort_word != 0u && warp == 1)
+  if (gave_up != 0u && warp == 1 && rank == 0)
   {
     // MMAs issued after the give-up may still run: tensor memory is released only after they have
     // completed (a commit tracks every MMA issued before it); bounded like every other wait
     if (elect_one())
     {
-      umma_commit(smem_u32(&drain_bar));
+      if (PAIR)
+      {
+        umma_commit_pair_local(smem_u32(&drain_bar));
+      }
+      else
+      {
+        umma_commit(smem_u32(&drain_bar));
+      }
     }
     __syncwarp();
     const uint32_t addr = smem_u32(&drain_bar);
@@ -1127,10 +1310,22 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR)
+  {
+    // neither CTA's shared or tensor memory is touched by the other one after this
+    cluster_sync_all();
+  }
   if (warp == 1)
   {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (PAIR)
+    {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    else
+    {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
   }
 }
 
@@ -1183,12 +1378,33 @@ int make_map_bf16(CUtensorMap *map, const void *base, uint64_t inner, uint64_t o
 // a whole SM, and one that finds its SM taken waits for the collective to end.
 int sm_count_umma() { return persistent_ctas("CAIFQ_UMMA_CTAS"); }
 
-template <int WMODE, bool BWD, int BN, bool GROUPED>
+// CTA pairs that a launch may use (a pair takes the two SMs of one TPC)
+int pair_count_umma() { return sm_count_umma() / 2; }
+
+// smallest number of resident pairs any pair-mode kernel reported for a device so far (0 = none launched yet)
+std::atomic<int> g_pair_capacity[kMaxDevices];
+
+// Whether 256-wide tiles go to CTA pairs or to single CTAs.  Measured on 4096 x 4096, 8192 tokens: a bf16
+// weight (operand fed by copies alone) runs 9 % faster on pairs (1211-1327 against 1109-1219 TFLOP/s); a
+// quantized weight does not (int8 980-1150 on pairs, 1026-1140 on single CTAs; int4 950-1015 against
+// 1007-1190): there the dequant warps' work per flop is the same in both forms and it, not the operand traffic,
+// is the limit.  So pairs are the default for bf16 weights only; CAIFQ_UMMA_PAIR=1 / 0 forces them on / off.
+bool pairs_enabled(int mode)
+{
+  const char *e = std::getenv("CAIFQ_UMMA_PAIR");
+  if (e == nullptr)
+  {
+    return mode == W_BF16;
+  }
+  return std::atoi(e) != 0;
+}
+
+template <int WMODE, bool BWD, int BN, bool GROUPED, bool PAIR = false>
 int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const UmmaParams &p,
                 const typename GroupSel<GROUPED>::type &gt, cudaStream_t s)
 {
-  auto kernel = linear_umma_kernel<WMODE, BWD, BN, GROUPED>;
-  constexpr int SMEM_BYTES = TileCfg<BN, planes_of(WMODE)>::SMEM_BYTES;
+  auto kernel = linear_umma_kernel<WMODE, BWD, BN, GROUPED, PAIR>;
+  constexpr int SMEM_BYTES = TileCfg<BN, planes_of(WMODE), PAIR>::SMEM_BYTES;
   static std::atomic<bool> configured[kMaxDevices];
   int dev = 0;
   CAIFQ_CHECK_CUDA(cudaGetDevice(&dev));
@@ -1203,6 +1419,44 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtens
     configured[dev].store(true, std::memory_order_release);
   }
   const int64_t tiles = static_cast<int64_t>(p.num_m_tiles) * p.num_n_tiles;
+  if (PAIR)
+  {
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // The grid is persistent, so it must not hold more pairs than the device keeps resident at a time (a
+    // pair that waited for another one to finish would double the launch's time): ask once per device.
+    static std::atomic<int> resident[kMaxDevices];
+    int cap = resident[dev].load(std::memory_order_acquire);
+    if (cap == 0)
+    {
+      cfg.gridDim = dim3(static_cast<unsigned>(2 * (device_sm_count() / 2)), 1, 1);
+      int clusters = 0;
+      CAIFQ_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+      cap = clusters > 0 ? clusters : 1;
+      resident[dev].store(cap, std::memory_order_release);
+      int seen = g_pair_capacity[dev].load(std::memory_order_relaxed);
+      while ((seen == 0 || cap < seen) && !g_pair_capacity[dev].compare_exchange_weak(seen, cap))
+      {
+      }
+    }
+    int pairs = pair_count_umma() < cap ? pair_count_umma() : cap;
+    if (tiles < pairs)
+    {
+      pairs = static_cast<int>(tiles);
+    }
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+    CAIFQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_h, p, gt));
+    return CAIFQ_OK;
+  }
   const int grid = tiles < sm_count_umma() ? static_cast<int>(tiles) : sm_count_umma();
   kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_h, p, gt);
   CAIFQ_CHECK_LAUNCH();
@@ -1223,6 +1477,17 @@ int wmode_of(const caifq_weight &w, int compute_dtype)
 }
 
 }  // namespace
+
+int umma_pair_capacity()
+{
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+  {
+    cudaGetLastError();
+    return 0;
+  }
+  return g_pair_capacity[dev].load(std::memory_order_relaxed);
+}
 
 bool umma_supported(const LinearArgs &g)
 {
@@ -1296,7 +1561,13 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   p.num_m_tiles = static_cast<int>((g.m + BM - 1) / BM);
   // 256-wide tiles feed the tensor core better per shared-memory byte; 128-wide ones keep a
   // second accumulator set so the epilogue overlaps the next tile.  CAIFQ_UMMA_BN overrides.
-  int bn = ((p.n_total % 256) == 0 && static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma())
+  // A 256-wide tile goes to a CTA pair (half the operand bytes per SM and flop, two accumulator sets) when
+  // there are enough tiles for the pairs, else to a single CTA when there are enough for the SMs.
+  const int mode = wmode_of(w, g.compute_dtype);
+  const bool pair = pairs_enabled(mode) && (p.n_total % 256) == 0 &&
+                    static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= pair_count_umma();
+  int bn = (pair || ((p.n_total % 256) == 0 &&
+                     static_cast<int64_t>(p.num_m_tiles) * (p.n_total / 256) >= sm_count_umma()))
                ? 256
                : 128;
   if (const char *e = std::getenv("CAIFQ_UMMA_BN"))
@@ -1307,9 +1578,9 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
       bn = v;
     }
   }
-  if (w.storage == CAIFQ_I4 && g.compute_dtype == CAIFQ_F32)
+  if (w.storage == CAIFQ_I4 && g.compute_dtype == CAIFQ_F32 && !(pair && bn == 256))
   {
-    bn = 128;   // the two-plane mode has 128-wide tiles only
+    bn = 128;   // a single CTA has 128-wide tiles only in the two-plane mode
   }
   p.num_n_tiles = p.n_total / bn;
 
@@ -1320,12 +1591,11 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
   {
     return rc;
   }
-  const int mode = wmode_of(w, g.compute_dtype);
   if (mode == W_BF16)
   {
     // the [out, in] weight itself: forward boxes are 64 k x 128 n rows, backward 64 n x 64 k rows
     rc = make_map_bf16(&map_b, w.codes, static_cast<uint64_t>(w.in_dim), static_cast<uint64_t>(w.out_dim),
-                       g.backward ? BK : bn);
+                       g.backward ? BK : ((pair && bn == 256) ? 128 : bn));
     if (rc != CAIFQ_OK)
     {
       return rc;
@@ -1350,6 +1620,17 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
     }
     p.lora_rhs = static_cast<const uint8_t *>(g.lora_rhs);
   }
+#define CAIFQ_UMMA_PAIR_CASE(MODE)                                                                      \
+  if (mode == MODE && bn == 256 && pair)                                                                \
+  {                                                                                                     \
+    return g.backward ? launch_inst<MODE, true, 256, false, true>(map_a, map_b, map_h, p, NoGroupTable{}, s)   \
+                      : launch_inst<MODE, false, 256, false, true>(map_a, map_b, map_h, p, NoGroupTable{}, s); \
+  }
+  CAIFQ_UMMA_PAIR_CASE(W_I8)
+  CAIFQ_UMMA_PAIR_CASE(W_I4)
+  CAIFQ_UMMA_PAIR_CASE(W_BF16)
+  CAIFQ_UMMA_PAIR_CASE(W_I4S)
+#undef CAIFQ_UMMA_PAIR_CASE
 #define CAIFQ_UMMA_CASE(MODE)                                                        \
   if (mode == MODE && bn == 128)                                                     \
   {                                                                                  \
@@ -1462,11 +1743,33 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     p.num_m_tiles = tiles;
     // (for the experts' shapes the wide tile measured 3 % faster with int4 too, unlike the square case)
     // (an accumulating epilogue reads the output first: with 128-wide tiles it overlaps the next tile)
-    const int bn = (mode != W_I4S && !g.accumulate && (p.n_total % 256) == 0 &&
-                    static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma())
+    // (pairs keep two accumulator sets at 256 columns, so the accumulating epilogue and the two-plane mode
+    // can have the wide tile there)
+    const bool pair = pairs_enabled(mode) && (p.n_total % 256) == 0 &&
+                      static_cast<int64_t>(tiles) * (p.n_total / 256) >= pair_count_umma();
+    const int bn = (pair || (mode != W_I4S && !g.accumulate && (p.n_total % 256) == 0 &&
+                             static_cast<int64_t>(tiles) * (p.n_total / 256) >= sm_count_umma()))
                        ? 256
                        : 128;
     p.num_n_tiles = p.n_total / bn;
+#define CAIFQ_UMMA_GROUP_PAIR_CASE(MODE)                                                           \
+  if (mode == MODE && pair)                                                                        \
+  {                                                                                                \
+    rc = g.backward ? launch_inst<MODE, true, 256, true, true>(map_a, map_a, map_a, p, gt, s)      \
+                    : launch_inst<MODE, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);    \
+  }
+    CAIFQ_UMMA_GROUP_PAIR_CASE(W_I8)
+    CAIFQ_UMMA_GROUP_PAIR_CASE(W_I4)
+    CAIFQ_UMMA_GROUP_PAIR_CASE(W_I4S)
+#undef CAIFQ_UMMA_GROUP_PAIR_CASE
+    if (pair)
+    {
+      if (rc != CAIFQ_OK)
+      {
+        return rc;
+      }
+      continue;
+    }
 #define CAIFQ_UMMA_GROUP_CASE(MODE)                                                              \
   if (mode == MODE && bn == 128)                                                                 \
   {                                                                                              \
@@ -1551,7 +1854,6 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
   p.group_size = w0.group_size;
   p.groups_per_row = (w0.group_size > 0) ? w0.in_dim / w0.group_size : 0;
   p.swiglu = 1;
-  p.num_n_tiles = w0.out_dim / 64;
   CUtensorMap map_a;
   int rc = make_map_bf16(&map_a, g.x, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(total_rows), BM_SUB);
   if (rc != CAIFQ_OK)
@@ -1582,7 +1884,26 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
       continue;
     }
     p.num_m_tiles = tiles;
-    if (mode == W_I8)
+    // 128 features of each projection per tile on a CTA pair, 64 on a single CTA
+    const bool pair = pairs_enabled(mode) && (w0.out_dim % 128) == 0 &&
+                      static_cast<int64_t>(tiles) * (w0.out_dim / 128) >= pair_count_umma();
+    p.num_n_tiles = w0.out_dim / (pair ? 128 : 64);
+    if (pair)
+    {
+      if (mode == W_I8)
+      {
+        rc = launch_inst<W_I8, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);
+      }
+      else if (mode == W_I4S)
+      {
+        rc = launch_inst<W_I4S, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);
+      }
+      else
+      {
+        rc = launch_inst<W_I4, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);
+      }
+    }
+    else if (mode == W_I8)
     {
       rc = launch_inst<W_I8, false, 128, true>(map_a, map_a, map_a, p, gt, s);
     }

@@ -57,6 +57,7 @@ _SIGNATURES = {
     "caifq_version": (ctypes.c_char_p, []),
     "caifq_device_ok": (ctypes.c_int, []),
     "caifq_device_status": (ctypes.c_int, []),
+    "caifq_umma_pair_capacity": (ctypes.c_int32, []),
     "caifq_selftest_stall_next_decode": (None, []),
     "caifq_selftest_stall_next_umma": (None, []),
     "caifq_set_cta_limit": (None, [_i32]),

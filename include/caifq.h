@@ -119,6 +119,10 @@ CAIFQ_API void caifq_selftest_stall_next_umma(void);
  * made after the call.  (No counterpart in the reference, which is single-device.)
  */
 CAIFQ_API void caifq_set_cta_limit(int32_t max_ctas);
+/* The tensor-core kernel runs 256-wide tiles on pairs of CTAs (two SMs of one cluster).  Returns how many
+ * pairs the current device keeps resident at a time, as reported by the occupancy query of the launches made
+ * so far on it (0 before the first such launch).  Diagnostic; no counterpart in the reference. */
+CAIFQ_API int32_t caifq_umma_pair_capacity(void);
 
 /* ---- quantize / dequantize (bit-exact with the reference kernels) -------- */
 

@@ -341,3 +341,54 @@ def test_umma_wait_that_runs_out_raises_the_flag_and_returns():
     assert nv.lib().caifq_device_status() == 0
     assert torch.equal(y, y2)
     assert max_rel_err(dx.cpu().numpy(), orc.frozen_linear_backward(dy_np, wc, orc.BF16)) <= TOL_16
+
+
+@pytest.mark.parametrize("storage,compute,tol", [
+    (orc.I8, orc.BF16, TOL_16),
+    (orc.I8, orc.F32, TOL_F32),
+    (orc.I4, orc.BF16, TOL_16),
+    (orc.I4, orc.F32, TOL_F32),
+    (orc.BF16, orc.F32, TOL_F32),
+])
+def test_umma_cta_pairs_equal_single_ctas(storage, compute, tol, monkeypatch):
+    """256-wide tiles on CTA pairs (one `cta_group::2` MMA of 256 rows over two SMs, operands staged half
+    and half, barriers of the leader CTA signalled across the cluster) accumulate every output element
+    over k in the same order as a single CTA's two 128-row MMAs: the results are bit-equal, for the
+    forward pass (K-major weights) and dX (MN-major), and sampled rows hold the oracle's bound."""
+    m, in_dim, out_dim = 10007, 512, 1024
+    weight, wc, x_np, x, dy_np, dy = _umma_case(storage, compute, m, in_dim, out_dim, 9100 + storage)
+    monkeypatch.setenv("CAIFQ_UMMA_PAIR", "0")
+    y1 = nv.linear_fwd(weight, x, torch.float32, compute)
+    dx1 = nv.linear_dx(weight, dy, torch.bfloat16, compute)
+    monkeypatch.setenv("CAIFQ_UMMA_PAIR", "1")
+    y2 = nv.linear_fwd(weight, x, torch.float32, compute)
+    assert nv.last_path() == "umma"
+    dx2 = nv.linear_dx(weight, dy, torch.bfloat16, compute)
+    assert nv.lib().caifq_device_status() == 0
+    assert nv.lib().caifq_umma_pair_capacity() >= 1
+    assert torch.equal(y1, y2)
+    assert torch.equal(dx1, dx2)
+    rows = np.r_[0:8, 5000:5008, m - 8:m]
+    assert max_rel_err(y2[rows].cpu().numpy(), orc.frozen_linear_forward(x_np[rows], wc, compute)) <= tol
+    want_dx = orc.round_through(orc.frozen_linear_backward(dy_np[rows], wc, compute), orc.BF16)
+    assert max_rel_err(dx2[rows].float().cpu().numpy(), want_dx) <= max(tol, 1e-2)   # one bf16 rounding of the output
+
+
+def test_umma_cta_pair_wait_that_runs_out_returns(monkeypatch):
+    """The give-up path with CTA pairs: the leader's wait runs out, both CTAs of every pair leave their
+    loops, meet at the cluster barrier, release their tensor memory, and the next launch is correct."""
+    import time
+
+    monkeypatch.setenv("CAIFQ_UMMA_PAIR", "1")
+    weight, wc, x_np, x, dy_np, dy = _umma_case(orc.I8, orc.BF16, 10007, 512, 1024, 4243)
+    y = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    assert nv.lib().caifq_device_status() == 0
+    nv.lib().caifq_selftest_stall_next_umma()
+    t0 = time.time()
+    nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 1.0
+    assert nv.lib().caifq_device_status() & 2
+    y2 = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
+    assert nv.lib().caifq_device_status() == 0
+    assert torch.equal(y, y2)

@@ -474,3 +474,31 @@ def test_lora_unfused_path_accumulates_into_the_tensor_core_epilogue():
     assert max_rel_err(dx.float().cpu().numpy(), want_dx) <= 2e-2
     assert max_rel_err(d_a.float().cpu().numpy(), want_da) <= 2e-2
     assert max_rel_err(d_b.float().cpu().numpy(), want_db) <= 2e-2
+
+
+@pytest.mark.parametrize("storage,compute", [(orc.I4, orc.BF16), (orc.I8, orc.F32)])
+def test_grouped_experts_on_cta_pairs_equal_single_ctas(storage, compute, monkeypatch):
+    """The grouped launches (fused gate/up/SwiGLU with 128 features of each projection per tile, down,
+    and the three dX launches incl. the accumulating one) on CTA pairs give the single-CTA results
+    bit for bit."""
+    experts, in_dim, hid = 6, 512, 384
+    rng = np.random.default_rng(6200 + storage)
+    counts = rng.integers(2000, 3500, experts)
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    total = int(offsets[-1])
+    gate, up, down = [], [], []
+    for _ in range(experts):
+        for lst, (o, i) in ((gate, (hid, in_dim)), (up, (hid, in_dim)), (down, (in_dim, hid))):
+            lst.append(make_weight(rng, o, i, storage, std=0.05)[0])
+    _, x = act(rng, total, in_dim, orc.BF16)
+    _, dy = act(rng, total, in_dim, orc.BF16)
+    results = []
+    for pair in ("0", "1"):
+        monkeypatch.setenv("CAIFQ_UMMA_PAIR", pair)
+        out, g, u = nv.grouped_expert_fwd(gate, up, down, offsets.tolist(), x, compute)
+        assert nv.last_path() == "umma-grouped"
+        dx = nv.grouped_expert_bwd(gate, up, down, offsets.tolist(), dy, g, u, compute)
+        assert nv.lib().caifq_device_status() == 0
+        results.append((out, g, u, dx))
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
