@@ -277,7 +277,9 @@ def test_dispatch_then_combine_with_unit_weights_is_a_sum_of_copies():
 
 
 # ------------------------------------------------------------ golden fixtures
-@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "*.npz"))) or [None])
+# (the layer_*.npz files hold whole-layer vectors in another format: tests/test_layer_golden.py replays those)
+@pytest.mark.parametrize("path", sorted(f for f in glob.glob(os.path.join(GOLDEN, "*.npz"))
+                                        if not os.path.basename(f).startswith("layer_")) or [None])
 def test_oracle_reproduces_reference_golden_vectors(path):
     """Fixtures under tests/golden/ hold inputs and the outputs of the reference's
     own kernels (captured on a B200 by tests/golden/make_golden.py)."""
