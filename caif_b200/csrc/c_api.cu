@@ -515,6 +515,50 @@ int caifq_linear_fwd_gather(const caifq_weight *w, const void *x, int32_t x_dtyp
   return launch_linear_decode(args, static_cast<cudaStream_t>(stream));
 }
 
+int caifq_linear_fwd_multi(const caifq_weight *ws, int32_t num_weights, const void *x, int32_t x_dtype, int64_t m,
+                           void *y, int32_t y_dtype, int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_linear_fwd_multi";
+  CAIFQ_CHECK_ARG(ws != nullptr && num_weights >= 1 && num_weights <= 4, "%s: 1 to 4 weights", who);
+  for (int i = 0; i < num_weights; ++i)
+  {
+    const int rc = check_weight(&ws[i], who);
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+  }
+  CAIFQ_CHECK_ARG(m >= 0, "%s: negative m", who);
+  CAIFQ_CHECK_ARG(is_float_dtype(x_dtype) && is_float_dtype(y_dtype) && is_float_dtype(compute_dtype),
+                  "%s: activation/output/compute dtypes must be F32, F16 or BF16", who);
+  if (m == 0)
+  {
+    return CAIFQ_OK;
+  }
+  CAIFQ_CHECK_ARG(x != nullptr && y != nullptr, "%s: null activation or output pointer", who);
+  LinearArgs args{};
+  args.w = ws[0];
+  args.backward = false;
+  args.a = x;
+  args.a_dtype = x_dtype;
+  args.a_prescale = 1.0f;
+  args.m = m;
+  args.c = y;
+  args.c_dtype = y_dtype;
+  args.accumulate = false;
+  args.compute_dtype = compute_dtype;
+  args.more = ws + 1;
+  args.num_more = num_weights - 1;
+  if (!decode_supported(args))
+  {
+    set_error("%s: only few-token calls the decode kernel takes (m <= 16, bf16 x, int4 or per-tensor int8, weights of "
+              "one storage, row length and scale rule, each but the last with a multiple of 8 rows)", who);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  set_path("decode");
+  return launch_linear_decode(args, static_cast<cudaStream_t>(stream));
+}
+
 int caifq_linear_dx(const caifq_weight *w, const void *dy, int32_t dy_dtype, int64_t m, void *dx, int32_t dx_dtype,
                     int32_t compute_dtype, void *stream)
 {

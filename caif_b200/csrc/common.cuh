@@ -212,6 +212,10 @@ struct LinearArgs
   int num_peers;
   int64_t c_ld;
   int64_t c_col0;
+  // Optional further layers that share the input (few-token kernel only): their rows follow w's in one
+  // launch and their outputs follow w's in the columns of c ([m, out + sum of their out_dims]).
+  const caifq_weight *more;
+  int num_more;
 };
 
 constexpr int kMaxPeers = 8;

@@ -201,10 +201,16 @@ __device__ __forceinline__ void sts_f32x2(uint32_t addr, float a, float b)
 }
 
 
+constexpr int kMaxSegments = 4;   // code matrices one launch may stream (layers that share their input)
+
 struct DecodeParams
 {
-  const uint8_t *codes;   // [out, in] packed
-  const void *scales;     // int4: fp16 per group; int8: fp32[1] or null
+  // The rows of the launch are the rows of up to kMaxSegments code matrices laid end to end (q/k/v or
+  // gate/up of one input): segment i covers rows seg_row0[i] .. seg_row0[i+1]; a single layer is one segment.
+  const uint8_t *codes[kMaxSegments];   // [out_i, in] packed
+  const void *scales[kMaxSegments];     // int4: fp16 per group; int8: fp32[1] or null
+  int seg_row0[kMaxSegments + 1];
+  int num_seg;
   const __nv_bfloat16 *x; // [m, in]
   void *y[kMaxPeers];     // [m, y_ld] on every GPU that receives the result (own buffer included)
   int num_y;
@@ -278,11 +284,28 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     const uint32_t code_bytes = static_cast<uint32_t>(rows) * p.row_bytes;
     const uint32_t scale_bytes = (BITS == 4) ? static_cast<uint32_t>(rows * p.groups_per_row * 2) : 0u;
     mbar_expect_tx(&full_bar[s], code_bytes + scale_bytes + (item == 0 ? p.stall_bytes : 0u));
-    bulk_g2s(stage, p.codes + static_cast<size_t>(row0) * p.row_bytes, code_bytes, &full_bar[s]);
-    if (BITS == 4)
+    // an item that straddles two code matrices takes one pair of copies from each
+    int row = row0;
+    while (row < row0 + rows)
     {
-      const uint8_t *src = static_cast<const uint8_t *>(p.scales) + static_cast<size_t>(row0) * p.groups_per_row * 2;
-      bulk_g2s(stage + static_cast<uint32_t>(kItemRows) * p.row_stride, src, scale_bytes, &full_bar[s]);
+      int sg = 0;
+      while (sg + 1 < p.num_seg && row >= p.seg_row0[sg + 1])
+      {
+        ++sg;
+      }
+      const int n = min(row0 + rows, p.seg_row0[sg + 1]) - row;
+      const size_t local = static_cast<size_t>(row - p.seg_row0[sg]);
+      const uint32_t done_rows = static_cast<uint32_t>(row - row0);
+      bulk_g2s(stage + done_rows * p.row_bytes, p.codes[sg] + local * p.row_bytes, static_cast<uint32_t>(n) * p.row_bytes,
+               &full_bar[s]);
+      if (BITS == 4)
+      {
+        const uint32_t per_row = static_cast<uint32_t>(p.groups_per_row) * 2u;
+        const uint8_t *src = static_cast<const uint8_t *>(p.scales[sg]) + local * per_row;
+        bulk_g2s(stage + static_cast<uint32_t>(kItemRows) * p.row_stride + done_rows * per_row, src,
+                 static_cast<uint32_t>(n) * per_row, &full_bar[s]);
+      }
+      row += n;
     }
   };
 
@@ -418,11 +441,30 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
           static_cast<uint32_t>(warp) * part_warp_bytes + static_cast<uint32_t>(g * p.tokp + 2 * t) * 4u;
     }
   }
-  float tensor_scale = 1.0f;
-  if (BITS == 8 && p.scales != nullptr)
+  // int8: the per-tensor scale of every segment; an output row takes the one of its segment
+  float seg_scale[kMaxSegments];
+#pragma unroll
+  for (int sg = 0; sg < kMaxSegments; ++sg)
   {
-    tensor_scale = static_cast<const float *>(p.scales)[0];
+    seg_scale[sg] = 1.0f;
+    if (BITS == 8 && sg < p.num_seg && p.scales[sg] != nullptr)
+    {
+      seg_scale[sg] = static_cast<const float *>(p.scales[sg])[0];
+    }
   }
+  auto tensor_scale_of = [&](int row)
+  {
+    float v = seg_scale[0];
+#pragma unroll
+    for (int sg = 1; sg < kMaxSegments; ++sg)
+    {
+      if (sg < p.num_seg && row >= p.seg_row0[sg])
+      {
+        v = seg_scale[sg];
+      }
+    }
+    return v;
+  };
   int s = 0;             // ring stage of the current item
   uint32_t s_par = 0;    // its phase parity
   bool ok = true;
@@ -676,6 +718,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
       const int row = row_begin + (round_begin + item) * kItemRows + r16;
       if (row < row_end)
       {
+        const float tensor_scale = (BITS == 8) ? tensor_scale_of(row) : 1.0f;
 #pragma unroll
         for (int i = 0; i < 4; ++i)
         {
@@ -714,15 +757,17 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
           acc[i] += lds_f32(src + static_cast<uint32_t>(w) * part_warp_bytes + static_cast<uint32_t>(i * p.tokp) * 4u);
         }
       }
+      const int row = row_begin + (round_begin + item) * kItemRows + 4 * rq;
       if (BITS == 8)
       {
+        // (four rows that start on a multiple of four lie in one segment: segments start on multiples of 8)
+        const float tensor_scale = tensor_scale_of(row);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
         {
           acc[i] *= tensor_scale;
         }
       }
-      const int row = row_begin + (round_begin + item) * kItemRows + 4 * rq;
       // plain stores; with peers they travel over NVLink and are complete when the kernel is
       const int64_t idx = static_cast<int64_t>(token) * p.y_ld + p.y_col0 + row;
       if (p.vec4 && row + 3 < row_end)
@@ -913,9 +958,38 @@ Layout layout_for(const caifq_weight &w, int64_t m)
 
 }  // namespace
 
+// The launch's rows: the layer's own, or those of all the layers that share the input laid end to end.
+static caifq_weight all_rows(const LinearArgs &args)
+{
+  caifq_weight w = args.w;
+  for (int i = 0; i < args.num_more; ++i)
+  {
+    w.out_dim += args.more[i].out_dim;
+  }
+  return w;
+}
+
 bool decode_supported(const LinearArgs &args)
 {
-  const caifq_weight &w = args.w;
+  if (args.num_more < 0 || args.num_more >= kMaxSegments || (args.num_more > 0 && args.more == nullptr))
+  {
+    return false;
+  }
+  for (int i = 0; i < args.num_more; ++i)
+  {
+    // layers of one launch have one storage, row length, scale rule; every one but the last ends on a
+    // multiple of 8 rows, so that every copy of a straddling item stays a multiple of 16 bytes
+    const caifq_weight &o = args.more[i];
+    const caifq_weight &prev = (i == 0) ? args.w : args.more[i - 1];
+    if (o.storage != args.w.storage || o.in_dim != args.w.in_dim || o.scheme != args.w.scheme ||
+        o.group_size != args.w.group_size || (o.scales == nullptr) != (args.w.scales == nullptr) ||
+        (prev.out_dim % kRowQuantum) != 0 || o.out_dim < 1 || (reinterpret_cast<uintptr_t>(o.codes) & 15u) != 0 ||
+        (reinterpret_cast<uintptr_t>(o.scales) & 15u) != 0)
+    {
+      return false;
+    }
+  }
+  const caifq_weight w = all_rows(args);
   const int x_dtype = args.a_dtype;
   const int64_t m = args.m;
   const int y_dtype = args.c_dtype;
@@ -990,12 +1064,25 @@ bool decode_supported(const LinearArgs &args)
 
 int launch_linear_decode(const LinearArgs &args, cudaStream_t s)
 {
-  const caifq_weight &w = args.w;
+  const caifq_weight w = all_rows(args);
   const int64_t m = args.m;
   const int y_dtype = args.c_dtype;
   DecodeParams p{};
-  p.codes = static_cast<const uint8_t *>(w.codes);
-  p.scales = w.scales;
+  p.num_seg = 1 + args.num_more;
+  p.seg_row0[0] = 0;
+  for (int i = 0; i < p.num_seg; ++i)
+  {
+    const caifq_weight &seg = (i == 0) ? args.w : args.more[i - 1];
+    p.codes[i] = static_cast<const uint8_t *>(seg.codes);
+    p.scales[i] = seg.scales;
+    p.seg_row0[i + 1] = p.seg_row0[i] + seg.out_dim;
+  }
+  for (int i = p.num_seg; i < kMaxSegments; ++i)
+  {
+    p.codes[i] = nullptr;
+    p.scales[i] = nullptr;
+    p.seg_row0[i + 1] = p.seg_row0[p.num_seg];
+  }
   p.x = static_cast<const __nv_bfloat16 *>(args.a);
   if (args.num_peers > 0)
   {

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "caifq_cast": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _vp]),
     "caifq_weight_materialize": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _vp]),
     "caifq_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_linear_fwd_multi": (ctypes.c_int, [ctypes.POINTER(CWeight), _i32, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_linear_fwd_gather": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, ctypes.POINTER(_vp), _i32,
                                                _i64, _i64, _i32, _i32, _vp]),
     "caifq_linear_dx": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
@@ -270,6 +271,19 @@ def linear_fwd(w, x, out_dtype=torch.float32, compute=F32, out=None):
     _check(lib().caifq_linear_fwd(w.ref(), _ptr(x), dtype_code(x), m, _ptr(out), dtype_code(out), compute, _stream()),
            "linear_fwd")
     return out
+
+
+def linear_fwd_multi(ws, x, out_dtype=torch.float32, compute=F32, out=None):
+    """Few-token forward of several frozen linears that share x (q/k/v, gate/up) in one launch:
+    y[m, sum out_i], weight i's outputs at columns sum_{j<i} out_j."""
+    _need_cuda(x)
+    m = x.numel() // ws[0].in_dim
+    total = sum(w.out_dim for w in ws)
+    y = out if out is not None else torch.empty((m, total), dtype=out_dtype, device=x.device)
+    arr = _weight_array(ws)
+    _check(lib().caifq_linear_fwd_multi(arr, len(ws), _ptr(x), dtype_code(x), m, _ptr(y), dtype_code(y), compute,
+                                        _stream()), "caifq_linear_fwd_multi")
+    return y
 
 
 def linear_fwd_gather(w, x, peer_ptrs, y_ld, y_col0, y_dtype=F32, compute=F32):

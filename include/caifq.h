@@ -194,6 +194,19 @@ CAIFQ_API int caifq_linear_fwd_gather(const caifq_weight *w, const void *x, int3
                                       void *const *y_peers, int32_t num_peers, int64_t y_ld, int64_t y_col0,
                                       int32_t y_dtype, int32_t compute_dtype, void *stream);
 
+/*
+ * Several frozen linears that share their input, few tokens: the q/k/v projections of an attention
+ * block (src/caif_device_multi_head_attention.cpp:544-546) or gate/up of an FFN
+ * (src/caif_device_ffn.cpp:324,335), which the reference runs as separate ForwardImpl calls.  One
+ * persistent launch streams all the code matrices, so the per-launch latency is paid once:
+ *   y[m, sum_i out_i] = x[m, in] . [W_0; W_1; ...]_deq^T      (weight i's outputs at columns sum_{j<i} out_j)
+ * Every output element has the bits caifq_linear_fwd gives for its own layer.  1 to 4 weights of one
+ * storage (int4 or per-tensor int8), in_dim, scheme and group size, each but the last with a multiple of 8
+ * rows; m <= 16, bf16 x.  Other calls are refused with CAIFQ_ERR_UNSUPPORTED (use caifq_linear_fwd per layer).
+ */
+CAIFQ_API int caifq_linear_fwd_multi(const caifq_weight *ws, int32_t num_weights, const void *x, int32_t x_dtype,
+                                     int64_t m, void *y, int32_t y_dtype, int32_t compute_dtype, void *stream);
+
 /* Name of the kernel family the last caifq_linear_fwd / caifq_linear_dx call
  * on this thread chose ("decode", "umma", "generic"); for tests and reports. */
 CAIFQ_API const char *caifq_last_path(void);

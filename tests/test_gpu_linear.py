@@ -392,3 +392,39 @@ def test_umma_cta_pair_wait_that_runs_out_returns(monkeypatch):
     y2 = nv.linear_fwd(weight, x, torch.float32, orc.BF16)
     assert nv.lib().caifq_device_status() == 0
     assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("storage,outs,m", [
+    (orc.I4, (4096, 1024, 1024), 1),        # q, k, v of the Llama-shaped block
+    (orc.I4, (4096, 1024, 1024), 16),
+    (orc.I4, (1416, 1032, 520), 4),         # boundaries that are multiples of 8 but not of 16: items straddle layers
+    (orc.I8, (1416, 1032, 520, 264), 9),    # int8: every layer has its own per-tensor scale
+    (orc.I4, (14336, 14336), 4),            # gate, up
+])
+def test_decode_several_layers_that_share_the_input_in_one_launch(storage, outs, m):
+    """caifq_linear_fwd_multi: one persistent launch streams the code matrices of all layers; every output
+    has the bits the layer's own caifq_linear_fwd call gives, and holds the oracle's bound."""
+    in_dim = 4096 if outs[0] >= 4096 else 1024
+    rng = np.random.default_rng(7700 + sum(outs) + m)
+    ws, wcs = [], []
+    for o in outs:
+        w, codes, scales = make_weight(rng, o, in_dim, storage)
+        ws.append(w)
+        wcs.append(_oracle_w(w, codes, scales, orc.F32))
+    x_np, x = act(rng, m, in_dim, orc.BF16)
+    y = nv.linear_fwd_multi(ws, x, torch.float32, orc.F32)
+    assert nv.last_path() == "decode"
+    assert nv.lib().caifq_device_status() == 0
+    col = 0
+    for w, wc in zip(ws, wcs):
+        single = nv.linear_fwd(w, x, torch.float32, orc.F32)
+        assert nv.last_path() == "decode"
+        assert torch.equal(y[:, col:col + w.out_dim], single)
+        assert max_rel_err(single.cpu().numpy(), orc.frozen_linear_forward(x_np, wc, orc.F32)) <= TOL_F32
+        col += w.out_dim
+    # refused, not mis-computed: a layer (not the last) whose row count is not a multiple of 8, and many tokens
+    odd = [make_weight(rng, 1028, in_dim, storage)[0], ws[0]]
+    with pytest.raises(nv.CaifqError):
+        nv.linear_fwd_multi(odd, x, torch.float32, orc.F32)
+    with pytest.raises(nv.CaifqError):
+        nv.linear_fwd_multi(ws, act(rng, 32, in_dim, orc.BF16)[1], torch.float32, orc.F32)
