@@ -746,7 +746,52 @@ def bench_c2(ctx):
         result["parity"] = parity
     if peer is not None:
         peer.close()
+    if world == 1:
+        # beside the single-call figure, never instead of it: layers that share their input in one launch
+        result["multi_weight"] = _c2_multi_weight(ctx, weights, xs)
     return result
+
+
+def _c2_multi_weight(ctx, weights, xs):
+    """Two [14336, 4096] int4 layers that share x (gate and up of the Llama-shaped FFN) per launch of
+    caifq_linear_fwd_multi, four pairs of weight copies (235 MB > L2) in turn, M in {1, 4, 16}."""
+    nv, torch, dev = ctx.nv, ctx.torch, ctx.dev
+    pairs = [weights[2 * i:2 * i + 2] for i in range(C2_COPIES // 2)]
+    outs = {m: [torch.empty(m, 2 * C2_OUT, dtype=torch.float32, device=dev) for _ in pairs] for m in C2_MS}
+
+    def one_pass():
+        for m in C2_MS:
+            for i, pair in enumerate(pairs):
+                nv.linear_fwd_multi(pair, xs[m], torch.float32, nv.F32, out=outs[m][i])
+
+    passes = 16
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        one_pass()
+        one_pass()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(passes):
+                one_pass()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    launches = reps * passes * len(C2_MS) * len(pairs)
+    us = a.elapsed_time(b) * 1e3 / launches
+    algo = sum(c2_bytes(m, 2 * C2_OUT) for m in C2_MS) / len(C2_MS)
+    gbs = algo / us / 1e3
+    return {"workload": "gate+up: two [14336, 4096] int4 g128 layers sharing x per launch, M in {1,4,16}",
+            "value": gbs, "unit": "GB/s", "us_per_launch": us, "launches_timed": launches,
+            "frac_of_hbm_peak": gbs / ctx.peaks["hbm_gbs"]}
 
 
 def bench_c3(ctx):

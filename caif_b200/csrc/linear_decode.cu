@@ -284,6 +284,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_decode_kernel(const __grid
     const uint32_t code_bytes = static_cast<uint32_t>(rows) * p.row_bytes;
     const uint32_t scale_bytes = (BITS == 4) ? static_cast<uint32_t>(rows * p.groups_per_row * 2) : 0u;
     mbar_expect_tx(&full_bar[s], code_bytes + scale_bytes + (item == 0 ? p.stall_bytes : 0u));
+    if (p.num_seg == 1)
+    {
+      bulk_g2s(stage, p.codes[0] + static_cast<size_t>(row0) * p.row_bytes, code_bytes, &full_bar[s]);
+      if (BITS == 4)
+      {
+        const uint8_t *src = static_cast<const uint8_t *>(p.scales[0]) + static_cast<size_t>(row0) * p.groups_per_row * 2;
+        bulk_g2s(stage + static_cast<uint32_t>(kItemRows) * p.row_stride, src, scale_bytes, &full_bar[s]);
+      }
+      return;
+    }
     // an item that straddles two code matrices takes one pair of copies from each
     int row = row0;
     while (row < row0 + rows)

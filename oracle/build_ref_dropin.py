@@ -7,6 +7,10 @@ programs, compiled from its unmodified sources, run on this library's kernels.
                                                   with the definitions of ForwardImpl and BackwardImpl taken out
                                                   and oracle/ref_dropin/frozen_linear_bodies.inc (calls into the
                                                   C ABI) put in their place; everything else is the reference's text
+  oracle/_ref/gen/caif_device_lora_adapter.cpp    generated likewise: the reference's two bodies renamed to
+                                                  ...Reference (kept for base layers that are not frozen linears)
+                                                  and oracle/ref_dropin/lora_adapter_bodies.inc appended
+  oracle/_ref/gen/include/*.h                     copies of two reference headers with the added declarations
   oracle/_ref/libcaif_ref_dropin.so               all other reference objects (as built by build_ref_layers.py)
                                                   + the generated unit, linked against caif_b200/libcaifq.so
   oracle/_ref/bin/<test>                          the reference's own tests/test_device_frozen_linear.cpp,
@@ -33,6 +37,8 @@ GEN_DIR = os.path.join(REF_DIR, "gen")
 BIN_DIR = os.path.join(REF_DIR, "bin")
 DROPIN_SO = os.path.join(REF_DIR, "libcaif_ref_dropin.so")
 BODIES = os.path.join(HERE, "ref_dropin", "frozen_linear_bodies.inc")
+LORA_BODIES = os.path.join(HERE, "ref_dropin", "lora_adapter_bodies.inc")
+GEN_INC = os.path.join(GEN_DIR, "include")
 TESTS = ("test_device_frozen_linear", "test_device_lora_adapter", "test_device_moe_frozen_expert",
          "test_pluggable_projections")
 REPLACED = ("ForwardImpl", "BackwardImpl")
@@ -49,7 +55,34 @@ def _cut_function(text, name):
     return text[:m.start()] + text[end:]
 
 
+def _gen_headers():
+    """Copies of two reference headers with the declarations the bindings add: public, non-virtual members
+    only, so the classes' layout and vtables are those every other translation unit sees."""
+    os.makedirs(GEN_INC, exist_ok=True)
+    inc = os.path.join(layers.REFERENCE_ROOT, "include", "caif")
+    with open(os.path.join(inc, "caif_device_frozen_linear.h")) as f:
+        text = f.read()
+    anchor = "    bool IsPrefetched()const override{return _is_prefetched;}\n"
+    at = text.index(anchor) + len(anchor)
+    text = text[:at] + "    caifq_weight AsCaifq()const;   // codes, scales and dims as the C ABI takes them\n" + text[at:]
+    text = text.replace('#include "caif_device_layer.h"\n', '#include "caifq.h"\n#include "caif_device_layer.h"\n', 1)
+    with open(os.path.join(GEN_INC, "caif_device_frozen_linear.h"), "w") as f:
+        f.write(text)
+    with open(os.path.join(inc, "caif_device_lora_adapter.h")) as f:
+        text = f.read()
+    anchor = "    CAIF_DeviceTensor BackwardImpl(const CAIF_DeviceTensor &grad_output,CAIF_RunContext &ctx)override;\n"
+    at = text.index(anchor) + len(anchor)
+    text = (text[:at] +
+            "    CAIF_DeviceTensor ForwardImplReference(const CAIF_DeviceTensor &input,CAIF_RunContext &ctx);\n"
+            "    CAIF_DeviceTensor BackwardImplReference(const CAIF_DeviceTensor &grad_output,CAIF_RunContext &ctx);\n" +
+            text[at:])
+    with open(os.path.join(GEN_INC, "caif_device_lora_adapter.h"), "w") as f:
+        f.write(text)
+
+
 def generate():
+    """Writes the generated translation units; returns their paths."""
+    _gen_headers()
     src = os.path.join(layers.REFERENCE_ROOT, "src", "caif_device_frozen_linear.cpp")
     with open(src) as f:
         text = f.read()
@@ -61,12 +94,30 @@ def generate():
     at = text.index(marker)
     # the bodies go before the explicit instantiations, inside the reference's namespace
     text = text[:at] + bodies + "\n" + text[at:]
-    text = '#include "caifq.h"\n' + text
     os.makedirs(GEN_DIR, exist_ok=True)
     out = os.path.join(GEN_DIR, "caif_device_frozen_linear.cpp")
     with open(out, "w") as f:
         f.write(text)
-    return out
+
+    # the LoRA adapter: the reference's two bodies stay, under another name, as the path for other base layers
+    src = os.path.join(layers.REFERENCE_ROOT, "src", "caif_device_lora_adapter.cpp")
+    with open(src) as f:
+        text = f.read()
+    for name in REPLACED:
+        old = "CAIF_DeviceLoRAAdapter<ComputeT,StorageT>::%s(" % name
+        if text.count(old) != 1:
+            raise RuntimeError("reference LoRA adapter: definition of %s not found" % name)
+        text = text.replace(old, "CAIF_DeviceLoRAAdapter<ComputeT,StorageT>::%sReference(" % name)
+    with open(LORA_BODIES) as f:
+        bodies = f.read()
+    marker = "template class CAIF_DeviceLoRAAdapter<float,float>;"
+    at = text.index(marker)
+    text = text[:at] + bodies + "\n" + text[at:]
+    text = '#include "caifq.h"\n#include "caif_device_frozen_linear.h"\n' + text
+    out_lora = os.path.join(GEN_DIR, "caif_device_lora_adapter.cpp")
+    with open(out_lora, "w") as f:
+        f.write(text)
+    return [out, out_lora]
 
 
 def _includes():
@@ -88,14 +139,18 @@ def build():
     if not os.path.exists(libcaifq):
         raise RuntimeError("build caif_b200/libcaifq.so first (python -m caif_b200.build)")
     cxx = ["g++", "-std=c++23", "-O1", "-fPIC", "-fopenmp", "-DUSE_CAIF_CUDA=1", "-w"] + _includes()
-    gen = generate()
-    obj = os.path.join(GEN_DIR, "caif_device_frozen_linear.o")
-    subprocess.check_call(cxx + ["-c", gen, "-o", obj])
+    gen_objs = []
+    for gen in generate():
+        obj = gen[:-4] + ".o"
+        # the generated header copies shadow the reference's for these two units only
+        subprocess.check_call(cxx[:1] + ["-I", GEN_INC] + cxx[1:] + ["-c", gen, "-o", obj])
+        gen_objs.append(obj)
     others = sorted(os.path.join(layers.OBJ_DIR, o) for o in os.listdir(layers.OBJ_DIR)
-                    if o.endswith(".o") and o not in ("caif_device_frozen_linear.o", "ref_layers_shim.o"))
+                    if o.endswith(".o") and o not in ("caif_device_frozen_linear.o", "caif_device_lora_adapter.o",
+                                                      "ref_layers_shim.o"))
     blas = layers.scipy_openblas()
     rpaths = ["$ORIGIN", "$ORIGIN/../../caif_b200", os.path.dirname(blas), "/usr/local/cuda/lib64"]
-    link = ["g++", "-shared", "-fopenmp", "-o", DROPIN_SO, obj] + others + [
+    link = ["g++", "-shared", "-fopenmp", "-o", DROPIN_SO] + gen_objs + others + [
         "-L" + os.path.dirname(libcaifq), "-lcaifq", "-L/usr/local/cuda/lib64", "-lcublas", "-lcublasLt", "-lcudart",
         "-lcudnn", blas, "-lpthread", "-ldl", "-lm"] + ["-Wl,-rpath," + p for p in rpaths]
     subprocess.check_call(link)
