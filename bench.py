@@ -813,8 +813,9 @@ def bench_c3(ctx):
     def step():
         i = state["i"] % n_sets
         state["i"] += 1
-        _, hidden = nv.lora_linear_fwd(weight, lora, xs[i], compute=nv.F32)
-        dx, _, _ = nv.lora_linear_bwd(weight, lora, dys[i], xs[i], hidden, compute=nv.F32)
+        # (the entry points that may expand the weight once per call into their workspace)
+        _, hidden = nv.lora_linear_fwd(weight, lora, xs[i], compute=nv.F32, expanded=True)
+        dx, _, _ = nv.lora_linear_bwd(weight, lora, dys[i], xs[i], hidden, compute=nv.F32, expanded=True)
         return dx
 
     for _ in range(max(args.warmup, 3)):
@@ -1036,8 +1037,8 @@ def bench_c4lin(ctx):
     d_b = {o // world: torch.empty(o // world, r_lora, dtype=torch.bfloat16, device=dev) for o in (4096, 1024, 14336)}
     ws_bytes = 0
     for w, l in model[0]:
-        ws_bytes = max(ws_bytes, int(nv.lib().caifq_lora_fwd_workspace_bytes(w.ref(), l.ref(), tokens)),
-                       int(nv.lib().caifq_lora_bwd_workspace_bytes(w.ref(), l.ref(), tokens)))
+        ws_bytes = max(ws_bytes, nv.lora_fwd_workspace_bytes(w, l, tokens, nv.BF16, expanded=True),
+                       nv.lora_bwd_workspace_bytes(w, l, tokens, nv.BF16, expanded=True))
     workspace = torch.empty(ws_bytes + 256, dtype=torch.uint8, device=dev)
     comm = torch.cuda.Stream() if world > 1 else None
     group = None
@@ -1082,13 +1083,13 @@ def bench_c4lin(ctx):
             for p, ((w, l), (_, o, i)) in enumerate(zip(layer, C4_PROJ)):
                 if world == 1:
                     nv.lora_linear_fwd(w, l, x_by_in[i], compute=nv.BF16, out=y_by_out[o], hidden=hid[0][p],
-                                       workspace=workspace)
+                                       workspace=workspace, expanded=True)
                     continue
                 b = n & 1
                 if n >= 2:
                     main.wait_event(ev_done[b])
                 nv.lora_linear_fwd(w, l, x_by_in[i], compute=nv.BF16, out=y_send[b][o // world], hidden=hid[0][p],
-                                   workspace=workspace)
+                                   workspace=workspace, expanded=True)
                 comm.wait_stream(main)
                 with torch.cuda.stream(comm):
                     dist.all_gather_into_tensor(y_full[b][o], y_send[b][o // world], group=group)
@@ -1100,12 +1101,12 @@ def bench_c4lin(ctx):
                 (w, l), (_, o, i) = layer[p], C4_PROJ[p]
                 if world == 1:
                     nv.lora_linear_bwd(w, l, dy_by_out[o], x_by_in[i], hid[0][p], compute=nv.BF16, dx=dx_by_in[i],
-                                       d_a=d_a[i], d_b=d_b[o], workspace=workspace)
+                                       d_a=d_a[i], d_b=d_b[o], workspace=workspace, expanded=True)
                     continue
                 b = n & 1
                 main.wait_event(ev_done[b])
                 nv.lora_linear_bwd(w, l, dy_by_out[o // world], x_by_in[i], hid[0][p], compute=nv.BF16,
-                                   dx=dx_send[b][i], d_a=da_send[b][i], d_b=d_b[o // world], workspace=workspace)
+                                   dx=dx_send[b][i], d_a=da_send[b][i], d_b=d_b[o // world], workspace=workspace, expanded=True)
                 comm.wait_stream(main)
                 with torch.cuda.stream(comm):
                     dist.reduce_scatter_tensor(dx_part[i], dx_send[b][i], group=group)
@@ -1304,9 +1305,15 @@ def main():
     ap.add_argument("--workload", default=None, help="shorthand for --workloads with one entry")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--c2-layers", type=int, default=None,
+                    help="layer passes per c2 step instead of 32 (a short step for profiler captures; the line "
+                         "then does not describe the configured workload)")
     args = ap.parse_args()
     if args.workload:
         args.workloads = args.workload
+    if args.c2_layers is not None and args.c2_layers >= 1:
+        global C2_LAYERS
+        C2_LAYERS = args.c2_layers
     if args.impl == "reference":
         run_reference(args)
     else:

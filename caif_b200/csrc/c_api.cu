@@ -182,7 +182,7 @@ Force forced_path()
 
 int linear_any(const caifq_weight *w, bool backward, const void *a, int a_dtype, float a_prescale, int64_t m,
                void *c, int c_dtype, bool accumulate, int compute_dtype, cudaStream_t s, const char *who,
-               const void *lora_lhs = nullptr, const void *lora_rhs = nullptr)
+               const void *lora_lhs = nullptr, const void *lora_rhs = nullptr, const float *c_scale = nullptr)
 {
   const int rc = check_weight(w, who);
   if (rc != CAIFQ_OK)
@@ -210,6 +210,7 @@ int linear_any(const caifq_weight *w, bool backward, const void *a, int a_dtype,
   args.compute_dtype = compute_dtype;
   args.lora_lhs = lora_lhs;
   args.lora_rhs = lora_rhs;
+  args.c_scale = c_scale;
   if (lora_lhs != nullptr)
   {
     // the fused LoRA k-block exists on the tensor-core path only; callers check fused_lora_ok() first
@@ -288,6 +289,29 @@ bool fused_lora_ok(const caifq_weight *w, const caifq_lora *l, const void *act, 
   }
   probe.backward = true;
   return umma_supported(probe);
+}
+
+// Many-token calls may expand the weight once per call into a bf16 matrix in the caller's workspace and feed
+// it to the tensor core with plain tile copies on CTA pairs (1.43-1.55 PFLOP/s per launch at 4096 x 4096,
+// 8192 tokens) instead of converting every tile again in the dequant warps of every CTA (1.1-1.3): the
+// conversion is then done once per weight, not once per weight and 256 rows of tokens.  Worth its 10-15 us
+// from a few thousand tokens on.  int4 needs bf16 compute (fp32 compute keeps the two-term form).
+bool expand_ok(const caifq_weight *w, const caifq_lora *l, const void *act, int64_t m, int compute_dtype)
+{
+  if (m < 4096 || !fused_lora_ok(w, l, act, m, compute_dtype))
+  {
+    return false;
+  }
+  if (w->storage == CAIFQ_I4 && compute_dtype != CAIFQ_BF16)
+  {
+    return false;
+  }
+  return (w->in_dim % 256) == 0 && (w->out_dim % 256) == 0;
+}
+
+size_t expanded_weight_bytes(const caifq_weight *w)
+{
+  return align256(static_cast<size_t>(w->in_dim) * static_cast<size_t>(w->out_dim) * 2);
 }
 
 // scale the base kernel applies in its epilogue (what the padded LoRA operand must be divided by)
@@ -470,6 +494,13 @@ int caifq_linear_fwd(const caifq_weight *w, const void *x, int32_t x_dtype, int6
                     static_cast<cudaStream_t>(stream), "caifq_linear_fwd");
 }
 
+int caifq_linear_fwd_residual(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *y_inout,
+                              int32_t y_dtype, int32_t compute_dtype, void *stream)
+{
+  return linear_any(w, false, x, x_dtype, 1.0f, m, y_inout, y_dtype, true, compute_dtype,
+                    static_cast<cudaStream_t>(stream), "caifq_linear_fwd_residual");
+}
+
 int caifq_linear_fwd_gather(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m, void *const *y_peers,
                             int32_t num_peers, int64_t y_ld, int64_t y_col0, int32_t y_dtype, int32_t compute_dtype,
                             void *stream)
@@ -590,10 +621,15 @@ size_t caifq_lora_fwd_workspace_bytes(const caifq_weight *w, const caifq_lora *l
   return lora_fwd_ws(w, m).total;
 }
 
-int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
-                          void *hidden, void *workspace, int32_t compute_dtype, void *stream)
+}  // extern "C"
+
+namespace
 {
-  const char *who = "caifq_lora_linear_fwd";
+const void *const kAlignedProbe = reinterpret_cast<const void *>(static_cast<uintptr_t>(256));
+
+int lora_fwd_impl(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y, void *hidden,
+                  void *workspace, int32_t compute_dtype, void *stream, bool may_expand, const char *who)
+{
   const int rc = check_lora(w, lora, who);
   if (rc != CAIFQ_OK)
   {
@@ -625,6 +661,19 @@ int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const v
     {
       return r;
     }
+    if (may_expand && expand_ok(w, lora, x, m, compute_dtype))
+    {
+      // the weight as a bf16 matrix behind the other scratch, then the same launch on it
+      void *wb = base + ws.total;
+      r = launch_expand_to_bf16(*w, wb, s);
+      if (r != CAIFQ_OK)
+      {
+        return r;
+      }
+      const caifq_weight wbf = float_weight(wb, CAIFQ_BF16, w->out_dim, w->in_dim);
+      return linear_any(&wbf, false, x, sd, 1.0f, m, y, sd, false, compute_dtype, s, who, base + ws.hs, base + ws.bp,
+                        epilogue_scale_ptr(w));
+    }
     return linear_any(w, false, x, sd, 1.0f, m, y, sd, false, compute_dtype, s, who, base + ws.hs, base + ws.bp);
   }
   // hidden = x . A^T, rounded to the storage dtype as the reference materialises it
@@ -649,6 +698,33 @@ int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const v
   // frozen base on top: y = round(round(x . W^T) + y)
   return linear_any(w, false, x, sd, 1.0f, m, y, sd, true, compute_dtype, s, who);
 }
+}  // namespace
+
+extern "C" {
+
+int caifq_lora_linear_fwd(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
+                          void *hidden, void *workspace, int32_t compute_dtype, void *stream)
+{
+  return lora_fwd_impl(w, lora, x, m, y, hidden, workspace, compute_dtype, stream, false, "caifq_lora_linear_fwd");
+}
+
+size_t caifq_lora_fwd_workspace_bytes_expanded(const caifq_weight *w, const caifq_lora *lora, int64_t m,
+                                               int32_t compute_dtype)
+{
+  if (w == nullptr || lora == nullptr || m <= 0)
+  {
+    return 0;
+  }
+  const size_t plain = lora_fwd_ws(w, m).total;
+  return expand_ok(w, lora, kAlignedProbe, m, compute_dtype) ? plain + expanded_weight_bytes(w) : plain;
+}
+
+int caifq_lora_linear_fwd_expanded(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m, void *y,
+                                   void *hidden, void *workspace, int32_t compute_dtype, void *stream)
+{
+  return lora_fwd_impl(w, lora, x, m, y, hidden, workspace, compute_dtype, stream, true,
+                       "caifq_lora_linear_fwd_expanded");
+}
 
 size_t caifq_lora_bwd_workspace_bytes(const caifq_weight *w, const caifq_lora *lora, int64_t m)
 {
@@ -659,11 +735,14 @@ size_t caifq_lora_bwd_workspace_bytes(const caifq_weight *w, const caifq_lora *l
   return lora_bwd_ws(w, lora, m).total;
 }
 
-int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
-                          const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
-                          int32_t compute_dtype, void *stream)
+}  // extern "C"
+
+namespace
 {
-  const char *who = "caifq_lora_linear_bwd";
+int lora_bwd_impl(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x, const void *hidden,
+                  int64_t m, void *dx, void *d_a, void *d_b, void *workspace, int32_t compute_dtype, void *stream,
+                  bool may_expand, const char *who)
+{
   const int rc = check_lora(w, lora, who);
   if (rc != CAIFQ_OK)
   {
@@ -709,6 +788,18 @@ int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const v
       return r;
     }
     // dx = dy . W + dHs . Ap in one tensor-core launch
+    if (may_expand && expand_ok(w, lora, dy, m, compute_dtype))
+    {
+      void *wb = wbase + ws.total;
+      r = launch_expand_to_bf16(*w, wb, s);
+      if (r != CAIFQ_OK)
+      {
+        return r;
+      }
+      const caifq_weight wbf = float_weight(wb, CAIFQ_BF16, w->out_dim, w->in_dim);
+      return linear_any(&wbf, true, dy, sd, 1.0f, m, dx, sd, false, compute_dtype, s, who, wbase + ws.dhs,
+                        wbase + ws.ap, epilogue_scale_ptr(w));
+    }
     return linear_any(w, true, dy, sd, 1.0f, m, dx, sd, false, compute_dtype, s, who, wbase + ws.dhs, wbase + ws.ap);
   }
   // dB[out, r] = (scale . dy)^T . hidden
@@ -738,6 +829,36 @@ int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const v
     return r;
   }
   return linear_any(w, true, dy, sd, 1.0f, m, dx, sd, true, compute_dtype, s, who);
+}
+}  // namespace
+
+extern "C" {
+
+int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
+                          const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
+                          int32_t compute_dtype, void *stream)
+{
+  return lora_bwd_impl(w, lora, dy, x, hidden, m, dx, d_a, d_b, workspace, compute_dtype, stream, false,
+                       "caifq_lora_linear_bwd");
+}
+
+size_t caifq_lora_bwd_workspace_bytes_expanded(const caifq_weight *w, const caifq_lora *lora, int64_t m,
+                                               int32_t compute_dtype)
+{
+  if (w == nullptr || lora == nullptr || m <= 0 || lora->rank <= 0)
+  {
+    return 0;
+  }
+  const size_t plain = lora_bwd_ws(w, lora, m).total;
+  return expand_ok(w, lora, kAlignedProbe, m, compute_dtype) ? plain + expanded_weight_bytes(w) : plain;
+}
+
+int caifq_lora_linear_bwd_expanded(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
+                                   const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
+                                   int32_t compute_dtype, void *stream)
+{
+  return lora_bwd_impl(w, lora, dy, x, hidden, m, dx, d_a, d_b, workspace, compute_dtype, stream, true,
+                       "caifq_lora_linear_bwd_expanded");
 }
 
 // ------------------------------------------------- LoRA backward, no allocation

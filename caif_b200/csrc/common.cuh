@@ -182,6 +182,9 @@ int launch_dequantize_int4(const uint8_t *packed, const uint16_t *scales, float 
                            cudaStream_t s);
 int launch_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_t n, cudaStream_t s);
 int launch_weight_materialize(const caifq_weight &w, void *dst, int dst_dtype, cudaStream_t s);
+// int8 / int4 codes -> a bf16 [out, in] matrix for the tensor core: int8 codes as exact integers (the scale
+// is left to the epilogue), int4 as bf16(scale * code), the reference's dequantize-then-cast value
+int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s);
 
 // One frozen-linear product.  forward: c[m,out] = a[m,in] . W^T;  backward:
 // c[m,in] = a[m,out] . W.  `a_prescale` != 1 multiplies a on load and rounds the
@@ -205,6 +208,9 @@ struct LinearArgs
   // for backward.  Both already carry every scale so that acc_total * epilogue scale is right.
   const void *lora_lhs;
   const void *lora_rhs;
+  // bf16 weights on the tensor-core path only: a device scalar the fp32 accumulator is multiplied by in the
+  // epilogue (the per-tensor scale of int8 codes that were expanded to exact bf16 integers); null = 1
+  const float *c_scale;
   // Optional fused all-gather of a column-parallel forward (few-token kernel only): when
   // num_peers > 0 every output element goes to c_peers[r] for all r (this GPU's own buffer
   // included, `c` is ignored) at row pitch c_ld and column offset c_col0.

@@ -153,23 +153,34 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
 // every wait of the CTA returns at once, so the roles run through the rest of their loops without
 // spinning (on garbage: the results are wrong and the host sees the flag) and the kernel ends within
 // about one limit, TMEM released.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
+{
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_word, uint32_t limit)
 {
+  // A barrier that is already complete costs one poll and nothing else: the abort word is looked at only
+  // once a wait actually has to wait (reading it before every poll cost 12 % of the kernel's throughput).
+  if (mbar_try(bar, parity))
+  {
+    return true;
+  }
   if (*abort_word != 0u)
   {
     return false;
   }
   for (uint32_t spin = 0; spin < limit; ++spin)
   {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done)
+    if (mbar_try(bar, parity))
     {
       return true;
     }
@@ -444,6 +455,7 @@ struct UmmaParams
   int num_m_tiles;
   int num_n_tiles;
   const uint8_t *lora_rhs;  // null = no LoRA k-block
+  const float *c_scale;     // bf16 weights only: factor of the fp32 accumulator in the epilogue (null = 1)
   // Fused gate/up/SwiGLU forward of a frozen expert (forward, 128-wide tiles, 16-bit outputs): a tile's
   // columns 0..63 are features [64 j, 64 j + 64) of the gate projection, columns 64..127 the same
   // features of the up projection.  c receives gate(x), c_up up(x), c_hidden silu(gate(x)) * up(x),
@@ -552,7 +564,8 @@ __device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams
 template <int WMODE, bool BWD, int BN, bool GROUPED, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const __grid_constant__ CUtensorMap map_h, const UmmaParams p,
+                   const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_l,
+                   const UmmaParams p,
                    const __grid_constant__ typename GroupSel<GROUPED>::type gt)
 {
   constexpr int PLANES = planes_of(WMODE);
@@ -713,18 +726,21 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             {
               mbar_expect_tx(b_full(s), B_STAGE_BYTES * CTAS);
             }
+            // the LoRA k-block (number num_kb) takes its weight-side operand, the padded factor, from map_l
+            const CUtensorMap *bmap = (kb < num_kb) ? &map_b : &map_l;
+            const int kc = (kb < num_kb) ? kb * BK : 0;
             if (BWD)
             {
               // [k rows][n cols]: boxes of 64 n x 64 k land as the MN-major blocks
 #pragma unroll
               for (int nb = 0; nb < BNC / 64; ++nb)
               {
-                load(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, &map_b, nc0 + nb * 64, kb * BK, b_full(s));
+                load(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, bmap, nc0 + nb * 64, kc, b_full(s));
               }
             }
             else
             {
-              load(b_addr(s), &map_b, kb * BK, nc0, b_full(s));
+              load(b_addr(s), bmap, kc, nc0, b_full(s));
             }
           }
           if (++s == STAGES)
@@ -837,6 +853,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (WMODE == W_I8 && tw.scales != nullptr)
       {
         out_scale = __ldg(static_cast<const float *>(tw.scales));
+      }
+      if (WMODE == W_BF16 && p.c_scale != nullptr)
+      {
+        out_scale = __ldg(p.c_scale);
       }
       wait(acc_full(acc), acc_par);
       tc_fence_after();
@@ -1400,7 +1420,8 @@ bool pairs_enabled(int mode)
 }
 
 template <int WMODE, bool BWD, int BN, bool GROUPED, bool PAIR = false>
-int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const UmmaParams &p,
+int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtensorMap &map_h, const CUtensorMap &map_l,
+                const UmmaParams &p,
                 const typename GroupSel<GROUPED>::type &gt, cudaStream_t s)
 {
   auto kernel = linear_umma_kernel<WMODE, BWD, BN, GROUPED, PAIR>;
@@ -1454,11 +1475,11 @@ int launch_inst(const CUtensorMap &map_a, const CUtensorMap &map_b, const CUtens
       pairs = static_cast<int>(tiles);
     }
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
-    CAIFQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_h, p, gt));
+    CAIFQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_h, map_l, p, gt));
     return CAIFQ_OK;
   }
   const int grid = tiles < sm_count_umma() ? static_cast<int>(tiles) : sm_count_umma();
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_h, p, gt);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, s>>>(map_a, map_b, map_h, map_l, p, gt);
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }
@@ -1606,25 +1627,34 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
     map_b = map_a;
   }
   CUtensorMap map_h = map_a;
+  CUtensorMap map_l = map_b;
+  p.c_scale = (mode == W_BF16) ? g.c_scale : nullptr;
   if (g.lora_lhs != nullptr && g.lora_rhs != nullptr)
   {
-    if (mode == W_BF16)
-    {
-      set_error("frozen linear (umma): the fused LoRA k-block needs a quantized base weight");
-      return CAIFQ_ERR_UNSUPPORTED;
-    }
     rc = make_map_bf16(&map_h, g.lora_lhs, 64, static_cast<uint64_t>(g.m), BM_SUB);
     if (rc != CAIFQ_OK)
     {
       return rc;
     }
     p.lora_rhs = static_cast<const uint8_t *>(g.lora_rhs);
+    if (mode == W_BF16)
+    {
+      // the padded factor as a copy source: [N, 64] (forward, boxes of 64 k x the CTA's rows) or
+      // [64, N] (backward, boxes of 64 n x 64 k), like the weight itself
+      rc = g.backward ? make_map_bf16(&map_l, g.lora_rhs, static_cast<uint64_t>(p.n_total), 64, BK)
+                      : make_map_bf16(&map_l, g.lora_rhs, 64, static_cast<uint64_t>(p.n_total),
+                                      (pair && bn == 256) ? 128 : bn);
+      if (rc != CAIFQ_OK)
+      {
+        return rc;
+      }
+    }
   }
 #define CAIFQ_UMMA_PAIR_CASE(MODE)                                                                      \
   if (mode == MODE && bn == 256 && pair)                                                                \
   {                                                                                                     \
-    return g.backward ? launch_inst<MODE, true, 256, false, true>(map_a, map_b, map_h, p, NoGroupTable{}, s)   \
-                      : launch_inst<MODE, false, 256, false, true>(map_a, map_b, map_h, p, NoGroupTable{}, s); \
+    return g.backward ? launch_inst<MODE, true, 256, false, true>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s)   \
+                      : launch_inst<MODE, false, 256, false, true>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s); \
   }
   CAIFQ_UMMA_PAIR_CASE(W_I8)
   CAIFQ_UMMA_PAIR_CASE(W_I4)
@@ -1634,13 +1664,13 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
 #define CAIFQ_UMMA_CASE(MODE)                                                        \
   if (mode == MODE && bn == 128)                                                     \
   {                                                                                  \
-    return g.backward ? launch_inst<MODE, true, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s)   \
-                      : launch_inst<MODE, false, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s); \
+    return g.backward ? launch_inst<MODE, true, 128, false>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s)   \
+                      : launch_inst<MODE, false, 128, false>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s); \
   }                                                                                  \
   if (mode == MODE && bn == 256)                                                     \
   {                                                                                  \
-    return g.backward ? launch_inst<MODE, true, 256, false>(map_a, map_b, map_h, p, NoGroupTable{}, s)   \
-                      : launch_inst<MODE, false, 256, false>(map_a, map_b, map_h, p, NoGroupTable{}, s); \
+    return g.backward ? launch_inst<MODE, true, 256, false>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s)   \
+                      : launch_inst<MODE, false, 256, false>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s); \
   }
   CAIFQ_UMMA_CASE(W_I8)
   CAIFQ_UMMA_CASE(W_I4)
@@ -1648,8 +1678,8 @@ int launch_linear_umma(const LinearArgs &g, cudaStream_t s)
 #undef CAIFQ_UMMA_CASE
   if (mode == W_I4S)   // two operand planes: 128-wide tiles only
   {
-    return g.backward ? launch_inst<W_I4S, true, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s)
-                      : launch_inst<W_I4S, false, 128, false>(map_a, map_b, map_h, p, NoGroupTable{}, s);
+    return g.backward ? launch_inst<W_I4S, true, 128, false>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s)
+                      : launch_inst<W_I4S, false, 128, false>(map_a, map_b, map_h, map_l, p, NoGroupTable{}, s);
   }
   set_error("frozen linear (umma): unsupported weight storage %d", w.storage);
   return CAIFQ_ERR_UNSUPPORTED;
@@ -1755,8 +1785,8 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
 #define CAIFQ_UMMA_GROUP_PAIR_CASE(MODE)                                                           \
   if (mode == MODE && pair)                                                                        \
   {                                                                                                \
-    rc = g.backward ? launch_inst<MODE, true, 256, true, true>(map_a, map_a, map_a, p, gt, s)      \
-                    : launch_inst<MODE, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);    \
+    rc = g.backward ? launch_inst<MODE, true, 256, true, true>(map_a, map_a, map_a, map_a, p, gt, s)      \
+                    : launch_inst<MODE, false, 256, true, true>(map_a, map_a, map_a, map_a, p, gt, s);    \
   }
     CAIFQ_UMMA_GROUP_PAIR_CASE(W_I8)
     CAIFQ_UMMA_GROUP_PAIR_CASE(W_I4)
@@ -1773,21 +1803,21 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
 #define CAIFQ_UMMA_GROUP_CASE(MODE)                                                              \
   if (mode == MODE && bn == 128)                                                                 \
   {                                                                                              \
-    rc = g.backward ? launch_inst<MODE, true, 128, true>(map_a, map_a, map_a, p, gt, s)          \
-                    : launch_inst<MODE, false, 128, true>(map_a, map_a, map_a, p, gt, s);        \
+    rc = g.backward ? launch_inst<MODE, true, 128, true>(map_a, map_a, map_a, map_a, p, gt, s)          \
+                    : launch_inst<MODE, false, 128, true>(map_a, map_a, map_a, map_a, p, gt, s);        \
   }                                                                                              \
   if (mode == MODE && bn == 256)                                                                 \
   {                                                                                              \
-    rc = g.backward ? launch_inst<MODE, true, 256, true>(map_a, map_a, map_a, p, gt, s)          \
-                    : launch_inst<MODE, false, 256, true>(map_a, map_a, map_a, p, gt, s);        \
+    rc = g.backward ? launch_inst<MODE, true, 256, true>(map_a, map_a, map_a, map_a, p, gt, s)          \
+                    : launch_inst<MODE, false, 256, true>(map_a, map_a, map_a, map_a, p, gt, s);        \
   }
     CAIFQ_UMMA_GROUP_CASE(W_I8)
     CAIFQ_UMMA_GROUP_CASE(W_I4)
 #undef CAIFQ_UMMA_GROUP_CASE
     if (mode == W_I4S)
     {
-      rc = g.backward ? launch_inst<W_I4S, true, 128, true>(map_a, map_a, map_a, p, gt, s)
-                      : launch_inst<W_I4S, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+      rc = g.backward ? launch_inst<W_I4S, true, 128, true>(map_a, map_a, map_a, map_a, p, gt, s)
+                      : launch_inst<W_I4S, false, 128, true>(map_a, map_a, map_a, map_a, p, gt, s);
     }
     if (rc != CAIFQ_OK)
     {
@@ -1892,28 +1922,28 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
     {
       if (mode == W_I8)
       {
-        rc = launch_inst<W_I8, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);
+        rc = launch_inst<W_I8, false, 256, true, true>(map_a, map_a, map_a, map_a, p, gt, s);
       }
       else if (mode == W_I4S)
       {
-        rc = launch_inst<W_I4S, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);
+        rc = launch_inst<W_I4S, false, 256, true, true>(map_a, map_a, map_a, map_a, p, gt, s);
       }
       else
       {
-        rc = launch_inst<W_I4, false, 256, true, true>(map_a, map_a, map_a, p, gt, s);
+        rc = launch_inst<W_I4, false, 256, true, true>(map_a, map_a, map_a, map_a, p, gt, s);
       }
     }
     else if (mode == W_I8)
     {
-      rc = launch_inst<W_I8, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+      rc = launch_inst<W_I8, false, 128, true>(map_a, map_a, map_a, map_a, p, gt, s);
     }
     else if (mode == W_I4S)
     {
-      rc = launch_inst<W_I4S, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+      rc = launch_inst<W_I4S, false, 128, true>(map_a, map_a, map_a, map_a, p, gt, s);
     }
     else
     {
-      rc = launch_inst<W_I4, false, 128, true>(map_a, map_a, map_a, p, gt, s);
+      rc = launch_inst<W_I4, false, 128, true>(map_a, map_a, map_a, map_a, p, gt, s);
     }
     if (rc != CAIFQ_OK)
     {

@@ -460,6 +460,89 @@ int launch_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_
   }
 }
 
+// ---- codes -> bf16 operand matrix (many-token LoRA calls expand the weight once per call) ----
+// One thread per 16 bytes of codes.  int8: 16 codes become exact bf16 integers with byte permutes and
+// one bf16 subtraction per pair.  int4: 32 codes times their group's fp16 scale in fp32, rounded once to
+// bf16 -- the value the reference's dequantize kernel followed by its cast to bf16 gives
+// (src/caif_cuda_kernels_quant.cu:364-420, src/caif_device_frozen_linear.cpp:319-334).
+__global__ void expand_int8_to_bf16_kernel(const uint4 *codes, uint4 *dst, int64_t chunks)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
+  {
+    const uint4 v = __ldg(codes + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+    {
+      const uint32_t a = __byte_perm(w[k], 0u, 0x4140);   // [b0, 0, b1, 0]
+      const uint32_t b = __byte_perm(w[k], 0u, 0x4342);   // [b2, 0, b3, 0]
+      // low 7 bits in the mantissa of 128.0; the sign bit selects 128.0 or 256.0 to subtract
+      uint32_t lo, hi;
+      asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
+      asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
+      o[2 * k] = lo;
+      o[2 * k + 1] = hi;
+    }
+    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+__global__ void expand_int4_to_bf16_kernel(const uint4 *codes, const __half *scales, uint4 *dst, int64_t chunks,
+                                           int group_size)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
+  {
+    const uint4 v = __ldg(codes + i);
+    const float scale = __half2float(scales[(i * 32) / group_size]);   // 32 codes lie in one group
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+    {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+      {
+        // byte j of the word: low nibble is the even element, high nibble the odd one
+        const int byte = static_cast<int>((w[k] >> (8 * j)) & 0xFFu);
+        const float e = static_cast<float>((byte & 0xF) >= 8 ? (byte & 0xF) - 16 : (byte & 0xF)) * scale;
+        const float d = static_cast<float>((byte >> 4) >= 8 ? (byte >> 4) - 16 : (byte >> 4)) * scale;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
+      }
+      dst[4 * i + k] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s)
+{
+  const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;
+  if (w.storage == CAIFQ_I8 && (total % 16) == 0)
+  {
+    const int64_t chunks = total / 16;
+    expand_int8_to_bf16_kernel<<<grid_for(chunks), kBlock, 0, s>>>(static_cast<const uint4 *>(w.codes),
+                                                                  static_cast<uint4 *>(dst), chunks);
+  }
+  else if (w.storage == CAIFQ_I4 && (total % 32) == 0 && w.scales != nullptr && w.group_size > 0 &&
+           (w.group_size % 32) == 0)
+  {
+    const int64_t chunks = total / 32;
+    expand_int4_to_bf16_kernel<<<grid_for(chunks), kBlock, 0, s>>>(static_cast<const uint4 *>(w.codes),
+                                                                  static_cast<const __half *>(w.scales),
+                                                                  static_cast<uint4 *>(dst), chunks, w.group_size);
+  }
+  else
+  {
+    set_error("expand_to_bf16: unsupported weight (storage %d)", w.storage);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
 int launch_weight_materialize(const caifq_weight &w, void *dst, int dst_dtype, cudaStream_t s)
 {
   const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;

@@ -70,6 +70,7 @@ _SIGNATURES = {
     "caifq_cast": (ctypes.c_int, [_vp, _i32, _vp, _i32, _i64, _vp]),
     "caifq_weight_materialize": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _vp]),
     "caifq_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_linear_fwd_residual": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_linear_fwd_multi": (ctypes.c_int, [ctypes.POINTER(CWeight), _i32, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_linear_fwd_gather": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, ctypes.POINTER(_vp), _i32,
                                                _i64, _i64, _i32, _i32, _vp]),
@@ -78,6 +79,14 @@ _SIGNATURES = {
     "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
                                              _vp, _i32, _vp]),
     "caifq_lora_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
+    "caifq_lora_fwd_workspace_bytes_expanded": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64,
+                                                                  _i32]),
+    "caifq_lora_bwd_workspace_bytes_expanded": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64,
+                                                                  _i32]),
+    "caifq_lora_linear_fwd_expanded": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp,
+                                                      _vp, _vp, _i32, _vp]),
+    "caifq_lora_linear_bwd_expanded": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _vp, _vp,
+                                                      _i64, _vp, _vp, _vp, _vp, _i32, _vp]),
     "caifq_lora_linear_bwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _vp, _vp, _i64,
                                              _vp, _vp, _vp, _vp, _i32, _vp]),
     "caifq_lora_bwd_noalloc_max_bytes": (ctypes.c_size_t, []),
@@ -273,6 +282,15 @@ def linear_fwd(w, x, out_dtype=torch.float32, compute=F32, out=None):
     return out
 
 
+def linear_fwd_residual(w, x, residual, compute=F32):
+    """residual [m, out] += W-path(x) in place, with the roundings of cast-then-Add; returns residual."""
+    _need_cuda(x, residual)
+    m = x.numel() // w.in_dim
+    _check(lib().caifq_linear_fwd_residual(w.ref(), _ptr(x), dtype_code(x), m, _ptr(residual), dtype_code(residual),
+                                           compute, _stream()), "caifq_linear_fwd_residual")
+    return residual
+
+
 def linear_fwd_multi(ws, x, out_dtype=torch.float32, compute=F32, out=None):
     """Few-token forward of several frozen linears that share x (q/k/v, gate/up) in one launch:
     y[m, sum out_i], weight i's outputs at columns sum_{j<i} out_j."""
@@ -321,25 +339,40 @@ class Lora:
         return ctypes.byref(self.c)
 
 
-def lora_linear_fwd(w, lora, x, compute=F32, out=None, hidden=None, workspace=None):
+def lora_fwd_workspace_bytes(w, lora, m, compute=F32, expanded=False):
+    if expanded:
+        return int(lib().caifq_lora_fwd_workspace_bytes_expanded(w.ref(), lora.ref(), m, compute))
+    return int(lib().caifq_lora_fwd_workspace_bytes(w.ref(), lora.ref(), m))
+
+
+def lora_bwd_workspace_bytes(w, lora, m, compute=F32, expanded=False):
+    if expanded:
+        return int(lib().caifq_lora_bwd_workspace_bytes_expanded(w.ref(), lora.ref(), m, compute))
+    return int(lib().caifq_lora_bwd_workspace_bytes(w.ref(), lora.ref(), m))
+
+
+def lora_linear_fwd(w, lora, x, compute=F32, out=None, hidden=None, workspace=None, expanded=False):
     """y = W-path(x) + (alpha/r) . (x . A^T) . B^T.  `out`, `hidden` and `workspace` (a uint8 tensor of at
-    least caifq_lora_fwd_workspace_bytes) may be passed in to keep the call free of allocations."""
+    least lora_fwd_workspace_bytes) may be passed in to keep the call free of allocations.  expanded=True
+    uses the entry point that may expand the weight once per call into the (larger) workspace."""
     _need_cuda(x)
     m = x.numel() // w.in_dim
     y = out if out is not None else torch.empty(tuple(x.shape[:-1]) + (w.out_dim,), dtype=x.dtype, device=x.device)
     if hidden is None:
         hidden = torch.empty((m, lora.rank), dtype=x.dtype, device=x.device)
-    ws_bytes = int(lib().caifq_lora_fwd_workspace_bytes(w.ref(), lora.ref(), m))
+    ws_bytes = lora_fwd_workspace_bytes(w, lora, m, compute, expanded)
     if workspace is None:
         workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=x.device)
     elif workspace.numel() < ws_bytes:
         raise CaifqError("lora_linear_fwd: workspace of %d bytes, %d needed" % (workspace.numel(), ws_bytes))
-    _check(lib().caifq_lora_linear_fwd(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), _ptr(workspace),
-                                       compute, _stream()), "lora_linear_fwd")
+    fn = lib().caifq_lora_linear_fwd_expanded if expanded else lib().caifq_lora_linear_fwd
+    _check(fn(w.ref(), lora.ref(), _ptr(x), m, _ptr(y), _ptr(hidden), _ptr(workspace), compute, _stream()),
+           "lora_linear_fwd")
     return y, hidden
 
 
-def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32, dx=None, d_a=None, d_b=None, workspace=None):
+def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32, dx=None, d_a=None, d_b=None, workspace=None,
+                    expanded=False):
     _need_cuda(dy, x, hidden)
     m = dy.numel() // w.out_dim
     if dx is None:
@@ -348,13 +381,14 @@ def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32, dx=None, d_a=None, d_b=
         d_a = torch.empty_like(lora.a)
     if d_b is None:
         d_b = torch.empty_like(lora.b)
-    ws_bytes = int(lib().caifq_lora_bwd_workspace_bytes(w.ref(), lora.ref(), m))
+    ws_bytes = lora_bwd_workspace_bytes(w, lora, m, compute, expanded)
     if workspace is None:
         workspace = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dy.device)
     elif workspace.numel() < ws_bytes:
         raise CaifqError("lora_linear_bwd: workspace of %d bytes, %d needed" % (workspace.numel(), ws_bytes))
-    _check(lib().caifq_lora_linear_bwd(w.ref(), lora.ref(), _ptr(dy), _ptr(x), _ptr(hidden), m, _ptr(dx), _ptr(d_a),
-                                       _ptr(d_b), _ptr(workspace), compute, _stream()), "lora_linear_bwd")
+    fn = lib().caifq_lora_linear_bwd_expanded if expanded else lib().caifq_lora_linear_bwd
+    _check(fn(w.ref(), lora.ref(), _ptr(dy), _ptr(x), _ptr(hidden), m, _ptr(dx), _ptr(d_a), _ptr(d_b),
+              _ptr(workspace), compute, _stream()), "lora_linear_bwd")
     return dx, d_a, d_b
 
 
@@ -425,7 +459,9 @@ def moe_dispatch(x, expert_indices, dispatch_map, expert_offsets, total_assigned
     _need_cuda(x, expert_indices, dispatch_map, expert_offsets)
     tokens, dim = x.shape
     top_k = expert_indices.shape[1]
-    buf = torch.zeros((total_assigned, dim), dtype=x.dtype, device=x.device)
+    # every row below expert_offsets[E] is written exactly once; like the reference's layer
+    # (src/caif_device_moe_layer.cpp:457-462, Uninitialized workspaces) the buffer is not cleared first
+    buf = torch.empty((total_assigned, dim), dtype=x.dtype, device=x.device)
     _check(lib().caifq_moe_dispatch(_ptr(x), dtype_code(x), _ptr(expert_indices), _ptr(dispatch_map),
                                     _ptr(expert_offsets), _ptr(buf), tokens, dim, top_k, _stream()), "moe_dispatch")
     return buf
@@ -446,7 +482,7 @@ def moe_combine_bwd_grad_expert(grad_output, expert_indices, weights, dispatch_m
     _need_cuda(grad_output, expert_indices, weights, dispatch_map, expert_offsets)
     tokens, dim = grad_output.shape
     top_k = expert_indices.shape[1]
-    gbuf = torch.zeros((total_assigned, dim), dtype=grad_output.dtype, device=grad_output.device)
+    gbuf = torch.empty((total_assigned, dim), dtype=grad_output.dtype, device=grad_output.device)   # as above (:723-728)
     _check(lib().caifq_moe_combine_bwd_grad_expert(_ptr(grad_output), dtype_code(grad_output), _ptr(expert_indices),
                                                    _ptr(weights), _ptr(dispatch_map), _ptr(expert_offsets),
                                                    _ptr(gbuf), tokens, dim, top_k, _stream()),

@@ -195,6 +195,17 @@ CAIFQ_API int caifq_linear_fwd_gather(const caifq_weight *w, const void *x, int3
                                       int32_t y_dtype, int32_t compute_dtype, void *stream);
 
 /*
+ * ForwardImpl followed by the residual Add of the block that owns the layer
+ * (CAIF_DevicePreNormBlock::ForwardLoop, src/caif_device_pre_norm_block.cpp:116-124: x = x + sub_out) for the
+ * projection that ends a sub-layer (attention's o, the FFN's down): y_inout [m, out] holds the residual
+ * stream on entry and, on return, round(round(x . W_deq^T) + residual), both roundings to y_dtype -- the
+ * value the reference's cast of the projection output followed by CAIF_Ops::Add gives.  The add runs in the
+ * epilogue of the product, so the residual stream is read and written once and no sub_out tensor exists.
+ */
+CAIFQ_API int caifq_linear_fwd_residual(const caifq_weight *w, const void *x, int32_t x_dtype, int64_t m,
+                                        void *y_inout, int32_t y_dtype, int32_t compute_dtype, void *stream);
+
+/*
  * Several frozen linears that share their input, few tokens: the q/k/v projections of an attention
  * block (src/caif_device_multi_head_attention.cpp:544-546) or gate/up of an FFN
  * (src/caif_device_ffn.cpp:324,335), which the reference runs as separate ForwardImpl calls.  One
@@ -243,6 +254,29 @@ CAIFQ_API size_t caifq_lora_bwd_workspace_bytes(const caifq_weight *w, const cai
 CAIFQ_API int caifq_lora_linear_bwd(const caifq_weight *w, const caifq_lora *lora, const void *dy, const void *x,
                           const void *hidden, int64_t m, void *dx, void *d_a, void *d_b, void *workspace,
                           int32_t compute_dtype, void *stream);
+
+/*
+ * The same two calls for hosts that can spare a larger workspace (no counterpart in the reference, whose
+ * cache_fp32 keeps an fp32 copy of every weight for good).  From a few thousand tokens on (m >= 4096, bf16
+ * adapter on an int8 base, or on an int4 base under bf16 compute, in_dim and out_dim multiples of 256) the
+ * weight is expanded ONCE per call into a bf16 [out, in] matrix behind the other scratch -- int8 codes as
+ * exact integers with the per-tensor scale left to the epilogue, int4 as bf16(scale * code), the value the
+ * reference's dequantize-then-cast gives -- and the tensor core is fed from it by plain tile copies on CTA
+ * pairs, instead of every CTA converting every weight tile again for each 256 rows of tokens.  Results: int8
+ * bit-equal to caifq_lora_linear_fwd / _bwd; int4 the reference's own operand (closer to it than the
+ * unexpanded form).  The workspace must hold caifq_lora_*_workspace_bytes_expanded(...) bytes (equal to the
+ * plain size for calls that are not expanded), 256-byte aligned.
+ */
+CAIFQ_API size_t caifq_lora_fwd_workspace_bytes_expanded(const caifq_weight *w, const caifq_lora *lora, int64_t m,
+                                                         int32_t compute_dtype);
+CAIFQ_API int caifq_lora_linear_fwd_expanded(const caifq_weight *w, const caifq_lora *lora, const void *x, int64_t m,
+                                             void *y, void *hidden, void *workspace, int32_t compute_dtype,
+                                             void *stream);
+CAIFQ_API size_t caifq_lora_bwd_workspace_bytes_expanded(const caifq_weight *w, const caifq_lora *lora, int64_t m,
+                                                         int32_t compute_dtype);
+CAIFQ_API int caifq_lora_linear_bwd_expanded(const caifq_weight *w, const caifq_lora *lora, const void *dy,
+                                             const void *x, const void *hidden, int64_t m, void *dx, void *d_a,
+                                             void *d_b, void *workspace, int32_t compute_dtype, void *stream);
 
 /*
  * caifq_lora_linear_bwd for callers that cannot hand over a workspace.

@@ -428,3 +428,29 @@ def test_decode_several_layers_that_share_the_input_in_one_launch(storage, outs,
         nv.linear_fwd_multi(odd, x, torch.float32, orc.F32)
     with pytest.raises(nv.CaifqError):
         nv.linear_fwd_multi(ws, act(rng, 32, in_dim, orc.BF16)[1], torch.float32, orc.F32)
+
+
+@pytest.mark.parametrize("storage,compute,sd,m", [
+    (orc.I4, orc.BF16, orc.BF16, 300),    # tensor-core path, bf16 residual stream
+    (orc.I8, orc.F32, orc.F32, 77),       # tensor-core path, fp32 stream
+    (orc.I4, orc.BF16, orc.BF16, 4),      # few tokens: the accumulate epilogue lives on the other kernels
+    (orc.F16, orc.F16, orc.F16, 20),      # generic kernel
+])
+def test_forward_with_the_residual_add_in_the_epilogue(storage, compute, sd, m):
+    """caifq_linear_fwd_residual: the block's x = x + sub_out with sub_out the projection's output cast to
+    the stream's dtype, computed in the product's epilogue: round(round(y) + residual)."""
+    in_dim, out_dim = 512, 384
+    rng = np.random.default_rng(8800 + storage + m)
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, storage)
+    wc = _oracle_w(weight, codes, scales, compute)
+    x_np, x = act(rng, m, in_dim, sd)
+    res_np, res = act(rng, m, out_dim, sd)
+    got = nv.linear_fwd_residual(weight, x, res.clone(), compute)
+    y = orc.round_through(orc.frozen_linear_forward(x_np, wc, compute), sd)
+    want = orc.round_through(y + res_np, sd)
+    tol = TOL_F32 if compute == orc.F32 else TOL_16
+    assert max_rel_err(got.float().cpu().numpy(), want) <= tol
+    # the same bits as the separate product followed by an add in the stream's dtype
+    sep = nv.linear_fwd(weight, x, TORCH_DTYPE[sd], compute)
+    if nv.last_path() != "decode":     # (the few-token kernel sums in another order than the kernel that accumulates)
+        assert torch.equal(got, (sep.float() + res.float()).to(TORCH_DTYPE[sd]))

@@ -502,3 +502,47 @@ def test_grouped_experts_on_cta_pairs_equal_single_ctas(storage, compute, monkey
         results.append((out, g, u, dx))
     for a, b in zip(*results):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I8, orc.BF16), (orc.I4, orc.BF16),
+                                             (orc.I4, orc.F32)])
+def test_lora_entry_points_that_expand_the_weight_once_per_call(storage, compute):
+    """caifq_lora_linear_fwd_expanded / _bwd_expanded at a many-token size: the weight goes through a bf16
+    copy in the workspace and the CTA-pair tile form.  int8: bit-equal to the plain entry points (exact
+    codes, scale in the epilogue).  int4 under bf16 compute: the reference's own operand bf16(scale * code),
+    so sampled rows hold the tight bound against the oracle.  int4 under fp32 compute is not expanded
+    (same workspace size, same bits)."""
+    m, in_dim, out_dim, rank = 4608, 512, 768, 16
+    rng = np.random.default_rng(9300 + storage + compute)
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, storage, std=0.05)
+    a_np = orc.round_through(rng.uniform(-1 / 16, 1 / 16, (rank, in_dim)).astype(np.float32), orc.BF16)
+    b_np = orc.round_through((rng.standard_normal((out_dim, rank)) * 0.05).astype(np.float32), orc.BF16)
+    lora = nv.Lora(to_dev(a_np, torch.bfloat16), to_dev(b_np, torch.bfloat16), 32.0)
+    x_np, x = act(rng, m, in_dim, orc.BF16)
+    dy_np, dy = act(rng, m, out_dim, orc.BF16)
+    plain_f = nv.lora_fwd_workspace_bytes(weight, lora, m, compute)
+    big_f = nv.lora_fwd_workspace_bytes(weight, lora, m, compute, expanded=True)
+    expands = not (storage == orc.I4 and compute == orc.F32)
+    assert big_f == plain_f + (in_dim * out_dim * 2 if expands else 0)
+    y0, h0 = nv.lora_linear_fwd(weight, lora, x, compute)
+    dx0, da0, db0 = nv.lora_linear_bwd(weight, lora, dy, x, h0, compute)
+    y1, h1 = nv.lora_linear_fwd(weight, lora, x, compute, expanded=True)
+    dx1, da1, db1 = nv.lora_linear_bwd(weight, lora, dy, x, h1, compute, expanded=True)
+    assert nv.lib().caifq_device_status() == 0
+    assert torch.equal(h0, h1)
+    # (dA and dB are token reductions with fp32 atomics: the same kernels in both calls, equal up to the order)
+    assert max_rel_err(da1.float().cpu().numpy(), da0.float().cpu().numpy()) <= 1e-2
+    assert max_rel_err(db1.float().cpu().numpy(), db0.float().cpu().numpy()) <= 1e-2
+    if storage == orc.I8 or not expands:
+        assert torch.equal(y0, y1) and torch.equal(dx0, dx1)
+    rows = np.r_[0:16, m - 16:m]
+    wc = orc.weight_to_compute(codes, scales, storage, in_dim, out_dim, compute, weight.scheme, weight.group_size)
+    base = orc.frozen_linear_forward(x_np[rows], wc, compute)
+    want_y, hid = orc.lora_forward(x_np[rows], base, a_np, b_np, 32.0, orc.BF16)
+    tol = 1e-2    # results are stored in bf16: one rounding of the output
+    assert max_rel_err(y1[rows].float().cpu().numpy(), want_y) <= tol
+    assert max_rel_err(y0[rows].float().cpu().numpy(), want_y) <= tol
+    # dx of the sampled rows (dA / dB need all rows and are equal to the plain entry point's, checked above)
+    base_dx = orc.frozen_linear_backward(dy_np[rows], wc, compute)
+    want_dx, _, _ = orc.lora_backward(dy_np[rows], x_np[rows], hid, base_dx, a_np, b_np, 32.0, orc.BF16)
+    assert max_rel_err(dx1[rows].float().cpu().numpy(), want_dx) <= 2e-2
