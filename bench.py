@@ -870,6 +870,10 @@ class _NativeMoeOps:
         self.num_experts = num_experts
         self.compute = compute
         self.saved = None
+        # scratch for the bf16 copies of this rank's experts, filled once per step (in the forward pass, inside
+        # the timed step) and read by the grouped launches of forward and backward
+        nbytes = nv.grouped_expert_expanded_bytes(gate, up, down, nv.BF16, compute)
+        self.expanded = torch.empty(nbytes, dtype=torch.uint8, device=up[0].codes.device) if nbytes > 0 else None
 
     def build_dispatch(self, idx):
         return self.nv.moe_build_dispatch(idx, self.num_experts, 0)
@@ -879,15 +883,17 @@ class _NativeMoeOps:
 
     def experts(self, packed, local_offsets):
         offs = [int(v) for v in local_offsets]
+        if self.expanded is not None:
+            self.nv.grouped_expert_expand(self.gate, self.up, self.down, self.expanded, self.nv.BF16, self.compute)
         out, g_out, u_out = self.nv.grouped_expert_fwd(self.gate, self.up, self.down, offs, packed,
-                                                       compute=self.compute)
+                                                       compute=self.compute, expanded=self.expanded)
         self.saved = (offs, g_out, u_out)
         return out
 
     def experts_bwd(self, packed_dy, local_offsets):
         offs, g_out, u_out = self.saved
         return self.nv.grouped_expert_bwd(self.gate, self.up, self.down, offs, packed_dy, g_out, u_out,
-                                          compute=self.compute)
+                                          compute=self.compute, expanded=self.expanded)
 
     def combine(self, buf, idx, wts, dmap, offsets, tokens):
         return self.nv.moe_combine(buf, idx, wts, dmap, offsets, tokens)

@@ -6,6 +6,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -112,6 +113,10 @@ size_t gemm_tn_scratch_bytes(int p, int q);
 int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
                    float u_prescale, int64_t m, int p, int q, cudaStream_t s);
 int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
+int launch_lora_adamw(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a, float *m_b,
+                      float *v_b, int64_t n_a, int64_t n_b, int dtype, float lr, float beta1, float beta2,
+                      float epsilon, float weight_decay, float bias_correction1, float bias_correction2,
+                      cudaStream_t s);
 bool skinny_supported(int dtype, int rank, int k);
 int launch_skinny_nt(const void *x, const void *a, void *h, void *hs, float x_prescale, float hs_mul,
                      const float *hs_div, int64_t m, int k, int rank, cudaStream_t s);
@@ -945,6 +950,21 @@ int caifq_moe_router_softmax(const void *logits, const void *bias, void *probs, 
   return launch_moe_router_softmax(logits, bias, probs, dtype, rows, cols, static_cast<cudaStream_t>(stream));
 }
 
+int caifq_lora_adamw_step(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a, float *m_b,
+                          float *v_b, int32_t rank, int32_t in_dim, int32_t out_dim, int32_t dtype, float lr,
+                          float beta1, float beta2, float epsilon, float weight_decay, float bias_correction1,
+                          float bias_correction2, void *stream)
+{
+  const char *who = "caifq_lora_adamw_step";
+  CAIFQ_CHECK_ARG(rank > 0 && in_dim > 0 && out_dim > 0, "%s: bad shape", who);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(a && b && d_a && d_b && m_a && v_a && m_b && v_b, "%s: null pointer", who);
+  CAIFQ_CHECK_ARG(bias_correction1 != 0.0f && bias_correction2 != 0.0f, "%s: zero bias correction", who);
+  return launch_lora_adamw(a, b, d_a, d_b, m_a, v_a, m_b, v_b, static_cast<int64_t>(rank) * in_dim,
+                           static_cast<int64_t>(out_dim) * rank, dtype, lr, beta1, beta2, epsilon, weight_decay,
+                           bias_correction1, bias_correction2, static_cast<cudaStream_t>(stream));
+}
+
 int caifq_scale(const void *src, void *dst, int32_t dtype, float factor, int64_t n, void *stream)
 {
   CAIFQ_CHECK_ARG(n >= 0, "caifq_scale: negative n");
@@ -1246,6 +1266,221 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
     return r;
   }
   return grouped_linear(gate, num_experts, expert_offsets_host, true, g_gate, dx, dtype, true, compute_dtype, s, who);
+}
+
+}  // extern "C"
+
+// ---- frozen experts on bf16 copies of their weights, expanded once per step -----------------------
+
+namespace
+{
+struct ExpandedExperts
+{
+  bool ok;
+  size_t up_off, down_off, gate_off, total;
+};
+
+// Experts of one quantized shape on bf16 rows whose products the grouped tensor-core launches take.
+ExpandedExperts expanded_layout(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                                int num_experts, int dtype, int compute_dtype)
+{
+  ExpandedExperts l{};
+  l.ok = false;
+  if (up == nullptr || down == nullptr || num_experts < 1 || dtype != CAIFQ_BF16)
+  {
+    return l;
+  }
+  const caifq_weight &u0 = up[0];
+  const caifq_weight &d0 = down[0];
+  const bool i8 = (u0.storage == CAIFQ_I8);
+  if (!(i8 && (compute_dtype == CAIFQ_BF16 || compute_dtype == CAIFQ_F32)) &&
+      !(u0.storage == CAIFQ_I4 && compute_dtype == CAIFQ_BF16))
+  {
+    return l;
+  }
+  if ((u0.in_dim % 128) != 0 || (u0.out_dim % 128) != 0)
+  {
+    return l;
+  }
+  for (int e = 0; e < num_experts; ++e)
+  {
+    const caifq_weight *set[3] = {&up[e], &down[e], gate != nullptr ? &gate[e] : nullptr};
+    for (int k = 0; k < 3; ++k)
+    {
+      const caifq_weight *w = set[k];
+      if (w == nullptr)
+      {
+        continue;
+      }
+      const caifq_weight &r = (k == 1) ? d0 : u0;
+      if (w->storage != u0.storage || w->scheme != u0.scheme || w->group_size != u0.group_size ||
+          w->in_dim != r.in_dim || w->out_dim != r.out_dim || (reinterpret_cast<uintptr_t>(w->codes) & 15u) != 0 ||
+          (i8 && w->scales != nullptr && w->scheme != CAIFQ_PER_TENSOR) || (!i8 && w->scales == nullptr) ||
+          (!i8 && (w->group_size % 32 != 0 || w->in_dim % w->group_size != 0)))
+      {
+        return l;
+      }
+    }
+  }
+  const size_t one = align256(static_cast<size_t>(u0.in_dim) * static_cast<size_t>(u0.out_dim) * 2 * num_experts);
+  l.up_off = 0;
+  l.down_off = one;
+  l.gate_off = 2 * one;
+  l.total = (gate != nullptr ? 3 : 2) * one;
+  l.ok = true;
+  return l;
+}
+
+// bf16 views of the expanded copies; an int8 expert's per-tensor scale rides in `scales` for the epilogue
+void expanded_views(const caifq_weight *src, int num_experts, const char *base, std::vector<caifq_weight> &out)
+{
+  out.resize(static_cast<size_t>(num_experts));
+  const size_t stride = static_cast<size_t>(src[0].in_dim) * static_cast<size_t>(src[0].out_dim) * 2;
+  for (int e = 0; e < num_experts; ++e)
+  {
+    caifq_weight w{};
+    w.codes = base + static_cast<size_t>(e) * stride;
+    w.scales = (src[e].storage == CAIFQ_I8) ? src[e].scales : nullptr;
+    w.storage = CAIFQ_BF16;
+    w.scheme = CAIFQ_PER_TENSOR;
+    w.group_size = src[e].group_size;
+    w.in_dim = src[e].in_dim;
+    w.out_dim = src[e].out_dim;
+    out[static_cast<size_t>(e)] = w;
+  }
+}
+
+// every product of the step must be a grouped tensor-core launch on the views (the per-expert loop would not
+// know about the scale riding in `scales`)
+bool views_supported(const std::vector<caifq_weight> &ws, int num_experts, const int32_t *offsets, bool backward,
+                     const void *a, void *c, bool accumulate, int compute_dtype)
+{
+  GroupedLinearArgs g{};
+  g.weights = ws.data();
+  g.num_experts = num_experts;
+  g.offsets = offsets;
+  g.backward = backward;
+  g.a = a;
+  g.a_dtype = CAIFQ_BF16;
+  g.c = c;
+  g.c_dtype = CAIFQ_BF16;
+  g.accumulate = accumulate;
+  g.compute_dtype = compute_dtype;
+  return forced_path() == Force::None && umma_grouped_supported(g);
+}
+}  // namespace
+
+extern "C" {
+
+size_t caifq_grouped_expert_expanded_bytes(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                                           int32_t num_experts, int32_t dtype, int32_t compute_dtype)
+{
+  const ExpandedExperts l = expanded_layout(gate, up, down, num_experts, dtype, compute_dtype);
+  return l.ok ? l.total : 0;
+}
+
+int caifq_grouped_expert_expand(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                                int32_t num_experts, void *expanded, int32_t dtype, int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_grouped_expert_expand";
+  const ExpandedExperts l = expanded_layout(gate, up, down, num_experts, dtype, compute_dtype);
+  if (!l.ok)
+  {
+    set_error("%s: these experts are not expanded (caifq_grouped_expert_expanded_bytes is 0)", who);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  CAIFQ_CHECK_ARG(expanded != nullptr && (reinterpret_cast<uintptr_t>(expanded) & 255u) == 0,
+                  "%s: the buffer must be 256-byte aligned", who);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char *base = static_cast<char *>(expanded);
+  int r = launch_expand_grouped_to_bf16(up, num_experts, base + l.up_off, s);
+  if (r == CAIFQ_OK)
+  {
+    r = launch_expand_grouped_to_bf16(down, num_experts, base + l.down_off, s);
+  }
+  if (r == CAIFQ_OK && gate != nullptr)
+  {
+    r = launch_expand_grouped_to_bf16(gate, num_experts, base + l.gate_off, s);
+  }
+  return r;
+}
+
+int caifq_grouped_expert_fwd_expanded(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                                      int32_t num_experts, const int32_t *expert_offsets_host, const void *x, void *out,
+                                      void *gate_out, void *up_out, void *hidden_ws, const void *expanded,
+                                      int32_t dtype, int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_grouped_expert_fwd_expanded";
+  const int rc = check_experts(gate, up, down, num_experts, expert_offsets_host, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  const ExpandedExperts l = expanded_layout(gate, up, down, num_experts, dtype, compute_dtype);
+  if (l.ok && expanded != nullptr && x != nullptr && out != nullptr && hidden_ws != nullptr && up_out != nullptr)
+  {
+    const char *base = static_cast<const char *>(expanded);
+    std::vector<caifq_weight> vu, vd, vg;
+    expanded_views(up, num_experts, base + l.up_off, vu);
+    expanded_views(down, num_experts, base + l.down_off, vd);
+    if (gate != nullptr)
+    {
+      expanded_views(gate, num_experts, base + l.gate_off, vg);
+    }
+    bool ok = views_supported(vu, num_experts, expert_offsets_host, false, x, up_out, false, compute_dtype) &&
+              views_supported(vd, num_experts, expert_offsets_host, false, hidden_ws, out, false, compute_dtype);
+    if (ok && gate != nullptr)
+    {
+      ok = gate_out != nullptr &&
+           views_supported(vg, num_experts, expert_offsets_host, false, x, gate_out, false, compute_dtype);
+    }
+    if (ok)
+    {
+      return caifq_grouped_expert_fwd(gate != nullptr ? vg.data() : nullptr, vu.data(), vd.data(), num_experts,
+                                      expert_offsets_host, x, out, gate_out, up_out, hidden_ws, dtype, compute_dtype,
+                                      stream);
+    }
+  }
+  return caifq_grouped_expert_fwd(gate, up, down, num_experts, expert_offsets_host, x, out, gate_out, up_out, hidden_ws,
+                                  dtype, compute_dtype, stream);
+}
+
+int caifq_grouped_expert_bwd_expanded(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                                      int32_t num_experts, const int32_t *expert_offsets_host, const void *dy,
+                                      const void *gate_out, const void *up_out, void *dx, void *ws,
+                                      const void *expanded, int32_t dtype, int32_t compute_dtype, void *stream)
+{
+  const char *who = "caifq_grouped_expert_bwd_expanded";
+  const int rc = check_experts(gate, up, down, num_experts, expert_offsets_host, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  const ExpandedExperts l = expanded_layout(gate, up, down, num_experts, dtype, compute_dtype);
+  if (l.ok && expanded != nullptr && dy != nullptr && dx != nullptr && ws != nullptr)
+  {
+    const char *base = static_cast<const char *>(expanded);
+    std::vector<caifq_weight> vu, vd, vg;
+    expanded_views(up, num_experts, base + l.up_off, vu);
+    expanded_views(down, num_experts, base + l.down_off, vd);
+    if (gate != nullptr)
+    {
+      expanded_views(gate, num_experts, base + l.gate_off, vg);
+    }
+    bool ok = views_supported(vd, num_experts, expert_offsets_host, true, dy, ws, false, compute_dtype) &&
+              views_supported(vu, num_experts, expert_offsets_host, true, ws, dx, false, compute_dtype);
+    if (ok && gate != nullptr)
+    {
+      ok = views_supported(vg, num_experts, expert_offsets_host, true, ws, dx, true, compute_dtype);
+    }
+    if (ok)
+    {
+      return caifq_grouped_expert_bwd(gate != nullptr ? vg.data() : nullptr, vu.data(), vd.data(), num_experts,
+                                      expert_offsets_host, dy, gate_out, up_out, dx, ws, dtype, compute_dtype, stream);
+    }
+  }
+  return caifq_grouped_expert_bwd(gate, up, down, num_experts, expert_offsets_host, dy, gate_out, up_out, dx, ws, dtype,
+                                  compute_dtype, stream);
 }
 
 }  // extern "C"

@@ -456,6 +456,7 @@ struct UmmaParams
   int num_n_tiles;
   const uint8_t *lora_rhs;  // null = no LoRA k-block
   const float *c_scale;     // bf16 weights only: factor of the fp32 accumulator in the epilogue (null = 1)
+  int expert_rows;          // grouped bf16 weights: rows of one expert's matrix in the stacked [E * rows, in] matrix
   // Fused gate/up/SwiGLU forward of a frozen expert (forward, 128-wide tiles, 16-bit outputs): a tile's
   // columns 0..63 are features [64 j, 64 j + 64) of the gate projection, columns 64..127 the same
   // features of the up projection.  c receives gate(x), c_up up(x), c_hidden silu(gate(x)) * up(x),
@@ -504,6 +505,7 @@ struct GroupSel<true>
 // What a tile of the schedule works on.
 struct TileWork
 {
+  int expert;        // grouped mode: index of the expert inside this launch's table
   int n_tile;
   int64_t row0;      // first activation / output row of the tile
   int64_t row_end;   // rows at or beyond this one belong to somebody else
@@ -522,6 +524,7 @@ __device__ __forceinline__ TileWork locate_tile<false>(int tile, const UmmaParam
   // column tiles fastest: the CTAs running at one time share a few row tiles of the activations
   // (read from memory once) and sweep the weight, which stays in L2
   TileWork t;
+  t.expert = 0;
   t.n_tile = tile % p.num_n_tiles;
   t.row0 = static_cast<int64_t>(tile / p.num_n_tiles) * BM;
   t.row_end = p.m;
@@ -551,6 +554,7 @@ __device__ __forceinline__ TileWork locate_tile<true>(int tile, const UmmaParams
     }
   }
   TileWork t;
+  t.expert = lo;
   t.n_tile = tile % p.num_n_tiles;
   t.row0 = static_cast<int64_t>(gt.offsets[lo]) + static_cast<int64_t>(mt - gt.mtile_start[lo]) * BM;
   t.row_end = gt.offsets[lo + 1];
@@ -729,18 +733,35 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // the LoRA k-block (number num_kb) takes its weight-side operand, the padded factor, from map_l
             const CUtensorMap *bmap = (kb < num_kb) ? &map_b : &map_l;
             const int kc = (kb < num_kb) ? kb * BK : 0;
-            if (BWD)
+            // grouped: the experts' matrices lie stacked in one [E * rows, in] matrix
+            const int erow = GROUPED ? tw.expert * p.expert_rows : 0;
+            if (!BWD && p.swiglu)
+            {
+              // HALF features of the gate projection (map_b) and the same features of the up projection (map_l)
+              constexpr int HALF = BN / 2;
+              const int f0 = erow + n_tile * HALF;
+              if (PAIR)
+              {
+                load(b_addr(s), (rank == 0) ? &map_b : &map_l, kc, f0, b_full(s));
+              }
+              else
+              {
+                load(b_addr(s), &map_b, kc, f0, b_full(s));
+                load(b_addr(s) + static_cast<uint32_t>(HALF) * 128u, &map_l, kc, f0, b_full(s));
+              }
+            }
+            else if (BWD)
             {
               // [k rows][n cols]: boxes of 64 n x 64 k land as the MN-major blocks
 #pragma unroll
               for (int nb = 0; nb < BNC / 64; ++nb)
               {
-                load(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, bmap, nc0 + nb * 64, kc, b_full(s));
+                load(b_addr(s) + static_cast<uint32_t>(nb) * 8192u, bmap, nc0 + nb * 64, erow + kc, b_full(s));
               }
             }
             else
             {
-              load(b_addr(s), bmap, kc, nc0, b_full(s));
+              load(b_addr(s), bmap, kc, erow + nc0, b_full(s));
             }
           }
           if (++s == STAGES)
@@ -850,8 +871,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const TileWork tw = locate_tile<GROUPED>(tile, p, gt);
       const int n_tile = tw.n_tile;
       float out_scale = 1.0f;
-      if (WMODE == W_I8 && tw.scales != nullptr)
+      if ((WMODE == W_I8 || (WMODE == W_BF16 && GROUPED)) && tw.scales != nullptr)
       {
+        // (grouped bf16 weights: expanded int8 codes, whose per-tensor scale the table still carries)
         out_scale = __ldg(static_cast<const float *>(tw.scales));
       }
       if (WMODE == W_BF16 && p.c_scale != nullptr)
@@ -864,7 +886,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       {
         constexpr int HALF = BN / 2;   // features of each projection in a tile
         float up_scale = 1.0f;
-        if (WMODE == W_I8 && tw.scales_up != nullptr)
+        if ((WMODE == W_I8 || (WMODE == W_BF16 && GROUPED)) && tw.scales_up != nullptr)
         {
           up_scale = __ldg(static_cast<const float *>(tw.scales_up));
         }
@@ -1693,9 +1715,22 @@ bool umma_grouped_supported(const GroupedLinearArgs &g)
     return false;
   }
   const caifq_weight &w0 = g.weights[0];
-  if (w0.storage != CAIFQ_I8 && w0.storage != CAIFQ_I4)
+  if (w0.storage != CAIFQ_I8 && w0.storage != CAIFQ_I4 && w0.storage != CAIFQ_BF16)
   {
     return false;
+  }
+  if (w0.storage == CAIFQ_BF16)
+  {
+    // bf16 experts (expanded copies) are fed by tile copies from ONE tensor map: their matrices must lie
+    // stacked, expert e at e * out * in elements behind expert 0
+    const size_t stride = static_cast<size_t>(w0.in_dim) * static_cast<size_t>(w0.out_dim) * 2;
+    for (int e = 0; e < g.num_experts; ++e)
+    {
+      if (static_cast<const char *>(g.weights[e].codes) != static_cast<const char *>(w0.codes) + e * stride)
+      {
+        return false;
+      }
+    }
   }
   LinearArgs probe{};
   probe.w = w0;
@@ -1775,6 +1810,36 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     // (an accumulating epilogue reads the output first: with 128-wide tiles it overlaps the next tile)
     // (pairs keep two accumulator sets at 256 columns, so the accumulating epilogue and the two-plane mode
     // can have the wide tile there)
+    if (mode == W_BF16)
+    {
+      // stacked bf16 experts: one map over [count * out, in]; pairs when the width allows, else 128-wide tiles
+      const bool wide = (p.n_total % 256) == 0 && static_cast<int64_t>(tiles) * (p.n_total / 256) >= pair_count_umma() &&
+                        pairs_enabled(mode);
+      p.num_n_tiles = p.n_total / (wide ? 256 : 128);
+      p.expert_rows = w0.out_dim;
+      CUtensorMap map_b;
+      rc = make_map_bf16(&map_b, g.weights[first].codes, static_cast<uint64_t>(w0.in_dim),
+                         static_cast<uint64_t>(count) * static_cast<uint64_t>(w0.out_dim), g.backward ? BK : 128);
+      if (rc != CAIFQ_OK)
+      {
+        return rc;
+      }
+      if (wide)
+      {
+        rc = g.backward ? launch_inst<W_BF16, true, 256, true, true>(map_a, map_b, map_a, map_b, p, gt, s)
+                        : launch_inst<W_BF16, false, 256, true, true>(map_a, map_b, map_a, map_b, p, gt, s);
+      }
+      else
+      {
+        rc = g.backward ? launch_inst<W_BF16, true, 128, true>(map_a, map_b, map_a, map_b, p, gt, s)
+                        : launch_inst<W_BF16, false, 128, true>(map_a, map_b, map_a, map_b, p, gt, s);
+      }
+      if (rc != CAIFQ_OK)
+      {
+        return rc;
+      }
+      continue;
+    }
     const bool pair = pairs_enabled(mode) && (p.n_total % 256) == 0 &&
                       static_cast<int64_t>(tiles) * (p.n_total / 256) >= pair_count_umma();
     const int bn = (pair || (mode != W_I4S && !g.accumulate && (p.n_total % 256) == 0 &&
@@ -1918,7 +1983,25 @@ int launch_linear_umma_swiglu(const GroupedSwigluArgs &g, cudaStream_t s)
     const bool pair = pairs_enabled(mode) && (w0.out_dim % 128) == 0 &&
                       static_cast<int64_t>(tiles) * (w0.out_dim / 128) >= pair_count_umma();
     p.num_n_tiles = w0.out_dim / (pair ? 128 : 64);
-    if (pair)
+    if (mode == W_BF16)
+    {
+      p.expert_rows = w0.out_dim;
+      CUtensorMap map_g;
+      CUtensorMap map_u;
+      const uint64_t rows = static_cast<uint64_t>(count) * static_cast<uint64_t>(w0.out_dim);
+      rc = make_map_bf16(&map_g, g.gate[first].codes, static_cast<uint64_t>(w0.in_dim), rows, pair ? 128 : 64);
+      if (rc == CAIFQ_OK)
+      {
+        rc = make_map_bf16(&map_u, g.up[first].codes, static_cast<uint64_t>(w0.in_dim), rows, pair ? 128 : 64);
+      }
+      if (rc != CAIFQ_OK)
+      {
+        return rc;
+      }
+      rc = pair ? launch_inst<W_BF16, false, 256, true, true>(map_a, map_g, map_a, map_u, p, gt, s)
+                : launch_inst<W_BF16, false, 128, true>(map_a, map_g, map_a, map_u, p, gt, s);
+    }
+    else if (pair)
     {
       if (mode == W_I8)
       {

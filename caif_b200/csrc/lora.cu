@@ -4,6 +4,8 @@
 // (CAIF_Ops::MatMulTransposeA with beta = 0: the destination is overwritten),
 // and the in-place Scale.  Operands are read in the adapter's storage dtype,
 // products accumulate in fp32, the result is rounded once to the storage dtype.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace caifq
@@ -569,6 +571,90 @@ int launch_lora_pad_a(const void *a, void *ap, int n, int rank, cudaStream_t s)
 {
   lora_pad_a_kernel<<<148 * 2, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(a), static_cast<__nv_bfloat16 *>(ap), n,
                                            rank);
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+// AdamW step of the two LoRA factors in one launch (the reference steps every parameter tensor with its own
+// launch of fused_adam_kernel, src/caif_cuda_kernels_optimizers.cu:49-92).  Same arithmetic in the same
+// order, all in fp32 with fp32 moments; only the loads and stores of the factors and their gradients cross
+// to the storage dtype.
+struct AdamwParams
+{
+  void *param[2];
+  const void *grad[2];
+  float *m[2];
+  float *v[2];
+  int64_t n[2];
+  int dtype;
+  float lr, beta1, beta2, epsilon, weight_decay, bias_correction1, bias_correction2;
+};
+
+__global__ void lora_adamw_kernel(const AdamwParams a)
+{
+  const int64_t total = a.n[0] + a.n[1];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+  {
+    const int t = (i < a.n[0]) ? 0 : 1;
+    const int64_t idx = (t == 0) ? i : i - a.n[0];
+    float p = load_as_float(a.param[t], idx, a.dtype);
+    const float g = load_as_float(a.grad[t], idx, a.dtype);
+    float m_val = a.m[t][idx];
+    float v_val = a.v[t][idx];
+    if (a.weight_decay != 0.0f)
+    {
+      p = p * (1.0f - a.lr * a.weight_decay);
+    }
+    // The reference's expressions beta1*m + (1-beta1)*g and beta2*v + (1-beta2)*g*g compile to one multiply and
+    // one fused multiply-add each; which product is fused decides the last bit.  Written out so that this
+    // kernel does not depend on the compiler making the same choice (checked bit for bit against the
+    // reference kernel): the gradient term is the fused one.
+    m_val = fmaf(__fsub_rn(1.0f, a.beta1), g, __fmul_rn(a.beta1, m_val));
+    v_val = fmaf(__fmul_rn(__fsub_rn(1.0f, a.beta2), g), g, __fmul_rn(a.beta2, v_val));
+    const float m_hat = m_val / a.bias_correction1;
+    const float v_hat = v_val / a.bias_correction2;
+    p = p - a.lr * m_hat / (sqrtf(v_hat) + a.epsilon);
+    store_from_float(a.param[t], idx, a.dtype, p);
+    a.m[t][idx] = m_val;
+    a.v[t][idx] = v_val;
+  }
+}
+
+int launch_lora_adamw(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a, float *m_b,
+                      float *v_b, int64_t n_a, int64_t n_b, int dtype, float lr, float beta1, float beta2,
+                      float epsilon, float weight_decay, float bias_correction1, float bias_correction2,
+                      cudaStream_t s)
+{
+  AdamwParams p{};
+  p.param[0] = a;
+  p.param[1] = b;
+  p.grad[0] = d_a;
+  p.grad[1] = d_b;
+  p.m[0] = m_a;
+  p.m[1] = m_b;
+  p.v[0] = v_a;
+  p.v[1] = v_b;
+  p.n[0] = n_a;
+  p.n[1] = n_b;
+  p.dtype = dtype;
+  p.lr = lr;
+  p.beta1 = beta1;
+  p.beta2 = beta2;
+  p.epsilon = epsilon;
+  p.weight_decay = weight_decay;
+  p.bias_correction1 = bias_correction1;
+  p.bias_correction2 = bias_correction2;
+  int64_t g = (n_a + n_b + 255) / 256;
+  if (g > 148 * 8)
+  {
+    g = 148 * 8;
+  }
+  if (g < 1)
+  {
+    return CAIFQ_OK;
+  }
+  lora_adamw_kernel<<<static_cast<unsigned>(g), 256, 0, s>>>(p);
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

@@ -517,6 +517,122 @@ __global__ void expand_int4_to_bf16_kernel(const uint4 *codes, const __half *sca
   }
 }
 
+// The same for a run of experts of one shape in ONE launch: expert e's matrix goes to dst + e * out * in
+// elements, so the copies lie stacked as one [E * out, in] matrix.
+constexpr int kExpandGroup = 64;
+struct ExpandTable
+{
+  const uint4 *codes[kExpandGroup];
+  const __half *scales[kExpandGroup];
+};
+
+__device__ __forceinline__ void expand_int8_chunk(const uint4 v, uint4 *dst)
+{
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+  {
+    const uint32_t a = __byte_perm(w[k], 0u, 0x4140);
+    const uint32_t b = __byte_perm(w[k], 0u, 0x4342);
+    uint32_t lo, hi;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
+    o[2 * k] = lo;
+    o[2 * k + 1] = hi;
+  }
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+__device__ __forceinline__ void expand_int4_chunk(const uint4 v, const float scale, uint4 *dst)
+{
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+  {
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+      const int byte = static_cast<int>((w[k] >> (8 * j)) & 0xFFu);
+      const float e = __fmul_rn(static_cast<float>((byte & 0xF) >= 8 ? (byte & 0xF) - 16 : (byte & 0xF)), scale);
+      const float d = __fmul_rn(static_cast<float>((byte >> 4) >= 8 ? (byte >> 4) - 16 : (byte >> 4)), scale);
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
+    }
+    dst[k] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <int STORAGE>
+__global__ void expand_grouped_kernel(const __grid_constant__ ExpandTable t, uint4 *dst, int64_t chunks, int group_size)
+{
+  const int e = blockIdx.y;
+  const uint4 *codes = t.codes[e];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  constexpr int OUT = (STORAGE == CAIFQ_I8) ? 2 : 4;   // 16-byte pieces of bf16 per 16 bytes of codes
+  uint4 *out = dst + static_cast<int64_t>(e) * chunks * OUT;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
+  {
+    const uint4 v = __ldg(codes + i);
+    if (STORAGE == CAIFQ_I8)
+    {
+      expand_int8_chunk(v, out + 2 * i);
+    }
+    else
+    {
+      expand_int4_chunk(v, __half2float(t.scales[e][(i * 32) / group_size]), out + 4 * i);
+    }
+  }
+}
+
+int launch_expand_grouped_to_bf16(const caifq_weight *ws, int count, void *dst, cudaStream_t s)
+{
+  const caifq_weight &w0 = ws[0];
+  const int64_t total = static_cast<int64_t>(w0.in_dim) * w0.out_dim;
+  const bool i8 = (w0.storage == CAIFQ_I8);
+  if (!(i8 && (total % 16) == 0) &&
+      !(w0.storage == CAIFQ_I4 && (total % 32) == 0 && w0.group_size > 0 && (w0.group_size % 32) == 0))
+  {
+    set_error("expand_grouped_to_bf16: unsupported weight (storage %d)", w0.storage);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  const int64_t chunks = total / (i8 ? 16 : 32);
+  for (int first = 0; first < count; first += kExpandGroup)
+  {
+    const int n = (count - first < kExpandGroup) ? (count - first) : kExpandGroup;
+    ExpandTable t{};
+    for (int e = 0; e < n; ++e)
+    {
+      t.codes[e] = static_cast<const uint4 *>(ws[first + e].codes);
+      t.scales[e] = static_cast<const __half *>(ws[first + e].scales);
+      if (!i8 && t.scales[e] == nullptr)
+      {
+        set_error("expand_grouped_to_bf16: int4 expert %d has no scales", first + e);
+        return CAIFQ_ERR_INVALID;
+      }
+    }
+    int gx = grid_for(chunks);
+    const int cap = (148 * 8 + n - 1) / n;   // about eight CTAs per SM over all experts
+    if (gx > cap)
+    {
+      gx = cap;
+    }
+    uint4 *out = static_cast<uint4 *>(dst) + static_cast<int64_t>(first) * total / 8;
+    const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(n));
+    if (i8)
+    {
+      expand_grouped_kernel<CAIFQ_I8><<<grid, kBlock, 0, s>>>(t, out, chunks, 0);
+    }
+    else
+    {
+      expand_grouped_kernel<CAIFQ_I4><<<grid, kBlock, 0, s>>>(t, out, chunks, w0.group_size);
+    }
+    CAIFQ_CHECK_LAUNCH();
+  }
+  return CAIFQ_OK;
+}
+
 int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s)
 {
   const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;

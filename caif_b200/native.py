@@ -78,6 +78,9 @@ _SIGNATURES = {
     "caifq_lora_fwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
                                              _vp, _i32, _vp]),
+    "caifq_lora_adamw_step": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
+                                             ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+                                             ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
     "caifq_lora_bwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_fwd_workspace_bytes_expanded": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64,
                                                                   _i32]),
@@ -106,6 +109,16 @@ _SIGNATURES = {
     "caifq_linear_dx_sharded": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _vp, _i32, _i32, _i32,
                                                _vp, _vp]),
     "caifq_rows_all_to_all": (ctypes.c_int, [_vp, ctypes.POINTER(_i64), _vp, ctypes.POINTER(_i64), _i64, _vp, _vp]),
+    "caifq_grouped_expert_expanded_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
+                                                              ctypes.POINTER(CWeight), _i32, _i32, _i32]),
+    "caifq_grouped_expert_expand": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
+                                                   ctypes.POINTER(CWeight), _i32, _vp, _i32, _i32, _vp]),
+    "caifq_grouped_expert_fwd_expanded": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
+                                                         ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp,
+                                                         _vp, _vp, _vp, _vp, _i32, _i32, _vp]),
+    "caifq_grouped_expert_bwd_expanded": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
+                                                         ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp,
+                                                         _vp, _vp, _vp, _vp, _i32, _i32, _vp]),
     "caifq_grouped_expert_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CWeight),
                                                 ctypes.POINTER(CWeight), _i32, ctypes.POINTER(_i32), _vp, _vp, _vp,
                                                 _vp, _vp, _i32, _i32, _vp]),
@@ -392,6 +405,20 @@ def lora_linear_bwd(w, lora, dy, x, hidden, compute=F32, dx=None, d_a=None, d_b=
     return dx, d_a, d_b
 
 
+def lora_adamw_step(lora, d_a, d_b, m_a, v_a, m_b, v_b, lr, beta1, beta2, epsilon, weight_decay, step):
+    """AdamW on the adapter's A and B in place (one launch); moments are fp32 tensors shaped like A and B."""
+    _need_cuda(lora.a, lora.b, d_a, d_b, m_a, v_a, m_b, v_b)
+    import numpy as _np
+    bc1 = float(_np.float32(1.0) - _np.float32(beta1) ** _np.float32(step))
+    bc2 = float(_np.float32(1.0) - _np.float32(beta2) ** _np.float32(step))
+    rank, in_dim = lora.a.shape
+    out_dim = lora.b.shape[0]
+    _check(lib().caifq_lora_adamw_step(_ptr(lora.a), _ptr(lora.b), _ptr(d_a), _ptr(d_b), _ptr(m_a), _ptr(v_a),
+                                       _ptr(m_b), _ptr(v_b), rank, in_dim, out_dim, dtype_code(lora.a), lr, beta1,
+                                       beta2, epsilon, weight_decay, bc1, bc2, _stream()), "lora_adamw_step")
+    return bc1, bc2
+
+
 def lora_linear_bwd_noalloc(w, lora, dy, x, hidden, compute=F32):
     """caifq_lora_linear_bwd_noalloc: the scratch comes from the buffer built into the
     library, so this wrapper allocates only the three result tensors."""
@@ -520,9 +547,26 @@ def _weight_array(ws):
     return arr
 
 
-def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32):
+def grouped_expert_expanded_bytes(gate, up, down, dtype=BF16, compute=F32):
+    """Bytes of the scratch that holds the bf16 copies of these experts' weights (0: not expanded)."""
+    return int(lib().caifq_grouped_expert_expanded_bytes(_weight_array(gate) if gate is not None else None,
+                                                         _weight_array(up), _weight_array(down), len(up), dtype,
+                                                         compute))
+
+
+def grouped_expert_expand(gate, up, down, expanded, dtype=BF16, compute=F32):
+    """Fill `expanded` (uint8 tensor of grouped_expert_expanded_bytes) with the bf16 copies, once per step."""
+    _need_cuda(expanded)
+    _check(lib().caifq_grouped_expert_expand(_weight_array(gate) if gate is not None else None, _weight_array(up),
+                                             _weight_array(down), len(up), _ptr(expanded), dtype, compute, _stream()),
+           "grouped_expert_expand")
+    return expanded
+
+
+def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32, expanded=None):
     """gate/up/down: lists of Weight (gate=None: experts without a gate projection; the gate output
-    returned is then None); offsets_host: list of E+1 ints; x: packed [total, in]."""
+    returned is then None); offsets_host: list of E+1 ints; x: packed [total, in].  expanded: the buffer
+    grouped_expert_expand filled for these tables (the launches then read bf16 weight tiles from it)."""
     _need_cuda(x)
     n_exp = len(up)
     total = int(offsets_host[-1])
@@ -532,6 +576,13 @@ def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32):
     up_out = torch.empty((total, hid), dtype=x.dtype, device=x.device)
     hidden = torch.empty((total, hid), dtype=x.dtype, device=x.device)
     offs = (ctypes.c_int32 * (n_exp + 1))(*[int(v) for v in offsets_host])
+    if expanded is not None:
+        _check(lib().caifq_grouped_expert_fwd_expanded(_weight_array(gate) if gate is not None else None,
+                                                       _weight_array(up), _weight_array(down), n_exp, offs, _ptr(x),
+                                                       _ptr(out), _ptr(gate_out), _ptr(up_out), _ptr(hidden),
+                                                       _ptr(expanded), dtype_code(x), compute, _stream()),
+               "grouped_expert_fwd_expanded")
+        return out, gate_out, up_out
     _check(lib().caifq_grouped_expert_fwd(_weight_array(gate) if gate is not None else None, _weight_array(up),
                                           _weight_array(down), n_exp, offs,
                                           _ptr(x), _ptr(out), _ptr(gate_out), _ptr(up_out), _ptr(hidden),
@@ -539,7 +590,7 @@ def grouped_expert_fwd(gate, up, down, offsets_host, x, compute=F32):
     return out, gate_out, up_out
 
 
-def grouped_expert_bwd(gate, up, down, offsets_host, dy, gate_out, up_out, compute=F32):
+def grouped_expert_bwd(gate, up, down, offsets_host, dy, gate_out, up_out, compute=F32, expanded=None):
     _need_cuda(dy, gate_out, up_out)
     n_exp = len(up)
     total = int(offsets_host[-1])
@@ -547,6 +598,13 @@ def grouped_expert_bwd(gate, up, down, offsets_host, dy, gate_out, up_out, compu
     dx = torch.empty((total, up[0].in_dim), dtype=dy.dtype, device=dy.device)
     ws = torch.empty((3, max(total, 1), hid), dtype=dy.dtype, device=dy.device)
     offs = (ctypes.c_int32 * (n_exp + 1))(*[int(v) for v in offsets_host])
+    if expanded is not None:
+        _check(lib().caifq_grouped_expert_bwd_expanded(_weight_array(gate) if gate is not None else None,
+                                                       _weight_array(up), _weight_array(down), n_exp, offs, _ptr(dy),
+                                                       _ptr(gate_out), _ptr(up_out), _ptr(dx), _ptr(ws),
+                                                       _ptr(expanded), dtype_code(dy), compute, _stream()),
+               "grouped_expert_bwd_expanded")
+        return dx
     _check(lib().caifq_grouped_expert_bwd(_weight_array(gate) if gate is not None else None, _weight_array(up),
                                           _weight_array(down), n_exp, offs,
                                           _ptr(dy), _ptr(gate_out), _ptr(up_out), _ptr(dx), _ptr(ws),

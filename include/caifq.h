@@ -279,6 +279,19 @@ CAIFQ_API int caifq_lora_linear_bwd_expanded(const caifq_weight *w, const caifq_
                                              void *d_b, void *workspace, int32_t compute_dtype, void *stream);
 
 /*
+ * The optimizer step of the adapter: AdamW with decoupled weight decay on A [rank, in] and B [out, rank] in
+ * ONE launch (the reference steps each parameter tensor with its own launch_fused_adam,
+ * src/caif_cuda_kernels_optimizers.cu:49-92,217-245).  Same arithmetic in the same order, fp32 math and fp32
+ * moments m, v per factor; A, B, dA, dB in `dtype`.  bias_correction1/2 are 1 - beta^t, computed by the
+ * caller as the reference's optimizer does.  Results are bit-identical to the reference kernel.  After the
+ * step the host calls nothing else: no cached copy of the factors exists in this library.
+ */
+CAIFQ_API int caifq_lora_adamw_step(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a,
+                                    float *m_b, float *v_b, int32_t rank, int32_t in_dim, int32_t out_dim,
+                                    int32_t dtype, float lr, float beta1, float beta2, float epsilon,
+                                    float weight_decay, float bias_correction1, float bias_correction2, void *stream);
+
+/*
  * caifq_lora_linear_bwd for callers that cannot hand over a workspace.
  * (No counterpart in the reference: its layers always own their scratch as
  * CAIF_DeviceTensor objects.)
@@ -396,6 +409,42 @@ CAIFQ_API int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_wei
                              int32_t num_experts, const int32_t *expert_offsets_host, const void *dy,
                              const void *gate_out, const void *up_out, void *dx, void *ws, int32_t dtype,
                              int32_t compute_dtype, void *stream);
+
+/*
+ * The same two calls on bf16 copies of the experts' weights that the host expands once per step (no
+ * counterpart in the reference, whose cache_fp32 keeps fp32 copies of every expert for good: 2.2 GB for the
+ * 64 experts of the MoE config, against 1.1 GB of scratch here that the host may reuse for anything else
+ * between steps).  With quantized experts of one shape on bf16 rows (int8, or int4 under bf16 compute; in and
+ * hidden multiples of 128):
+ *   caifq_grouped_expert_expanded_bytes   size of the scratch, 0 when these experts are not expanded
+ *   caifq_grouped_expert_expand           one launch per projection writes all experts' matrices, stacked, as
+ *                                         bf16: int8 codes as exact integers (scale left to the epilogue), int4
+ *                                         as bf16(scale * code), the reference's dequantize-then-cast value
+ *   caifq_grouped_expert_fwd_expanded /   the grouped launches read their weight tiles from the copies with
+ *   caifq_grouped_expert_bwd_expanded     plain tile copies (on CTA pairs where the width allows) instead of
+ *                                         converting every tile in every CTA; `expanded` is the buffer that
+ *                                         caifq_grouped_expert_expand filled for the same tables.  With
+ *                                         expanded == NULL, or experts that are not expanded, they are the
+ *                                         plain calls.
+ * Results: int8 bit-equal to the plain calls; int4 the reference's own operand values.
+ */
+CAIFQ_API size_t caifq_grouped_expert_expanded_bytes(const caifq_weight *gate, const caifq_weight *up,
+                                                     const caifq_weight *down, int32_t num_experts, int32_t dtype,
+                                                     int32_t compute_dtype);
+CAIFQ_API int caifq_grouped_expert_expand(const caifq_weight *gate, const caifq_weight *up, const caifq_weight *down,
+                                          int32_t num_experts, void *expanded, int32_t dtype, int32_t compute_dtype,
+                                          void *stream);
+CAIFQ_API int caifq_grouped_expert_fwd_expanded(const caifq_weight *gate, const caifq_weight *up,
+                                                const caifq_weight *down, int32_t num_experts,
+                                                const int32_t *expert_offsets_host, const void *x, void *out,
+                                                void *gate_out, void *up_out, void *hidden_ws, const void *expanded,
+                                                int32_t dtype, int32_t compute_dtype, void *stream);
+CAIFQ_API int caifq_grouped_expert_bwd_expanded(const caifq_weight *gate, const caifq_weight *up,
+                                                const caifq_weight *down, int32_t num_experts,
+                                                const int32_t *expert_offsets_host, const void *dy,
+                                                const void *gate_out, const void *up_out, void *dx, void *ws,
+                                                const void *expanded, int32_t dtype, int32_t compute_dtype,
+                                                void *stream);
 
 /* ---- sharded over the GPUs of one box ------------------------------------- */
 /*

@@ -8,7 +8,7 @@ script produces.
   oracle/_ref/libcaif_ref_kernels.so    nvcc, from the reference's unmodified
                                         src/caif_cuda_kernels_quant.cu, _moe.cu,
                                         _attention_support.cu (router softmax) and
-                                        _elementwise.cu compiled where they lie,
+                                        _elementwise.cu, _optimizers.cu compiled where they lie,
                                         plus oracle/ref_shim.cu
 
 Both outputs are binaries kept out of version control.  The second one is only
@@ -52,7 +52,8 @@ def build_reference_kernels(force=False):
     sources = [os.path.join(ref_src, "caif_cuda_kernels_quant.cu"),
                os.path.join(ref_src, "caif_cuda_kernels_moe.cu"),
                os.path.join(ref_src, "caif_cuda_kernels_attention_support.cu"),
-               os.path.join(ref_src, "caif_cuda_kernels_elementwise.cu")]
+               os.path.join(ref_src, "caif_cuda_kernels_elementwise.cu"),
+               os.path.join(ref_src, "caif_cuda_kernels_optimizers.cu")]
     shim = os.path.join(HERE, "ref_shim.cu")
     if not all(os.path.exists(s) for s in sources):
         return REF_SO if os.path.exists(REF_SO) else None

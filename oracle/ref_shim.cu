@@ -2,8 +2,9 @@
 //
 // TEST INFRASTRUCTURE ONLY.  oracle/build.py compiles this file together with
 // the reference's unmodified src/caif_cuda_kernels_quant.cu, src/caif_cuda_kernels_moe.cu,
-// src/caif_cuda_kernels_attention_support.cu (the router's softmax) and
-// src/caif_cuda_kernels_elementwise.cu (read in place from the reference checkout,
+// src/caif_cuda_kernels_attention_support.cu (the router's softmax),
+// src/caif_cuda_kernels_elementwise.cu and src/caif_cuda_kernels_optimizers.cu (the AdamW step of
+// the LoRA factors) (read in place from the reference checkout,
 // never copied) into oracle/_ref/libcaif_ref_kernels.so.  The GPU tests load
 // that library to check the CPU oracle and the product kernels bit for bit
 // against what the reference itself computes.  Every pointer is a device
@@ -18,6 +19,7 @@
 #include "caif_cuda_kernels_moe.cuh"
 #include "caif_cuda_kernels_attention_support.cuh"
 #include "caif_cuda_kernels_elementwise.cuh"
+#include "caif_cuda_kernels_optimizers.cuh"
 
 extern "C" {
 
@@ -142,6 +144,21 @@ void ref_scale_bf16(const void *input, void *output, float factor, int64_t n, vo
   launch_elementwise_mul_scalar<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input), factor,
                                                static_cast<__nv_bfloat16 *>(output), n,
                                                static_cast<cudaStream_t>(stream));
+}
+
+void ref_fused_adam_f32(float *param, const float *grad, float *m, float *v, float lr, float beta1, float beta2,
+                        float epsilon, float weight_decay, float bc1, float bc2, int64_t n, void *stream)
+{
+  launch_fused_adam<float>(param, grad, m, v, lr, beta1, beta2, epsilon, weight_decay, bc1, bc2, n,
+                           static_cast<cudaStream_t>(stream));
+}
+
+void ref_fused_adam_bf16(void *param, const void *grad, float *m, float *v, float lr, float beta1, float beta2,
+                         float epsilon, float weight_decay, float bc1, float bc2, int64_t n, void *stream)
+{
+  launch_fused_adam<__nv_bfloat16>(static_cast<__nv_bfloat16 *>(param), static_cast<const __nv_bfloat16 *>(grad), m, v,
+                                   lr, beta1, beta2, epsilon, weight_decay, bc1, bc2, n,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -150,3 +150,11 @@ def scale_bf16(x, factor):
     out = torch.empty_like(x)
     lib().ref_scale_bf16(_p(x), _p(out), ctypes.c_float(factor), ctypes.c_int64(x.numel()), _s())
     return out
+
+
+def fused_adam(param, grad, m, v, lr, beta1, beta2, epsilon, weight_decay, bc1, bc2):
+    """The reference's launch_fused_adam (src/caif_cuda_kernels_optimizers.cu:217-245) in place on param, m, v."""
+    fn = lib().ref_fused_adam_f32 if param.dtype == torch.float32 else lib().ref_fused_adam_bf16
+    fn(_p(param), _p(grad), _p(m), _p(v), ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2),
+       ctypes.c_float(epsilon), ctypes.c_float(weight_decay), ctypes.c_float(bc1), ctypes.c_float(bc2),
+       ctypes.c_int64(param.numel()), _s())

@@ -546,3 +546,82 @@ def test_lora_entry_points_that_expand_the_weight_once_per_call(storage, compute
     base_dx = orc.frozen_linear_backward(dy_np[rows], wc, compute)
     want_dx, _, _ = orc.lora_backward(dy_np[rows], x_np[rows], hid, base_dx, a_np, b_np, 32.0, orc.BF16)
     assert max_rel_err(dx1[rows].float().cpu().numpy(), want_dx) <= 2e-2
+
+
+@pytest.mark.parametrize("storage,compute,gated", [(orc.I8, orc.F32, True), (orc.I8, orc.BF16, False),
+                                                   (orc.I4, orc.BF16, True), (orc.I4, orc.BF16, False)])
+def test_grouped_experts_on_bf16_copies_expanded_once_per_step(storage, compute, gated):
+    """caifq_grouped_expert_expand + _fwd_expanded / _bwd_expanded: the grouped launches read stacked bf16
+    copies of the experts' weights (one tensor map per projection, CTA pairs where the width allows).
+    int8: bit-equal to the plain calls.  int4: the reference's own operand values; rows of three experts
+    hold the bound against the oracle."""
+    experts, in_dim, hid = 6, 512, 384
+    rng = np.random.default_rng(9700 + storage + compute + gated)
+    counts = rng.integers(2000, 3500, experts)
+    counts[2] = 0
+    offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    total = int(offsets[-1])
+    gate, up, down, o_gate, o_up, o_down = [], [], [], [], [], []
+    for _ in range(experts):
+        for lst, olst, (o, i) in ((gate, o_gate, (hid, in_dim)), (up, o_up, (hid, in_dim)),
+                                  (down, o_down, (in_dim, hid))):
+            w, codes, scales = make_weight(rng, o, i, storage, std=0.05)
+            lst.append(w)
+            olst.append(orc.weight_to_compute(codes, scales, storage, i, o, compute, w.scheme, w.group_size))
+    if not gated:
+        gate, o_gate = None, [None] * experts
+    x_np, x = act(rng, total, in_dim, orc.BF16)
+    dy_np, dy = act(rng, total, in_dim, orc.BF16)
+    nbytes = nv.grouped_expert_expanded_bytes(gate, up, down, nv.BF16, compute)
+    assert nbytes == (3 if gated else 2) * experts * in_dim * hid * 2
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    nv.grouped_expert_expand(gate, up, down, buf, nv.BF16, compute)
+    out0, g0, u0 = nv.grouped_expert_fwd(gate, up, down, offsets.tolist(), x, compute)
+    dx0 = nv.grouped_expert_bwd(gate, up, down, offsets.tolist(), dy, g0, u0, compute)
+    out1, g1, u1 = nv.grouped_expert_fwd(gate, up, down, offsets.tolist(), x, compute, expanded=buf)
+    assert nv.last_path() == "umma-grouped"
+    dx1 = nv.grouped_expert_bwd(gate, up, down, offsets.tolist(), dy, g1, u1, compute, expanded=buf)
+    assert nv.last_path() == "umma-grouped"
+    assert nv.lib().caifq_device_status() == 0
+    if storage == orc.I8:
+        assert torch.equal(out0, out1) and torch.equal(u0, u1) and torch.equal(dx0, dx1)
+        assert (not gated) or torch.equal(g0, g1)
+    for e in (0, 3, experts - 1):
+        lo, hi = int(offsets[e]), int(offsets[e]) + 24
+        want, g, u = orc.frozen_expert_forward(x_np[lo:hi], o_gate[e], o_up[e], o_down[e], compute, orc.BF16)
+        assert max_rel_err(out1[lo:hi].float().cpu().numpy(), want) <= 2e-2
+        assert max_rel_err(u1[lo:hi].float().cpu().numpy(), u) <= 2e-2
+        want_dx = orc.frozen_expert_backward(dy_np[lo:hi], g, u, o_gate[e], o_up[e], o_down[e], compute, orc.BF16)
+        assert max_rel_err(dx1[lo:hi].float().cpu().numpy(), want_dx) <= 2e-2
+    # a non-bf16 row dtype is not expanded: size 0, and the expanded calls are the plain ones
+    assert nv.grouped_expert_expanded_bytes(gate, up, down, nv.F32, compute) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("weight_decay", [0.0, 0.01])
+def test_lora_adamw_step_bit_exact_with_the_reference_kernel(dtype, weight_decay):
+    """caifq_lora_adamw_step (A and B in one launch) against the reference's fused_adam_kernel run once per
+    factor: parameters and both moments bit for bit, over three steps."""
+    if not ref.available():
+        pytest.skip("reference kernels not built")
+    rank, in_dim, out_dim = 16, 384, 520
+    g = torch.Generator(device="cuda").manual_seed(31)
+    a = (torch.rand(rank, in_dim, generator=g, device="cuda") - 0.5).to(dtype)
+    b = (torch.randn(out_dim, rank, generator=g, device="cuda") * 0.01).to(dtype)
+    lora = nv.Lora(a.clone(), b.clone(), 32.0)
+    mine = [torch.zeros(rank, in_dim, device="cuda"), torch.zeros(rank, in_dim, device="cuda"),
+            torch.zeros(out_dim, rank, device="cuda"), torch.zeros(out_dim, rank, device="cuda")]
+    theirs = [t.clone() for t in mine]
+    ra, rb = a.clone(), b.clone()
+    lr, beta1, beta2, eps = 1e-3, 0.9, 0.999, 1e-8
+    for step in (1, 2, 3):
+        d_a = (torch.randn(rank, in_dim, generator=g, device="cuda") * 0.1).to(dtype)
+        d_b = (torch.randn(out_dim, rank, generator=g, device="cuda") * 0.1).to(dtype)
+        bc1, bc2 = nv.lora_adamw_step(lora, d_a, d_b, mine[0], mine[1], mine[2], mine[3], lr, beta1, beta2, eps,
+                                      weight_decay, step)
+        ref.fused_adam(ra, d_a, theirs[0], theirs[1], lr, beta1, beta2, eps, weight_decay, bc1, bc2)
+        ref.fused_adam(rb, d_b, theirs[2], theirs[3], lr, beta1, beta2, eps, weight_decay, bc1, bc2)
+        assert torch.equal(lora.a, ra) and torch.equal(lora.b, rb)
+        for x, y in zip(mine, theirs):
+            assert torch.equal(x, y)
+    assert not torch.equal(lora.a, a)
