@@ -857,7 +857,7 @@ def bench_c3(ctx):
         "metric": METRIC["c3"][0], "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": SCALING["c3"],
         "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config_for("c3", 1),
-        "roofline": roofline, "e2e": e2e, "gpu_launches": 11 * steps, "clocks": clocks,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": 13 * steps, "clocks": clocks,   # 11 + the two weight expansions
     }
 
 
@@ -1007,7 +1007,7 @@ def bench_c5(ctx):
                      "peak_source": ctx.peaks["source"], "kernel": "frozen experts path '%s'" % path,
                      "note": "expert GEMM flops over the whole step (dispatch, SwiGLU, combine and their backward "
                              "kernels%s included in the time)" % (", both all-to-alls" if world > 1 else "")},
-        "e2e": e2e, "gpu_launches": 13 * steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": (13 + (3 if ops.expanded is not None else 0)) * steps, "clocks": clocks,
     }
     if parity is not None:
         result["parity"] = parity
@@ -1201,7 +1201,7 @@ def bench_c4lin(ctx):
                      "traffic": None, "peak_source": ctx.peaks["source"], "kernel": "frozen linear path '%s'" % path,
                      "note": "flops of the 224 projections (fwd + dX + LoRA) over the whole step; the step is seconds "
                              "long, so the sustained peak is the fair denominator"},
-        "e2e": e2e, "gpu_launches": layers * len(C4_PROJ) * 11 * steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": layers * len(C4_PROJ) * 13 * steps, "clocks": clocks,
     }
     if world > 1:
         total = sum(coll_bytes.values())
