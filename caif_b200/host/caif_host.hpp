@@ -804,12 +804,14 @@ class CAIF_DeviceLoRAAdapter : public CAIF_DeviceLayerTyped<ComputeT, StorageT>
       CAIF_DeviceTensor hidden = CAIF_DeviceTensor::Uninitialized({n, _config.Rank()}, Stream(), sd);
       const caifq_weight w = _frozen->AsCaifqWeight();
       const caifq_lora l = AsCaifqLora();
-      const size_t ws_bytes = caifq_lora_fwd_workspace_bytes(&w, &l, n);
+      // (the entry points that may expand the weight once per call: the layer owns stream-ordered scratch)
+      const int32_t cd = static_cast<int32_t>(Base_t::ComputeDtype());
+      const size_t ws_bytes = caifq_lora_fwd_workspace_bytes_expanded(&w, &l, n, cd);
       CAIF_DeviceTensor ws =
           CAIF_DeviceTensor::Uninitialized({static_cast<uint32_t>(ws_bytes)}, Stream(), Dtype_e::Int8);
-      CAIF_CheckCaifq(caifq_lora_linear_fwd(&w, &l, input.DeviceDataRaw(), n, output.DeviceDataRaw(),
-                                            hidden.DeviceDataRaw(), ws.DeviceDataRaw(),
-                                            static_cast<int32_t>(Base_t::ComputeDtype()), Stream().Handle()),
+      CAIF_CheckCaifq(caifq_lora_linear_fwd_expanded(&w, &l, input.DeviceDataRaw(), n, output.DeviceDataRaw(),
+                                                     hidden.DeviceDataRaw(), ws.DeviceDataRaw(), cd,
+                                                     Stream().Handle()),
                       "LoRAAdapter::Forward");
       if (ctx.Training())
       {
@@ -833,14 +835,16 @@ class CAIF_DeviceLoRAAdapter : public CAIF_DeviceLayerTyped<ComputeT, StorageT>
       CAIF_DeviceTensor grad_input = CAIF_DeviceTensor::Uninitialized(in_shape, Stream(), sd);
       const caifq_weight w = _frozen->AsCaifqWeight();
       const caifq_lora l = AsCaifqLora();
-      const size_t ws_bytes = caifq_lora_bwd_workspace_bytes(&w, &l, n);
+      const int32_t cd = static_cast<int32_t>(Base_t::ComputeDtype());
+      const size_t ws_bytes = caifq_lora_bwd_workspace_bytes_expanded(&w, &l, n, cd);
       CAIF_DeviceTensor ws =
           CAIF_DeviceTensor::Uninitialized({static_cast<uint32_t>(ws_bytes)}, Stream(), Dtype_e::Int8);
-      CAIF_CheckCaifq(caifq_lora_linear_bwd(&w, &l, grad_output.DeviceDataRaw(), _cached_input.DeviceDataRaw(),
-                                            _cached_lora_hidden.DeviceDataRaw(), n, grad_input.DeviceDataRaw(),
-                                            _grad_lora_a.DeviceDataRaw(), _grad_lora_b.DeviceDataRaw(),
-                                            ws.DeviceDataRaw(), static_cast<int32_t>(Base_t::ComputeDtype()),
-                                            Stream().Handle()),
+      CAIF_CheckCaifq(caifq_lora_linear_bwd_expanded(&w, &l, grad_output.DeviceDataRaw(),
+                                                     _cached_input.DeviceDataRaw(),
+                                                     _cached_lora_hidden.DeviceDataRaw(), n,
+                                                     grad_input.DeviceDataRaw(), _grad_lora_a.DeviceDataRaw(),
+                                                     _grad_lora_b.DeviceDataRaw(), ws.DeviceDataRaw(), cd,
+                                                     Stream().Handle()),
                       "LoRAAdapter::Backward");
       // the workspace is freed when `ws` goes out of scope; cudaFree waits for the work that uses it
       return grad_input;
