@@ -1259,6 +1259,36 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
   {
     return r;
   }
+  if (up[0].storage == CAIFQ_BF16 && gate[0].storage == CAIFQ_BF16 && up[0].scales == nullptr &&
+      gate[0].scales == nullptr && forced_path() == Force::None)
+  {
+    // (expanded int8 experts carry a per-expert scale for the epilogue, which differs between the two
+    // projections: they keep the two launches)
+    // Stacked bf16 experts (the expanded copies): dx = g_up . W_up + g_gate . W_gate as ONE launch whose
+    // reduction runs over both operand pairs, accumulated in fp32 and rounded once (the reference rounds each
+    // product to the storage dtype and adds them: one more rounding, same bound).  No read-modify-write of dx.
+    GroupedLinearArgs g{};
+    g.weights = up;
+    g.num_experts = num_experts;
+    g.offsets = expert_offsets_host;
+    g.backward = true;
+    g.a = g_up;
+    g.a_dtype = dtype;
+    g.c = dx;
+    g.c_dtype = dtype;
+    g.accumulate = false;
+    g.compute_dtype = compute_dtype;
+    GroupedLinearArgs g2 = g;
+    g2.weights = gate;
+    g2.a = g_gate;
+    if (umma_grouped_supported(g) && umma_grouped_supported(g2) && num_experts <= 80)
+    {
+      g.weights2 = gate;
+      g.a2 = g_gate;
+      set_path("umma-grouped");
+      return launch_linear_umma_grouped(g, s);
+    }
+  }
   // dx = round(up.Bwd(g_up)); dx = round(round(gate.Bwd(g_gate)) + dx): the reference's Add(gi_up, gi_gate)
   r = grouped_linear(up, num_experts, expert_offsets_host, true, g_up, dx, dtype, false, compute_dtype, s, who);
   if (r != CAIFQ_OK)

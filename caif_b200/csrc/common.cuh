@@ -246,6 +246,9 @@ struct GroupedLinearArgs
   int c_dtype;
   bool accumulate;
   int compute_dtype;
+  // Optional second operand pair (stacked bf16 experts only): c = a . W + a2 . W2 in one accumulation, rounded once
+  const caifq_weight *weights2;
+  const void *a2;
 };
 // gate(x), up(x) and silu(gate(x)) * up(x) of a run of frozen experts in one launch
 // (CAIF_DeviceMoEFrozenExpert::ForwardImpl up to the down projection,

@@ -457,6 +457,8 @@ struct UmmaParams
   const uint8_t *lora_rhs;  // null = no LoRA k-block
   const float *c_scale;     // bf16 weights only: factor of the fp32 accumulator in the epilogue (null = 1)
   int expert_rows;          // grouped bf16 weights: rows of one expert's matrix in the stacked [E * rows, in] matrix
+  int dual_k;               // bf16 weights: the reduction runs over two operand pairs, C = A.W + A2.W2 (A2 through
+                            // map_h, W2 through map_l), num_kb k-blocks each
   // Fused gate/up/SwiGLU forward of a frozen expert (forward, 128-wide tiles, 16-bit outputs): a tile's
   // columns 0..63 are features [64 j, 64 j + 64) of the gate projection, columns 64..127 the same
   // features of the up projection.  c receives gate(x), c_up up(x), c_hidden silu(gate(x)) * up(x),
@@ -673,7 +675,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   const int num_tiles = p.num_m_tiles * p.num_n_tiles;
   const int num_kb = p.k_total / BK;
   // with a LoRA product the loop runs one more k-block whose operands are the padded factors
-  const int num_kb_all = num_kb + ((p.lora_rhs != nullptr) ? 1 : 0);
+  const int num_kb_all = (p.dual_k ? 2 * num_kb : num_kb) + ((p.lora_rhs != nullptr) ? 1 : 0);
 
   if (warp == 0)
   {
@@ -720,7 +722,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
             else
             {
-              load(a_addr(s, mt), &map_h, 0, row_tile + mt * BM_SUB, a_full(s));
+              // the LoRA k-block's activation-side operand, or the second operand pair's k-block
+              load(a_addr(s, mt), &map_h, p.dual_k ? (kb - num_kb) * BK : 0, row_tile + mt * BM_SUB, a_full(s));
             }
           }
           if (WMODE == W_BF16)
@@ -732,7 +735,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             }
             // the LoRA k-block (number num_kb) takes its weight-side operand, the padded factor, from map_l
             const CUtensorMap *bmap = (kb < num_kb) ? &map_b : &map_l;
-            const int kc = (kb < num_kb) ? kb * BK : 0;
+            const int kc = (kb < num_kb) ? kb * BK : (p.dual_k ? (kb - num_kb) * BK : 0);
             // grouped: the experts' matrices lie stacked in one [E * rows, in] matrix
             const int erow = GROUPED ? tw.expert * p.expert_rows : 0;
             if (!BWD && p.swiglu)
@@ -1824,15 +1827,33 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
       {
         return rc;
       }
+      // second operand pair (dX of two projections that share their input: C = A.W + A2.W2 in one accumulation)
+      CUtensorMap map_a2 = map_a;
+      CUtensorMap map_b2 = map_b;
+      p.dual_k = 0;
+      if (g.weights2 != nullptr && g.a2 != nullptr)
+      {
+        rc = make_map_bf16(&map_a2, g.a2, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(total_rows), BM_SUB);
+        if (rc == CAIFQ_OK)
+        {
+          rc = make_map_bf16(&map_b2, g.weights2[first].codes, static_cast<uint64_t>(w0.in_dim),
+                             static_cast<uint64_t>(count) * static_cast<uint64_t>(w0.out_dim), g.backward ? BK : 128);
+        }
+        if (rc != CAIFQ_OK)
+        {
+          return rc;
+        }
+        p.dual_k = 1;
+      }
       if (wide)
       {
-        rc = g.backward ? launch_inst<W_BF16, true, 256, true, true>(map_a, map_b, map_a, map_b, p, gt, s)
-                        : launch_inst<W_BF16, false, 256, true, true>(map_a, map_b, map_a, map_b, p, gt, s);
+        rc = g.backward ? launch_inst<W_BF16, true, 256, true, true>(map_a, map_b, map_a2, map_b2, p, gt, s)
+                        : launch_inst<W_BF16, false, 256, true, true>(map_a, map_b, map_a2, map_b2, p, gt, s);
       }
       else
       {
-        rc = g.backward ? launch_inst<W_BF16, true, 128, true>(map_a, map_b, map_a, map_b, p, gt, s)
-                        : launch_inst<W_BF16, false, 128, true>(map_a, map_b, map_a, map_b, p, gt, s);
+        rc = g.backward ? launch_inst<W_BF16, true, 128, true>(map_a, map_b, map_a2, map_b2, p, gt, s)
+                        : launch_inst<W_BF16, false, 128, true>(map_a, map_b, map_a2, map_b2, p, gt, s);
       }
       if (rc != CAIFQ_OK)
       {

@@ -491,31 +491,7 @@ __global__ void expand_int8_to_bf16_kernel(const uint4 *codes, uint4 *dst, int64
 }
 
 __global__ void expand_int4_to_bf16_kernel(const uint4 *codes, const __half *scales, uint4 *dst, int64_t chunks,
-                                           int group_size)
-{
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
-  {
-    const uint4 v = __ldg(codes + i);
-    const float scale = __half2float(scales[(i * 32) / group_size]);   // 32 codes lie in one group
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-    {
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-      {
-        // byte j of the word: low nibble is the even element, high nibble the odd one
-        const int byte = static_cast<int>((w[k] >> (8 * j)) & 0xFFu);
-        const float e = static_cast<float>((byte & 0xF) >= 8 ? (byte & 0xF) - 16 : (byte & 0xF)) * scale;
-        const float d = static_cast<float>((byte >> 4) >= 8 ? (byte >> 4) - 16 : (byte >> 4)) * scale;
-        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
-      }
-      dst[4 * i + k] = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-  }
-}
+                                           int group_size);
 
 // The same for a run of experts of one shape in ONE launch: expert e's matrix goes to dst + e * out * in
 // elements, so the copies lie stacked as one [E * out, in] matrix.
@@ -547,17 +523,22 @@ __device__ __forceinline__ void expand_int8_chunk(const uint4 v, uint4 *dst)
 
 __device__ __forceinline__ void expand_int4_chunk(const uint4 v, const float scale, uint4 *dst)
 {
+  // Nibbles to floats without integer-to-float conversions: the offset-binary nibble u = q + 8 is dropped into
+  // the mantissa of 2^23 (exact), 2^23 + 8 is subtracted (exact), the product with the scale is rounded once in
+  // fp32 and once to bf16: bf16(fp32(scale * q)), the value of the reference's dequantize followed by its cast.
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  const float base = 8388616.0f;   // 2^23 + 8
 #pragma unroll
   for (int k = 0; k < 4; ++k)
   {
+    const uint32_t ev = (w[k] & 0x0F0F0F0Fu) ^ 0x08080808u;          // elements 0, 2, 4, 6 of the word
+    const uint32_t od = ((w[k] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // elements 1, 3, 5, 7
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j)
     {
-      const int byte = static_cast<int>((w[k] >> (8 * j)) & 0xFFu);
-      const float e = __fmul_rn(static_cast<float>((byte & 0xF) >= 8 ? (byte & 0xF) - 16 : (byte & 0xF)), scale);
-      const float d = __fmul_rn(static_cast<float>((byte >> 4) >= 8 ? (byte >> 4) - 16 : (byte >> 4)), scale);
+      const float e = __fmul_rn(__uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base, scale);
+      const float d = __fmul_rn(__uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base, scale);
       asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
     }
     dst[k] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -583,6 +564,17 @@ __global__ void expand_grouped_kernel(const __grid_constant__ ExpandTable t, uin
     {
       expand_int4_chunk(v, __half2float(t.scales[e][(i * 32) / group_size]), out + 4 * i);
     }
+  }
+}
+
+__global__ void expand_int4_to_bf16_kernel(const uint4 *codes, const __half *scales, uint4 *dst, int64_t chunks,
+                                           int group_size)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
+  {
+    // 32 codes lie in one group
+    expand_int4_chunk(__ldg(codes + i), __half2float(scales[(i * 32) / group_size]), dst + 4 * i);
   }
 }
 
