@@ -113,6 +113,9 @@ size_t gemm_tn_scratch_bytes(int p, int q);
 int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
                    float u_prescale, int64_t m, int p, int q, cudaStream_t s);
 int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
+int launch_moe_route_grouped(const void *input, const void *bias, void *scores_out, int *indices, void *weights,
+                             int dtype, int batch, int dim, int k, int n_group, int topk_group, int apply_sigmoid,
+                             cudaStream_t s);
 int launch_lora_adamw(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a, float *m_b,
                       float *v_b, int64_t n_a, int64_t n_b, int dtype, float lr, float beta1, float beta2,
                       float epsilon, float weight_decay, float bias_correction1, float bias_correction2,
@@ -948,6 +951,21 @@ int caifq_moe_router_softmax(const void *logits, const void *bias, void *probs, 
   CAIFQ_CHECK_ARG(is_float_dtype(dtype), "caifq_moe_router_softmax: dtype must be F32, F16 or BF16");
   CAIFQ_CHECK_ARG(rows == 0 || (logits && probs), "caifq_moe_router_softmax: null pointer");
   return launch_moe_router_softmax(logits, bias, probs, dtype, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_route_grouped(const void *input, int32_t input_is_logits, const void *selection_bias, void *scores_out,
+                            int32_t *indices, void *weights, int32_t dtype, int32_t batch, int32_t dim, int32_t k,
+                            int32_t n_group, int32_t topk_group, void *stream)
+{
+  const char *who = "caifq_moe_route_grouped";
+  CAIFQ_CHECK_ARG(batch >= 0 && dim > 0 && k > 0 && k <= dim, "%s: bad shape", who);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(n_group >= 1 && n_group <= 1024 && (dim % n_group) == 0 && topk_group >= 1 && topk_group <= n_group,
+                  "%s: n_group must divide the expert count and topk_group lie in 1..n_group", who);
+  CAIFQ_CHECK_ARG(batch == 0 || (input && indices && weights), "%s: null pointer", who);
+  CAIFQ_CHECK_ARG(n_group <= 32, "%s: at most 32 groups", who);
+  return launch_moe_route_grouped(input, selection_bias, scores_out, indices, weights, dtype, batch, dim, k, n_group,
+                                  topk_group, input_is_logits ? 1 : 0, static_cast<cudaStream_t>(stream));
 }
 
 int caifq_lora_adamw_step(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a, float *m_b,

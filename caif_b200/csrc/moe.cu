@@ -93,6 +93,156 @@ __global__ void topk_kernel(const T *__restrict__ input, int *__restrict__ indic
   }
 }
 
+// ------------------------------------------- sigmoid / group-limited top-k routing
+// CAIF_DeviceMoERouter::Route for SigmoidNoauxTc gating and for group-limited routing
+// (src/caif_device_moe_router.cpp:286-376): scores = sigmoid(logits) (or the probabilities given), a per-token
+// selection copy with the selection-only bias added (bias_add_2d: T(float + float)), the DeepSeek group mask
+// (moe_group_mask_kernel: a group's score is the sum of its two largest entries, the topk_group best groups
+// stay, ties to the lowest group, everything else becomes T(-1e30)), top-k on the selection with the
+// reference's order, and combine weights gathered from the ORIGINAL scores when a bias was used.  The
+// reference runs five kernels with thread 0 of a block doing the scans; here one warp does a token in one
+// pass with the same comparisons in the same order, so indices and weights are bit-identical.
+template <typename T>
+__global__ void route_grouped_kernel(const T *__restrict__ input, const T *__restrict__ bias, T *__restrict__ scores_out,
+                                     int *__restrict__ indices, T *__restrict__ weights, int batch, int dim, int k,
+                                     int n_group, int topk_group, int apply_sigmoid)
+{
+  extern __shared__ float s_route[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * warps_per_block + warp;
+  if (row >= batch)
+  {
+    return;
+  }
+  float *sel = s_route + static_cast<size_t>(warp) * (2 * dim + 64);   // selection scores
+  float *orig = sel + dim;                                              // original scores
+  float *grp = orig + dim;                                              // group scores, then keep flags
+  float *keep = grp + 32;
+  const T *src = input + static_cast<size_t>(row) * dim;
+  for (int d = lane; d < dim; d += 32)
+  {
+    T score = src[d];
+    if (apply_sigmoid)
+    {
+      const float x = to_f<T>(src[d]);
+      score = from_f<T>(1.0f / (1.0f + expf(-x)));
+    }
+    if (scores_out != nullptr)
+    {
+      scores_out[static_cast<size_t>(row) * dim + d] = score;
+    }
+    const float sf = to_f<T>(score);
+    orig[d] = sf;
+    sel[d] = (bias != nullptr) ? to_f<T>(from_f<T>(sf + to_f<T>(bias[d]))) : sf;
+  }
+  __syncwarp();
+  if (n_group > 1)
+  {
+    const int per_group = dim / n_group;
+    // lane g scores group g: the two largest entries in the reference's scan order
+    for (int g0 = 0; g0 < n_group; g0 += 32)
+    {
+      const int g = g0 + lane;
+      if (g < n_group)
+      {
+        float top1 = kNegSentinel;
+        float top2 = kNegSentinel;
+        for (int j = 0; j < per_group; ++j)
+        {
+          const float v = sel[g * per_group + j];
+          if (v > top1)
+          {
+            top2 = top1;
+            top1 = v;
+          }
+          else if (v > top2)
+          {
+            top2 = v;
+          }
+        }
+        grp[g] = top1 + top2;
+        keep[g] = 0.0f;
+      }
+    }
+    __syncwarp();
+    for (int r = 0; r < topk_group; ++r)
+    {
+      // the first strictly largest group score from group 0 upwards; (sentinel, group 0) when none exceeds it
+      float best = kNegSentinel;
+      int best_g = 0;
+      for (int g = lane; g < n_group; g += 32)
+      {
+        if (grp[g] > best)
+        {
+          best = grp[g];
+          best_g = g;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+      {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        const int og = __shfl_xor_sync(0xFFFFFFFFu, best_g, o);
+        if (ov > best || (ov == best && og < best_g))
+        {
+          best = ov;
+          best_g = og;
+        }
+      }
+      if (lane == 0)
+      {
+        keep[best_g] = 1.0f;
+        grp[best_g] = kNegSentinel;
+      }
+      __syncwarp();
+    }
+    const float masked = to_f<T>(from_f<T>(kNegSentinel));
+    for (int d = lane; d < dim; d += 32)
+    {
+      if (keep[d / per_group] == 0.0f)
+      {
+        sel[d] = masked;
+      }
+    }
+    __syncwarp();
+  }
+  for (int i = 0; i < k; ++i)
+  {
+    float best = kNegSentinel;
+    int best_idx = 0;
+    for (int d = lane; d < dim; d += 32)
+    {
+      const float v = sel[d];
+      if (v > best)
+      {
+        best = v;
+        best_idx = d;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, best_idx, o);
+      if (ov > best || (ov == best && oi < best_idx))
+      {
+        best = ov;
+        best_idx = oi;
+      }
+    }
+    if (lane == 0)
+    {
+      indices[static_cast<size_t>(row) * k + i] = best_idx;
+      // with a selection-only bias the combine weight is the original score at the chosen expert
+      weights[static_cast<size_t>(row) * k + i] = (bias != nullptr) ? from_f<T>(orig[best_idx]) : from_f<T>(best);
+      sel[best_idx] = kNegSentinel;
+    }
+    __syncwarp();
+  }
+}
+
 // -------------------------------------------------------------- normalize rows
 // The reference uses a block of 256 threads: thread t sums elements t, t+256,
 // ... and a shared-memory tree (stride 128..1) adds the 256 partials.  A warp
@@ -793,6 +943,34 @@ int launch_moe_topk(const void *probs, int dtype, int *indices, void *values, in
   const int grid = (batch + warps - 1) / warps;
   CAIFQ_DISPATCH_FLOAT(dtype, (topk_kernel<T><<<grid, warps * 32, smem, s>>>(
                                   static_cast<const T *>(probs), indices, static_cast<T *>(values), batch, dim, k)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_route_grouped(const void *input, const void *bias, void *scores_out, int *indices, void *weights,
+                             int dtype, int batch, int dim, int k, int n_group, int topk_group, int apply_sigmoid,
+                             cudaStream_t s)
+{
+  if (batch <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const size_t per_warp = (static_cast<size_t>(2) * dim + 64) * sizeof(float);
+  int warps = 8;
+  while (warps > 1 && warps * per_warp > 40 * 1024)
+  {
+    warps >>= 1;
+  }
+  if (warps * per_warp > 48 * 1024)
+  {
+    set_error("moe_route_grouped: dim=%d too large", dim);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  const int grid = (batch + warps - 1) / warps;
+  CAIFQ_DISPATCH_FLOAT(dtype, (route_grouped_kernel<T><<<grid, warps * 32, warps * per_warp, s>>>(
+                                  static_cast<const T *>(input), static_cast<const T *>(bias),
+                                  static_cast<T *>(scores_out), indices, static_cast<T *>(weights), batch, dim, k,
+                                  n_group, topk_group, apply_sigmoid)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

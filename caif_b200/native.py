@@ -78,6 +78,7 @@ _SIGNATURES = {
     "caifq_lora_fwd_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _i64]),
     "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
                                              _vp, _i32, _vp]),
+    "caifq_moe_route_grouped": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "caifq_lora_adamw_step": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
                                              ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                                              ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
@@ -452,6 +453,20 @@ def moe_normalize_rows(x):
     _check(lib().caifq_moe_normalize_rows(_ptr(x), _ptr(out), dtype_code(x), batch, dim, _stream()),
            "moe_normalize_rows")
     return out
+
+
+def moe_route_grouped(x, k, logits=True, bias=None, n_group=1, topk_group=1):
+    """Sigmoid (logits=True) or given scores, selection-only bias, group mask, top-k, gathered weights:
+    returns (scores, indices, weights)."""
+    _need_cuda(x, bias)
+    batch, dim = x.shape
+    scores = torch.empty_like(x)
+    idx = torch.empty((batch, k), dtype=torch.int32, device=x.device)
+    wts = torch.empty((batch, k), dtype=x.dtype, device=x.device)
+    _check(lib().caifq_moe_route_grouped(_ptr(x), 1 if logits else 0, _ptr(bias), _ptr(scores), _ptr(idx), _ptr(wts),
+                                         dtype_code(x), batch, dim, k, n_group, topk_group, _stream()),
+           "moe_route_grouped")
+    return scores, idx, wts
 
 
 def moe_softmax(logits, bias=None):

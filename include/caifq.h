@@ -343,6 +343,25 @@ CAIFQ_API int caifq_moe_normalize_rows(const void *input, void *output, int32_t 
  */
 CAIFQ_API int caifq_moe_router_softmax(const void *logits, const void *bias, void *probs, int32_t dtype, int32_t rows,
                              int32_t cols, void *stream);
+
+/*
+ * CAIF_DeviceMoERouter::Route for SigmoidNoauxTc gating and for DeepSeek group-limited routing
+ * (src/caif_device_moe_router.cpp:286-376) in one launch instead of the reference's Sigmoid, AddBias,
+ * MoEGroupMask, TopK and GatherTopKValues kernels:
+ *   scores    = sigmoid(input) when input_is_logits != 0 (launch_sigmoid_forward), else input as given
+ *               (softmax probabilities from caifq_moe_router_softmax); written to scores_out when non-NULL
+ *   selection = scores (+ selection_bias [dim], may be NULL: the aux-loss-free bias, for selection only)
+ *   n_group > 1: the experts of a token form n_group equal groups scored by the sum of their two largest
+ *               selection entries; all but the topk_group best groups are masked (launch_moe_group_mask)
+ *   indices   = top-k of the selection (largest first, ties to the lowest index)
+ *   weights   = the ORIGINAL scores at the chosen experts when a bias was given (launch_gather_topk_values),
+ *               else the selection values themselves
+ * Bit-identical to the reference kernels.  The caller applies norm_topk_prob and routed_scaling_factor with
+ * caifq_moe_normalize_rows and caifq_scale, as the router does.  At most 32 groups.
+ */
+CAIFQ_API int caifq_moe_route_grouped(const void *input, int32_t input_is_logits, const void *selection_bias,
+                                      void *scores_out, int32_t *indices, void *weights, int32_t dtype, int32_t batch,
+                                      int32_t dim, int32_t k, int32_t n_group, int32_t topk_group, void *stream);
 /* CAIF_Ops::Scale, src/caif_ops_device.cpp:3142-3160 (the router's routed_scaling_factor on the top-k
  * weights, src/caif_device_moe_router.cpp:394-407; LoRA's alpha/r): dst = T(float(src) * factor).
  * In place is allowed. */

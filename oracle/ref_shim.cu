@@ -20,6 +20,7 @@
 #include "caif_cuda_kernels_attention_support.cuh"
 #include "caif_cuda_kernels_elementwise.cuh"
 #include "caif_cuda_kernels_optimizers.cuh"
+#include "caif_cuda_kernels_activations.cuh"
 
 extern "C" {
 
@@ -159,6 +160,48 @@ void ref_fused_adam_bf16(void *param, const void *grad, float *m, float *v, floa
   launch_fused_adam<__nv_bfloat16>(static_cast<__nv_bfloat16 *>(param), static_cast<const __nv_bfloat16 *>(grad), m, v,
                                    lr, beta1, beta2, epsilon, weight_decay, bc1, bc2, n,
                                    static_cast<cudaStream_t>(stream));
+}
+
+void ref_sigmoid_f32(const float *in, float *out, int64_t n, void *stream)
+{
+  launch_sigmoid_forward<float>(in, out, n, static_cast<cudaStream_t>(stream));
+}
+
+void ref_sigmoid_bf16(const void *in, void *out, int64_t n, void *stream)
+{
+  launch_sigmoid_forward<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(in), static_cast<__nv_bfloat16 *>(out), n,
+                                        static_cast<cudaStream_t>(stream));
+}
+
+void ref_group_mask_f32(float *sel, int tokens, int experts, int n_group, int topk_group, void *stream)
+{
+  launch_moe_group_mask<float>(sel, tokens, experts, n_group, topk_group, static_cast<cudaStream_t>(stream));
+}
+
+void ref_group_mask_bf16(void *sel, int tokens, int experts, int n_group, int topk_group, void *stream)
+{
+  launch_moe_group_mask<__nv_bfloat16>(static_cast<__nv_bfloat16 *>(sel), tokens, experts, n_group, topk_group,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+void ref_gather_topk_f32(const float *scores, const int *indices, float *out, int tokens, int experts, int k,
+                         void *stream)
+{
+  launch_gather_topk_values<float>(scores, indices, out, tokens, experts, k, static_cast<cudaStream_t>(stream));
+}
+
+void ref_gather_topk_bf16(const void *scores, const int *indices, void *out, int tokens, int experts, int k,
+                          void *stream)
+{
+  launch_gather_topk_values<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(scores), indices,
+                                           static_cast<__nv_bfloat16 *>(out), tokens, experts, k,
+                                           static_cast<cudaStream_t>(stream));
+}
+
+void ref_topk_bf16(const void *input, int *indices, void *values, int batch, int dim, int k, void *stream)
+{
+  launch_topk<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input), indices, static_cast<__nv_bfloat16 *>(values),
+                             batch, dim, k, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -158,3 +158,38 @@ def fused_adam(param, grad, m, v, lr, beta1, beta2, epsilon, weight_decay, bc1, 
     fn(_p(param), _p(grad), _p(m), _p(v), ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2),
        ctypes.c_float(epsilon), ctypes.c_float(weight_decay), ctypes.c_float(bc1), ctypes.c_float(bc2),
        ctypes.c_int64(param.numel()), _s())
+
+
+def _typed(name, t):
+    return getattr(lib(), name + ("_f32" if t.dtype == torch.float32 else "_bf16"))
+
+
+def sigmoid(x):
+    out = torch.empty_like(x)
+    _typed("ref_sigmoid", x)(_p(x), _p(out), ctypes.c_int64(x.numel()), _s())
+    return out
+
+
+def group_mask_(sel, n_group, topk_group):
+    """launch_moe_group_mask, in place on the [tokens, experts] selection scores."""
+    tokens, experts = sel.shape
+    _typed("ref_group_mask", sel)(_p(sel), ctypes.c_int(tokens), ctypes.c_int(experts), ctypes.c_int(n_group),
+                                  ctypes.c_int(topk_group), _s())
+    return sel
+
+
+def topk_any(x, k):
+    batch, dim = x.shape
+    idx = torch.empty((batch, k), dtype=torch.int32, device=x.device)
+    val = torch.empty((batch, k), dtype=x.dtype, device=x.device)
+    _typed("ref_topk", x)(_p(x), _p(idx), _p(val), ctypes.c_int(batch), ctypes.c_int(dim), ctypes.c_int(k), _s())
+    return idx, val
+
+
+def gather_topk(scores, idx):
+    tokens, experts = scores.shape
+    k = idx.shape[1]
+    out = torch.empty((tokens, k), dtype=scores.dtype, device=scores.device)
+    _typed("ref_gather_topk", scores)(_p(scores), _p(idx), _p(out), ctypes.c_int(tokens), ctypes.c_int(experts),
+                                      ctypes.c_int(k), _s())
+    return out

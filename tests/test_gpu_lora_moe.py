@@ -625,3 +625,40 @@ def test_lora_adamw_step_bit_exact_with_the_reference_kernel(dtype, weight_decay
         for x, y in zip(mine, theirs):
             assert torch.equal(x, y)
     assert not torch.equal(lora.a, a)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("use_bias,n_group,topk_group,logits", [
+    (True, 8, 3, True),      # DeepSeek-V3-style: sigmoid scores, selection-only bias, group-limited
+    (True, 1, 1, True),      # sigmoid + bias, no groups
+    (False, 8, 4, True),     # sigmoid, groups, no bias
+    (False, 4, 2, False),    # softmax probabilities given, groups (DeepSeek-V2 group-limited greedy)
+])
+def test_grouped_sigmoid_routing_bit_exact_with_the_reference_kernels(dtype, use_bias, n_group, topk_group, logits):
+    """caifq_moe_route_grouped against the reference's own kernel sequence (Sigmoid, AddBias, MoEGroupMask, TopK,
+    GatherTopKValues as CAIF_DeviceMoERouter::Route chains them): scores, indices and weights bit for bit;
+    ties (repeated scores) included."""
+    if not ref.available():
+        pytest.skip("reference kernels not built")
+    tokens, experts, k = 777, 64, 6
+    g = torch.Generator(device="cuda").manual_seed(77 + n_group)
+    x = (torch.randn(tokens, experts, generator=g, device="cuda") * 2.0).to(dtype)
+    x[5, 10:20] = x[5, 3]          # ties inside and across groups
+    x[6] = 0.25
+    if not logits:
+        x = nv.moe_softmax(x)
+    bias = (torch.randn(experts, generator=g, device="cuda") * 0.1).to(dtype) if use_bias else None
+    scores, idx, wts = nv.moe_route_grouped(x, k, logits=logits, bias=bias, n_group=n_group, topk_group=topk_group)
+    r_scores = ref.sigmoid(x) if logits else x
+    sel = ref.bias_add(r_scores, bias) if use_bias else r_scores.clone()
+    if n_group > 1:
+        ref.group_mask_(sel, n_group, topk_group)
+    r_idx, r_val = ref.topk_any(sel, k)
+    r_wts = ref.gather_topk(r_scores, r_idx) if use_bias else r_val
+    assert torch.equal(scores, r_scores)
+    assert torch.equal(idx, r_idx)
+    assert torch.equal(wts, r_wts)
+    # every chosen expert lies in one of the topk_group groups the token kept
+    if n_group > 1:
+        groups = (idx // (experts // n_group)).cpu().numpy()
+        assert max(len(set(row)) for row in groups) <= topk_group
