@@ -506,13 +506,14 @@ def test_grouped_experts_on_cta_pairs_equal_single_ctas(storage, compute, monkey
 
 @pytest.mark.parametrize("storage,compute", [(orc.I8, orc.F32), (orc.I8, orc.BF16), (orc.I4, orc.BF16),
                                              (orc.I4, orc.F32)])
-def test_lora_entry_points_that_expand_the_weight_once_per_call(storage, compute):
+@pytest.mark.parametrize("m", [4608, 5003])
+def test_lora_entry_points_that_expand_the_weight_once_per_call(storage, compute, m):
     """caifq_lora_linear_fwd_expanded / _bwd_expanded at a many-token size: the weight goes through a bf16
     copy in the workspace and the CTA-pair tile form.  int8: bit-equal to the plain entry points (exact
     codes, scale in the epilogue).  int4 under bf16 compute: the reference's own operand bf16(scale * code),
     so sampled rows hold the tight bound against the oracle.  int4 under fp32 compute is not expanded
     (same workspace size, same bits)."""
-    m, in_dim, out_dim, rank = 4608, 512, 768, 16
+    in_dim, out_dim, rank = 512, 768, 16
     rng = np.random.default_rng(9300 + storage + compute)
     weight, codes, scales = make_weight(rng, out_dim, in_dim, storage, std=0.05)
     a_np = orc.round_through(rng.uniform(-1 / 16, 1 / 16, (rank, in_dim)).astype(np.float32), orc.BF16)
