@@ -587,6 +587,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   constexpr int ACC_COLS = Cfg::ACC_COLS;
   constexpr int ACC_BUFS = Cfg::ACC_BUFS;
   constexpr uint32_t CTAS = PAIR ? 2u : 1u;   // CTAs that work on one tile
+  // A bf16 weight needs no dequant warps: four of them join the epilogue, so every quarter of the accumulator's
+  // lanes is drained by two warps that take alternate 32-column chunks.
+  constexpr int EPI_GROUPS = (WMODE == W_BF16) ? 2 : 1;
     constexpr int DEQ_TEAMS = deq_teams(PAIR);
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[MAX_STAGES * 3 + 4];
@@ -641,7 +644,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     for (int a = 0; a < ACC_BUFS; ++a)
     {
       mbar_init(acc_full(a), 1);
-      mbar_init(acc_empty(a), 4 * CTAS);
+      mbar_init(acc_empty(a), 4 * EPI_GROUPS * CTAS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -863,10 +866,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     }
   }
-  else if (warp < DEQ_WARP0)
+  else if (warp < DEQ_WARP0 + 4 * (EPI_GROUPS - 1))
   {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+    const int epi_group = (warp - 2) >> 2;   // 0, or 1 for the warps that joined from the dequant role
     int acc = 0;
     uint32_t acc_par = 0;
     for (int tile = worker; tile < num_tiles; tile += workers)
@@ -901,6 +905,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
           for (int cb = 0; cb < HALF / 32; ++cb)
           {
+            if (EPI_GROUPS > 1 && (cb % EPI_GROUPS) != epi_group)
+            {
+              continue;
+            }
             uint32_t rg[32];
             uint32_t ru[32];
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
@@ -952,6 +960,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
         for (int cb = 0; cb < BN / 32; ++cb)
         {
+          if (EPI_GROUPS > 1 && (cb % EPI_GROUPS) != epi_group)
+          {
+            continue;
+          }
           uint32_t r[32];
           const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                  static_cast<uint32_t>(acc * ACC_COLS + mt * BN + cb * 32);
