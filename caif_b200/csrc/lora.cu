@@ -303,37 +303,71 @@ skinny_tn_kernel(const __nv_bfloat16 *__restrict__ u, const __nv_bfloat16 *__res
   {
     c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
   }
-  for (int64_t mb = m_begin; mb < m_end; mb += TN_ROWS)
+  // A tile of 64 tokens x 128 columns of U (16-byte chunks, coalesced) and 64 x R of V goes through registers
+  // into shared memory; the next tile's loads are issued before the current tile's MMAs, so they are in
+  // flight while the tensor core works.
+  constexpr int U_PER_THREAD = TN_ROWS * (TN_COLS / 8) / STN_THREADS;   // 4
+  static_assert(TN_ROWS * (TN_COLS / 8) % STN_THREADS == 0, "whole chunks per thread");
+  static_assert(TN_ROWS * NT <= 2 * STN_THREADS, "at most two chunks of V per thread");
+  uint4 ru[U_PER_THREAD];
+  uint4 rv[2];
+  auto fetch = [&](int64_t mb)
   {
-    // stage 64 tokens x 64 columns of U (16-byte chunks, coalesced) and 64 x R of V
-    for (int e = tid; e < TN_ROWS * (TN_COLS / 8); e += STN_THREADS)
+#pragma unroll
+    for (int i = 0; i < U_PER_THREAD; ++i)
     {
+      const int e = tid + i * STN_THREADS;
       const int rr = e / (TN_COLS / 8);
       const int ch = e % (TN_COLS / 8);
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      ru[i] = make_uint4(0u, 0u, 0u, 0u);
       if (mb + rr < m_end && c0 + ch * 8 < big)
       {
-        val = __ldg(reinterpret_cast<const uint4 *>(u + (mb + rr) * big + c0 + ch * 8));
-        if (u_prescale != 1.0f)
-        {
-          val = make_uint4(scale2(val.x, u_prescale), scale2(val.y, u_prescale), scale2(val.z, u_prescale),
-                           scale2(val.w, u_prescale));
-        }
+        ru[i] = __ldg(reinterpret_cast<const uint4 *>(u + (mb + rr) * big + c0 + ch * 8));
       }
-      *reinterpret_cast<uint4 *>(&su[rr][ch * 8]) = val;
     }
-    for (int e = tid; e < TN_ROWS * NT; e += STN_THREADS)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
     {
-      const int rr = e / NT;
-      const int ch = e % NT;
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
-      if (mb + rr < m_end)
+      const int e = tid + i * STN_THREADS;
+      rv[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (e < TN_ROWS * NT && mb + e / NT < m_end)
       {
-        val = __ldg(reinterpret_cast<const uint4 *>(v + (mb + rr) * R + ch * 8));
+        rv[i] = __ldg(reinterpret_cast<const uint4 *>(v + (mb + e / NT) * R + (e % NT) * 8));
       }
-      *reinterpret_cast<uint4 *>(&sv[rr][ch * 8]) = val;
+    }
+  };
+  if (m_begin < m_end)
+  {
+    fetch(m_begin);
+  }
+  for (int64_t mb = m_begin; mb < m_end; mb += TN_ROWS)
+  {
+#pragma unroll
+    for (int i = 0; i < U_PER_THREAD; ++i)
+    {
+      const int e = tid + i * STN_THREADS;
+      uint4 val = ru[i];
+      if (u_prescale != 1.0f)
+      {
+        val = make_uint4(scale2(val.x, u_prescale), scale2(val.y, u_prescale), scale2(val.z, u_prescale),
+                         scale2(val.w, u_prescale));
+      }
+      *reinterpret_cast<uint4 *>(&su[e / (TN_COLS / 8)][(e % (TN_COLS / 8)) * 8]) = val;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+    {
+      const int e = tid + i * STN_THREADS;
+      if (e < TN_ROWS * NT)
+      {
+        *reinterpret_cast<uint4 *>(&sv[e / NT][(e % NT) * 8]) = rv[i];
+      }
     }
     __syncthreads();
+    if (mb + TN_ROWS < m_end)
+    {
+      fetch(mb + TN_ROWS);
+    }
 #pragma unroll
     for (int k16 = 0; k16 < TN_ROWS / 16; ++k16)
     {
