@@ -460,121 +460,71 @@ int launch_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_
   }
 }
 
-// ---- codes -> bf16 operand matrix (many-token LoRA calls expand the weight once per call) ----
-// One thread per 16 bytes of codes.  int8: 16 codes become exact bf16 integers with byte permutes and
-// one bf16 subtraction per pair.  int4: 32 codes times their group's fp16 scale in fp32, rounded once to
-// bf16 -- the value the reference's dequantize kernel followed by its cast to bf16 gives
-// (src/caif_cuda_kernels_quant.cu:364-420, src/caif_device_frozen_linear.cpp:319-334).
-__global__ void expand_int8_to_bf16_kernel(const uint4 *codes, uint4 *dst, int64_t chunks)
+// ---- codes -> bf16 operand matrix (many-token calls expand the weight once per call / step) ----
+// One thread per 16 bytes of OUTPUT (eight weights: 8 bytes of int8 codes or 4 bytes of int4 codes), so a
+// warp reads 256 / 128 contiguous bytes and writes 512 contiguous bytes per instruction.  int8: exact bf16
+// integers with byte permutes and one bf16 subtraction per pair.  int4: the offset-binary nibble is dropped
+// into the mantissa of 2^23 (exact), 2^23 + 8 subtracted (exact), the product with the group's fp16 scale
+// rounded once in fp32 and once to bf16 -- the value the reference's dequantize kernel followed by its cast
+// to bf16 gives (src/caif_cuda_kernels_quant.cu:364-420, src/caif_device_frozen_linear.cpp:319-334).
+__device__ __forceinline__ uint4 expand_int8x8(const uint2 v)
 {
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
-  {
-    const uint4 v = __ldg(codes + i);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t o[8];
+  const uint32_t w[2] = {v.x, v.y};
+  uint32_t o[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-    {
-      const uint32_t a = __byte_perm(w[k], 0u, 0x4140);   // [b0, 0, b1, 0]
-      const uint32_t b = __byte_perm(w[k], 0u, 0x4342);   // [b2, 0, b3, 0]
-      // low 7 bits in the mantissa of 128.0; the sign bit selects 128.0 or 256.0 to subtract
-      uint32_t lo, hi;
-      asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
-      asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
-      o[2 * k] = lo;
-      o[2 * k + 1] = hi;
-    }
-    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+  for (int k = 0; k < 2; ++k)
+  {
+    const uint32_t a = __byte_perm(w[k], 0u, 0x4140);   // [b0, 0, b1, 0]
+    const uint32_t b = __byte_perm(w[k], 0u, 0x4342);   // [b2, 0, b3, 0]
+    // low 7 bits in the mantissa of 128.0; the sign bit selects 128.0 or 256.0 to subtract
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o[2 * k]) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o[2 * k + 1]) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
   }
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-__global__ void expand_int4_to_bf16_kernel(const uint4 *codes, const __half *scales, uint4 *dst, int64_t chunks,
-                                           int group_size);
+__device__ __forceinline__ uint4 expand_int4x8(const uint32_t w, const float scale)
+{
+  const float base = 8388616.0f;   // 2^23 + 8
+  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;          // elements 0, 2, 4, 6 of the word
+  const uint32_t od = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // elements 1, 3, 5, 7
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+  {
+    const float e = __fmul_rn(__uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base, scale);
+    const float d = __fmul_rn(__uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base, scale);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
 
-// The same for a run of experts of one shape in ONE launch: expert e's matrix goes to dst + e * out * in
-// elements, so the copies lie stacked as one [E * out, in] matrix.
+// `units` = weights / 8 of one matrix; blockIdx.y selects the matrix (expert) of a stacked run
 constexpr int kExpandGroup = 64;
 struct ExpandTable
 {
-  const uint4 *codes[kExpandGroup];
+  const void *codes[kExpandGroup];
   const __half *scales[kExpandGroup];
 };
 
-__device__ __forceinline__ void expand_int8_chunk(const uint4 v, uint4 *dst)
-{
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  uint32_t o[8];
-#pragma unroll
-  for (int k = 0; k < 4; ++k)
-  {
-    const uint32_t a = __byte_perm(w[k], 0u, 0x4140);
-    const uint32_t b = __byte_perm(w[k], 0u, 0x4342);
-    uint32_t lo, hi;
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
-    o[2 * k] = lo;
-    o[2 * k + 1] = hi;
-  }
-  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-}
-
-__device__ __forceinline__ void expand_int4_chunk(const uint4 v, const float scale, uint4 *dst)
-{
-  // Nibbles to floats without integer-to-float conversions: the offset-binary nibble u = q + 8 is dropped into
-  // the mantissa of 2^23 (exact), 2^23 + 8 is subtracted (exact), the product with the scale is rounded once in
-  // fp32 and once to bf16: bf16(fp32(scale * q)), the value of the reference's dequantize followed by its cast.
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  const float base = 8388616.0f;   // 2^23 + 8
-#pragma unroll
-  for (int k = 0; k < 4; ++k)
-  {
-    const uint32_t ev = (w[k] & 0x0F0F0F0Fu) ^ 0x08080808u;          // elements 0, 2, 4, 6 of the word
-    const uint32_t od = ((w[k] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // elements 1, 3, 5, 7
-    uint32_t o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-    {
-      const float e = __fmul_rn(__uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base, scale);
-      const float d = __fmul_rn(__uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base, scale);
-      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
-    }
-    dst[k] = make_uint4(o[0], o[1], o[2], o[3]);
-  }
-}
-
 template <int STORAGE>
-__global__ void expand_grouped_kernel(const __grid_constant__ ExpandTable t, uint4 *dst, int64_t chunks, int group_size)
+__global__ void expand_kernel(const __grid_constant__ ExpandTable t, uint4 *dst, int64_t units, int group_size)
 {
   const int e = blockIdx.y;
-  const uint4 *codes = t.codes[e];
+  uint4 *out = dst + static_cast<int64_t>(e) * units;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  constexpr int OUT = (STORAGE == CAIFQ_I8) ? 2 : 4;   // 16-byte pieces of bf16 per 16 bytes of codes
-  uint4 *out = dst + static_cast<int64_t>(e) * chunks * OUT;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < units; i += stride)
   {
-    const uint4 v = __ldg(codes + i);
     if (STORAGE == CAIFQ_I8)
     {
-      expand_int8_chunk(v, out + 2 * i);
+      out[i] = expand_int8x8(__ldg(static_cast<const uint2 *>(t.codes[e]) + i));
     }
     else
     {
-      expand_int4_chunk(v, __half2float(t.scales[e][(i * 32) / group_size]), out + 4 * i);
+      // eight codes lie in one group
+      const float scale = __half2float(t.scales[e][(i * 8) / group_size]);
+      out[i] = expand_int4x8(__ldg(static_cast<const uint32_t *>(t.codes[e]) + i), scale);
     }
-  }
-}
-
-__global__ void expand_int4_to_bf16_kernel(const uint4 *codes, const __half *scales, uint4 *dst, int64_t chunks,
-                                           int group_size)
-{
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < chunks; i += stride)
-  {
-    // 32 codes lie in one group
-    expand_int4_chunk(__ldg(codes + i), __half2float(scales[(i * 32) / group_size]), dst + 4 * i);
   }
 }
 
@@ -583,73 +533,53 @@ int launch_expand_grouped_to_bf16(const caifq_weight *ws, int count, void *dst, 
   const caifq_weight &w0 = ws[0];
   const int64_t total = static_cast<int64_t>(w0.in_dim) * w0.out_dim;
   const bool i8 = (w0.storage == CAIFQ_I8);
-  if (!(i8 && (total % 16) == 0) &&
-      !(w0.storage == CAIFQ_I4 && (total % 32) == 0 && w0.group_size > 0 && (w0.group_size % 32) == 0))
+  if ((total % 8) != 0 || (!i8 && !(w0.storage == CAIFQ_I4 && w0.group_size > 0 && (w0.group_size % 8) == 0)))
   {
-    set_error("expand_grouped_to_bf16: unsupported weight (storage %d)", w0.storage);
+    set_error("expand_to_bf16: unsupported weight (storage %d)", w0.storage);
     return CAIFQ_ERR_UNSUPPORTED;
   }
-  const int64_t chunks = total / (i8 ? 16 : 32);
+  const int64_t units = total / 8;
   for (int first = 0; first < count; first += kExpandGroup)
   {
     const int n = (count - first < kExpandGroup) ? (count - first) : kExpandGroup;
     ExpandTable t{};
     for (int e = 0; e < n; ++e)
     {
-      t.codes[e] = static_cast<const uint4 *>(ws[first + e].codes);
+      t.codes[e] = ws[first + e].codes;
       t.scales[e] = static_cast<const __half *>(ws[first + e].scales);
       if (!i8 && t.scales[e] == nullptr)
       {
-        set_error("expand_grouped_to_bf16: int4 expert %d has no scales", first + e);
+        set_error("expand_to_bf16: int4 weight %d has no scales", first + e);
+        return CAIFQ_ERR_INVALID;
+      }
+      if ((reinterpret_cast<uintptr_t>(t.codes[e]) & 7u) != 0)
+      {
+        set_error("expand_to_bf16: codes of weight %d are not 8-byte aligned", first + e);
         return CAIFQ_ERR_INVALID;
       }
     }
-    int gx = grid_for(chunks);
-    const int cap = (148 * 8 + n - 1) / n;   // about eight CTAs per SM over all experts
+    int gx = grid_for(units);
+    const int cap = (148 * 8 + n - 1) / n;   // about eight CTAs per SM over all matrices
     if (gx > cap)
     {
       gx = cap;
     }
-    uint4 *out = static_cast<uint4 *>(dst) + static_cast<int64_t>(first) * total / 8;
+    uint4 *out = static_cast<uint4 *>(dst) + static_cast<int64_t>(first) * units;
     const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(n));
     if (i8)
     {
-      expand_grouped_kernel<CAIFQ_I8><<<grid, kBlock, 0, s>>>(t, out, chunks, 0);
+      expand_kernel<CAIFQ_I8><<<grid, kBlock, 0, s>>>(t, out, units, 0);
     }
     else
     {
-      expand_grouped_kernel<CAIFQ_I4><<<grid, kBlock, 0, s>>>(t, out, chunks, w0.group_size);
+      expand_kernel<CAIFQ_I4><<<grid, kBlock, 0, s>>>(t, out, units, w0.group_size);
     }
     CAIFQ_CHECK_LAUNCH();
   }
   return CAIFQ_OK;
 }
 
-int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s)
-{
-  const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;
-  if (w.storage == CAIFQ_I8 && (total % 16) == 0)
-  {
-    const int64_t chunks = total / 16;
-    expand_int8_to_bf16_kernel<<<grid_for(chunks), kBlock, 0, s>>>(static_cast<const uint4 *>(w.codes),
-                                                                  static_cast<uint4 *>(dst), chunks);
-  }
-  else if (w.storage == CAIFQ_I4 && (total % 32) == 0 && w.scales != nullptr && w.group_size > 0 &&
-           (w.group_size % 32) == 0)
-  {
-    const int64_t chunks = total / 32;
-    expand_int4_to_bf16_kernel<<<grid_for(chunks), kBlock, 0, s>>>(static_cast<const uint4 *>(w.codes),
-                                                                  static_cast<const __half *>(w.scales),
-                                                                  static_cast<uint4 *>(dst), chunks, w.group_size);
-  }
-  else
-  {
-    set_error("expand_to_bf16: unsupported weight (storage %d)", w.storage);
-    return CAIFQ_ERR_UNSUPPORTED;
-  }
-  CAIFQ_CHECK_LAUNCH();
-  return CAIFQ_OK;
-}
+int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s) { return launch_expand_grouped_to_bf16(&w, 1, dst, s); }
 
 int launch_weight_materialize(const caifq_weight &w, void *dst, int dst_dtype, cudaStream_t s)
 {
