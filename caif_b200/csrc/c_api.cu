@@ -1256,11 +1256,53 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
   char *g_hidden = static_cast<char *>(ws);
   char *g_gate = g_hidden + total * hid * es;
   char *g_up = g_gate + total * hid * es;
-  int r = grouped_linear(down, num_experts, expert_offsets_host, true, dy, g_hidden, dtype, false, compute_dtype, s,
-                         who);
-  if (r != CAIFQ_OK)
+  int r = CAIFQ_OK;
+  bool swiglu_done = false;
+  if (gate != nullptr && dtype == CAIFQ_BF16 && forced_path() == Force::None)
   {
-    return r;
+    // down^T with the SwiGLU backward in its epilogue: g_gate and g_up leave the launch, g_hidden is never stored
+    GroupedLinearArgs g{};
+    g.weights = down;
+    g.num_experts = num_experts;
+    g.offsets = expert_offsets_host;
+    g.backward = true;
+    g.a = dy;
+    g.a_dtype = dtype;
+    g.c = g_gate;
+    g.c_dtype = dtype;
+    g.accumulate = false;
+    g.compute_dtype = compute_dtype;
+    static const bool grouping = []() {
+      const char *e = std::getenv("CAIFQ_GROUPED");
+      return e == nullptr || e[0] != '0';
+    }();
+    static const bool fuse = []() {
+      const char *e = std::getenv("CAIFQ_FUSED_SWIGLU");
+      return e == nullptr || e[0] != '0';
+    }();
+    if (grouping && fuse && umma_grouped_supported(g) && (reinterpret_cast<uintptr_t>(gate_out) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(up_out) & 15u) == 0 && (reinterpret_cast<uintptr_t>(g_up) & 15u) == 0)
+    {
+      g.sb_gate = gate_out;
+      g.sb_up = up_out;
+      g.sb_g_up = g_up;
+      set_path("umma-grouped");
+      r = launch_linear_umma_grouped(g, s);
+      if (r != CAIFQ_OK)
+      {
+        return r;
+      }
+      swiglu_done = true;
+    }
+  }
+  if (!swiglu_done)
+  {
+    r = grouped_linear(down, num_experts, expert_offsets_host, true, dy, g_hidden, dtype, false, compute_dtype, s,
+                       who);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
   }
   if (gate == nullptr)
   {
@@ -1272,10 +1314,13 @@ int caifq_grouped_expert_bwd(const caifq_weight *gate, const caifq_weight *up, c
     }
     return grouped_linear(up, num_experts, expert_offsets_host, true, g_up, dx, dtype, false, compute_dtype, s, who);
   }
-  r = launch_swiglu_bwd(g_hidden, gate_out, up_out, g_gate, g_up, dtype, total * hid, s);
-  if (r != CAIFQ_OK)
+  if (!swiglu_done)
   {
-    return r;
+    r = launch_swiglu_bwd(g_hidden, gate_out, up_out, g_gate, g_up, dtype, total * hid, s);
+    if (r != CAIFQ_OK)
+    {
+      return r;
+    }
   }
   if (up[0].storage == CAIFQ_BF16 && gate[0].storage == CAIFQ_BF16 && up[0].scales == nullptr &&
       gate[0].scales == nullptr && forced_path() == Force::None)

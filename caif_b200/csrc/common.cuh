@@ -249,6 +249,12 @@ struct GroupedLinearArgs
   // Optional second operand pair (stacked bf16 experts only): c = a . W + a2 . W2 in one accumulation, rounded once
   const caifq_weight *weights2;
   const void *a2;
+  // Optional SwiGLU backward in the epilogue of the dX launch that produces the hidden activation's gradient
+  // (backward, bf16, no accumulate): c receives g_gate, sb_g_up receives g_up; sb_gate / sb_up are the forward's
+  // gate(x) and up(x), all [total_rows, in_dim of the weights]
+  const void *sb_gate;
+  const void *sb_up;
+  void *sb_g_up;
 };
 // gate(x), up(x) and silu(gate(x)) * up(x) of a run of frozen experts in one launch
 // (CAIF_DeviceMoEFrozenExpert::ForwardImpl up to the down projection,

@@ -457,6 +457,12 @@ struct UmmaParams
   const uint8_t *lora_rhs;  // null = no LoRA k-block
   const float *c_scale;     // bf16 weights only: factor of the fp32 accumulator in the epilogue (null = 1)
   int expert_rows;          // grouped bf16 weights: rows of one expert's matrix in the stacked [E * rows, in] matrix
+  // dX launch whose result is the gradient of the experts' hidden activation (down^T): instead of storing it, the
+  // epilogue applies the SwiGLU backward to it and stores the gradients of the gate and up projections' outputs
+  // (c: g_gate, sb_g_up: g_up), reading the forward's gate(x) and up(x) (sb_gate, sb_up).  bf16 only.
+  const void *sb_gate;
+  const void *sb_up;
+  void *sb_g_up;
   int dual_k;               // bf16 weights: the reduction runs over two operand pairs, C = A.W + A2.W2 (A2 through
                             // map_h, W2 through map_l), num_kb k-blocks each
   // Fused gate/up/SwiGLU forward of a frozen expert (forward, 128-wide tiles, 16-bit outputs): a tile's
@@ -969,10 +975,54 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                                  static_cast<uint32_t>(acc * ACC_COLS + mt * BN + cb * 32);
           tmem_ld32(taddr, r);
           tmem_ld_wait();
-          if (row < tw.row_end)
+          // (the last column tile may reach past the output's width when the width is not a multiple of the
+          // tile's: those columns, computed on zero or foreign weight rows, are not stored)
+          if (row < tw.row_end && n_tile * BN + cb * 32 < p.n_total)
           {
             const int64_t off = row * p.n_total + static_cast<int64_t>(n_tile) * BN + cb * 32;
-            if (p.c_dtype == CAIFQ_F32)
+            if (BWD && p.sb_gate != nullptr)
+            {
+              // g_hidden = round(acc); g_up = round(g_hidden * round(silu(gate))); g_gate = round(round(g_hidden *
+              // up) * silu'(gate)): the separate kernel's rounding points (see swiglu_bwd_kernel)
+              const uint4 *gt4 = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.sb_gate) + off);
+              const uint4 *up4 = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(p.sb_up) + off);
+              uint4 *dg = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.c) + off);
+              uint4 *du = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.sb_g_up) + off);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+              {
+                const uint4 gq = __ldg(gt4 + q);
+                const uint4 uq = __ldg(up4 + q);
+                const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+                const uint32_t uw[4] = {uq.x, uq.y, uq.z, uq.w};
+                uint32_t pg[4], pu[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                {
+                  float og[2], ou[2];
+#pragma unroll
+                  for (int z = 0; z < 2; ++z)
+                  {
+                    const float x = z ? __uint_as_float(gw[e] & 0xFFFF0000u) : __uint_as_float(gw[e] << 16);
+                    const float uv = z ? __uint_as_float(uw[e] & 0xFFFF0000u) : __uint_as_float(uw[e] << 16);
+                    const float gh = round_through<CAIFQ_BF16>(__uint_as_float(r[8 * q + 2 * e + z]) * out_scale);
+                    // one fast exponential and one fast reciprocal per element: 256 x 128 elements per tile must
+                    // fit beside the next tile's MMAs (the exact expf and two IEEE divisions did not: 2x slower);
+                    // fp32 relative error ~1e-6 before the bf16 roundings
+                    const float sg = __fdividef(1.0f, 1.0f + __expf(-x));
+                    const float act = round_through<CAIFQ_BF16>(x * sg);
+                    ou[z] = gh * act;
+                    const float gv = round_through<CAIFQ_BF16>(gh * uv);
+                    og[z] = gv * sg * fmaf(x, 1.0f - sg, 1.0f);
+                  }
+                  pg[e] = pack_bf16x2(og[0], og[1]);
+                  pu[e] = pack_bf16x2(ou[0], ou[1]);
+                }
+                dg[q] = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                du[q] = make_uint4(pu[0], pu[1], pu[2], pu[3]);
+              }
+            }
+            else if (p.c_dtype == CAIFQ_F32)
             {
               float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.c) + off);
 #pragma unroll
@@ -1793,6 +1843,13 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
   p.in_dim = w0.in_dim;
   p.group_size = w0.group_size;
   p.groups_per_row = (w0.group_size > 0) ? w0.in_dim / w0.group_size : 0;
+  if (g.backward && g.sb_gate != nullptr && g.sb_up != nullptr && g.sb_g_up != nullptr && g.c_dtype == CAIFQ_BF16 &&
+      !g.accumulate)
+  {
+    p.sb_gate = g.sb_gate;
+    p.sb_up = g.sb_up;
+    p.sb_g_up = g.sb_g_up;
+  }
   CUtensorMap map_a;
   int rc = make_map_bf16(&map_a, g.a, static_cast<uint64_t>(p.k_total), static_cast<uint64_t>(total_rows), BM_SUB);
   if (rc != CAIFQ_OK)
@@ -1828,9 +1885,11 @@ int launch_linear_umma_grouped(const GroupedLinearArgs &g, cudaStream_t s)
     if (mode == W_BF16)
     {
       // stacked bf16 experts: one map over [count * out, in]; pairs when the width allows, else 128-wide tiles
-      const bool wide = (p.n_total % 256) == 0 && static_cast<int64_t>(tiles) * (p.n_total / 256) >= pair_count_umma() &&
-                        pairs_enabled(mode);
-      p.num_n_tiles = p.n_total / (wide ? 256 : 128);
+      // (a width that is a multiple of 128 only, like 1408, still takes 256-wide pair tiles: the last tile's upper
+      // half is masked in the epilogue, 9 % of wasted MMAs against 62 -> 85 % tensor activity)
+      const int wide_tiles = (p.n_total + 255) / 256;
+      const bool wide = static_cast<int64_t>(tiles) * wide_tiles >= pair_count_umma() && pairs_enabled(mode);
+      p.num_n_tiles = wide ? wide_tiles : p.n_total / 128;
       p.expert_rows = w0.out_dim;
       CUtensorMap map_b;
       rc = make_map_bf16(&map_b, g.weights[first].codes, static_cast<uint64_t>(w0.in_dim),
