@@ -1007,7 +1007,7 @@ def bench_c5(ctx):
                      "peak_source": ctx.peaks["source"], "kernel": "frozen experts path '%s'" % path,
                      "note": "expert GEMM flops over the whole step (dispatch, SwiGLU, combine and their backward "
                              "kernels%s included in the time)" % (", both all-to-alls" if world > 1 else "")},
-        "e2e": e2e, "gpu_launches": (13 + (3 if ops.expanded is not None else 0)) * steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": (11 if ops.expanded is not None else 9) * steps, "clocks": clocks,
     }
     if parity is not None:
         result["parity"] = parity
