@@ -857,7 +857,7 @@ def bench_c3(ctx):
         "metric": METRIC["c3"][0], "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": SCALING["c3"],
         "vs_baseline": None, "dtype": "bf16 (fp32 accumulate)", "data": "synthetic", "config": config_for("c3", 1),
-        "roofline": roofline, "e2e": e2e, "gpu_launches": 13 * steps, "clocks": clocks,   # 11 + the two weight expansions
+        "roofline": roofline, "e2e": e2e, "gpu_launches": 10 * steps, "clocks": clocks,   # forward 3, backward 7 kernels
     }
 
 
@@ -1201,7 +1201,7 @@ def bench_c4lin(ctx):
                      "traffic": None, "peak_source": ctx.peaks["source"], "kernel": "frozen linear path '%s'" % path,
                      "note": "flops of the 224 projections (fwd + dX + LoRA) over the whole step; the step is seconds "
                              "long, so the sustained peak is the fair denominator"},
-        "e2e": e2e, "gpu_launches": layers * len(C4_PROJ) * 13 * steps, "clocks": clocks,
+        "e2e": e2e, "gpu_launches": layers * len(C4_PROJ) * 10 * steps, "clocks": clocks,
     }
     if world > 1:
         total = sum(coll_bytes.values())

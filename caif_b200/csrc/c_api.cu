@@ -128,6 +128,8 @@ int launch_skinny_tn(const void *u, const void *v, void *c, float *scratch, floa
 int launch_lora_pad_b(const void *b, void *bp, int n, int rank, cudaStream_t s);
 int launch_lora_transpose_b(const void *b, void *bt, int n, int rank, cudaStream_t s);
 int launch_lora_pad_a(const void *a, void *ap, int n, int rank, cudaStream_t s);
+int launch_expand_prepare(const caifq_weight &w, void *wb, const void *a, const void *b, void *bp, void *bt, void *ap,
+                          int rank, cudaStream_t s);
 
 namespace
 {
@@ -659,7 +661,11 @@ int lora_fwd_impl(const caifq_weight *w, const caifq_lora *lora, const void *x, 
     // then one tensor-core launch computes x . W^T and Hs . Bp^T into the same accumulators.
     const LoraFwdWs ws = lora_fwd_ws(w, m);
     char *base = static_cast<char *>(workspace);
-    int r = launch_lora_pad_b(lora->b, base + ws.bp, w->out_dim, lora->rank, s);
+    const bool expand = may_expand && expand_ok(w, lora, x, m, compute_dtype);
+    void *wb = base + ws.total;   // (expanded calls) the weight as a bf16 matrix behind the other scratch
+    // the padded B factor, and with it the expansion of the weight where the call expands: one launch
+    int r = expand ? launch_expand_prepare(*w, wb, lora->a, lora->b, base + ws.bp, nullptr, nullptr, lora->rank, s)
+                   : launch_lora_pad_b(lora->b, base + ws.bp, w->out_dim, lora->rank, s);
     if (r == CAIFQ_OK)
     {
       r = launch_skinny_nt(x, lora->a, hidden, base + ws.hs, 1.0f, scale, epilogue_scale_ptr(w), m, w->in_dim,
@@ -669,15 +675,8 @@ int lora_fwd_impl(const caifq_weight *w, const caifq_lora *lora, const void *x, 
     {
       return r;
     }
-    if (may_expand && expand_ok(w, lora, x, m, compute_dtype))
+    if (expand)
     {
-      // the weight as a bf16 matrix behind the other scratch, then the same launch on it
-      void *wb = base + ws.total;
-      r = launch_expand_to_bf16(*w, wb, s);
-      if (r != CAIFQ_OK)
-      {
-        return r;
-      }
       const caifq_weight wbf = float_weight(wb, CAIFQ_BF16, w->out_dim, w->in_dim);
       return linear_any(&wbf, false, x, sd, 1.0f, m, y, sd, false, compute_dtype, s, who, base + ws.hs, base + ws.bp,
                         epilogue_scale_ptr(w));
@@ -772,10 +771,21 @@ int lora_bwd_impl(const caifq_weight *w, const caifq_lora *lora, const void *dy,
   if (fused_lora_ok(w, lora, dy, m, compute_dtype) && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0)
   {
     // dH = (scale . dy) . B through the transposed copy of B; dHs = dH / epilogue scale, padded
-    int r = launch_lora_transpose_b(lora->b, wbase + ws.bt, w->out_dim, lora->rank, s);
-    if (r == CAIFQ_OK)
+    const bool expand = may_expand && expand_ok(w, lora, dy, m, compute_dtype);
+    void *wb = wbase + ws.total;
+    int r = CAIFQ_OK;
+    if (expand)
     {
-      r = launch_lora_pad_a(lora->a, wbase + ws.ap, w->in_dim, lora->rank, s);
+      // transposed B, padded A and the expansion of the weight in one launch
+      r = launch_expand_prepare(*w, wb, lora->a, lora->b, nullptr, wbase + ws.bt, wbase + ws.ap, lora->rank, s);
+    }
+    else
+    {
+      r = launch_lora_transpose_b(lora->b, wbase + ws.bt, w->out_dim, lora->rank, s);
+      if (r == CAIFQ_OK)
+      {
+        r = launch_lora_pad_a(lora->a, wbase + ws.ap, w->in_dim, lora->rank, s);
+      }
     }
     if (r == CAIFQ_OK)
     {
@@ -796,14 +806,8 @@ int lora_bwd_impl(const caifq_weight *w, const caifq_lora *lora, const void *dy,
       return r;
     }
     // dx = dy . W + dHs . Ap in one tensor-core launch
-    if (may_expand && expand_ok(w, lora, dy, m, compute_dtype))
+    if (expand)
     {
-      void *wb = wbase + ws.total;
-      r = launch_expand_to_bf16(*w, wb, s);
-      if (r != CAIFQ_OK)
-      {
-        return r;
-      }
       const caifq_weight wbf = float_weight(wb, CAIFQ_BF16, w->out_dim, w->in_dim);
       return linear_any(&wbf, true, dy, sd, 1.0f, m, dx, sd, false, compute_dtype, s, who, wbase + ws.dhs,
                         wbase + ws.ap, epilogue_scale_ptr(w));

@@ -96,6 +96,39 @@ __device__ __forceinline__ void store_from_float(void *p, int64_t i, int dtype, 
   }
 }
 
+// ---- eight quantized codes -> eight bf16 values (one 16-byte store), used by the expansion kernels
+__device__ __forceinline__ uint4 expand_int8x8(const uint2 v)
+{
+  const uint32_t w[2] = {v.x, v.y};
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 2; ++k)
+  {
+    const uint32_t a = __byte_perm(w[k], 0u, 0x4140);   // [b0, 0, b1, 0]
+    const uint32_t b = __byte_perm(w[k], 0u, 0x4342);   // [b2, 0, b3, 0]
+    // low 7 bits in the mantissa of 128.0; the sign bit selects 128.0 or 256.0 to subtract
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o[2 * k]) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o[2 * k + 1]) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__device__ __forceinline__ uint4 expand_int4x8(const uint32_t w, const float scale)
+{
+  const float base = 8388616.0f;   // 2^23 + 8
+  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;          // elements 0, 2, 4, 6 of the word
+  const uint32_t od = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // elements 1, 3, 5, 7
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+  {
+    const float e = __fmul_rn(__uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base, scale);
+    const float d = __fmul_rn(__uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base, scale);
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // Round an fp32 value through a 16-bit float dtype (nearest even) and back.
 template <int DTYPE>
 __device__ __forceinline__ float round_through(float v)

@@ -585,6 +585,116 @@ int launch_skinny_tn(const void *u, const void *v, void *c, float *scratch, floa
   return CAIFQ_OK;
 }
 
+// The weight's expansion to bf16 and the small re-layouts of the LoRA factors that a call needs, in ONE launch
+// (they are independent of each other and each of them alone is mostly launch latency):
+//   blockIdx.y == 0: the expansion (8 weights per thread and step);
+//   blockIdx.y == 1: Bp = pad(B) [n_b, 64]      (forward), or
+//                    Bt = B^T [r, n_b] and Ap = pad(A) [64, n_a]   (backward).
+struct ExpandPrepare
+{
+  const void *codes;
+  const __half *scales;
+  uint4 *wb;
+  int64_t units;      // weights / 8
+  int group_size;
+  const __nv_bfloat16 *a;   // [r, n_a]
+  const __nv_bfloat16 *b;   // [n_b, r]
+  __nv_bfloat16 *bp;        // forward: [n_b, 64]
+  __nv_bfloat16 *bt;        // backward: [r, n_b]
+  __nv_bfloat16 *ap;        // backward: [64, n_a]
+  int n_a, n_b, r;
+};
+
+template <int STORAGE>
+__global__ void expand_prepare_kernel(const ExpandPrepare p)
+{
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (blockIdx.y == 0)
+  {
+    for (int64_t i = first; i < p.units; i += stride)
+    {
+      if (STORAGE == CAIFQ_I8)
+      {
+        p.wb[i] = expand_int8x8(__ldg(static_cast<const uint2 *>(p.codes) + i));
+      }
+      else
+      {
+        p.wb[i] = expand_int4x8(__ldg(static_cast<const uint32_t *>(p.codes) + i),
+                                __half2float(p.scales[(i * 8) / p.group_size]));
+      }
+    }
+    return;
+  }
+  const __nv_bfloat16 zero = __float2bfloat16(0.0f);
+  if (p.bp != nullptr)
+  {
+    const int64_t total = static_cast<int64_t>(p.n_b) * 64;
+    for (int64_t i = first; i < total; i += stride)
+    {
+      const int col = static_cast<int>(i & 63);
+      p.bp[i] = (col < p.r) ? p.b[(i >> 6) * p.r + col] : zero;
+    }
+  }
+  if (p.bt != nullptr)
+  {
+    const int64_t total = static_cast<int64_t>(p.n_b) * p.r;
+    for (int64_t i = first; i < total; i += stride)
+    {
+      p.bt[i] = p.b[(i % p.n_b) * p.r + i / p.n_b];
+    }
+  }
+  if (p.ap != nullptr)
+  {
+    const int64_t total = static_cast<int64_t>(64) * p.n_a;
+    const int64_t live = static_cast<int64_t>(p.r) * p.n_a;
+    for (int64_t i = first; i < total; i += stride)
+    {
+      p.ap[i] = (i < live) ? p.a[i] : zero;
+    }
+  }
+}
+
+// forward: bp != null; backward: bt and ap != null.  The weight must be one launch_expand_to_bf16 takes.
+int launch_expand_prepare(const caifq_weight &w, void *wb, const void *a, const void *b, void *bp, void *bt, void *ap,
+                          int rank, cudaStream_t s)
+{
+  const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;
+  const bool i8 = (w.storage == CAIFQ_I8);
+  if ((total % 8) != 0 || (!i8 && !(w.storage == CAIFQ_I4 && w.scales != nullptr && w.group_size > 0 &&
+                                    (w.group_size % 8) == 0)) ||
+      (reinterpret_cast<uintptr_t>(w.codes) & 7u) != 0)
+  {
+    set_error("expand_prepare: unsupported weight (storage %d)", w.storage);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  ExpandPrepare p{};
+  p.codes = w.codes;
+  p.scales = static_cast<const __half *>(w.scales);
+  p.wb = static_cast<uint4 *>(wb);
+  p.units = total / 8;
+  p.group_size = w.group_size;
+  p.a = static_cast<const __nv_bfloat16 *>(a);
+  p.b = static_cast<const __nv_bfloat16 *>(b);
+  p.bp = static_cast<__nv_bfloat16 *>(bp);
+  p.bt = static_cast<__nv_bfloat16 *>(bt);
+  p.ap = static_cast<__nv_bfloat16 *>(ap);
+  p.n_a = w.in_dim;
+  p.n_b = w.out_dim;
+  p.r = rank;
+  const dim3 grid(148 * 8, 2);
+  if (i8)
+  {
+    expand_prepare_kernel<CAIFQ_I8><<<grid, 256, 0, s>>>(p);
+  }
+  else
+  {
+    expand_prepare_kernel<CAIFQ_I4><<<grid, 256, 0, s>>>(p);
+  }
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
 int launch_lora_pad_b(const void *b, void *bp, int n, int rank, cudaStream_t s)
 {
   lora_pad_b_kernel<<<148 * 2, 256, 0, s>>>(static_cast<const __nv_bfloat16 *>(b), static_cast<__nv_bfloat16 *>(bp), n,

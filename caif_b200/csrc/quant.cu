@@ -467,38 +467,6 @@ int launch_cast(const void *src, int src_dtype, void *dst, int dst_dtype, int64_
 // into the mantissa of 2^23 (exact), 2^23 + 8 subtracted (exact), the product with the group's fp16 scale
 // rounded once in fp32 and once to bf16 -- the value the reference's dequantize kernel followed by its cast
 // to bf16 gives (src/caif_cuda_kernels_quant.cu:364-420, src/caif_device_frozen_linear.cpp:319-334).
-__device__ __forceinline__ uint4 expand_int8x8(const uint2 v)
-{
-  const uint32_t w[2] = {v.x, v.y};
-  uint32_t o[4];
-#pragma unroll
-  for (int k = 0; k < 2; ++k)
-  {
-    const uint32_t a = __byte_perm(w[k], 0u, 0x4140);   // [b0, 0, b1, 0]
-    const uint32_t b = __byte_perm(w[k], 0u, 0x4342);   // [b2, 0, b3, 0]
-    // low 7 bits in the mantissa of 128.0; the sign bit selects 128.0 or 256.0 to subtract
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o[2 * k]) : "r"((a & 0x007F007Fu) | 0x43004300u), "r"((a & 0x00800080u) | 0x43004300u));
-    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(o[2 * k + 1]) : "r"((b & 0x007F007Fu) | 0x43004300u), "r"((b & 0x00800080u) | 0x43004300u));
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
-}
-
-__device__ __forceinline__ uint4 expand_int4x8(const uint32_t w, const float scale)
-{
-  const float base = 8388616.0f;   // 2^23 + 8
-  const uint32_t ev = (w & 0x0F0F0F0Fu) ^ 0x08080808u;          // elements 0, 2, 4, 6 of the word
-  const uint32_t od = ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;   // elements 1, 3, 5, 7
-  uint32_t o[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j)
-  {
-    const float e = __fmul_rn(__uint_as_float(__byte_perm(ev, 0x4B000000u, 0x7440 + j)) - base, scale);
-    const float d = __fmul_rn(__uint_as_float(__byte_perm(od, 0x4B000000u, 0x7440 + j)) - base, scale);
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[j]) : "f"(d), "f"(e));
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
-}
-
 // `units` = weights / 8 of one matrix; blockIdx.y selects the matrix (expert) of a stacked run
 constexpr int kExpandGroup = 64;
 struct ExpandTable
