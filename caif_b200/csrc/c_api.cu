@@ -113,6 +113,13 @@ size_t gemm_tn_scratch_bytes(int p, int q);
 int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
                    float u_prescale, int64_t m, int p, int q, cudaStream_t s);
 int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
+int launch_moe_router_bwd(const void *grad_w, const void *probs, const int *indices, const void *balance_bias,
+                          const void *z_lse_scaled, void *grad_topk, void *grad_logits, int dtype, int tokens,
+                          int experts, int top_k, int sigmoid_gate, int normalize, float scaling, int exact_jacobian,
+                          cudaStream_t s);
+int launch_moe_aux_losses(const void *logits, const void *probs, const int *expert_offsets, void *balance_bias,
+                          void *lse, void *z_lse_scaled, float *sums, int dtype, int tokens, int experts, int top_k,
+                          float balance_weight, float z_weight, cudaStream_t s);
 int launch_moe_route_grouped(const void *input, const void *bias, void *scores_out, int *indices, void *weights,
                              int dtype, int batch, int dim, int k, int n_group, int topk_group, int apply_sigmoid,
                              cudaStream_t s);
@@ -970,6 +977,40 @@ int caifq_moe_route_grouped(const void *input, int32_t input_is_logits, const vo
   CAIFQ_CHECK_ARG(n_group <= 32, "%s: at most 32 groups", who);
   return launch_moe_route_grouped(input, selection_bias, scores_out, indices, weights, dtype, batch, dim, k, n_group,
                                   topk_group, input_is_logits ? 1 : 0, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_router_bwd(const void *grad_weights, const void *probs, const int32_t *indices, const void *balance_bias,
+                         const void *z_lse_scaled, void *grad_topk, void *grad_logits, int32_t dtype, int32_t tokens,
+                         int32_t experts, int32_t top_k, int32_t sigmoid_gate, int32_t normalize,
+                         float routed_scaling_factor, int32_t exact_jacobian, void *stream)
+{
+  const char *who = "caifq_moe_router_bwd";
+  CAIFQ_CHECK_ARG(tokens >= 0 && experts > 0 && top_k > 0 && top_k <= 32 && top_k <= experts,
+                  "%s: bad shape tokens=%d experts=%d top_k=%d (top_k <= 32)", who, tokens, experts, top_k);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(tokens == 0 || (grad_weights && probs && indices && grad_logits), "%s: null pointer", who);
+  CAIFQ_CHECK_ARG(!(sigmoid_gate && (balance_bias || z_lse_scaled)),
+                  "%s: sigmoid gating takes no load-balance or z-loss operand", who);
+  return launch_moe_router_bwd(grad_weights, probs, indices, balance_bias, z_lse_scaled, grad_topk, grad_logits,
+                               dtype, tokens, experts, top_k, sigmoid_gate ? 1 : 0, normalize ? 1 : 0,
+                               routed_scaling_factor, exact_jacobian ? 1 : 0, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_aux_losses(const void *logits, const void *probs, const int32_t *expert_offsets, void *balance_bias,
+                         void *lse, void *z_lse_scaled, float *sums, int32_t dtype, int32_t tokens, int32_t experts,
+                         int32_t top_k, float balance_weight, float z_weight, void *stream)
+{
+  const char *who = "caifq_moe_aux_losses";
+  CAIFQ_CHECK_ARG(tokens > 0 && experts > 0 && top_k > 0, "%s: bad shape tokens=%d experts=%d top_k=%d", who, tokens,
+                  experts, top_k);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(sums != nullptr, "%s: sums is null", who);
+  CAIFQ_CHECK_ARG(expert_offsets != nullptr || (probs == nullptr && balance_bias == nullptr),
+                  "%s: the load-balance terms need expert_offsets", who);
+  CAIFQ_CHECK_ARG(logits != nullptr || (lse == nullptr && z_lse_scaled == nullptr),
+                  "%s: the z-loss terms need logits", who);
+  return launch_moe_aux_losses(logits, probs, expert_offsets, balance_bias, lse, z_lse_scaled, sums, dtype, tokens,
+                               experts, top_k, balance_weight, z_weight, static_cast<cudaStream_t>(stream));
 }
 
 int caifq_lora_adamw_step(void *a, void *b, const void *d_a, const void *d_b, float *m_a, float *v_a, float *m_b,

@@ -386,6 +386,300 @@ __global__ void router_softmax_kernel(const T *__restrict__ logits, const T *__r
   }
 }
 
+// --------------------------------------------------------------- router backward
+// CAIF_DeviceMoERouter::BackwardRoutingAuxAware (src/caif_device_moe_router.cpp:529-733) reaches
+// grad_logits through up to seven launches, each rounding to the storage type: the normalize Jacobian
+// over the chosen scores (src/caif_cuda_kernels_moe.cu:128-171), Scale by routed_scaling_factor, Zeros +
+// ScatterAdd into [tokens, experts] (:553-572), AddBias of the load-balance column term, the softmax
+// Jacobian (src/caif_cuda_kernels_attention_support.cu:464-530) and the z-loss term (_moe.cu:1376-1395);
+// sigmoid gating ends with SigmoidBackward (src/caif_cuda_kernels_activations.cu:189-228) instead.  Here
+// one warp owns a token and does all of it with the row of grad_probs in shared memory.  Every
+// intermediate is rounded to T where the reference stores it, and every reduction adds in the reference's
+// order (an xor butterfly over 32 lanes for the top-k sums; for the softmax dot 128 threads striding the
+// row with fused multiply-adds, a butterfly per warp and (w0 + w2) + (w1 + w3) across the four warps), so
+// the result has the reference's bits.
+//
+// The reference calls SoftmaxBackward(probs, grad_probs, grad_logits): the cached probabilities sit in
+// the kernel's grad_output slot and grad_probs in its output slot, which evaluates
+// grad_probs * (probs - dot) rather than probs * (grad_probs - dot).  `exact_jacobian` == 0 keeps that
+// evaluation (parity with the reference); 1 gives the softmax Jacobian itself.
+constexpr float kTopkSumEps = 1e-12f;
+
+template <typename T>
+__global__ void router_bwd_kernel(const T *__restrict__ grad_w, const T *__restrict__ probs,
+                                  const int *__restrict__ indices, const T *__restrict__ balance_bias,
+                                  const T *__restrict__ z_lse_scaled, T *__restrict__ grad_topk,
+                                  T *__restrict__ grad_logits, int tokens, int experts, int top_k, int sigmoid_gate,
+                                  int normalize, float scaling, int exact_jacobian)
+{
+  extern __shared__ float rb_rows[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * warps_per_block + warp;
+  if (t >= tokens)
+  {
+    return;
+  }
+  float *gp = rb_rows + static_cast<size_t>(warp) * experts;
+  const T *p_row = probs + static_cast<size_t>(t) * experts;
+  for (int c = lane; c < experts; c += 32)
+  {
+    gp[c] = 0.0f;
+  }
+  int idx = -1;
+  float p_k = 0.0f;
+  float g_k = 0.0f;
+  if (lane < top_k)
+  {
+    idx = indices[static_cast<size_t>(t) * top_k + lane];
+    g_k = to_f<T>(grad_w[static_cast<size_t>(t) * top_k + lane]);
+    if (idx >= 0 && idx < experts)
+    {
+      p_k = to_f<T>(p_row[idx]);
+    }
+  }
+  float gt = g_k;
+  if (normalize != 0)
+  {
+    float sum = p_k;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+    {
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
+    }
+    sum = fmaxf(sum, kTopkSumEps);
+    const float inv = __fdiv_rn(1.0f, sum);
+    float dot = __fmul_rn(__fmul_rn(p_k, inv), g_k);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+    {
+      dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
+    }
+    gt = to_f<T>(from_f<T>(__fmul_rn(__fsub_rn(g_k, dot), inv)));
+  }
+  if (scaling != 1.0f)
+  {
+    gt = to_f<T>(from_f<T>(__fmul_rn(gt, scaling)));
+  }
+  if (grad_topk != nullptr && lane < top_k)
+  {
+    grad_topk[static_cast<size_t>(t) * top_k + lane] = from_f<T>(gt);
+  }
+  __syncwarp();
+  // the scatter: one add per chosen expert, rounded to T like the reference's atomic on T
+  for (int k = 0; k < top_k; ++k)
+  {
+    const int ik = __shfl_sync(0xFFFFFFFFu, idx, k);
+    const float vk = __shfl_sync(0xFFFFFFFFu, gt, k);
+    if (lane == 0 && ik >= 0 && ik < experts)
+    {
+      gp[ik] = to_f<T>(from_f<T>(__fadd_rn(gp[ik], vk)));
+    }
+  }
+  __syncwarp();
+  T *out = grad_logits + static_cast<size_t>(t) * experts;
+  if (sigmoid_gate != 0)
+  {
+    for (int c = lane; c < experts; c += 32)
+    {
+      const float ov = to_f<T>(p_row[c]);
+      out[c] = from_f<T>(__fmul_rn(__fmul_rn(gp[c], ov), __fsub_rn(1.0f, ov)));
+    }
+    return;
+  }
+  if (balance_bias != nullptr)
+  {
+    for (int c = lane; c < experts; c += 32)
+    {
+      gp[c] = to_f<T>(from_f<T>(__fadd_rn(gp[c], to_f<T>(balance_bias[c]))));
+    }
+    __syncwarp();
+  }
+  float part[4];
+#pragma unroll
+  for (int w = 0; w < 4; ++w)
+  {
+    part[w] = 0.0f;
+    for (int c = 32 * w + lane; c < experts; c += 128)
+    {
+      part[w] = __fmaf_rn(to_f<T>(p_row[c]), gp[c], part[w]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+    {
+      part[w] += __shfl_xor_sync(0xFFFFFFFFu, part[w], off);
+    }
+  }
+  const float dot = __fadd_rn(__fadd_rn(part[0], part[2]), __fadd_rn(part[1], part[3]));
+  const float lse = (z_lse_scaled != nullptr) ? to_f<T>(z_lse_scaled[t]) : 0.0f;
+  for (int c = lane; c < experts; c += 32)
+  {
+    const float p = to_f<T>(p_row[c]);
+    const float g = gp[c];
+    const float y = exact_jacobian != 0 ? p : g;
+    const float dy = exact_jacobian != 0 ? g : p;
+    T v = from_f<T>(__fmul_rn(y, __fsub_rn(dy, dot)));
+    if (z_lse_scaled != nullptr)
+    {
+      v = from_f<T>(__fmaf_rn(lse, p, to_f<T>(v)));
+    }
+    out[c] = v;
+  }
+}
+
+// ------------------------------------------------------------------- aux losses
+// CAIF_DeviceMoELayer::ComputeBalanceLoss / ComputeZLoss and the two gradient operands its backward
+// builds (src/caif_device_moe_layer.cpp:792-835, 853-925).  Pass 1, one warp per token: the row's
+// logsumexp in the order of the reference's 256-thread shared-memory tree (for rows up to 256 wide: pairs
+// (c, c + 128), (c, c + 64), (c, c + 32), then 16 ... 1), rounded to T as the cached tensor is, its
+// square rounded to T summed into sums[1], the scaled copy for the z-loss gradient, and the column sums
+// of the probabilities into sums[2 ...].  Pass 2, one CTA: the two loss values and the per-expert
+// load-balance term.  The reference adds each column sequentially over the tokens and its sum of squares
+// with atomics; the sums here add in another order, so the two loss values agree to rounding, not bits.
+template <typename T>
+__global__ void aux_rows_kernel(const T *__restrict__ logits, const T *__restrict__ probs, T *__restrict__ lse_out,
+                                T *__restrict__ z_lse_scaled, float *__restrict__ sums, int tokens, int experts,
+                                float z_scale)
+{
+  extern __shared__ float aux_cols[];   // [experts] column sums of this CTA, then one slot for the squares
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int warps_per_block = blockDim.x >> 5;
+  for (int c = threadIdx.x; c <= experts; c += blockDim.x)
+  {
+    aux_cols[c] = 0.0f;
+  }
+  __syncthreads();
+  float sq = 0.0f;
+  for (int t = blockIdx.x * warps_per_block + warp; t < tokens; t += gridDim.x * warps_per_block)
+  {
+    if (probs != nullptr)
+    {
+      const T *p_row = probs + static_cast<size_t>(t) * experts;
+      for (int c = lane; c < experts; c += 32)
+      {
+        atomicAdd(&aux_cols[c], to_f<T>(p_row[c]));
+      }
+    }
+    if (logits != nullptr)
+    {
+      const T *x = logits + static_cast<size_t>(t) * experts;
+      // thread tid of the reference's block holds columns tid, tid + 256, ...; lane l plays threads
+      // l + 32 j, j = 0..7
+      float vmax[8];
+      float m = kNegSentinel;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+      {
+        vmax[j] = kNegSentinel;
+        for (int c = lane + 32 * j; c < experts; c += 256)
+        {
+          vmax[j] = fmaxf(vmax[j], to_f<T>(x[c]));
+        }
+        m = fmaxf(m, vmax[j]);
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+      {
+        m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, off));
+      }
+      float e[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+      {
+        e[j] = 0.0f;
+        for (int c = lane + 32 * j; c < experts; c += 256)
+        {
+          e[j] += expf(to_f<T>(x[c]) - m);
+        }
+      }
+      // strides 128, 64, 32 of the tree fold thread t + stride into thread t
+      float v = __fadd_rn(__fadd_rn(__fadd_rn(e[0], e[4]), __fadd_rn(e[2], e[6])),
+                          __fadd_rn(__fadd_rn(e[1], e[5]), __fadd_rn(e[3], e[7])));
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+      {
+        v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+      }
+      const T lse_t = from_f<T>(m + logf(v));
+      const float lse_f = to_f<T>(lse_t);
+      if (lane == 0)
+      {
+        if (lse_out != nullptr)
+        {
+          lse_out[t] = lse_t;
+        }
+        if (z_lse_scaled != nullptr)
+        {
+          z_lse_scaled[t] = from_f<T>(__fmul_rn(lse_f, z_scale));
+        }
+        sq += to_f<T>(from_f<T>(__fmul_rn(lse_f, lse_f)));
+      }
+    }
+  }
+  if (lane == 0 && logits != nullptr)
+  {
+    atomicAdd(&aux_cols[experts], sq);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < experts; c += blockDim.x)
+  {
+    if (probs != nullptr)
+    {
+      atomicAdd(&sums[2 + c], aux_cols[c]);
+    }
+  }
+  if (threadIdx.x == 0 && logits != nullptr)
+  {
+    atomicAdd(&sums[1], aux_cols[experts]);
+  }
+}
+
+template <typename T>
+__global__ void aux_finish_kernel(float *__restrict__ sums, const int *__restrict__ expert_offsets,
+                                  T *__restrict__ balance_bias, int tokens, int experts, int top_k,
+                                  float balance_weight, float z_weight, int have_logits, int have_probs)
+{
+  if (balance_bias != nullptr)
+  {
+    // scale * count in the reference's float operations, stored as T
+    const float denom = __fmul_rn(__fmul_rn(static_cast<float>(tokens), static_cast<float>(tokens)),
+                                  static_cast<float>(top_k));
+    const float scale = __fdiv_rn(__fmul_rn(balance_weight, static_cast<float>(experts)), denom);
+    for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    {
+      const int count = expert_offsets[e + 1] - expert_offsets[e];
+      balance_bias[e] = from_f<T>(__fmul_rn(scale, static_cast<float>(count)));
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+  {
+    float balance = 0.0f;
+    if (have_probs != 0)
+    {
+      const float total = __fmul_rn(static_cast<float>(tokens), static_cast<float>(top_k));
+      float loss = 0.0f;
+      for (int e = 0; e < experts; ++e)
+      {
+        const int count = expert_offsets[e + 1] - expert_offsets[e];
+        const float fraction = __fdiv_rn(static_cast<float>(count), total);
+        const float mean_p = __fdiv_rn(to_f<T>(from_f<T>(sums[2 + e])), static_cast<float>(tokens));
+        loss = __fadd_rn(loss, __fmul_rn(fraction, mean_p));
+      }
+      balance = __fmul_rn(__fmul_rn(balance_weight, static_cast<float>(experts)), loss);
+    }
+    float z = 0.0f;
+    if (have_logits != 0)
+    {
+      z = __fdiv_rn(__fmul_rn(z_weight, to_f<T>(from_f<T>(sums[1]))), static_cast<float>(tokens));
+    }
+    sums[0] = balance;
+    sums[1] = z;
+  }
+}
+
 // ------------------------------------------------------------------ dispatch map
 // Stable counting rank on the device.  One CTA walks the [T*k] index list in
 // chunks of blockDim entries; inside a chunk, warps rank equal experts with
@@ -1001,6 +1295,69 @@ int launch_moe_router_softmax(const void *logits, const void *bias, void *probs,
   CAIFQ_DISPATCH_FLOAT(dtype, (router_softmax_kernel<T><<<grid, warps * 32, 0, s>>>(
                                   static_cast<const T *>(logits), static_cast<const T *>(bias),
                                   static_cast<T *>(probs), rows, cols)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_router_bwd(const void *grad_w, const void *probs, const int *indices, const void *balance_bias,
+                          const void *z_lse_scaled, void *grad_topk, void *grad_logits, int dtype, int tokens,
+                          int experts, int top_k, int sigmoid_gate, int normalize, float scaling, int exact_jacobian,
+                          cudaStream_t s)
+{
+  if (tokens <= 0)
+  {
+    return CAIFQ_OK;
+  }
+  const size_t per_warp = static_cast<size_t>(experts) * sizeof(float);
+  int warps = 8;
+  while (warps > 1 && warps * per_warp > 40 * 1024)
+  {
+    warps >>= 1;
+  }
+  if (warps * per_warp > 48 * 1024)
+  {
+    set_error("moe_router_bwd: experts=%d too many", experts);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  const int grid = (tokens + warps - 1) / warps;
+  CAIFQ_DISPATCH_FLOAT(dtype, (router_bwd_kernel<T><<<grid, warps * 32, warps * per_warp, s>>>(
+                                  static_cast<const T *>(grad_w), static_cast<const T *>(probs), indices,
+                                  static_cast<const T *>(balance_bias), static_cast<const T *>(z_lse_scaled),
+                                  static_cast<T *>(grad_topk), static_cast<T *>(grad_logits), tokens, experts, top_k,
+                                  sigmoid_gate, normalize, scaling, exact_jacobian)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_aux_losses(const void *logits, const void *probs, const int *expert_offsets, void *balance_bias,
+                          void *lse, void *z_lse_scaled, float *sums, int dtype, int tokens, int experts, int top_k,
+                          float balance_weight, float z_weight, cudaStream_t s)
+{
+  cudaError_t err = cudaMemsetAsync(sums, 0, sizeof(float) * (2 + static_cast<size_t>(experts)), s);
+  if (err != cudaSuccess)
+  {
+    set_error("moe_aux_losses: memset failed: %s", cudaGetErrorString(err));
+    return CAIFQ_ERR_CUDA;
+  }
+  if (tokens > 0 && (logits != nullptr || probs != nullptr))
+  {
+    const int warps = 8;
+    int grid = (tokens + warps - 1) / warps;
+    if (grid > 592)
+    {
+      grid = 592;   // four CTAs per SM; each adds its column sums once
+    }
+    const float z_scale = 2.0f * z_weight / static_cast<float>(tokens);
+    const size_t smem = (static_cast<size_t>(experts) + 1) * sizeof(float);
+    CAIFQ_DISPATCH_FLOAT(dtype, (aux_rows_kernel<T><<<grid, warps * 32, smem, s>>>(
+                                    static_cast<const T *>(logits), static_cast<const T *>(probs),
+                                    static_cast<T *>(lse), static_cast<T *>(z_lse_scaled), sums, tokens, experts,
+                                    z_scale)));
+    CAIFQ_CHECK_LAUNCH();
+  }
+  CAIFQ_DISPATCH_FLOAT(dtype, (aux_finish_kernel<T><<<1, 256, 0, s>>>(
+                                  sums, expert_offsets, static_cast<T *>(balance_bias), tokens, experts, top_k,
+                                  balance_weight, z_weight, logits != nullptr ? 1 : 0, probs != nullptr ? 1 : 0)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

@@ -79,6 +79,10 @@ _SIGNATURES = {
     "caifq_lora_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), ctypes.POINTER(CLora), _vp, _i64, _vp, _vp,
                                              _vp, _i32, _vp]),
     "caifq_moe_route_grouped": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "caifq_moe_router_bwd": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
+                                            ctypes.c_float, _i32, _vp]),
+    "caifq_moe_aux_losses": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float,
+                                            ctypes.c_float, _vp]),
     "caifq_lora_adamw_step": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
                                              ctypes.c_float, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                                              ctypes.c_float, ctypes.c_float, ctypes.c_float, _vp]),
@@ -467,6 +471,38 @@ def moe_route_grouped(x, k, logits=True, bias=None, n_group=1, topk_group=1):
                                          dtype_code(x), batch, dim, k, n_group, topk_group, _stream()),
            "moe_route_grouped")
     return scores, idx, wts
+
+
+def moe_router_bwd(grad_weights, probs, indices, balance_bias=None, z_lse_scaled=None, sigmoid_gate=False,
+                   normalize=True, scaling=1.0, exact_jacobian=False):
+    """Gradient of the routing weights back to the router's logits: returns (grad_logits [tokens, experts],
+    grad_topk [tokens, top_k])."""
+    _need_cuda(grad_weights, probs, indices, balance_bias, z_lse_scaled)
+    tokens, experts = probs.shape
+    top_k = indices.shape[1]
+    grad_logits = torch.empty_like(probs)
+    grad_topk = torch.empty_like(grad_weights)
+    _check(lib().caifq_moe_router_bwd(_ptr(grad_weights), _ptr(probs), _ptr(indices), _ptr(balance_bias),
+                                      _ptr(z_lse_scaled), _ptr(grad_topk), _ptr(grad_logits), dtype_code(probs),
+                                      tokens, experts, top_k, 1 if sigmoid_gate else 0, 1 if normalize else 0,
+                                      float(scaling), 1 if exact_jacobian else 0, _stream()), "moe_router_bwd")
+    return grad_logits, grad_topk
+
+
+def moe_aux_losses(logits, probs, expert_offsets, top_k, balance_weight, z_weight):
+    """Load-balance and z loss with the operands of their gradients: returns (sums, balance_bias, lse,
+    z_lse_scaled); sums[0], sums[1] are the two loss values, sums[2:] the column sums of probs."""
+    _need_cuda(logits, probs, expert_offsets)
+    ref = probs if probs is not None else logits
+    tokens, experts = ref.shape
+    sums = torch.empty(2 + experts, dtype=torch.float32, device=ref.device)
+    bias = torch.empty(experts, dtype=ref.dtype, device=ref.device) if probs is not None else None
+    lse = torch.empty(tokens, dtype=ref.dtype, device=ref.device) if logits is not None else None
+    zls = torch.empty(tokens, dtype=ref.dtype, device=ref.device) if logits is not None else None
+    _check(lib().caifq_moe_aux_losses(_ptr(logits), _ptr(probs), _ptr(expert_offsets), _ptr(bias), _ptr(lse),
+                                      _ptr(zls), _ptr(sums), dtype_code(ref), tokens, experts, top_k,
+                                      float(balance_weight), float(z_weight), _stream()), "moe_aux_losses")
+    return sums, bias, lse, zls
 
 
 def moe_softmax(logits, bias=None):

@@ -362,6 +362,49 @@ CAIFQ_API int caifq_moe_router_softmax(const void *logits, const void *bias, voi
 CAIFQ_API int caifq_moe_route_grouped(const void *input, int32_t input_is_logits, const void *selection_bias,
                                       void *scores_out, int32_t *indices, void *weights, int32_t dtype, int32_t batch,
                                       int32_t dim, int32_t k, int32_t n_group, int32_t topk_group, void *stream);
+/*
+ * CAIF_DeviceMoERouter::BackwardRoutingAuxAware up to grad_logits (src/caif_device_moe_router.cpp:529-733) in
+ * one launch instead of NormalizeRowsBackwardTopKGather, Scale, Zeros, ScatterAdd, AddBias, SoftmaxBackward
+ * and MoEZLossGradAdd (SigmoidBackward for sigmoid gating), bit-identical to that chain:
+ *   grad_topk   = normalize != 0 ? (grad_weights - dot(w, grad_weights)) / s : grad_weights, with
+ *                 p = probs at the chosen experts, s = max(sum p, 1e-12), w = p / s
+ *                 (src/caif_cuda_kernels_moe.cu:128-171); then * routed_scaling_factor when it is not 1.
+ *                 Written to grad_topk [tokens, top_k] when non-NULL (the router's GradTopkPreview).
+ *   grad_probs  = scatter of grad_topk to [tokens, experts] (+ balance_bias [experts] per column, may be NULL)
+ *   sigmoid_gate != 0: grad_logits = grad_probs * probs * (1 - probs); balance_bias and z_lse_scaled must be
+ *                 NULL (the reference refuses them for SigmoidNoauxTc).
+ *   else        grad_logits = softmax backward of grad_probs (+ z_lse_scaled[t] * probs, may be NULL).
+ * exact_jacobian selects how the softmax backward is evaluated.  The reference calls
+ * SoftmaxBackward(CachedProbs(), grad_probs, grad_logits) (src/caif_device_moe_router.cpp:702) against the
+ * signature (grad_output, output, grad_input) (include/caif/caif_ops.h:650), so its kernel computes
+ * grad_probs * (probs - dot(probs, grad_probs)); 0 reproduces that bit for bit, 1 computes
+ * probs * (grad_probs - dot(probs, grad_probs)).  The two linear-layer products that follow in the reference
+ * (grad_w_router += x^T grad_logits, grad_input = grad_logits w_router^T) are caifq_linear_* calls of the host.
+ * top_k <= 32.  indices are int32, [tokens, top_k]; entries outside [0, experts) are skipped.
+ */
+CAIFQ_API int caifq_moe_router_bwd(const void *grad_weights, const void *probs, const int32_t *indices,
+                                   const void *balance_bias, const void *z_lse_scaled, void *grad_topk,
+                                   void *grad_logits, int32_t dtype, int32_t tokens, int32_t experts, int32_t top_k,
+                                   int32_t sigmoid_gate, int32_t normalize, float routed_scaling_factor,
+                                   int32_t exact_jacobian, void *stream);
+/*
+ * The auxiliary losses of CAIF_DeviceMoELayer and the operands their gradients enter the router backward
+ * with (src/caif_device_moe_layer.cpp:792-835 and 853-925), on the device, with no host round trip:
+ *   sums[0] = balance_weight * experts * sum_e (count_e / (tokens * top_k)) * (sum_t probs[t, e] / tokens)
+ *   sums[1] = z_weight * sum_t lse_t^2 / tokens,  lse_t = logsumexp(logits[t, :]) rounded to `dtype`
+ *   sums[2 + e] = sum_t probs[t, e]                              (sums: device float [2 + experts])
+ *   balance_bias[e] = balance_weight * experts / (tokens^2 * top_k) * count_e     ([experts], may be NULL)
+ *   lse[t], z_lse_scaled[t] = lse_t, lse_t * 2 * z_weight / tokens               ([tokens], may be NULL)
+ * count_e = expert_offsets[e + 1] - expert_offsets[e] (the offsets caifq_moe_build_dispatch wrote).
+ * logits may be NULL (no z-loss: sums[1] = 0) and probs may be NULL (no balance loss: sums[0] = 0).
+ * lse, z_lse_scaled and balance_bias are bit-identical to the reference's tensors (its logsumexp tree order,
+ * src/caif_cuda_kernels_elementwise.cu:930-990); the two loss values add their terms in another order
+ * than the reference's sequential column sums and atomics and agree to rounding.
+ */
+CAIFQ_API int caifq_moe_aux_losses(const void *logits, const void *probs, const int32_t *expert_offsets,
+                                   void *balance_bias, void *lse, void *z_lse_scaled, float *sums, int32_t dtype,
+                                   int32_t tokens, int32_t experts, int32_t top_k, float balance_weight,
+                                   float z_weight, void *stream);
 /* CAIF_Ops::Scale, src/caif_ops_device.cpp:3142-3160 (the router's routed_scaling_factor on the top-k
  * weights, src/caif_device_moe_router.cpp:394-407; LoRA's alpha/r): dst = T(float(src) * factor).
  * In place is allowed. */

@@ -708,6 +708,236 @@ ORC_EXPORT void orc_router_softmax(const float *logits, const float *bias, int r
   }
 }
 
+/* Router backward up to grad_logits: CAIF_DeviceMoERouter::BackwardRoutingAuxAware,   */
+/* src/caif_device_moe_router.cpp:529-733, as the chain of kernels it launches, every   */
+/* intermediate rounded through `dtype` where the reference stores a tensor:            */
+/*  1. normalize Jacobian over the chosen scores (src/caif_cuda_kernels_moe.cu:128-171):*/
+/*     32 lanes, lane k < top_k holding p_k and g_k, sums by xor butterfly 16..1,       */
+/*     s = max(sum p, 1e-12), inv = 1/s, dot = sum (p_k inv) g_k, out = (g_k - dot) inv */
+/*  2. Scale by routed_scaling_factor when it is not 1                                  */
+/*  3. Zeros + ScatterAdd to [tokens, experts] (:553-572)                               */
+/*  4. sigmoid gating: g * p * (1 - p) (src/caif_cuda_kernels_activations.cu:189-228)   */
+/*     softmax gating: AddBias of balance_bias (src/caif_cuda_kernels_elementwise.cu:   */
+/*     124-137), then attention_softmax_backward_kernel                                 */
+/*     (src/caif_cuda_kernels_attention_support.cu:464-530) called with (probs,         */
+/*     grad_probs) in its (grad_output, output) slots (router.cpp:702): 128 threads,    */
+/*     thread t accumulating columns t, t+128, ... with a fused multiply-add, a         */
+/*     butterfly per warp, (w0 + w2) + (w1 + w3) across the warps, then                 */
+/*     dx = y (dy - dot) with y = grad_probs, dy = probs; exact_jacobian != 0 swaps     */
+/*     them into the softmax Jacobian proper.  Then the z-loss term                     */
+/*     fma(lse_scaled[t], p, dx) (src/caif_cuda_kernels_moe.cu:1376-1395).              */
+static float orc_butterfly_sum(float *lanes)
+{
+  for (int off = 16; off > 0; off >>= 1)
+  {
+    float next[32];
+    for (int l = 0; l < 32; ++l)
+    {
+      next[l] = lanes[l] + lanes[l ^ off];
+    }
+    memcpy(lanes, next, sizeof(next));
+  }
+  return lanes[0];
+}
+
+static float orc_round1(float v, int dtype)
+{
+  orc_round_through(&v, 1, dtype);
+  return v;
+}
+
+ORC_EXPORT void orc_router_backward(const float *grad_w, const float *probs, const int32_t *indices,
+                                    const float *balance_bias, const float *z_lse_scaled, int tokens, int experts,
+                                    int top_k, int sigmoid_gate, int normalize, float scaling, int exact_jacobian,
+                                    int dtype, float *grad_topk, float *grad_logits)
+{
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < tokens; ++t)
+  {
+    const float *p_row = probs + (int64_t)t * experts;
+    float *gp = (float *)calloc((size_t)experts, sizeof(float));
+    float gt[32];
+    float lanes[32];
+    float pk[32];
+    for (int k = 0; k < 32; ++k)
+    {
+      const int idx = k < top_k ? indices[(int64_t)t * top_k + k] : -1;
+      pk[k] = (k < top_k && idx >= 0 && idx < experts) ? p_row[idx] : 0.0f;
+      gt[k] = k < top_k ? grad_w[(int64_t)t * top_k + k] : 0.0f;
+    }
+    if (normalize)
+    {
+      memcpy(lanes, pk, sizeof(lanes));
+      const float sum = fmaxf(orc_butterfly_sum(lanes), 1e-12f);
+      const float inv = 1.0f / sum;
+      for (int k = 0; k < 32; ++k)
+      {
+        lanes[k] = (pk[k] * inv) * gt[k];
+      }
+      const float dot = orc_butterfly_sum(lanes);
+      for (int k = 0; k < top_k; ++k)
+      {
+        gt[k] = orc_round1((gt[k] - dot) * inv, dtype);
+      }
+    }
+    for (int k = 0; k < top_k; ++k)
+    {
+      if (scaling != 1.0f)
+      {
+        gt[k] = orc_round1(gt[k] * scaling, dtype);
+      }
+      if (grad_topk != NULL)
+      {
+        grad_topk[(int64_t)t * top_k + k] = gt[k];
+      }
+      const int idx = indices[(int64_t)t * top_k + k];
+      if (idx >= 0 && idx < experts)
+      {
+        gp[idx] = orc_round1(gp[idx] + gt[k], dtype);
+      }
+    }
+    float *out = grad_logits + (int64_t)t * experts;
+    if (sigmoid_gate)
+    {
+      for (int c = 0; c < experts; ++c)
+      {
+        out[c] = orc_round1((gp[c] * p_row[c]) * (1.0f - p_row[c]), dtype);
+      }
+      free(gp);
+      continue;
+    }
+    if (balance_bias != NULL)
+    {
+      for (int c = 0; c < experts; ++c)
+      {
+        gp[c] = orc_round1(gp[c] + balance_bias[c], dtype);
+      }
+    }
+    float warp_sum[4];
+    for (int w = 0; w < 4; ++w)
+    {
+      for (int l = 0; l < 32; ++l)
+      {
+        float acc = 0.0f;
+        for (int c = 32 * w + l; c < experts; c += 128)
+        {
+          acc = fmaf(p_row[c], gp[c], acc);
+        }
+        lanes[l] = acc;
+      }
+      warp_sum[w] = orc_butterfly_sum(lanes);
+    }
+    const float dot = (warp_sum[0] + warp_sum[2]) + (warp_sum[1] + warp_sum[3]);
+    for (int c = 0; c < experts; ++c)
+    {
+      const float y = exact_jacobian ? p_row[c] : gp[c];
+      const float dy = exact_jacobian ? gp[c] : p_row[c];
+      float v = orc_round1(y * (dy - dot), dtype);
+      if (z_lse_scaled != NULL)
+      {
+        v = orc_round1(fmaf(z_lse_scaled[t], p_row[c], v), dtype);
+      }
+      out[c] = v;
+    }
+    free(gp);
+  }
+}
+
+/* Auxiliary losses of CAIF_DeviceMoELayer, src/caif_device_moe_layer.cpp:792-835 and   */
+/* 853-925.  logsumexp_kernel (src/caif_cuda_kernels_elementwise.cu:930-990): 256       */
+/* threads, thread t over columns t, t+256, ...; max, then sum of expf(x - max), both   */
+/* through the shared-memory tree (strides 128 ... 1); lse = max + logf(sum), stored    */
+/* through `dtype`.  z loss = zw * T(sum_t T(lse_t^2)) / tokens; z_lse_scaled =         */
+/* T(lse * (2 zw / tokens)).  Balance loss = bw * E * sum_e (count_e / (tokens k)) *    */
+/* (T(sum_t probs[t,e]) / tokens) with the column sums added sequentially over t        */
+/* (sum_axis0_kernel, :800-816); balance_bias[e] = T(bw E / (tokens^2 k) * count_e).    */
+/* losses[0] = balance, losses[1] = z.  logits or probs may be NULL.                    */
+ORC_EXPORT void orc_moe_aux_losses(const float *logits, const float *probs, const int32_t *counts, int tokens,
+                                   int experts, int top_k, float balance_weight, float z_weight, int dtype,
+                                   float *balance_bias, float *lse, float *z_lse_scaled, float *losses)
+{
+  losses[0] = 0.0f;
+  losses[1] = 0.0f;
+  if (probs != NULL)
+  {
+    const float total = (float)tokens * (float)top_k;
+    float loss = 0.0f;
+    for (int e = 0; e < experts; ++e)
+    {
+      float sum = 0.0f;
+      for (int t = 0; t < tokens; ++t)
+      {
+        sum += probs[(int64_t)t * experts + e];
+      }
+      const float mean_p = orc_round1(sum, dtype) / (float)tokens;
+      loss += ((float)counts[e] / total) * mean_p;
+    }
+    losses[0] = balance_weight * (float)experts * loss;
+    if (balance_bias != NULL)
+    {
+      const float denom = (float)tokens * (float)tokens * (float)top_k;
+      const float scale = balance_weight * (float)experts / denom;
+      for (int e = 0; e < experts; ++e)
+      {
+        balance_bias[e] = orc_round1(scale * (float)counts[e], dtype);
+      }
+    }
+  }
+  if (logits != NULL)
+  {
+    const float z_scale = 2.0f * z_weight / (float)tokens;
+    float total = 0.0f;
+    for (int t = 0; t < tokens; ++t)
+    {
+      const float *x = logits + (int64_t)t * experts;
+      float smax[256];
+      float ssum[256];
+      for (int i = 0; i < 256; ++i)
+      {
+        smax[i] = -1e30f;
+        for (int c = i; c < experts; c += 256)
+        {
+          smax[i] = fmaxf(smax[i], x[c]);
+        }
+      }
+      for (int stride = 128; stride > 0; stride >>= 1)
+      {
+        for (int i = 0; i < stride; ++i)
+        {
+          smax[i] = fmaxf(smax[i], smax[i + stride]);
+        }
+      }
+      const float m = smax[0];
+      for (int i = 0; i < 256; ++i)
+      {
+        ssum[i] = 0.0f;
+        for (int c = i; c < experts; c += 256)
+        {
+          ssum[i] += expf(x[c] - m);
+        }
+      }
+      for (int stride = 128; stride > 0; stride >>= 1)
+      {
+        for (int i = 0; i < stride; ++i)
+        {
+          ssum[i] += ssum[i + stride];
+        }
+      }
+      const float l = orc_round1(m + logf(ssum[0]), dtype);
+      if (lse != NULL)
+      {
+        lse[t] = l;
+      }
+      if (z_lse_scaled != NULL)
+      {
+        z_lse_scaled[t] = orc_round1(l * z_scale, dtype);
+      }
+      total += orc_round1(l * l, dtype);
+    }
+    losses[1] = z_weight * orc_round1(total, dtype) / (float)tokens;
+  }
+}
+
 /* Dispatch map: CAIF_Ops::MoEBuildDispatchMapDevice,                        */
 /* src/caif_ops_device.cpp:4876-4950.  counts per expert (indices outside    */
 /* [0,E) ignored) -> capacity clamp -> exclusive prefix sum -> position of   */

@@ -347,6 +347,47 @@ def router_softmax(logits, bias=None, dtype=F32):
     return out
 
 
+def router_backward(grad_w, probs, indices, balance_bias=None, z_lse_scaled=None, sigmoid_gate=False,
+                    normalize=True, scaling=1.0, exact_jacobian=False, dtype=F32):
+    """grad_logits and grad_topk of CAIF_DeviceMoERouter::BackwardRoutingAuxAware
+    (src/caif_device_moe_router.cpp:529-733); inputs are fp32 arrays holding values already
+    representable in `dtype`, intermediates are rounded through `dtype` as the reference stores them."""
+    g = _c(grad_w, np.float32)
+    p = _c(probs, np.float32)
+    idx = _c(indices, np.int32)
+    tokens, experts = p.shape
+    top_k = idx.shape[1]
+    bb = None if balance_bias is None else _c(balance_bias, np.float32)
+    zl = None if z_lse_scaled is None else _c(z_lse_scaled, np.float32)
+    grad_topk = np.empty((tokens, top_k), np.float32)
+    grad_logits = np.empty((tokens, experts), np.float32)
+    lib().orc_router_backward(_p(g), _p(p), _p(idx), None if bb is None else _p(bb), None if zl is None else _p(zl),
+                              ctypes.c_int(tokens), ctypes.c_int(experts), ctypes.c_int(top_k),
+                              ctypes.c_int(1 if sigmoid_gate else 0), ctypes.c_int(1 if normalize else 0),
+                              ctypes.c_float(scaling), ctypes.c_int(1 if exact_jacobian else 0), ctypes.c_int(dtype),
+                              _p(grad_topk), _p(grad_logits))
+    return grad_logits, grad_topk
+
+
+def moe_aux_losses(logits, probs, counts, top_k, balance_weight, z_weight, dtype=F32):
+    """(losses[2], balance_bias, lse, z_lse_scaled) of CAIF_DeviceMoELayer's auxiliary losses
+    (src/caif_device_moe_layer.cpp:792-835, 853-925)."""
+    ref = probs if probs is not None else logits
+    tokens, experts = ref.shape
+    x = None if logits is None else _c(logits, np.float32)
+    p = None if probs is None else _c(probs, np.float32)
+    cnt = _c(counts, np.int32)
+    losses = np.zeros(2, np.float32)
+    bias = np.zeros(experts, np.float32)
+    lse = np.zeros(tokens, np.float32)
+    zls = np.zeros(tokens, np.float32)
+    lib().orc_moe_aux_losses(None if x is None else _p(x), None if p is None else _p(p), _p(cnt),
+                             ctypes.c_int(tokens), ctypes.c_int(experts), ctypes.c_int(top_k),
+                             ctypes.c_float(balance_weight), ctypes.c_float(z_weight), ctypes.c_int(dtype),
+                             _p(bias), _p(lse), _p(zls), _p(losses))
+    return losses, bias, lse, zls
+
+
 def build_dispatch_map(expert_indices, num_experts, capacity=0):
     idx = _c(expert_indices, np.int32)
     tokens, top_k = idx.shape

@@ -22,6 +22,48 @@
 #include "caif_cuda_kernels_optimizers.cuh"
 #include "caif_cuda_kernels_activations.cuh"
 
+// The launches of CAIF_DeviceMoERouter::BackwardRoutingAuxAware (src/caif_device_moe_router.cpp:529-733) up to
+// grad_logits, in its order and with its operand order: the normalize Jacobian over the chosen scores,
+// Scale by routed_scaling_factor, Zeros + ScatterAdd into [tokens, experts], AddBias of the load-balance
+// column term, then SoftmaxBackward called as (probs, grad_probs, grad_logits) -- the reference passes
+// the cached probabilities in the grad_output slot and grad_probs in the output slot -- and the z-loss
+// term; for sigmoid gating SigmoidBackward instead.  grad_topk [tokens, k] and grad_probs
+// [tokens, experts] are scratch the caller provides.
+template <typename T>
+static void router_backward_chain(const T *grad_w, const T *probs, const int *indices, const T *balance_bias,
+                                  const T *z_lse_scaled, T *grad_topk, T *grad_probs, T *grad_logits, int tokens,
+                                  int experts, int k, int sigmoid_gate, int normalize, float scaling, cudaStream_t s)
+{
+  if (normalize != 0)
+  {
+    launch_normalize_rows_backward_topk_gather<T>(grad_w, probs, indices, grad_topk, tokens, experts, k, s);
+  }
+  else
+  {
+    cudaMemcpyAsync(grad_topk, grad_w, sizeof(T) * static_cast<size_t>(tokens) * k, cudaMemcpyDeviceToDevice, s);
+  }
+  if (scaling != 1.0f)
+  {
+    launch_elementwise_mul_scalar<T>(grad_topk, scaling, grad_topk, static_cast<int64_t>(tokens) * k, s);
+  }
+  cudaMemsetAsync(grad_probs, 0, sizeof(T) * static_cast<size_t>(tokens) * experts, s);
+  launch_scatter_add<T>(grad_topk, indices, grad_probs, tokens, k, experts, s);
+  if (sigmoid_gate != 0)
+  {
+    launch_sigmoid_backward<T>(grad_probs, probs, grad_logits, static_cast<int64_t>(tokens) * experts, s);
+    return;
+  }
+  if (balance_bias != nullptr)
+  {
+    launch_bias_add_2d<T>(grad_probs, balance_bias, grad_probs, tokens, experts, s);
+  }
+  launch_attention_softmax_backward<T>(probs, grad_probs, grad_logits, tokens, experts, s);
+  if (z_lse_scaled != nullptr)
+  {
+    launch_moe_z_loss_grad<T>(z_lse_scaled, probs, grad_logits, tokens, experts, s);
+  }
+}
+
 extern "C" {
 
 void ref_quantize_int8_per_tensor(const float *x, void *q, void *scale, int64_t n, void *stream)
@@ -202,6 +244,51 @@ void ref_topk_bf16(const void *input, int *indices, void *values, int batch, int
 {
   launch_topk<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input), indices, static_cast<__nv_bfloat16 *>(values),
                              batch, dim, k, static_cast<cudaStream_t>(stream));
+}
+
+void ref_router_backward_f32(const float *grad_w, const float *probs, const int *indices, const float *balance_bias,
+                             const float *z_lse_scaled, float *grad_topk, float *grad_probs, float *grad_logits,
+                             int tokens, int experts, int k, int sigmoid_gate, int normalize, float scaling,
+                             void *stream)
+{
+  router_backward_chain<float>(grad_w, probs, indices, balance_bias, z_lse_scaled, grad_topk, grad_probs, grad_logits,
+                               tokens, experts, k, sigmoid_gate, normalize, scaling,
+                               static_cast<cudaStream_t>(stream));
+}
+
+void ref_router_backward_bf16(const void *grad_w, const void *probs, const int *indices, const void *balance_bias,
+                              const void *z_lse_scaled, void *grad_topk, void *grad_probs, void *grad_logits,
+                              int tokens, int experts, int k, int sigmoid_gate, int normalize, float scaling,
+                              void *stream)
+{
+  using B = __nv_bfloat16;
+  router_backward_chain<B>(static_cast<const B *>(grad_w), static_cast<const B *>(probs), indices,
+                           static_cast<const B *>(balance_bias), static_cast<const B *>(z_lse_scaled),
+                           static_cast<B *>(grad_topk), static_cast<B *>(grad_probs), static_cast<B *>(grad_logits),
+                           tokens, experts, k, sigmoid_gate, normalize, scaling, static_cast<cudaStream_t>(stream));
+}
+
+// the pieces of CAIF_DeviceMoELayer::ComputeZLoss / ComputeBalanceLoss (src/caif_device_moe_layer.cpp:853-925)
+void ref_logsumexp_f32(const float *input, float *out, int rows, int cols, void *stream)
+{
+  launch_logsumexp<float>(input, out, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+void ref_logsumexp_bf16(const void *input, float *out, int rows, int cols, void *stream)
+{
+  launch_logsumexp<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input), out, rows, cols,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+void ref_sum_axis0_f32(const float *input, float *out, int rows, int cols, void *stream)
+{
+  launch_sum_axis0<float>(input, out, rows, cols, static_cast<cudaStream_t>(stream));
+}
+
+void ref_sum_axis0_bf16(const void *input, float *out, int rows, int cols, void *stream)
+{
+  launch_sum_axis0<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(input), out, rows, cols,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -193,3 +193,38 @@ def gather_topk(scores, idx):
     _typed("ref_gather_topk", scores)(_p(scores), _p(idx), _p(out), ctypes.c_int(tokens), ctypes.c_int(experts),
                                       ctypes.c_int(k), _s())
     return out
+
+
+def _pn(t):
+    return ctypes.c_void_p(None) if t is None else _p(t)
+
+
+def router_backward(grad_w, probs, idx, balance_bias=None, z_lse_scaled=None, sigmoid_gate=False, normalize=True,
+                    scaling=1.0):
+    """The launches of CAIF_DeviceMoERouter::BackwardRoutingAuxAware up to grad_logits, in its order and with
+    its operand order (oracle/ref_shim.cu): returns (grad_logits, grad_topk)."""
+    tokens, experts = probs.shape
+    k = idx.shape[1]
+    grad_topk = torch.empty_like(grad_w)
+    grad_probs = torch.empty_like(probs)
+    grad_logits = torch.empty_like(probs)
+    _typed("ref_router_backward", probs)(_p(grad_w), _p(probs), _p(idx), _pn(balance_bias), _pn(z_lse_scaled),
+                                         _p(grad_topk), _p(grad_probs), _p(grad_logits), ctypes.c_int(tokens),
+                                         ctypes.c_int(experts), ctypes.c_int(k), ctypes.c_int(1 if sigmoid_gate else 0),
+                                         ctypes.c_int(1 if normalize else 0), ctypes.c_float(scaling), _s())
+    return grad_logits, grad_topk
+
+
+def logsumexp(x):
+    """launch_logsumexp: fp32 result per row."""
+    rows, cols = x.shape
+    out = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _typed("ref_logsumexp", x)(_p(x), _p(out), ctypes.c_int(rows), ctypes.c_int(cols), _s())
+    return out
+
+
+def sum_axis0(x):
+    rows, cols = x.shape
+    out = torch.empty(cols, dtype=torch.float32, device=x.device)
+    _typed("ref_sum_axis0", x)(_p(x), _p(out), ctypes.c_int(rows), ctypes.c_int(cols), _s())
+    return out

@@ -663,3 +663,97 @@ def test_grouped_sigmoid_routing_bit_exact_with_the_reference_kernels(dtype, use
     if n_group > 1:
         groups = (idx // (experts // n_group)).cpu().numpy()
         assert max(len(set(row)) for row in groups) <= topk_group
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sigmoid_gate,normalize,scaling,with_aux,experts,top_k", [
+    (False, True, 1.0, False, 64, 6),      # the MoE config's router
+    (False, True, 2.5, True, 64, 6),       # load-balance and z-loss operands, scaled weights
+    (True, True, 1.0, False, 64, 6),       # sigmoid gating, normalized
+    (True, False, 16.0, False, 256, 8),    # sigmoid gating, scaled only; rows wider than the softmax block
+    (False, True, 1.0, True, 160, 6),      # columns beyond 128: two per thread of the reference's block
+    (False, True, 1.0, True, 8, 2),
+])
+def test_router_backward_bit_exact_with_the_reference_chain(dtype, sigmoid_gate, normalize, scaling, with_aux,
+                                                            experts, top_k):
+    """caifq_moe_router_bwd against the reference's own launches (NormalizeRowsBackwardTopKGather, Scale,
+    Zeros + ScatterAdd, AddBias, SoftmaxBackward with the router's operand order, MoEZLossGradAdd;
+    SigmoidBackward for sigmoid gating): grad_logits and grad_topk bit for bit; the oracle agrees bit for
+    bit too; the softmax Jacobian proper (exact_jacobian) matches autograd."""
+    tokens = 1111
+    code = orc.F32 if dtype == torch.float32 else orc.BF16
+    g = torch.Generator(device="cuda").manual_seed(900 + experts)
+    logits = (torch.randn(tokens, experts, generator=g, device="cuda") * 2.0).to(dtype)
+    probs = nv.moe_route_grouped(logits, top_k)[0] if sigmoid_gate else nv.moe_softmax(logits)
+    idx, _ = nv.moe_topk(probs, top_k)
+    grad_w = torch.randn(tokens, top_k, generator=g, device="cuda").to(dtype)
+    bias = zls = None
+    if with_aux:
+        bias = (torch.rand(experts, generator=g, device="cuda") * 1e-3).to(dtype)
+        zls = (torch.randn(tokens, generator=g, device="cuda") * 1e-2).to(dtype)
+    got, got_topk = nv.moe_router_bwd(grad_w, probs, idx, bias, zls, sigmoid_gate, normalize, scaling)
+    f = lambda t: None if t is None else t.float().cpu().numpy()
+    want, want_topk = orc.router_backward(f(grad_w), f(probs), idx.cpu().numpy(), f(bias), f(zls), sigmoid_gate,
+                                          normalize, scaling, dtype=code)
+    assert np.array_equal(got_topk.float().cpu().numpy(), want_topk)
+    assert np.array_equal(got.float().cpu().numpy(), want)
+    if ref.available():
+        r_logits, r_topk = ref.router_backward(grad_w, probs, idx, bias, zls, sigmoid_gate, normalize, scaling)
+        assert torch.equal(r_topk, got_topk)
+        assert torch.equal(r_logits, got)
+    if dtype == torch.float32:
+        x = logits.double().requires_grad_(True)
+        scores = torch.sigmoid(x) if sigmoid_gate else torch.softmax(x, dim=-1)
+        chosen = torch.gather(scores, 1, idx.long())
+        w = chosen / chosen.sum(dim=-1, keepdim=True) if normalize else chosen
+        (w * scaling).backward(grad_w.double())
+        exact, _ = nv.moe_router_bwd(grad_w, probs, idx, None, None, sigmoid_gate, normalize, scaling,
+                                     exact_jacobian=True)
+        assert float((exact.double() - x.grad).abs().max()) <= 1e-4 * max(1.0, float(x.grad.abs().max()))
+
+
+def test_router_backward_rejects_aux_operands_for_sigmoid_gating():
+    probs = torch.rand(4, 8, device="cuda")
+    idx, _ = nv.moe_topk(probs, 2)
+    with pytest.raises(nv.CaifqError):
+        nv.moe_router_bwd(torch.ones(4, 2, device="cuda"), probs, idx, torch.zeros(8, device="cuda"), None, True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tokens,experts,top_k", [(16384, 64, 6), (777, 160, 4), (50, 8, 2)])
+def test_aux_losses_against_the_reference_kernels_and_the_oracle(dtype, tokens, experts, top_k):
+    """caifq_moe_aux_losses: logsumexp per row bit-identical to the reference's kernel (rounded to the storage
+    type as its cached tensor), the scaled copy and the per-expert load-balance term bit-identical to the
+    oracle's restatement of the host arithmetic, the two loss values within rounding of the reference's
+    sequential sums."""
+    code = orc.F32 if dtype == torch.float32 else orc.BF16
+    g = torch.Generator(device="cuda").manual_seed(tokens)
+    logits = (torch.randn(tokens, experts, generator=g, device="cuda") * 2.0).to(dtype)
+    probs = nv.moe_softmax(logits)
+    idx, _ = nv.moe_topk(probs, top_k)
+    _, offsets = nv.moe_build_dispatch(idx, experts)
+    bw, zw = 0.01, 0.001
+    sums, bias, lse, zls = nv.moe_aux_losses(logits, probs, offsets, top_k, bw, zw)
+    counts = np.diff(offsets.cpu().numpy())
+    o_losses, o_bias, o_lse, o_zls = orc.moe_aux_losses(logits.float().cpu().numpy(), probs.float().cpu().numpy(),
+                                                        counts, top_k, bw, zw, code)
+    assert np.array_equal(bias.float().cpu().numpy(), o_bias)
+    lse_np = lse.float().cpu().numpy()
+    # the host's expf / logf may differ from the device's in the last bit: the oracle bounds, the reference pins
+    assert np.max(np.abs(lse_np - o_lse)) <= (1e-6 if dtype == torch.float32 else 4e-2) * max(1.0, np.max(np.abs(o_lse)))
+    if ref.available():
+        r_lse = ref.logsumexp(logits).to(dtype)
+        assert torch.equal(r_lse, lse)
+        scale = np.float32(2.0) * np.float32(zw) / np.float32(tokens)
+        assert np.array_equal(zls.float().cpu().numpy(), orc.round_through(r_lse.float().cpu().numpy() * scale, code))
+        r_cols = ref.sum_axis0(probs)
+        assert torch.allclose(sums[2:], r_cols, rtol=1e-5, atol=1e-6)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    got = sums[:2].cpu().numpy()
+    assert abs(got[0] - o_losses[0]) <= tol * abs(o_losses[0])
+    assert abs(got[1] - o_losses[1]) <= tol * abs(o_losses[1])
+    # the pieces alone: no logits -> no z loss; no probs -> no balance loss
+    only_b = nv.moe_aux_losses(None, probs, offsets, top_k, bw, zw)[0].cpu().numpy()
+    only_z = nv.moe_aux_losses(logits, None, None, top_k, bw, zw)[0].cpu().numpy()
+    assert only_b[1] == 0.0 and abs(only_b[0] - got[0]) <= 1e-6 * abs(got[0])
+    assert only_z[0] == 0.0 and abs(only_z[1] - got[1]) <= 1e-6 * abs(got[1])

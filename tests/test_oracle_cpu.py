@@ -370,3 +370,54 @@ def test_router_softmax_restatement():
     assert np.array_equal(orc.router_softmax(np.zeros((1, 4), np.float32)), np.full((1, 4), 0.25, np.float32))
     p = orc.router_softmax(np.array([[0.0, -1e30, 0.0]], np.float32))
     assert p[0, 1] == 0.0 and p[0, 0] == 0.5
+
+
+@pytest.mark.parametrize("sigmoid_gate,normalize,scaling", [(False, True, 1.0), (False, True, 2.5), (True, True, 1.0),
+                                                            (True, False, 16.0)])
+def test_router_backward_restatement_against_autograd(sigmoid_gate, normalize, scaling):
+    """The oracle's router backward with the softmax Jacobian proper equals autograd through
+    scores -> gather at the chosen experts -> normalize -> scale; with the reference's operand
+    order (probs in the grad_output slot) it equals grad_probs * (probs - dot) instead."""
+    import torch
+    rng = np.random.default_rng(31)
+    tokens, experts, top_k = 37, 64, 6
+    logits = torch.tensor(rng.standard_normal((tokens, experts)), dtype=torch.float64, requires_grad=True)
+    scores = torch.sigmoid(logits) if sigmoid_gate else torch.softmax(logits, dim=-1)
+    idx = torch.topk(scores, top_k, dim=-1).indices
+    chosen = torch.gather(scores, 1, idx)
+    weights = chosen / chosen.sum(dim=-1, keepdim=True) if normalize else chosen
+    weights = weights * scaling
+    grad_w = torch.tensor(rng.standard_normal((tokens, top_k)), dtype=torch.float64)
+    weights.backward(grad_w)
+    got, _ = orc.router_backward(grad_w.numpy().astype(np.float32), scores.detach().numpy().astype(np.float32),
+                                 idx.numpy().astype(np.int32), sigmoid_gate=sigmoid_gate, normalize=normalize,
+                                 scaling=scaling, exact_jacobian=True)
+    want = logits.grad.numpy()
+    assert np.max(np.abs(got - want)) <= 1e-5 * max(1.0, np.max(np.abs(want)))
+    if not sigmoid_gate:
+        ref_form, grad_topk = orc.router_backward(grad_w.numpy().astype(np.float32),
+                                                  scores.detach().numpy().astype(np.float32),
+                                                  idx.numpy().astype(np.int32), normalize=normalize, scaling=scaling)
+        p = scores.detach().numpy()
+        gp = np.zeros_like(p)
+        np.put_along_axis(gp, idx.numpy(), grad_topk.astype(np.float64), axis=1)
+        dot = (p * gp).sum(axis=1, keepdims=True)
+        assert np.max(np.abs(ref_form - gp * (p - dot))) <= 1e-5
+
+
+def test_aux_losses_restatement_against_formulas():
+    rng = np.random.default_rng(5)
+    tokens, experts, top_k = 200, 64, 6
+    logits = rng.standard_normal((tokens, experts)).astype(np.float32) * 2
+    ex = np.exp(logits.astype(np.float64) - logits.max(axis=1, keepdims=True))
+    probs = (ex / ex.sum(axis=1, keepdims=True)).astype(np.float32)
+    counts = np.bincount(np.argsort(-probs, axis=1)[:, :top_k].ravel(), minlength=experts).astype(np.int32)
+    bw, zw = 0.01, 0.001
+    losses, bias, lse, zls = orc.moe_aux_losses(logits, probs, counts, top_k, bw, zw)
+    lse64 = np.log(np.exp(logits.astype(np.float64)).sum(axis=1))
+    assert np.allclose(lse, lse64, rtol=1e-6, atol=1e-6)
+    assert np.isclose(losses[1], zw * (lse64 ** 2).sum() / tokens, rtol=1e-5)
+    want_balance = bw * experts * ((counts / (tokens * top_k)) * (probs.astype(np.float64).sum(axis=0) / tokens)).sum()
+    assert np.isclose(losses[0], want_balance, rtol=1e-5)
+    assert np.allclose(bias, bw * experts * counts / (tokens * tokens * top_k), rtol=1e-6)
+    assert np.allclose(zls, lse64 * 2 * zw / tokens, rtol=1e-5)
