@@ -113,6 +113,8 @@ size_t gemm_tn_scratch_bytes(int p, int q);
 int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dtype, int compute_dtype,
                    float u_prescale, int64_t m, int p, int q, cudaStream_t s);
 int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
+int launch_moe_bias_update(void *bias, const int *counts, int dtype, int experts, float rate, int from_offsets,
+                           cudaStream_t s);
 int launch_moe_router_bwd(const void *grad_w, const void *probs, const int *indices, const void *balance_bias,
                           const void *z_lse_scaled, void *grad_topk, void *grad_logits, int dtype, int tokens,
                           int experts, int top_k, int sigmoid_gate, int normalize, float scaling, int exact_jacobian,
@@ -994,6 +996,17 @@ int caifq_moe_router_bwd(const void *grad_weights, const void *probs, const int3
   return launch_moe_router_bwd(grad_weights, probs, indices, balance_bias, z_lse_scaled, grad_topk, grad_logits,
                                dtype, tokens, experts, top_k, sigmoid_gate ? 1 : 0, normalize ? 1 : 0,
                                routed_scaling_factor, exact_jacobian ? 1 : 0, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_moe_bias_update(void *bias, const int32_t *counts, int32_t from_offsets, int32_t dtype, int32_t experts,
+                          float rate, void *stream)
+{
+  const char *who = "caifq_moe_bias_update";
+  CAIFQ_CHECK_ARG(experts > 0, "%s: bad expert count %d", who, experts);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(bias != nullptr && counts != nullptr, "%s: null pointer", who);
+  return launch_moe_bias_update(bias, counts, dtype, experts, rate, from_offsets ? 1 : 0,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int caifq_moe_aux_losses(const void *logits, const void *probs, const int32_t *expert_offsets, void *balance_bias,

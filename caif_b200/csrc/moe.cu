@@ -680,6 +680,43 @@ __global__ void aux_finish_kernel(float *__restrict__ sums, const int *__restric
   }
 }
 
+// ---------------------------------------------------------- aux-loss-free bias
+// launch_moe_bias_update (src/caif_cuda_kernels_moe.cu:481-537): every expert's selection bias moves by
+// `rate` towards balance, up when its load is under the mean and down when over.  The mean is the
+// reference's: 256 threads striding the counts, a shared-memory tree, one division (exact for loads
+// below 2^24, the same rounding beyond).  counts[e], or offsets[e + 1] - offsets[e] when `from_offsets`.
+template <typename T>
+__global__ void bias_update_kernel(T *__restrict__ bias, const int *__restrict__ counts, int experts, float rate,
+                                   int from_offsets)
+{
+  __shared__ float partial[256];
+  const int tid = threadIdx.x;
+  auto load = [&](int e) -> float
+  { return static_cast<float>(from_offsets != 0 ? counts[e + 1] - counts[e] : counts[e]); };
+  float local = 0.0f;
+  for (int e = tid; e < experts; e += 256)
+  {
+    local += load(e);
+  }
+  partial[tid] = local;
+  __syncthreads();
+  for (int stride = 128; stride > 0; stride >>= 1)
+  {
+    if (tid < stride)
+    {
+      partial[tid] += partial[tid + stride];
+    }
+    __syncthreads();
+  }
+  const float mean = __fdiv_rn(partial[0], static_cast<float>(experts));
+  for (int e = tid; e < experts; e += 256)
+  {
+    const float err = mean - load(e);
+    const float step = err > 0.0f ? rate : (err < 0.0f ? -rate : 0.0f);
+    bias[e] = from_f<T>(to_f<T>(bias[e]) + step);
+  }
+}
+
 // ------------------------------------------------------------------ dispatch map
 // Stable counting rank on the device.  One CTA walks the [T*k] index list in
 // chunks of blockDim entries; inside a chunk, warps rank equal experts with
@@ -1358,6 +1395,15 @@ int launch_moe_aux_losses(const void *logits, const void *probs, const int *expe
   CAIFQ_DISPATCH_FLOAT(dtype, (aux_finish_kernel<T><<<1, 256, 0, s>>>(
                                   sums, expert_offsets, static_cast<T *>(balance_bias), tokens, experts, top_k,
                                   balance_weight, z_weight, logits != nullptr ? 1 : 0, probs != nullptr ? 1 : 0)));
+  CAIFQ_CHECK_LAUNCH();
+  return CAIFQ_OK;
+}
+
+int launch_moe_bias_update(void *bias, const int *counts, int dtype, int experts, float rate, int from_offsets,
+                           cudaStream_t s)
+{
+  CAIFQ_DISPATCH_FLOAT(dtype, (bias_update_kernel<T><<<1, 256, 0, s>>>(static_cast<T *>(bias), counts, experts, rate,
+                                                                       from_offsets)));
   CAIFQ_CHECK_LAUNCH();
   return CAIFQ_OK;
 }

@@ -1,4 +1,4 @@
-"""Compile the C++23 host layer classes (caif_host.hpp + host_api.cpp) into
+"""Compile the C++23 host layer classes (caif_host.hpp, caif_safetensors.hpp + host_api.cpp) into
 caif_b200/libcaif_host.so, linked against libcaifq.so and the CUDA runtime."""
 import os
 import subprocess
@@ -12,7 +12,8 @@ CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 def build(force=False):
     srcs = [os.path.join(HERE, "host_api.cpp")]
-    deps = srcs + [os.path.join(HERE, "caif_host.hpp"), os.path.join(ROOT, "include", "caifq.h")]
+    deps = srcs + [os.path.join(HERE, "caif_host.hpp"), os.path.join(HERE, "caif_safetensors.hpp"),
+                   os.path.join(ROOT, "include", "caifq.h")]
     if not force and os.path.exists(LIB) and all(os.path.getmtime(d) <= os.path.getmtime(LIB) for d in deps):
         return LIB
     cmd = ["g++", "-std=c++23", "-O2", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-Wextra",

@@ -433,6 +433,9 @@ class CAIF_DeviceFrozenLinearBase
     virtual bool CacheFP32() const = 0;
     virtual uint32_t InputDim() const = 0;
     virtual uint32_t OutputDim() const = 0;
+    // what a loader needs before any weight is loaded: the stored dtype and the int4 group length
+    virtual CAIF_DataType::CAIF_DataType_e WeightStorageDtype() const = 0;
+    virtual uint32_t QuantGroupSize() const = 0;
     virtual void SetOffloadPolicy(const CAIF_OffloadPolicy::CAIF_OffloadPolicy_e) {}
     virtual CAIF_OffloadPolicy::CAIF_OffloadPolicy_e OffloadPolicy() const
     {
@@ -595,6 +598,8 @@ class CAIF_DeviceFrozenLinear : public CAIF_DeviceLayerTyped<ComputeT, StorageT>
     uint32_t InputDim() const override { return _input_dim; }
     uint32_t OutputDim() const override { return _output_dim; }
     uint32_t GroupSize() const { return _group_size; }
+    CAIF_DataType::CAIF_DataType_e WeightStorageDtype() const override { return Base_t::StorageDtype(); }
+    uint32_t QuantGroupSize() const override { return _group_size; }
 
     caifq_weight AsCaifqWeight() const override
     {

@@ -6,8 +6,10 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <vector>
 
 #include "caif_host.hpp"
+#include "caif_safetensors.hpp"
 
 using namespace instance;
 using Dtype_e = CAIF_DataType::CAIF_DataType_e;
@@ -337,4 +339,314 @@ CAIFH_API int caifh_frozen_tensor_fp32(void *handle, void *out, size_t out_bytes
 CAIFH_API int caifh_destroy(void *handle)
 {
   return guarded([&] { delete static_cast<LayerBox *>(handle); });
+}
+
+// ------------------------------------------------------------------ SafeTensors
+// One opened file (or checkpoint directory) per handle.  Strings come back in caller buffers; a list
+// comes back as its entries joined by '\n'.
+namespace
+{
+struct FileBox
+{
+  std::unique_ptr<CAIF_SafeTensorsFile> file;
+  CAIF_SafeTensorsFormat::ShardedHandle_t directory;
+  bool is_directory = false;
+
+  const CAIF_SafeTensorsFile &FileOf(const std::string &name) const
+  {
+    return is_directory ? directory.ShardOf(name) : *file;
+  }
+};
+
+std::string joined(const std::vector<std::string> &items)
+{
+  std::string out;
+  for (const std::string &s : items)
+  {
+    out += s;
+    out += '\n';
+  }
+  return out;
+}
+
+std::vector<std::string> split_lines(const char *text)
+{
+  std::vector<std::string> out;
+  std::string cur;
+  for (const char *p = text; p != nullptr && *p != '\0'; ++p)
+  {
+    if (*p == '\n')
+    {
+      out.push_back(cur);
+      cur.clear();
+    }
+    else
+    {
+      cur += *p;
+    }
+  }
+  if (!cur.empty())
+  {
+    out.push_back(cur);
+  }
+  return out;
+}
+
+void need_room(const std::string &s, size_t cap)
+{
+  if (s.size() + 1 > cap)
+  {
+    THROW_CAIFE("caller buffer too small: " + std::to_string(s.size() + 1) + " bytes needed");
+  }
+}
+}  // namespace
+
+CAIFH_API int caifh_st_open(const char *path, void **handle)
+{
+  return guarded([&] {
+    auto box = std::make_unique<FileBox>();
+    box->file = std::make_unique<CAIF_SafeTensorsFile>(path);
+    *handle = box.release();
+  });
+}
+
+// model.safetensors.index.json + shards, or a lone model.safetensors (CAIF_SafeTensorsFormat::OpenShardedHandle)
+CAIFH_API int caifh_st_open_directory(const char *directory, void **handle)
+{
+  return guarded([&] {
+    auto box = std::make_unique<FileBox>();
+    box->directory = CAIF_SafeTensorsFormat().OpenShardedHandle(directory);
+    box->is_directory = true;
+    *handle = box.release();
+  });
+}
+
+CAIFH_API int caifh_st_close(void *handle)
+{
+  return guarded([&] { delete static_cast<FileBox *>(handle); });
+}
+
+// tensor names: a file's in header order, a directory's in weight-map (sorted) order
+CAIFH_API int caifh_st_names(void *handle, char *buf, size_t cap)
+{
+  return guarded([&] {
+    auto *box = static_cast<FileBox *>(handle);
+    std::vector<std::string> names;
+    if (box->is_directory)
+    {
+      for (const auto &kv : box->directory.WeightMap())
+      {
+        names.push_back(kv.first);
+      }
+    }
+    else
+    {
+      names = box->file->NamesInFileOrder();
+    }
+    const std::string text = joined(names);
+    need_room(text, cap);
+    copy_string(text, buf, cap);
+  });
+}
+
+CAIFH_API int caifh_st_info(void *handle, const char *name, char *dtype, size_t dtype_cap, uint32_t *rank,
+                            uint32_t *shape, uint32_t shape_cap, uint64_t *begin, uint64_t *end, uint64_t *bytes,
+                            char *file_path, size_t file_cap)
+{
+  return guarded([&] {
+    auto *box = static_cast<FileBox *>(handle);
+    const CAIF_SafeTensorsFile &file = box->FileOf(name);
+    const auto &info = file.Info(name);
+    copy_string(info.dtype, dtype, dtype_cap);
+    *rank = static_cast<uint32_t>(info.shape.size());
+    if (info.shape.size() > shape_cap)
+    {
+      THROW_CAIFE("shape buffer too small");
+    }
+    std::copy(info.shape.begin(), info.shape.end(), shape);
+    *begin = info.data_offset_start;
+    *end = info.data_offset_end;
+    *bytes = file.CheckedBytes(info);
+    copy_string(file.Path(), file_path, file_cap);
+  });
+}
+
+// "__metadata__" as key '\n' value '\n' ... (a file only)
+CAIFH_API int caifh_st_metadata(void *handle, char *buf, size_t cap)
+{
+  return guarded([&] {
+    auto *box = static_cast<FileBox *>(handle);
+    if (box->is_directory)
+    {
+      THROW_CAIFE("metadata belongs to a file, not a directory");
+    }
+    std::vector<std::string> flat;
+    for (const auto &kv : box->file->Metadata())
+    {
+      flat.push_back(kv.first);
+      flat.push_back(kv.second);
+    }
+    const std::string text = joined(flat);
+    need_room(text, cap);
+    copy_string(text, buf, cap);
+  });
+}
+
+CAIFH_API int caifh_st_read(void *handle, const char *name, void *dst, size_t cap)
+{
+  return guarded([&] { static_cast<FileBox *>(handle)->FileOf(name).ReadRaw(name, dst, cap); });
+}
+
+// Host blobs to a file: dtypes are SafeTensors names, shapes are flattened rank by rank.
+CAIFH_API int caifh_st_save(const char *path, uint32_t count, const char *const *names, const char *const *dtypes,
+                            const uint32_t *ranks, const uint32_t *shapes, const void *const *data,
+                            uint32_t meta_count, const char *const *meta_keys, const char *const *meta_values)
+{
+  return guarded([&] {
+    std::vector<std::pair<std::string, CAIF_SafeTensorsFormat::HostBlob_t>> blobs;
+    const uint32_t *dim = shapes;
+    for (uint32_t i = 0; i < count; ++i)
+    {
+      CAIF_SafeTensorsFormat::HostBlob_t blob;
+      blob.dtype = dtypes[i];
+      blob.shape.assign(dim, dim + ranks[i]);
+      dim += ranks[i];
+      blob.data = data[i];
+      blobs.emplace_back(names[i], std::move(blob));
+    }
+    std::map<std::string, std::string> meta;
+    for (uint32_t i = 0; i < meta_count; ++i)
+    {
+      meta[meta_keys[i]] = meta_values[i];
+    }
+    CAIF_SafeTensorsFormat().SaveHost(path, blobs, meta);
+  });
+}
+
+// Device buffers to a file through CAIF_SafeTensorsFormat::Save (dtypes are CAIF_DataType_e values).
+CAIFH_API int caifh_st_save_device(const char *path, uint32_t count, const char *const *names, const int *dtypes,
+                                   const uint32_t *ranks, const uint32_t *shapes, void *const *device_data,
+                                   void *stream)
+{
+  return guarded([&] {
+    CAIF_CudaStream s(static_cast<cudaStream_t>(stream));
+    std::vector<CAIF_DeviceTensor> views;
+    views.reserve(count);
+    const uint32_t *dim = shapes;
+    for (uint32_t i = 0; i < count; ++i)
+    {
+      views.push_back(CAIF_DeviceTensor::WrapView(device_data[i], std::vector<uint32_t>(dim, dim + ranks[i]), s,
+                                                  static_cast<Dtype_e>(dtypes[i])));
+      dim += ranks[i];
+    }
+    std::vector<std::pair<std::string, const CAIF_DeviceTensor *>> list;
+    for (uint32_t i = 0; i < count; ++i)
+    {
+      list.emplace_back(names[i], &views[i]);
+    }
+    CAIF_SafeTensorsFormat().Save(path, list, {{"framework", "CAIF"}});
+  });
+}
+
+// A tensor of the file onto the device (native dtype) into caller memory of `cap` bytes.
+CAIFH_API int caifh_st_load_device(void *handle, const char *name, void *device_dst, size_t cap, void *stream)
+{
+  return guarded([&] {
+    CAIF_CudaStream s(static_cast<cudaStream_t>(stream));
+    CAIF_DeviceTensor t = static_cast<FileBox *>(handle)->FileOf(name).Load(name, s);
+    if (t.SizeBytes() > cap)
+    {
+      THROW_CAIFE("destination too small");
+    }
+    CAIF_CheckCuda(cudaMemcpyAsync(device_dst, t.DeviceDataRaw(), t.SizeBytes(), cudaMemcpyDeviceToDevice, s.Handle()),
+                   "copy");
+    CAIF_CheckCuda(cudaStreamSynchronize(s.Handle()), "sync");
+  });
+}
+
+// LoadFrozenLinear: weight (and scales) of a frozen linear layer straight from a file or directory;
+// scales_name may be "" when the stored tensor is a float one.
+CAIFH_API int caifh_load_frozen_linear(void *layer_handle, void *st_handle, const char *weight_name,
+                                       const char *scales_name)
+{
+  return guarded([&] {
+    auto *box = static_cast<LayerBox *>(layer_handle);
+    auto *files = static_cast<FileBox *>(st_handle);
+    const CAIF_SafeTensorsFile &file = files->FileOf(weight_name);
+    const std::string scales = scales_name != nullptr ? scales_name : "";
+    if (!scales.empty() && &files->FileOf(scales) != &file)
+    {
+      THROW_CAIFE("LoadFrozenLinear: weight and scales must live in the same shard");
+    }
+    LoadFrozenLinear(*frozen_of(box), file, weight_name, scales, *box->stream);
+  });
+}
+
+// ------------------------------------------------------------------ name mapping
+CAIFH_API int caifh_mapper_create(void **handle)
+{
+  return guarded([&] { *handle = new CAIF_WeightMapper(); });
+}
+
+CAIFH_API int caifh_mapper_destroy(void *handle)
+{
+  return guarded([&] { delete static_cast<CAIF_WeightMapper *>(handle); });
+}
+
+CAIFH_API int caifh_mapper_add(void *handle, int alias, const char *hf, const char *aif)
+{
+  return guarded([&] {
+    auto *m = static_cast<CAIF_WeightMapper *>(handle);
+    if (alias != 0)
+    {
+      m->AddAlias(hf, aif);
+    }
+    else
+    {
+      m->AddPrefixRule(hf, aif);
+    }
+  });
+}
+
+CAIFH_API int caifh_mapper_translate(void *handle, int hf_to_aif, const char *name, char *buf, size_t cap)
+{
+  return guarded([&] {
+    auto *m = static_cast<CAIF_WeightMapper *>(handle);
+    const std::string out = hf_to_aif != 0 ? m->HfToAif(name) : m->AifToHf(name);
+    need_room(out, cap);
+    copy_string(out, buf, cap);
+  });
+}
+
+// which: 0 MissingNames(aif names, available hf names), 1 UnmappedHfNames(available hf names),
+// 2 RequiredHfNames(aif names) as hf '\n' aif pairs.  Lists are '\n'-joined.
+CAIFH_API int caifh_mapper_query(void *handle, int which, const char *aif_names, const char *hf_names, char *buf,
+                                 size_t cap)
+{
+  return guarded([&] {
+    auto *m = static_cast<CAIF_WeightMapper *>(handle);
+    const std::vector<std::string> aif = split_lines(aif_names);
+    const std::vector<std::string> hf_list = split_lines(hf_names);
+    const std::set<std::string> hf(hf_list.begin(), hf_list.end());
+    std::vector<std::string> out;
+    if (which == 0)
+    {
+      out = m->MissingNames(aif, hf);
+    }
+    else if (which == 1)
+    {
+      out = m->UnmappedHfNames(hf);
+    }
+    else
+    {
+      for (const auto &pair : m->RequiredHfNames(aif))
+      {
+        out.push_back(pair.first);
+        out.push_back(pair.second);
+      }
+    }
+    const std::string text = joined(out);
+    need_room(text, cap);
+    copy_string(text, buf, cap);
+  });
 }

@@ -15,7 +15,10 @@ _lib = None
 EXPORTS = ["caifh_last_error", "caifh_frozen_linear_create", "caifh_load_weight_from_device",
            "caifh_load_scales_from_host", "caifh_lora_wrap", "caifh_forward", "caifh_backward", "caifh_description",
            "caifh_parameter_names", "caifh_counts", "caifh_parameter_copy", "caifh_frozen_tensor_fp32",
-           "caifh_moe_frozen_expert_create", "caifh_destroy"]
+           "caifh_moe_frozen_expert_create", "caifh_destroy", "caifh_st_open", "caifh_st_open_directory",
+           "caifh_st_close", "caifh_st_names", "caifh_st_info", "caifh_st_metadata", "caifh_st_read", "caifh_st_save",
+           "caifh_st_save_device", "caifh_st_load_device", "caifh_load_frozen_linear", "caifh_mapper_create",
+           "caifh_mapper_destroy", "caifh_mapper_add", "caifh_mapper_translate", "caifh_mapper_query"]
 
 
 class HostLayerError(RuntimeError):
@@ -138,3 +141,145 @@ class FrozenExpert(Layer):
         for layer in (gate, up, down):
             if layer is not None:
                 layer.h = ctypes.c_void_p()
+
+
+# ---------------------------------------------------------------------------- SafeTensors files
+_TEXT_CAP = 1 << 22
+
+
+def _strings(items):
+    arr = (ctypes.c_char_p * max(1, len(items)))()
+    for i, s in enumerate(items):
+        arr[i] = s.encode()
+    return arr
+
+
+def _flat_shapes(shapes):
+    flat = [d for shape in shapes for d in shape]
+    return ((ctypes.c_uint32 * max(1, len(shapes)))(*[len(s) for s in shapes]),
+            (ctypes.c_uint32 * max(1, len(flat)))(*flat))
+
+
+def save_safetensors(path, tensors, metadata=None):
+    """tensors: list of (name, SafeTensors dtype name, shape, bytes-like) written back to back in this order
+    (CAIF_SafeTensorsFormat::SaveHost)."""
+    metadata = metadata or {}
+    held = [bytes(t[3]) for t in tensors]
+    data = (ctypes.c_void_p * max(1, len(tensors)))()
+    for i, b in enumerate(held):
+        data[i] = ctypes.cast(ctypes.c_char_p(b), ctypes.c_void_p)
+    ranks, flat = _flat_shapes([t[2] for t in tensors])
+    keys = sorted(metadata)
+    _check(lib().caifh_st_save(path.encode(), ctypes.c_uint32(len(tensors)), _strings([t[0] for t in tensors]),
+                               _strings([t[1] for t in tensors]), ranks, flat, data, ctypes.c_uint32(len(keys)),
+                               _strings(keys), _strings([metadata[k] for k in keys])))
+
+
+def save_safetensors_device(path, tensors):
+    """tensors: list of (name, CAIF dtype code, shape, CUDA tensor holding the raw bytes); written through
+    CAIF_SafeTensorsFormat::Save with {"framework": "CAIF"} as metadata."""
+    data = (ctypes.c_void_p * max(1, len(tensors)))(*[t[3].data_ptr() for t in tensors])
+    ranks, flat = _flat_shapes([t[2] for t in tensors])
+    codes = (ctypes.c_int * max(1, len(tensors)))(*[int(t[1]) for t in tensors])
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _check(lib().caifh_st_save_device(path.encode(), ctypes.c_uint32(len(tensors)), _strings([t[0] for t in tensors]),
+                                      codes, ranks, flat, data, stream))
+
+
+class SafeTensors:
+    """One opened .safetensors file, or a checkpoint directory (index + shards)."""
+
+    def __init__(self, path, directory=False):
+        self.h = ctypes.c_void_p()
+        fn = lib().caifh_st_open_directory if directory else lib().caifh_st_open
+        _check(fn(path.encode(), ctypes.byref(self.h)))
+
+    def _text(self, fn, *args):
+        buf = ctypes.create_string_buffer(_TEXT_CAP)
+        _check(fn(self.h, *args, buf, ctypes.c_size_t(_TEXT_CAP)))
+        return buf.value.decode()
+
+    def names(self):
+        return [n for n in self._text(lib().caifh_st_names).split("\n") if n]
+
+    def metadata(self):
+        flat = self._text(lib().caifh_st_metadata).split("\n")[:-1]
+        return dict(zip(flat[0::2], flat[1::2]))
+
+    def info(self, name):
+        dtype = ctypes.create_string_buffer(16)
+        path = ctypes.create_string_buffer(4096)
+        rank, begin, end, nbytes = ctypes.c_uint32(), ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+        shape = (ctypes.c_uint32 * 16)()
+        _check(lib().caifh_st_info(self.h, name.encode(), dtype, ctypes.c_size_t(16), ctypes.byref(rank), shape,
+                                   ctypes.c_uint32(16), ctypes.byref(begin), ctypes.byref(end), ctypes.byref(nbytes),
+                                   path, ctypes.c_size_t(4096)))
+        return {"dtype": dtype.value.decode(), "shape": list(shape[:rank.value]), "begin": begin.value,
+                "end": end.value, "bytes": nbytes.value, "file": path.value.decode()}
+
+    def read(self, name):
+        n = self.info(name)["bytes"]
+        buf = ctypes.create_string_buffer(max(1, n))
+        _check(lib().caifh_st_read(self.h, name.encode(), buf, ctypes.c_size_t(n)))
+        return buf.raw[:n]
+
+    def load_device(self, name):
+        n = self.info(name)["bytes"]
+        out = torch.empty(max(1, n), dtype=torch.uint8, device="cuda")
+        _check(lib().caifh_st_load_device(self.h, name.encode(), ctypes.c_void_p(out.data_ptr()), ctypes.c_size_t(n),
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out[:n]
+
+    def load_frozen_linear(self, layer, weight_name, scales_name=""):
+        _check(lib().caifh_load_frozen_linear(layer.h, self.h, weight_name.encode(), scales_name.encode()))
+
+    def close(self):
+        if self.h:
+            lib().caifh_st_close(self.h)
+            self.h = ctypes.c_void_p()
+
+
+class WeightMapper:
+    """CAIF_WeightMapper: Hugging Face <-> CAIF tensor names."""
+
+    def __init__(self):
+        self.h = ctypes.c_void_p()
+        _check(lib().caifh_mapper_create(ctypes.byref(self.h)))
+
+    def add_prefix_rule(self, hf, aif):
+        _check(lib().caifh_mapper_add(self.h, 0, hf.encode(), aif.encode()))
+
+    def add_alias(self, hf, aif):
+        _check(lib().caifh_mapper_add(self.h, 1, hf.encode(), aif.encode()))
+
+    def _translate(self, direction, name):
+        buf = ctypes.create_string_buffer(4096)
+        _check(lib().caifh_mapper_translate(self.h, direction, name.encode(), buf, ctypes.c_size_t(4096)))
+        return buf.value.decode()
+
+    def hf_to_aif(self, name):
+        return self._translate(1, name)
+
+    def aif_to_hf(self, name):
+        return self._translate(0, name)
+
+    def _query(self, which, aif_names, hf_names):
+        buf = ctypes.create_string_buffer(_TEXT_CAP)
+        _check(lib().caifh_mapper_query(self.h, which, "\n".join(aif_names).encode(), "\n".join(hf_names).encode(),
+                                        buf, ctypes.c_size_t(_TEXT_CAP)))
+        return [n for n in buf.value.decode().split("\n") if n]
+
+    def missing_names(self, aif_names, available_hf):
+        return self._query(0, aif_names, available_hf)
+
+    def unmapped_hf_names(self, available_hf):
+        return self._query(1, [], available_hf)
+
+    def required_hf_names(self, aif_names):
+        flat = self._query(2, aif_names, [])
+        return list(zip(flat[0::2], flat[1::2]))
+
+    def close(self):
+        if self.h:
+            lib().caifh_mapper_destroy(self.h)
+            self.h = ctypes.c_void_p()

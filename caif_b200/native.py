@@ -81,6 +81,7 @@ _SIGNATURES = {
     "caifq_moe_route_grouped": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "caifq_moe_router_bwd": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
                                             ctypes.c_float, _i32, _vp]),
+    "caifq_moe_bias_update": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "caifq_moe_aux_losses": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float,
                                             ctypes.c_float, _vp]),
     "caifq_lora_adamw_step": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32,
@@ -503,6 +504,14 @@ def moe_aux_losses(logits, probs, expert_offsets, top_k, balance_weight, z_weigh
                                       _ptr(zls), _ptr(sums), dtype_code(ref), tokens, experts, top_k,
                                       float(balance_weight), float(z_weight), _stream()), "moe_aux_losses")
     return sums, bias, lse, zls
+
+
+def moe_bias_update(bias, counts, rate, from_offsets=False):
+    """Aux-loss-free balancing: bias moves by `rate` towards the mean load, in place."""
+    _need_cuda(bias, counts)
+    _check(lib().caifq_moe_bias_update(_ptr(bias), _ptr(counts), 1 if from_offsets else 0, dtype_code(bias),
+                                       bias.numel(), float(rate), _stream()), "moe_bias_update")
+    return bias
 
 
 def moe_softmax(logits, bias=None):

@@ -388,6 +388,15 @@ CAIFQ_API int caifq_moe_router_bwd(const void *grad_weights, const void *probs, 
                                    int32_t sigmoid_gate, int32_t normalize, float routed_scaling_factor,
                                    int32_t exact_jacobian, void *stream);
 /*
+ * CAIF_Ops::MoEBiasUpdate (src/caif_ops_device.cpp:4644-4672, launch_moe_bias_update,
+ * src/caif_cuda_kernels_moe.cu:481-537), the aux-loss-free balancing step of SigmoidNoauxTc routers
+ * (src/caif_device_moe_router.cpp:942): bias[e] += rate where the expert's load is under the mean load,
+ * -= rate where over, in place, rounded to `dtype`.  counts is device int32 [experts], or the
+ * [experts + 1] offsets caifq_moe_build_dispatch wrote when from_offsets != 0.  Bit-identical.
+ */
+CAIFQ_API int caifq_moe_bias_update(void *bias, const int32_t *counts, int32_t from_offsets, int32_t dtype,
+                                    int32_t experts, float rate, void *stream);
+/*
  * The auxiliary losses of CAIF_DeviceMoELayer and the operands their gradients enter the router backward
  * with (src/caif_device_moe_layer.cpp:792-835 and 853-925), on the device, with no host round trip:
  *   sums[0] = balance_weight * experts * sum_e (count_e / (tokens * top_k)) * (sum_t probs[t, e] / tokens)

@@ -13,7 +13,9 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <map>
 #include <memory>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -29,6 +31,8 @@
 #include "caif_device_tensor.h"
 #include "caif_ops.h"
 #include "caif_run_context.h"
+#include "caif_safetensors_format.h"
+#include "caif_weight_mapper.h"
 #include "caif_settings.h"
 
 using namespace instance;
@@ -386,6 +390,204 @@ __attribute__((visibility("default"))) int refl_host_matmul(int kind, void *a, v
 __attribute__((visibility("default"))) int refl_destroy(void *handle)
 {
   return guarded([&] { delete static_cast<Box *>(handle); });
+}
+
+// ---- the reference's SafeTensors reader / writer and name mapper -------------------------------
+// Lists come back as '\n'-joined text in the caller's buffer.  TensorInfos, Metadata and the mapper touch
+// no device; Save and Load go through CAIF_DeviceTensor::FromHostRaw / CopyToHostRaw.
+static void refl_text_out(const std::string &text, char *buf, size_t cap)
+{
+  if (text.size() + 1 > cap)
+  {
+    throw std::runtime_error("caller buffer too small");
+  }
+  std::memcpy(buf, text.c_str(), text.size() + 1);
+}
+
+static std::vector<std::string> refl_lines(const char *text)
+{
+  std::vector<std::string> out;
+  std::string cur;
+  for (const char *p = text; p != nullptr && *p != '\0'; ++p)
+  {
+    if (*p == '\n')
+    {
+      out.push_back(cur);
+      cur.clear();
+    }
+    else
+    {
+      cur += *p;
+    }
+  }
+  if (!cur.empty())
+  {
+    out.push_back(cur);
+  }
+  return out;
+}
+
+// one line per tensor, sorted by name: name '\t' dtype '\t' d0,d1,... '\t' begin '\t' end
+__attribute__((visibility("default"))) int refl_st_tensor_infos(const char *path, char *buf, size_t cap)
+{
+  return guarded([&] {
+    CAIF_SafeTensorsFormat fmt;
+    std::string text;
+    for (const auto &kv : fmt.TensorInfos(path))
+    {
+      text += kv.first + "\t" + kv.second.dtype + "\t";
+      for (size_t i = 0; i < kv.second.shape.size(); ++i)
+      {
+        text += (i ? "," : "") + std::to_string(kv.second.shape[i]);
+      }
+      text += "\t" + std::to_string(kv.second.data_offset_start) + "\t" + std::to_string(kv.second.data_offset_end) + "\n";
+    }
+    refl_text_out(text, buf, cap);
+  });
+}
+
+__attribute__((visibility("default"))) int refl_st_metadata(const char *path, char *buf, size_t cap)
+{
+  return guarded([&] {
+    CAIF_SafeTensorsFormat fmt;
+    std::string text;
+    for (const auto &kv : fmt.Metadata(path))
+    {
+      text += kv.first + "\n" + kv.second + "\n";
+    }
+    refl_text_out(text, buf, cap);
+  });
+}
+
+__attribute__((visibility("default"))) int refl_st_save(const char *path, uint32_t count, const char *const *names,
+                                                        const int *dtypes, const uint32_t *ranks,
+                                                        const uint32_t *shapes, const void *const *host_data,
+                                                        uint32_t meta_count, const char *const *meta_keys,
+                                                        const char *const *meta_values)
+{
+  return guarded([&] {
+    std::vector<CAIF_DeviceTensor> held;
+    held.reserve(count);
+    const uint32_t *dim = shapes;
+    for (uint32_t i = 0; i < count; ++i)
+    {
+      held.push_back(CAIF_DeviceTensor::FromHostRaw(host_data[i], std::vector<uint32_t>(dim, dim + ranks[i]), stream(),
+                                                    static_cast<Dtype_e>(dtypes[i])));
+      dim += ranks[i];
+    }
+    stream().Synchronize();
+    std::vector<std::pair<std::string, const CAIF_DeviceTensor *>> list;
+    for (uint32_t i = 0; i < count; ++i)
+    {
+      list.emplace_back(names[i], &held[i]);
+    }
+    std::map<std::string, std::string> meta;
+    for (uint32_t i = 0; i < meta_count; ++i)
+    {
+      meta[meta_keys[i]] = meta_values[i];
+    }
+    CAIF_SafeTensorsFormat().Save(path, list, meta);
+  });
+}
+
+// path: a file, or a checkpoint directory when from_directory != 0 (LoadTensorByName)
+__attribute__((visibility("default"))) int refl_st_load(const char *path, int from_directory, const char *name,
+                                                        void *out, size_t cap, int *dtype, size_t *bytes)
+{
+  return guarded([&] {
+    CAIF_SafeTensorsFormat fmt;
+    CAIF_DeviceTensor t;
+    if (from_directory != 0)
+    {
+      t = fmt.LoadTensorByName(path, name, stream());
+    }
+    else
+    {
+      std::map<std::string, CAIF_DeviceTensor> all = fmt.Load(path, stream());
+      auto it = all.find(name);
+      if (it == all.end())
+      {
+        throw std::runtime_error("tensor not in file");
+      }
+      t = std::move(it->second);
+    }
+    if (t.SizeBytes() > cap)
+    {
+      throw std::runtime_error("caller buffer too small");
+    }
+    t.CopyToHostRaw(out);
+    stream().Synchronize();
+    *dtype = static_cast<int>(t.Dtype());
+    *bytes = t.SizeBytes();
+  });
+}
+
+__attribute__((visibility("default"))) int refl_mapper_create(void **handle)
+{
+  return guarded([&] { *handle = new CAIF_WeightMapper(); });
+}
+
+__attribute__((visibility("default"))) int refl_mapper_destroy(void *handle)
+{
+  return guarded([&] { delete static_cast<CAIF_WeightMapper *>(handle); });
+}
+
+__attribute__((visibility("default"))) int refl_mapper_add(void *handle, int alias, const char *hf, const char *aif)
+{
+  return guarded([&] {
+    auto *m = static_cast<CAIF_WeightMapper *>(handle);
+    if (alias != 0)
+    {
+      m->AddAlias(hf, aif);
+    }
+    else
+    {
+      m->AddPrefixRule(hf, aif);
+    }
+  });
+}
+
+__attribute__((visibility("default"))) int refl_mapper_translate(void *handle, int hf_to_aif, const char *name,
+                                                                 char *buf, size_t cap)
+{
+  return guarded([&] {
+    auto *m = static_cast<CAIF_WeightMapper *>(handle);
+    refl_text_out(hf_to_aif != 0 ? m->HfToAif(name) : m->AifToHf(name), buf, cap);
+  });
+}
+
+__attribute__((visibility("default"))) int refl_mapper_query(void *handle, int which, const char *aif_names,
+                                                             const char *hf_names, char *buf, size_t cap)
+{
+  return guarded([&] {
+    auto *m = static_cast<CAIF_WeightMapper *>(handle);
+    const std::vector<std::string> aif = refl_lines(aif_names);
+    const std::vector<std::string> hf_list = refl_lines(hf_names);
+    const std::set<std::string> hf(hf_list.begin(), hf_list.end());
+    std::string text;
+    if (which == 0)
+    {
+      for (const auto &n : m->MissingNames(aif, hf))
+      {
+        text += n + "\n";
+      }
+    }
+    else if (which == 1)
+    {
+      for (const auto &n : m->UnmappedHfNames(hf))
+      {
+        text += n + "\n";
+      }
+    }
+    else
+    {
+      for (const auto &pr : m->RequiredHfNames(aif))
+      {
+        text += pr.first + "\n" + pr.second + "\n";
+      }
+    }
+    refl_text_out(text, buf, cap);
+  });
 }
 
 }  // extern "C"

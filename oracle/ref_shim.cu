@@ -291,4 +291,15 @@ void ref_sum_axis0_bf16(const void *input, float *out, int rows, int cols, void 
                                   static_cast<cudaStream_t>(stream));
 }
 
+void ref_bias_update_f32(float *bias, const int *counts, int experts, float rate, void *stream)
+{
+  launch_moe_bias_update<float>(bias, counts, experts, rate, static_cast<cudaStream_t>(stream));
+}
+
+void ref_bias_update_bf16(void *bias, const int *counts, int experts, float rate, void *stream)
+{
+  launch_moe_bias_update<__nv_bfloat16>(static_cast<__nv_bfloat16 *>(bias), counts, experts, rate,
+                                        static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

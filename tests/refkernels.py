@@ -228,3 +228,9 @@ def sum_axis0(x):
     out = torch.empty(cols, dtype=torch.float32, device=x.device)
     _typed("ref_sum_axis0", x)(_p(x), _p(out), ctypes.c_int(rows), ctypes.c_int(cols), _s())
     return out
+
+
+def bias_update_(bias, counts, rate):
+    """launch_moe_bias_update, in place."""
+    _typed("ref_bias_update", bias)(_p(bias), _p(counts), ctypes.c_int(bias.numel()), ctypes.c_float(rate), _s())
+    return bias

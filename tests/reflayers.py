@@ -150,3 +150,82 @@ def frozen_expert(gate, up, down, input_dim, hidden_dim, storage, compute):
         if layer is not None:
             layer.h = None
     return Layer(h, input_dim, input_dim)
+
+
+# ---- the reference's SafeTensors reader / writer and name mapper (oracle/ref_layers_shim.cpp) ----
+_CAP = 1 << 22
+
+
+def _strings(items):
+    arr = (ctypes.c_char_p * max(1, len(items)))()
+    for i, s in enumerate(items):
+        arr[i] = s.encode()
+    return arr
+
+
+def st_tensor_infos(path):
+    """{name: (dtype, shape, begin, end)} from CAIF_SafeTensorsFormat::TensorInfos (no device involved)."""
+    buf = ctypes.create_string_buffer(_CAP)
+    _check(lib().refl_st_tensor_infos(path.encode(), buf, ctypes.c_size_t(_CAP)))
+    out = {}
+    for line in buf.value.decode().split("\n"):
+        if line:
+            name, dtype, shape, begin, end = line.split("\t")
+            out[name] = (dtype, [int(d) for d in shape.split(",") if d], int(begin), int(end))
+    return out
+
+
+def st_metadata(path):
+    buf = ctypes.create_string_buffer(_CAP)
+    _check(lib().refl_st_metadata(path.encode(), buf, ctypes.c_size_t(_CAP)))
+    flat = buf.value.decode().split("\n")[:-1]
+    return dict(zip(flat[0::2], flat[1::2]))
+
+
+def st_save(path, tensors, metadata=None):
+    """tensors: list of (name, CAIF_DataType_e value, shape, bytes); CAIF_SafeTensorsFormat::Save (needs a GPU)."""
+    metadata = metadata or {}
+    held = [bytes(t[3]) for t in tensors]
+    data = (ctypes.c_void_p * max(1, len(tensors)))()
+    for i, b in enumerate(held):
+        data[i] = ctypes.cast(ctypes.c_char_p(b), ctypes.c_void_p)
+    flat = [d for t in tensors for d in t[2]]
+    ranks = (ctypes.c_uint32 * max(1, len(tensors)))(*[len(t[2]) for t in tensors])
+    shapes = (ctypes.c_uint32 * max(1, len(flat)))(*flat)
+    codes = (ctypes.c_int * max(1, len(tensors)))(*[int(t[1]) for t in tensors])
+    keys = sorted(metadata)
+    _check(lib().refl_st_save(path.encode(), ctypes.c_uint32(len(tensors)), _strings([t[0] for t in tensors]), codes,
+                              ranks, shapes, data, ctypes.c_uint32(len(keys)), _strings(keys),
+                              _strings([metadata[k] for k in keys])))
+
+
+def st_load(path, name, capacity, from_directory=False):
+    """(dtype code, bytes) of one tensor through CAIF_SafeTensorsFormat::Load / LoadTensorByName (needs a GPU)."""
+    buf = ctypes.create_string_buffer(max(1, capacity))
+    dtype, nbytes = ctypes.c_int(), ctypes.c_size_t()
+    _check(lib().refl_st_load(path.encode(), int(from_directory), name.encode(), buf, ctypes.c_size_t(capacity),
+                              ctypes.byref(dtype), ctypes.byref(nbytes)))
+    return dtype.value, buf.raw[:nbytes.value]
+
+
+class Mapper:
+    def __init__(self):
+        self.h = ctypes.c_void_p()
+        _check(lib().refl_mapper_create(ctypes.byref(self.h)))
+
+    def add(self, alias, hf, aif):
+        _check(lib().refl_mapper_add(self.h, int(alias), hf.encode(), aif.encode()))
+
+    def translate(self, hf_to_aif, name):
+        buf = ctypes.create_string_buffer(4096)
+        _check(lib().refl_mapper_translate(self.h, int(hf_to_aif), name.encode(), buf, ctypes.c_size_t(4096)))
+        return buf.value.decode()
+
+    def query(self, which, aif_names, hf_names):
+        buf = ctypes.create_string_buffer(_CAP)
+        _check(lib().refl_mapper_query(self.h, which, "\n".join(aif_names).encode(), "\n".join(hf_names).encode(),
+                                       buf, ctypes.c_size_t(_CAP)))
+        return [n for n in buf.value.decode().split("\n") if n]
+
+    def close(self):
+        lib().refl_mapper_destroy(self.h)

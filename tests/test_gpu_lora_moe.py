@@ -757,3 +757,26 @@ def test_aux_losses_against_the_reference_kernels_and_the_oracle(dtype, tokens, 
     only_z = nv.moe_aux_losses(logits, None, None, top_k, bw, zw)[0].cpu().numpy()
     assert only_b[1] == 0.0 and abs(only_b[0] - got[0]) <= 1e-6 * abs(got[0])
     assert only_z[0] == 0.0 and abs(only_z[1] - got[1]) <= 1e-6 * abs(got[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("experts", [64, 257])
+def test_aux_loss_free_bias_update_equals_the_reference_kernel(dtype, experts):
+    g = torch.Generator(device="cuda").manual_seed(experts)
+    counts = torch.randint(0, 3000, (experts,), generator=g, device="cuda", dtype=torch.int32)
+    counts[3] = counts[4]
+    if experts == 64:
+        counts[:] = 1536           # every load equals the mean: nothing moves
+        counts[0], counts[1] = 1530, 1542
+    bias = (torch.randn(experts, generator=g, device="cuda") * 0.01).to(dtype)
+    offsets = torch.cat([torch.zeros(1, dtype=torch.int32, device="cuda"), counts.cumsum(0).to(torch.int32)])
+    got = nv.moe_bias_update(bias.clone(), counts, 1e-3)
+    got_off = nv.moe_bias_update(bias.clone(), offsets, 1e-3, from_offsets=True)
+    mean = np.float32(counts.cpu().numpy().astype(np.float32).sum() / np.float32(experts))
+    err = mean - counts.cpu().numpy().astype(np.float32)
+    code = orc.F32 if dtype == torch.float32 else orc.BF16
+    want = orc.round_through(bias.float().cpu().numpy() + np.float32(1e-3) * np.sign(err).astype(np.float32), code)
+    assert np.array_equal(got.float().cpu().numpy(), want)
+    assert torch.equal(got, got_off)
+    if ref.available():
+        assert torch.equal(ref.bias_update_(bias.clone(), counts, 1e-3), got)
