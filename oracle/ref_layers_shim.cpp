@@ -28,6 +28,9 @@
 #include "caif_device_lora_adapter_config.h"
 #include "caif_device_moe_frozen_expert.h"
 #include "caif_device_moe_frozen_expert_config.h"
+#include "caif_device_moe_layer.h"
+#include "caif_device_moe_layer_factory.h"
+#include "caif_moe_overflow_strategy.h"
 #include "caif_device_tensor.h"
 #include "caif_ops.h"
 #include "caif_run_context.h"
@@ -160,6 +163,49 @@ int run(void *handle, bool backward, const void *x, int x_dtype, uint32_t rows, 
   });
 }
 }  // namespace
+
+// ---- the reference's whole MoE layer over frozen experts ------------------------------------------
+// CAIF_DeviceMoELayer built from expert handles (consumed) with the constructor that takes ready experts
+// (include/caif/caif_device_moe_layer.h:101-116): no shared experts, no router noise, no token dropping.
+// The router's weight [input_dim, num_experts] (and bias, when used) is overwritten with the caller's raw
+// bytes in the storage dtype.  refl_forward / refl_backward / refl_gradient then drive it like any layer.
+template <typename ComputeT, typename StorageT>
+static std::unique_ptr<CAIF_DeviceLayer> make_moe_layer(void *const *experts, uint32_t num_experts, uint32_t input_dim,
+                                                        uint32_t hidden_dim, uint32_t top_k, const void *router_w,
+                                                        const void *router_b, int gating_kind, int norm_topk,
+                                                        float scaling, float balance_w, float z_w)
+{
+  typedef CAIF_DeviceMoEExpertBase<ComputeT, StorageT> Expert_t;
+  std::vector<std::unique_ptr<Expert_t>> routed;
+  for (uint32_t e = 0; e < num_experts; ++e)
+  {
+    Box *box = static_cast<Box *>(experts[e]);
+    Expert_t *typed = dynamic_cast<Expert_t *>(box->layer.get());
+    if (typed == nullptr)
+    {
+      throw std::runtime_error("moe layer: expert handle has another compute / storage type");
+    }
+    box->layer.release();
+    delete box;
+    routed.emplace_back(typed);
+  }
+  std::vector<std::unique_ptr<Expert_t>> shared;
+  auto layer = std::make_unique<CAIF_DeviceMoELayer<ComputeT, StorageT>>(
+      input_dim, hidden_dim, top_k, router_b != nullptr, 0.0f, 0.0f,
+      CAIF_MoEOverflowStrategy::CAIF_MoEOverflowStrategy_e::NoDrop, balance_w, z_w, std::move(routed),
+      std::move(shared), stream(), static_cast<CAIF_DeviceMoELayerFactory::GatingKind_e>(gating_kind),
+      norm_topk != 0, scaling);
+  CAIF_DeviceTensor &w = layer->ParameterTensor(0);
+  w.CopyFromHostRaw(router_w, w.SizeBytes());
+  if (router_b != nullptr)
+  {
+    CAIF_DeviceTensor &b = layer->ParameterTensor(1);
+    b.CopyFromHostRaw(router_b, b.SizeBytes());
+  }
+  stream().Synchronize();
+  layer->ZeroGradients();
+  return layer;
+}
 
 extern "C" {
 
@@ -390,6 +436,58 @@ __attribute__((visibility("default"))) int refl_host_matmul(int kind, void *a, v
 __attribute__((visibility("default"))) int refl_destroy(void *handle)
 {
   return guarded([&] { delete static_cast<Box *>(handle); });
+}
+
+__attribute__((visibility("default"))) int refl_moe_layer_create(void *const *experts, uint32_t num_experts,
+                                                                 uint32_t input_dim, uint32_t hidden_dim,
+                                                                 uint32_t top_k, int storage, int compute,
+                                                                 const void *router_w, const void *router_b,
+                                                                 int gating_kind, int norm_topk, float scaling,
+                                                                 float balance_w, float z_w, void **handle)
+{
+  return guarded([&] {
+    auto box = std::make_unique<Box>();
+    const Dtype_e sd = static_cast<Dtype_e>(storage);
+    const Dtype_e cd = static_cast<Dtype_e>(compute);
+    if (sd == Dtype_e::Float32 && cd == Dtype_e::Float32)
+    {
+      box->layer = make_moe_layer<float, float>(experts, num_experts, input_dim, hidden_dim, top_k, router_w,
+                                                router_b, gating_kind, norm_topk, scaling, balance_w, z_w);
+    }
+    else if (sd == Dtype_e::BFloat16 && cd == Dtype_e::BFloat16)
+    {
+      box->layer = make_moe_layer<__nv_bfloat16, __nv_bfloat16>(experts, num_experts, input_dim, hidden_dim, top_k,
+                                                                router_w, router_b, gating_kind, norm_topk, scaling,
+                                                                balance_w, z_w);
+    }
+    else
+    {
+      throw std::runtime_error("moe layer: built for fp32/fp32 and bf16/bf16 only");
+    }
+    *handle = box.release();
+  });
+}
+
+// balance and z loss of the last forward pass (LastBalanceLoss / LastZLoss)
+__attribute__((visibility("default"))) int refl_moe_layer_losses(void *handle, float *balance, float *z)
+{
+  return guarded([&] {
+    Box *box = static_cast<Box *>(handle);
+    if (auto *a = dynamic_cast<CAIF_DeviceMoELayer<float, float> *>(box->layer.get()))
+    {
+      *balance = a->LastBalanceLoss();
+      *z = a->LastZLoss();
+    }
+    else if (auto *b = dynamic_cast<CAIF_DeviceMoELayer<__nv_bfloat16, __nv_bfloat16> *>(box->layer.get()))
+    {
+      *balance = b->LastBalanceLoss();
+      *z = b->LastZLoss();
+    }
+    else
+    {
+      throw std::runtime_error("handle is not a MoE layer");
+    }
+  });
 }
 
 // ---- the reference's SafeTensors reader / writer and name mapper -------------------------------

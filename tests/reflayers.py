@@ -229,3 +229,26 @@ class Mapper:
 
     def close(self):
         lib().refl_mapper_destroy(self.h)
+
+
+def moe_layer(experts, input_dim, hidden_dim, top_k, storage, compute, router_w_raw, router_b_raw=None,
+              sigmoid_gate=False, norm_topk=True, scaling=1.0, balance_weight=0.0, z_weight=0.0):
+    """The reference's CAIF_DeviceMoELayer over frozen experts (handles consumed): no shared experts, no noise,
+    no token dropping; router weight [input_dim, num_experts] (and bias) set from raw bytes in `storage`."""
+    h = ctypes.c_void_p()
+    arr = (ctypes.c_void_p * len(experts))(*[e.h for e in experts])
+    w = np.ascontiguousarray(router_w_raw)
+    b = np.ascontiguousarray(router_b_raw) if router_b_raw is not None else None
+    _check(lib().refl_moe_layer_create(arr, ctypes.c_uint32(len(experts)), ctypes.c_uint32(input_dim),
+                                       ctypes.c_uint32(hidden_dim), ctypes.c_uint32(top_k), storage, compute, _p(w),
+                                       _p(b), int(sigmoid_gate), int(norm_topk), ctypes.c_float(scaling),
+                                       ctypes.c_float(balance_weight), ctypes.c_float(z_weight), ctypes.byref(h)))
+    for e in experts:
+        e.h = None
+    return Layer(h, input_dim, input_dim)
+
+
+def moe_layer_losses(layer):
+    b, z = ctypes.c_float(), ctypes.c_float()
+    _check(lib().refl_moe_layer_losses(layer.h, ctypes.byref(b), ctypes.byref(z)))
+    return b.value, z.value

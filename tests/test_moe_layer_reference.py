@@ -1,0 +1,120 @@
+"""The whole frozen-MoE layer against the executing reference.
+
+The reference's CAIF_DeviceMoELayer (src/caif_device_moe_layer.cpp), built from its own unmodified sources with
+quantized frozen experts, runs forward and backward on the GPU; the same step is then made of this library's
+C-ABI calls in the order INTEGRATION.md gives for that layer (router product, softmax, top-k, normalize, scale,
+dispatch map, dispatch, grouped experts, combine; combine backward, grouped dX, dispatch backward, auxiliary
+losses, router backward, the router's two products).  Compared: the layer output, grad_input, the router
+weight gradient and both auxiliary losses.  The router backward runs with the reference's operand order of
+SoftmaxBackward (exact_jacobian = 0): that it matches the executing layer is the evidence for that reading."""
+import numpy as np
+import pytest
+import torch
+
+import caif_oracle as orc
+import reflayers as rl
+from caif_b200 import native as nv
+from gpu_util import max_rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _experts(rng, n, in_dim, hid, storage):
+    mine, theirs_args = [], []
+    for _ in range(n):
+        trio, raw = [], []
+        for out_dim, k_dim in ((hid, in_dim), (hid, in_dim), (in_dim, hid)):
+            w = (rng.standard_normal((out_dim, k_dim)) * 0.06).astype(np.float32)
+            if storage == orc.I4:
+                codes, scales = orc.quantize_int4(w, 128)
+                t_scales = torch.from_numpy(scales.view(np.int16)).cuda().view(torch.float16)
+            else:
+                codes, scales = orc.quantize_int8_per_tensor(w)
+                t_scales = to_dev(scales)
+            trio.append(nv.Weight(to_dev(codes), storage, k_dim, out_dim, t_scales, orc.PER_TENSOR, 128))
+            raw.append((k_dim, out_dim, codes, scales))
+        mine.append(trio)
+        theirs_args.append(raw)
+    return mine, theirs_args
+
+
+@pytest.mark.parametrize("storage,sd,top_k,scaling,bw,zw", [
+    (orc.I4, orc.F32, 2, 1.0, 0.0, 0.0),
+    (orc.I8, orc.F32, 3, 2.5, 0.01, 0.001),      # scaled weights, both auxiliary losses
+    (orc.I4, orc.F32, 2, 1.0, 0.02, 0.0),
+    (orc.I4, orc.BF16, 2, 1.0, 0.0, 0.0),
+])
+def test_moe_layer_step_equals_the_executing_reference(storage, sd, top_k, scaling, bw, zw):
+    if not rl.available():
+        pytest.skip("reference library not built")
+    rl.set_accuracy(True)
+    rng = np.random.default_rng(1000 + storage + top_k)
+    n_exp, in_dim, hid, tokens = 8, 256, 128, 333
+    tdt = torch.float32 if sd == orc.F32 else torch.bfloat16
+    mine, raw = _experts(rng, n_exp, in_dim, hid, storage)
+    router_w = orc.round_through((rng.standard_normal((in_dim, n_exp)) * 0.3).astype(np.float32), sd)
+    x = orc.round_through(rng.standard_normal((tokens, in_dim)).astype(np.float32), sd)
+    dy = orc.round_through(rng.standard_normal((tokens, in_dim)).astype(np.float32), sd)
+
+    # ---- the reference
+    ref_experts = []
+    for trio in raw:
+        layers = [rl.frozen_linear(k, o, storage, sd, codes, scales) for (k, o, codes, scales) in trio]
+        ref_experts.append(rl.frozen_expert(layers[0], layers[1], layers[2], in_dim, hid, sd, sd))
+    layer = rl.moe_layer(ref_experts, in_dim, hid, top_k, sd, sd, rl.to_raw(router_w, sd), scaling=scaling,
+                         balance_weight=bw, z_weight=zw)
+    want_y, _ = layer.forward(rl.to_raw(x, sd), sd, training=True)
+    want_losses = rl.moe_layer_losses(layer)
+    want_dx, _ = layer.backward(rl.to_raw(dy, sd), sd)
+    want_gw = layer.gradient(1, (in_dim, n_exp), sd)
+    layer.close()
+
+    # ---- the same step out of this library's calls
+    compute = sd
+    xd, dyd = to_dev(x, tdt), to_dev(dy, tdt)
+    wr = nv.Weight(to_dev(router_w, tdt), sd, n_exp, in_dim)       # [in_dim, E] read as out = in_dim, in = E
+    logits = nv.linear_dx(wr, xd, tdt, compute)                     # x . W
+    probs = nv.moe_softmax(logits)
+    idx, val = nv.moe_topk(probs, top_k)
+    w = nv.moe_normalize_rows(val)
+    if scaling != 1.0:
+        w = nv.scale(w, scaling)
+    dmap, off = nv.moe_build_dispatch(idx, n_exp)
+    offs = off.cpu().tolist()
+    total = offs[-1]
+    buf = nv.moe_dispatch(xd, idx, dmap, off, total)
+    gate, up, down = [t[0] for t in mine], [t[1] for t in mine], [t[2] for t in mine]
+    out_buf, g_out, u_out = nv.grouped_expert_fwd(gate, up, down, offs, buf, compute)
+    y = nv.moe_combine(out_buf, idx, w, dmap, off, tokens)
+    sums, bal_bias, zls = torch.zeros(2, device="cuda"), None, None
+    if bw > 0 or zw > 0:
+        sums, bal_bias, _, zls = nv.moe_aux_losses(logits if zw > 0 else None, probs if bw > 0 else None,
+                                                   off if bw > 0 else None, top_k, bw, zw)
+    g_buf = nv.moe_combine_bwd_grad_expert(dyd, idx, w, dmap, off, total)
+    g_w = nv.moe_combine_bwd_grad_weights(dyd, out_buf, idx, dmap, off)
+    dx_buf = nv.grouped_expert_bwd(gate, up, down, offs, g_buf, g_out, u_out, compute)
+    dx_e = nv.moe_dispatch_bwd(dx_buf, idx, dmap, off, tokens)
+    gl, _ = nv.moe_router_bwd(g_w, probs, idx, bal_bias if bw > 0 else None, zls if zw > 0 else None, False, True,
+                              scaling)
+    dx_r = nv.linear_fwd(wr, gl, tdt, compute)                      # grad_logits . W^T
+    dx = (dx_e.float() + dx_r.float()).to(tdt)
+    gw = (xd.double().t() @ gl.double()).float()                    # the router's weight gradient from grad_logits
+
+    # tokens whose k-th and (k+1)-th probabilities nearly tie may route differently after a last-bit
+    # difference in the router product; they are left out of the row-wise comparisons
+    top = torch.topk(probs.float(), top_k + 1, dim=-1).values
+    firm = ((top[:, top_k - 1] - top[:, top_k]) > (1e-5 if sd == orc.F32 else 2e-2) * top[:, 0]).cpu().numpy()
+    assert firm.mean() > (0.99 if sd == orc.F32 else 0.7)
+    tol = 1e-4 if sd == orc.F32 else 3e-2
+    assert max_rel_err(y.float().cpu().numpy()[firm], want_y[firm]) <= tol
+    assert max_rel_err(dx.float().cpu().numpy()[firm], want_dx[firm]) <= (5e-4 if sd == orc.F32 else tol)
+    if sd == orc.F32 and firm.all():
+        assert max_rel_err(gw.cpu().numpy(), want_gw) <= 5e-4
+        got = sums[:2].cpu().numpy()
+        for g, wv, on in ((got[0], want_losses[0], bw > 0), (got[1], want_losses[1], zw > 0)):
+            assert (abs(g - wv) <= 1e-4 * abs(wv)) if on else (g == 0.0 and wv == 0.0)
+        # the softmax Jacobian proper gives another router gradient than the executing reference's
+        gl_exact, _ = nv.moe_router_bwd(g_w, probs, idx, bal_bias if bw > 0 else None, zls if zw > 0 else None, False,
+                                        True, scaling, exact_jacobian=True)
+        gw_exact = (xd.double().t() @ gl_exact.double()).float()
+        assert max_rel_err(gw_exact.cpu().numpy(), want_gw) > 1e-2
