@@ -408,7 +408,11 @@ CAIFQ_API int caifq_moe_bias_update(void *bias, const int32_t *counts, int32_t f
  * logits may be NULL (no z-loss: sums[1] = 0) and probs may be NULL (no balance loss: sums[0] = 0).
  * lse, z_lse_scaled and balance_bias are bit-identical to the reference's tensors (its logsumexp tree order,
  * src/caif_cuda_kernels_elementwise.cu:930-990); the two loss values add their terms in another order
- * than the reference's sequential column sums and atomics and agree to rounding.
+ * than the reference's sequential column sums and agree to rounding.  One deliberate difference: the reference
+ * sums the squared logsumexp with launch_reduction_sum, whose kernel stores one partial per 256-element block
+ * (src/caif_cuda_kernels_elementwise.cu:450-493) into a one-element tensor (src/caif_device_moe_layer.cpp:911-913),
+ * so beyond 256 tokens its z loss holds the first block's partial only (and the other partials land past the
+ * tensor); sums[1] here is the sum over all tokens.  The z-loss GRADIENT operand is unaffected in both.
  */
 CAIFQ_API int caifq_moe_aux_losses(const void *logits, const void *probs, const int32_t *expert_offsets,
                                    void *balance_bias, void *lse, void *z_lse_scaled, float *sums, int32_t dtype,

@@ -852,6 +852,11 @@ ORC_EXPORT void orc_router_backward(const float *grad_w, const float *probs, con
 /* (T(sum_t probs[t,e]) / tokens) with the column sums added sequentially over t        */
 /* (sum_axis0_kernel, :800-816); balance_bias[e] = T(bw E / (tokens^2 k) * count_e).    */
 /* losses[0] = balance, losses[1] = z.  logits or probs may be NULL.                    */
+/* The z loss here sums over ALL tokens.  The executing reference reduces with           */
+/* launch_reduction_sum, one partial per 256-element block stored into a one-element     */
+/* tensor (:450-493 of the elementwise kernels, moe_layer.cpp:911-913), so for more than */
+/* 256 tokens it reports the first block's partial; tests/test_moe_layer_reference.py    */
+/* reproduces that figure from the first 256 rows of this function's lse.                */
 ORC_EXPORT void orc_moe_aux_losses(const float *logits, const float *probs, const int32_t *counts, int tokens,
                                    int experts, int top_k, float balance_weight, float z_weight, int dtype,
                                    float *balance_bias, float *lse, float *z_lse_scaled, float *losses)

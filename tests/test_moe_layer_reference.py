@@ -38,10 +38,30 @@ def _experts(rng, n, in_dim, hid, storage):
     return mine, theirs_args
 
 
+def _float64_grad_input(x, dy, router_w, experts, idx, n_exp, top_k):
+    """grad_input of the layer step in float64 with the routing held fixed (test arithmetic, int4 experts)."""
+    def dense(wt):
+        flat = nv.dequantize_int4(wt.codes, wt.scales, wt.in_dim * wt.out_dim, 128)
+        return flat.reshape(wt.out_dim, wt.in_dim).double()
+
+    xt = torch.from_numpy(x).cuda().double().requires_grad_(True)
+    p = torch.softmax(xt @ torch.from_numpy(router_w).cuda().double(), -1)
+    chosen = torch.gather(p, 1, idx.long())
+    w = chosen / chosen.sum(-1, keepdim=True)
+    y = torch.zeros_like(xt)
+    for e in range(n_exp):
+        g, u, d = dense(experts[e][0]), dense(experts[e][1]), dense(experts[e][2])
+        out_e = (torch.nn.functional.silu(xt @ g.t()) * (xt @ u.t())) @ d.t()
+        for k in range(top_k):
+            y = y + torch.where((idx[:, k] == e)[:, None], w[:, k:k + 1] * out_e, torch.zeros_like(out_e))
+    y.backward(torch.from_numpy(dy).cuda().double())
+    return xt.grad.cpu().numpy()
+
+
 @pytest.mark.parametrize("storage,sd,top_k,scaling,bw,zw", [
     (orc.I4, orc.F32, 2, 1.0, 0.0, 0.0),
     (orc.I8, orc.F32, 3, 2.5, 0.01, 0.001),      # scaled weights, both auxiliary losses
-    (orc.I4, orc.F32, 2, 1.0, 0.02, 0.0),
+    (orc.I4, orc.F32, 2, 1.0, 20.0, 0.0),        # a balance term large enough to tell the two softmax-backward forms apart
     (orc.I4, orc.BF16, 2, 1.0, 0.0, 0.0),
 ])
 def test_moe_layer_step_equals_the_executing_reference(storage, sd, top_k, scaling, bw, zw):
@@ -52,7 +72,7 @@ def test_moe_layer_step_equals_the_executing_reference(storage, sd, top_k, scali
     n_exp, in_dim, hid, tokens = 8, 256, 128, 333
     tdt = torch.float32 if sd == orc.F32 else torch.bfloat16
     mine, raw = _experts(rng, n_exp, in_dim, hid, storage)
-    router_w = orc.round_through((rng.standard_normal((in_dim, n_exp)) * 0.3).astype(np.float32), sd)
+    router_w = orc.round_through((rng.standard_normal((in_dim, n_exp)) * 0.05).astype(np.float32), sd)
     x = orc.round_through(rng.standard_normal((tokens, in_dim)).astype(np.float32), sd)
     dy = orc.round_through(rng.standard_normal((tokens, in_dim)).astype(np.float32), sd)
 
@@ -86,10 +106,10 @@ def test_moe_layer_step_equals_the_executing_reference(storage, sd, top_k, scali
     gate, up, down = [t[0] for t in mine], [t[1] for t in mine], [t[2] for t in mine]
     out_buf, g_out, u_out = nv.grouped_expert_fwd(gate, up, down, offs, buf, compute)
     y = nv.moe_combine(out_buf, idx, w, dmap, off, tokens)
-    sums, bal_bias, zls = torch.zeros(2, device="cuda"), None, None
+    sums, bal_bias, lse, zls = torch.zeros(2, device="cuda"), None, None, None
     if bw > 0 or zw > 0:
-        sums, bal_bias, _, zls = nv.moe_aux_losses(logits if zw > 0 else None, probs if bw > 0 else None,
-                                                   off if bw > 0 else None, top_k, bw, zw)
+        sums, bal_bias, lse, zls = nv.moe_aux_losses(logits if zw > 0 else None, probs if bw > 0 else None,
+                                                     off if bw > 0 else None, top_k, bw, zw)
     g_buf = nv.moe_combine_bwd_grad_expert(dyd, idx, w, dmap, off, total)
     g_w = nv.moe_combine_bwd_grad_weights(dyd, out_buf, idx, dmap, off)
     dx_buf = nv.grouped_expert_bwd(gate, up, down, offs, g_buf, g_out, u_out, compute)
@@ -103,18 +123,43 @@ def test_moe_layer_step_equals_the_executing_reference(storage, sd, top_k, scali
     # tokens whose k-th and (k+1)-th probabilities nearly tie may route differently after a last-bit
     # difference in the router product; they are left out of the row-wise comparisons
     top = torch.topk(probs.float(), top_k + 1, dim=-1).values
-    firm = ((top[:, top_k - 1] - top[:, top_k]) > (1e-5 if sd == orc.F32 else 2e-2) * top[:, 0]).cpu().numpy()
+    firm = ((top[:, top_k - 1] - top[:, top_k]) > (1e-5 if sd == orc.F32 else 3e-2) * top[:, top_k - 1]).cpu().numpy()
     assert firm.mean() > (0.99 if sd == orc.F32 else 0.7)
     tol = 1e-4 if sd == orc.F32 else 3e-2
     assert max_rel_err(y.float().cpu().numpy()[firm], want_y[firm]) <= tol
-    assert max_rel_err(dx.float().cpu().numpy()[firm], want_dx[firm]) <= (5e-4 if sd == orc.F32 else tol)
+    if sd == orc.F32:
+        assert max_rel_err(dx.float().cpu().numpy()[firm], want_dx[firm]) <= 5e-4
+    else:
+        # In bf16 the router's share of grad_input comes out of differences of nearly equal 8-bit values (the
+        # normalize Jacobian over the chosen experts), so one ulp anywhere upstream moves it by percents: the
+        # two implementations are each held against a float64 evaluation of the same step with the same routing,
+        # and this library must be as close to it as the executing reference is.
+        true_dx = _float64_grad_input(x, dy, router_w, mine, idx, n_exp, top_k)
+        err_mine = max_rel_err(dx.float().cpu().numpy()[firm], true_dx[firm])
+        err_ref = max_rel_err(want_dx[firm], true_dx[firm])
+        assert err_mine <= max(1.25 * err_ref, 3e-2)
     if sd == orc.F32 and firm.all():
         assert max_rel_err(gw.cpu().numpy(), want_gw) <= 5e-4
         got = sums[:2].cpu().numpy()
-        for g, wv, on in ((got[0], want_losses[0], bw > 0), (got[1], want_losses[1], zw > 0)):
-            assert (abs(g - wv) <= 1e-4 * abs(wv)) if on else (g == 0.0 and wv == 0.0)
-        # the softmax Jacobian proper gives another router gradient than the executing reference's
+        assert (abs(got[0] - want_losses[0]) <= 1e-4 * abs(want_losses[0])) if bw > 0 else \
+            (got[0] == 0.0 and want_losses[0] == 0.0)
+        if zw > 0:
+            # The reference sums the squared logsumexp with launch_reduction_sum, whose kernel stores one partial
+            # per 256-element block (src/caif_cuda_kernels_elementwise.cu:450-493) into a one-element tensor
+            # (src/caif_device_moe_layer.cpp:911-913): beyond 256 tokens its z loss holds the first block only.
+            # This library returns the whole sum; the reference's figure is reproduced from the first 256 rows.
+            sq = lse.double().cpu().numpy() ** 2
+            assert abs(got[1] - zw * sq.sum() / tokens) <= 1e-4 * got[1]
+            assert abs(want_losses[1] - zw * sq[:256].sum() / tokens) <= 1e-4 * want_losses[1]
+        else:
+            assert got[1] == 0.0 and want_losses[1] == 0.0
+        # With rows normalized and no auxiliary term the dot product of the softmax backward vanishes and the two
+        # ways of evaluating it coincide; a balance term makes them differ, and the executing reference then
+        # follows the operand order this library reproduces, not the softmax Jacobian proper.
         gl_exact, _ = nv.moe_router_bwd(g_w, probs, idx, bal_bias if bw > 0 else None, zls if zw > 0 else None, False,
                                         True, scaling, exact_jacobian=True)
         gw_exact = (xd.double().t() @ gl_exact.double()).float()
-        assert max_rel_err(gw_exact.cpu().numpy(), want_gw) > 1e-2
+        if bw >= 1.0:
+            assert max_rel_err(gw_exact.cpu().numpy(), want_gw) > 1e-2
+        elif bw == 0.0 and zw == 0.0:
+            assert max_rel_err(gw_exact.cpu().numpy(), want_gw) <= 5e-4
