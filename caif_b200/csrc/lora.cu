@@ -612,16 +612,56 @@ __global__ void expand_prepare_kernel(const ExpandPrepare p)
   const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (blockIdx.y == 0)
   {
-    for (int64_t i = first; i < p.units; i += stride)
+    // four units per thread and trip, a block width apart: the loads are all in flight before the first
+    // conversion and a warp's accesses stay contiguous
+    constexpr int kPerTrip = 4;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x * kPerTrip + threadIdx.x; base < p.units;
+         base += stride * kPerTrip)
     {
       if (STORAGE == CAIFQ_I8)
       {
-        p.wb[i] = expand_int8x8(__ldg(static_cast<const uint2 *>(p.codes) + i));
+        uint2 c[kPerTrip];
+#pragma unroll
+        for (int u = 0; u < kPerTrip; ++u)
+        {
+          const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+          c[u] = (i < p.units) ? __ldg(static_cast<const uint2 *>(p.codes) + i) : make_uint2(0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < kPerTrip; ++u)
+        {
+          const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+          if (i < p.units)
+          {
+            p.wb[i] = expand_int8x8(c[u]);
+          }
+        }
       }
       else
       {
-        p.wb[i] = expand_int4x8(__ldg(static_cast<const uint32_t *>(p.codes) + i),
-                                __half2float(p.scales[(i * 8) / p.group_size]));
+        uint32_t c[kPerTrip];
+        __half sc[kPerTrip];
+#pragma unroll
+        for (int u = 0; u < kPerTrip; ++u)
+        {
+          const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+          c[u] = 0u;
+          sc[u] = __half();
+          if (i < p.units)
+          {
+            c[u] = __ldg(static_cast<const uint32_t *>(p.codes) + i);
+            sc[u] = __ldg(p.scales + (i * 8) / p.group_size);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kPerTrip; ++u)
+        {
+          const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+          if (i < p.units)
+          {
+            p.wb[i] = expand_int4x8(c[u], __half2float(sc[u]));
+          }
+        }
       }
     }
     return;

@@ -480,18 +480,57 @@ __global__ void expand_kernel(const __grid_constant__ ExpandTable t, uint4 *dst,
 {
   const int e = blockIdx.y;
   uint4 *out = dst + static_cast<int64_t>(e) * units;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < units; i += stride)
+  // four units per thread and trip, a block width apart: all four loads are in flight before the first
+  // conversion, and a warp's accesses stay contiguous
+  constexpr int kPerTrip = 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x * kPerTrip;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x * kPerTrip + threadIdx.x; base < units;
+       base += stride)
   {
     if (STORAGE == CAIFQ_I8)
     {
-      out[i] = expand_int8x8(__ldg(static_cast<const uint2 *>(t.codes[e]) + i));
+      uint2 c[kPerTrip];
+#pragma unroll
+      for (int u = 0; u < kPerTrip; ++u)
+      {
+        const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+        c[u] = (i < units) ? __ldg(static_cast<const uint2 *>(t.codes[e]) + i) : make_uint2(0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < kPerTrip; ++u)
+      {
+        const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+        if (i < units)
+        {
+          out[i] = expand_int8x8(c[u]);
+        }
+      }
     }
     else
     {
-      // eight codes lie in one group
-      const float scale = __half2float(t.scales[e][(i * 8) / group_size]);
-      out[i] = expand_int4x8(__ldg(static_cast<const uint32_t *>(t.codes[e]) + i), scale);
+      uint32_t c[kPerTrip];
+      __half sc[kPerTrip];
+#pragma unroll
+      for (int u = 0; u < kPerTrip; ++u)
+      {
+        const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+        c[u] = 0u;
+        sc[u] = __half();
+        if (i < units)
+        {
+          c[u] = __ldg(static_cast<const uint32_t *>(t.codes[e]) + i);
+          sc[u] = __ldg(t.scales[e] + (i * 8) / group_size);   // eight codes lie in one group
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kPerTrip; ++u)
+      {
+        const int64_t i = base + static_cast<int64_t>(u) * blockDim.x;
+        if (i < units)
+        {
+          out[i] = expand_int4x8(c[u], __half2float(sc[u]));
+        }
+      }
     }
   }
 }
