@@ -654,20 +654,26 @@ def bench_c2(ctx):
                         "timed region (CUDA events around the step / 768 launches; includes inter-launch gaps)"}
 
     # end to end: host buffers in, host buffers out, through the C ABI, copies inside the timed region
-    hx = {m: xs[m].cpu().pin_memory() for m in C2_MS}
-    hy = {m: torch.empty(m, shard, dtype=torch.float32).pin_memory() for m in C2_MS}
-    # one device copy of x and one result buffer per launch of a pass, in two sets that alternate between
-    # passes: the copy-in of a launch runs while the launch before it still reads its own input, and a pass
-    # reuses the buffers of the pass two back, ordered by one event per pass and direction.  Copies ride two
-    # side streams (one per direction) beside the kernels.
-    dx = [{m: [torch.empty_like(xs[m]) for _ in range(C2_COPIES)] for m in C2_MS} for _ in range(2)]
-    dy_out = [{m: [torch.empty(m, shard, dtype=torch.float32, device=dev) for _ in range(C2_COPIES)] for m in C2_MS}
-              for _ in range(2)]
+    # One pinned block of inputs and one of results per pass (the 24 launches of one layer: M = 1, 4, 16 on the 8
+    # weight copies, every launch with its own input rows): one copy in before the pass and one copy out after
+    # it, on two side streams beside the kernels, so that the launches of a pass follow one another without a
+    # copy between them.  Two sets of device blocks alternate between passes: the copy-in of a pass runs while
+    # the pass before it computes, its copy-out while the next one does; a set is reused two passes later,
+    # ordered by one event per pass and direction.
+    hx = torch.cat([xs[m].cpu() for m in C2_MS for _ in range(C2_COPIES)]).pin_memory()
+    hy = torch.empty(C2_COPIES * rows_all, shard, dtype=torch.float32).pin_memory()
+    dx = [torch.empty(C2_COPIES * rows_all, C2_IN, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    dy_out = [torch.empty(C2_COPIES * rows_all, shard, dtype=torch.float32, device=dev) for _ in range(2)]
+    slot = {}
+    r0 = 0
+    for m in C2_MS:
+        for c in range(C2_COPIES):
+            slot[(m, c)] = (r0, r0 + m)
+            r0 += m
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    ev_in = {m: [torch.cuda.Event() for _ in range(C2_COPIES)] for m in C2_MS}
-    ev_k = {m: [torch.cuda.Event() for _ in range(C2_COPIES)] for m in C2_MS}
+    ev_h2d = [torch.cuda.Event() for _ in range(2)]            # the inputs of the pass on set b have arrived
     ev_pass_kernels = [torch.cuda.Event() for _ in range(2)]   # the kernels of the last pass on set b are done
-    ev_pass_d2h = [torch.cuda.Event() for _ in range(2)]       # ... and so are its copies to the host
+    ev_pass_d2h = [torch.cuda.Event() for _ in range(2)]       # ... and so is its copy to the host
 
     def e2e_pass(p):
         main = torch.cuda.current_stream()
@@ -675,19 +681,19 @@ def bench_c2(ctx):
         if p >= 2:
             s_in.wait_event(ev_pass_kernels[b])    # inputs of set b are free again
             main.wait_event(ev_pass_d2h[b])        # results of set b have left for the host
+        with torch.cuda.stream(s_in):
+            dx[b].copy_(hx, non_blocking=True)
+            ev_h2d[b].record(s_in)
+        main.wait_event(ev_h2d[b])
         for m in C2_MS:
             for c, w in enumerate(weights):
-                with torch.cuda.stream(s_in):
-                    dx[b][m][c].copy_(hx[m], non_blocking=True)
-                    ev_in[m][c].record(s_in)
-                main.wait_event(ev_in[m][c])
-                nv.linear_fwd(w, dx[b][m][c], compute=nv.F32, out=dy_out[b][m][c])
-                ev_k[m][c].record(main)
-                s_out.wait_event(ev_k[m][c])
-                with torch.cuda.stream(s_out):
-                    hy[m].copy_(dy_out[b][m][c], non_blocking=True)
+                lo, hi = slot[(m, c)]
+                nv.linear_fwd(w, dx[b][lo:hi], compute=nv.F32, out=dy_out[b][lo:hi])
         ev_pass_kernels[b].record(main)
-        ev_pass_d2h[b].record(s_out)
+        s_out.wait_event(ev_pass_kernels[b])
+        with torch.cuda.stream(s_out):
+            hy.copy_(dy_out[b], non_blocking=True)
+            ev_pass_d2h[b].record(s_out)
 
     def e2e_body():
         main = torch.cuda.current_stream()
