@@ -998,6 +998,111 @@ int caifq_moe_router_bwd(const void *grad_weights, const void *probs, const int3
                                routed_scaling_factor, exact_jacobian ? 1 : 0, static_cast<cudaStream_t>(stream));
 }
 
+// ---- several layers that share their input as one product over the concatenated weights ----
+namespace
+{
+int concat_check(const caifq_weight *ws, int32_t count, int64_t *rows_out, const char *who)
+{
+  CAIFQ_CHECK_ARG(ws != nullptr && count >= 1 && count <= 8, "%s: 1 to 8 weights", who);
+  int64_t rows = 0;
+  for (int i = 0; i < count; ++i)
+  {
+    const int rc = check_weight(&ws[i], who);
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+    CAIFQ_CHECK_ARG(ws[i].in_dim == ws[0].in_dim, "%s: weight %d has in_dim %d, weight 0 has %d", who, i,
+                    ws[i].in_dim, ws[0].in_dim);
+    CAIFQ_CHECK_ARG((ws[i].out_dim % 8) == 0, "%s: out_dim of weight %d must be a multiple of 8", who, i);
+    rows += ws[i].out_dim;
+  }
+  CAIFQ_CHECK_ARG(rows <= 0x7FFFFFFF, "%s: too many output features", who);
+  *rows_out = rows;
+  return CAIFQ_OK;
+}
+
+int concat_run(const caifq_weight *ws, int32_t count, bool backward, const void *a, int a_dtype, int64_t m,
+               void *c, int c_dtype, int compute_dtype, void *workspace, size_t workspace_bytes, cudaStream_t s,
+               const char *who)
+{
+  int64_t rows = 0;
+  int rc = concat_check(ws, count, &rows, who);
+  if (rc != CAIFQ_OK)
+  {
+    return rc;
+  }
+  CAIFQ_CHECK_ARG(compute_dtype == CAIFQ_BF16, "%s: the concatenated operand is bf16: compute dtype must be BF16", who);
+  const size_t need = align256(static_cast<size_t>(rows) * static_cast<size_t>(ws[0].in_dim) * 2);
+  CAIFQ_CHECK_ARG(workspace != nullptr && workspace_bytes >= need, "%s: workspace of %zu bytes needed, %zu given", who,
+                  need, workspace_bytes);
+  CAIFQ_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, "%s: workspace must be 256-byte aligned", who);
+  if (m == 0)
+  {
+    return CAIFQ_OK;
+  }
+  caifq_weight cat = float_weight(workspace, CAIFQ_BF16, static_cast<int>(rows), ws[0].in_dim);
+  LinearArgs probe{};
+  probe.w = cat;
+  probe.backward = backward;
+  probe.a = a;
+  probe.a_dtype = a_dtype;
+  probe.a_prescale = 1.0f;
+  probe.m = m;
+  probe.c = c;
+  probe.c_dtype = c_dtype;
+  probe.compute_dtype = compute_dtype;
+  if (!umma_supported(probe))
+  {
+    set_error("%s: needs the tensor-core path (bf16 activations, at least 32 rows, aligned buffers); call the layers "
+              "one by one, or caifq_linear_fwd_multi for up to 16 rows",
+              who);
+    return CAIFQ_ERR_UNSUPPORTED;
+  }
+  uint8_t *dst = static_cast<uint8_t *>(workspace);
+  for (int i = 0; i < count; ++i)
+  {
+    rc = launch_weight_to_bf16_scaled(ws[i], dst, s);
+    if (rc != CAIFQ_OK)
+    {
+      return rc;
+    }
+    dst += static_cast<size_t>(ws[i].out_dim) * static_cast<size_t>(ws[i].in_dim) * 2;
+  }
+  return linear_any(&cat, backward, a, a_dtype, 1.0f, m, c, c_dtype, false, compute_dtype, s, who);
+}
+}  // namespace
+
+size_t caifq_linear_concat_workspace_bytes(const caifq_weight *ws, int32_t count)
+{
+  if (ws == nullptr || count < 1)
+  {
+    return 0;
+  }
+  size_t rows = 0;
+  for (int i = 0; i < count; ++i)
+  {
+    rows += static_cast<size_t>(ws[i].out_dim);
+  }
+  return align256(rows * static_cast<size_t>(ws[0].in_dim) * 2);
+}
+
+int caifq_linear_fwd_concat(const caifq_weight *ws, int32_t count, const void *x, int32_t x_dtype, int64_t m,
+                            void *y, int32_t y_dtype, int32_t compute_dtype, void *workspace, size_t workspace_bytes,
+                            void *stream)
+{
+  return concat_run(ws, count, false, x, x_dtype, m, y, y_dtype, compute_dtype, workspace, workspace_bytes,
+                    static_cast<cudaStream_t>(stream), "caifq_linear_fwd_concat");
+}
+
+int caifq_linear_dx_concat(const caifq_weight *ws, int32_t count, const void *dy, int32_t dy_dtype, int64_t m,
+                           void *dx, int32_t dx_dtype, int32_t compute_dtype, void *workspace, size_t workspace_bytes,
+                           void *stream)
+{
+  return concat_run(ws, count, true, dy, dy_dtype, m, dx, dx_dtype, compute_dtype, workspace, workspace_bytes,
+                    static_cast<cudaStream_t>(stream), "caifq_linear_dx_concat");
+}
+
 int caifq_moe_bias_update(void *bias, const int32_t *counts, int32_t from_offsets, int32_t dtype, int32_t experts,
                           float rate, void *stream)
 {

@@ -218,6 +218,8 @@ int launch_weight_materialize(const caifq_weight &w, void *dst, int dst_dtype, c
 // int8 / int4 codes -> a bf16 [out, in] matrix for the tensor core: int8 codes as exact integers (the scale
 // is left to the epilogue), int4 as bf16(scale * code), the reference's dequantize-then-cast value
 int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s);
+// the weight as the bf16 matrix bf16 compute sees (scales inside the values): int4, int8 per-tensor, floats
+int launch_weight_to_bf16_scaled(const caifq_weight &w, void *dst, cudaStream_t s);
 // the same for `count` experts of one shape in one launch; expert e lands at dst + e * out * in elements
 int launch_expand_grouped_to_bf16(const caifq_weight *ws, int count, void *dst, cudaStream_t s);
 

@@ -588,6 +588,70 @@ int launch_expand_grouped_to_bf16(const caifq_weight *ws, int count, void *dst, 
 
 int launch_expand_to_bf16(const caifq_weight &w, void *dst, cudaStream_t s) { return launch_expand_grouped_to_bf16(&w, 1, dst, s); }
 
+// ---- a weight as the bf16 matrix the reference's ConvertToComputeDtype would hold for bf16 compute ----
+// (src/caif_device_frozen_linear.cpp:288-378): int8 per-tensor bf16(float(code) * scale), int4 as
+// expand_int4x8, bf16 copied, fp32 / fp16 rounded to bf16.  Used where several layers' weights are laid one
+// under the other into one operand (fused q/k/v), so the scale has to be inside the values.
+__global__ void expand_int8_scaled_kernel(const uint2 *__restrict__ codes, const float *__restrict__ scale,
+                                          uint4 *__restrict__ dst, int64_t units)
+{
+  const float sc = __ldg(scale);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < units; i += stride)
+  {
+    const uint2 v = __ldg(codes + i);
+    const uint32_t w[2] = {v.x, v.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+    {
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+      {
+        const float lo = __fmul_rn(static_cast<float>(static_cast<int8_t>((w[k] >> (16 * h)) & 0xFFu)), sc);
+        const float hi = __fmul_rn(static_cast<float>(static_cast<int8_t>((w[k] >> (16 * h + 8)) & 0xFFu)), sc);
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[2 * k + h]) : "f"(hi), "f"(lo));
+      }
+    }
+    dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+int launch_weight_to_bf16_scaled(const caifq_weight &w, void *dst, cudaStream_t s)
+{
+  const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;
+  if (w.storage == CAIFQ_I4)
+  {
+    return launch_expand_to_bf16(w, dst, s);
+  }
+  if (w.storage == CAIFQ_I8)
+  {
+    if (w.scheme != CAIFQ_PER_TENSOR || w.scales == nullptr || (total % 8) != 0 ||
+        (reinterpret_cast<uintptr_t>(w.codes) & 7u) != 0)
+    {
+      set_error("weight_to_bf16: int8 needs one per-tensor scale, 8-byte aligned codes and a multiple of 8 weights");
+      return CAIFQ_ERR_UNSUPPORTED;
+    }
+    const int64_t units = total / 8;
+    expand_int8_scaled_kernel<<<grid_for(units), kBlock, 0, s>>>(static_cast<const uint2 *>(w.codes),
+                                                               static_cast<const float *>(w.scales),
+                                                               static_cast<uint4 *>(dst), units);
+    CAIFQ_CHECK_LAUNCH();
+    return CAIFQ_OK;
+  }
+  if (w.storage == CAIFQ_BF16)
+  {
+    const cudaError_t err = cudaMemcpyAsync(dst, w.codes, static_cast<size_t>(total) * 2, cudaMemcpyDeviceToDevice, s);
+    if (err != cudaSuccess)
+    {
+      set_error("weight_to_bf16: copy failed: %s", cudaGetErrorString(err));
+      return CAIFQ_ERR_CUDA;
+    }
+    return CAIFQ_OK;
+  }
+  return launch_cast(w.codes, w.storage, dst, CAIFQ_BF16, total, s);
+}
+
 int launch_weight_materialize(const caifq_weight &w, void *dst, int dst_dtype, cudaStream_t s)
 {
   const int64_t total = static_cast<int64_t>(w.in_dim) * w.out_dim;

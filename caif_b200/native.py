@@ -72,6 +72,11 @@ _SIGNATURES = {
     "caifq_linear_fwd": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_linear_fwd_residual": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
     "caifq_linear_fwd_multi": (ctypes.c_int, [ctypes.POINTER(CWeight), _i32, _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
+    "caifq_linear_concat_workspace_bytes": (ctypes.c_size_t, [ctypes.POINTER(CWeight), _i32]),
+    "caifq_linear_fwd_concat": (ctypes.c_int, [ctypes.POINTER(CWeight), _i32, _vp, _i32, _i64, _vp, _i32, _i32, _vp,
+                                               ctypes.c_size_t, _vp]),
+    "caifq_linear_dx_concat": (ctypes.c_int, [ctypes.POINTER(CWeight), _i32, _vp, _i32, _i64, _vp, _i32, _i32, _vp,
+                                              ctypes.c_size_t, _vp]),
     "caifq_linear_fwd_gather": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, ctypes.POINTER(_vp), _i32,
                                                _i64, _i64, _i32, _i32, _vp]),
     "caifq_linear_dx": (ctypes.c_int, [ctypes.POINTER(CWeight), _vp, _i32, _i64, _vp, _i32, _i32, _vp]),
@@ -321,6 +326,23 @@ def linear_fwd_multi(ws, x, out_dtype=torch.float32, compute=F32, out=None):
     _check(lib().caifq_linear_fwd_multi(arr, len(ws), _ptr(x), dtype_code(x), m, _ptr(y), dtype_code(y), compute,
                                         _stream()), "caifq_linear_fwd_multi")
     return y
+
+
+def linear_concat(ws, act, backward=False, out_dtype=torch.bfloat16, workspace=None):
+    """Many-token product of several frozen linears that share their input as one launch over the concatenated
+    weights: forward y[m, sum out_i] = x . [W_0; W_1; ...]^T, or backward dx[m, in] = dy[m, sum out_i] . [W_0; ...]."""
+    _need_cuda(act, workspace)
+    arr = _weight_array(ws)
+    total = sum(w.out_dim for w in ws)
+    need = lib().caifq_linear_concat_workspace_bytes(arr, len(ws))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=act.device)
+    m = act.numel() // (total if backward else ws[0].in_dim)
+    out = torch.empty((m, ws[0].in_dim if backward else total), dtype=out_dtype, device=act.device)
+    fn = lib().caifq_linear_dx_concat if backward else lib().caifq_linear_fwd_concat
+    _check(fn(arr, len(ws), _ptr(act), dtype_code(act), m, _ptr(out), dtype_code(out), BF16, _ptr(workspace),
+              workspace.numel(), _stream()), "caifq_linear_concat")
+    return out
 
 
 def linear_fwd_gather(w, x, peer_ptrs, y_ld, y_col0, y_dtype=F32, compute=F32):

@@ -323,6 +323,29 @@ CAIFQ_API int caifq_lora_linear_bwd_noalloc(const caifq_weight *w, const caifq_l
                                             const void *x, const void *hidden, int64_t m, void *dx, void *d_a,
                                             void *d_b, int32_t compute_dtype, void *stream);
 
+/*
+ * Several frozen linears that share their input (q / k / v of an attention block, gate / up of an FFN) as ONE
+ * tensor-core product over their weights laid one under the other -- the fusion the reference applies to its
+ * own non-projection attention path (CHANGES.md:183-187) and SURVEY lists for the frozen projections:
+ *   fwd:  y [m, sum out_i] = x . [W_0; W_1; ...]^T     (columns of layer i start at sum_{j<i} out_j)
+ *   dx:   dx [m, in] = dy [m, sum out_i] . [W_0; W_1; ...]   one reduction over all layers' features instead of
+ *         one launch per layer accumulating into dx
+ * Each call first writes the layers' weights into `workspace` as the bf16 matrix the reference's
+ * ConvertToComputeDtype holds for bf16 compute (src/caif_device_frozen_linear.cpp:288-378: int4
+ * bf16(scale * code), int8 per-tensor bf16(float(code) * scale), floats rounded to bf16), then runs one launch
+ * on CTA pairs.  compute_dtype must be CAIFQ_BF16; activations bf16, m >= 32; all layers one in_dim; up to 8
+ * layers; workspace >= caifq_linear_concat_workspace_bytes, 256-byte aligned, free again when the call's work
+ * on `stream` is done.  Other calls are refused with CAIFQ_ERR_UNSUPPORTED (run the layers one by one, or
+ * caifq_linear_fwd_multi for up to 16 rows).
+ */
+CAIFQ_API size_t caifq_linear_concat_workspace_bytes(const caifq_weight *ws, int32_t count);
+CAIFQ_API int caifq_linear_fwd_concat(const caifq_weight *ws, int32_t count, const void *x, int32_t x_dtype,
+                                      int64_t m, void *y, int32_t y_dtype, int32_t compute_dtype, void *workspace,
+                                      size_t workspace_bytes, void *stream);
+CAIFQ_API int caifq_linear_dx_concat(const caifq_weight *ws, int32_t count, const void *dy, int32_t dy_dtype,
+                                     int64_t m, void *dx, int32_t dx_dtype, int32_t compute_dtype, void *workspace,
+                                     size_t workspace_bytes, void *stream);
+
 /* ---- MoE routing and dispatch -------------------------------------------- */
 
 /* launch_topk, src/caif_cuda_kernels_moe.cu:280-345: descending values, ties to

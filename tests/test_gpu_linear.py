@@ -454,3 +454,48 @@ def test_forward_with_the_residual_add_in_the_epilogue(storage, compute, sd, m):
     sep = nv.linear_fwd(weight, x, TORCH_DTYPE[sd], compute)
     if nv.last_path() != "decode":     # (the few-token kernel sums in another order than the kernel that accumulates)
         assert torch.equal(got, (sep.float() + res.float()).to(TORCH_DTYPE[sd]))
+
+
+@pytest.mark.parametrize("storage", [orc.I4, orc.I8, orc.BF16])
+def test_layers_sharing_their_input_as_one_product_over_concatenated_weights(storage):
+    """caifq_linear_fwd_concat / caifq_linear_dx_concat on the attention shapes of the Llama-like config scaled
+    down (q of 1024, k and v of 256 features over 512 inputs, 4099 tokens): the columns of every layer hold what
+    the oracle gives for that layer alone (weights as bf16 compute sees them), dX the sum over the layers, and
+    both agree with the per-layer calls."""
+    rng = np.random.default_rng(700 + storage)
+    in_dim, outs, m = 512, (1024, 256, 256), 4099
+    layers = [make_weight(rng, o, in_dim, storage, std=0.05) for o in outs]
+    ws = [l[0] for l in layers]
+    wc = [orc.weight_to_compute(l[1], l[2], storage, in_dim, o, orc.BF16, l[0].scheme, l[0].group_size)
+          for l, o in zip(layers, outs)]
+    x_np, x = act(rng, m, in_dim, orc.BF16)
+    dy_np, dy = act(rng, m, sum(outs), orc.BF16)
+    y = nv.linear_concat(ws, x, out_dtype=torch.float32)
+    assert nv.last_path() == "umma"
+    dx = nv.linear_concat(ws, dy, backward=True, out_dtype=torch.float32)
+    assert nv.lib().caifq_device_status() == 0
+    rows = np.r_[0:8, 2000:2008, m - 8:m]
+    col = 0
+    want_dx = np.zeros((rows.size, in_dim), np.float64)
+    per_layer_dx = torch.zeros(m, in_dim, device="cuda")
+    for w, c, o in zip(ws, wc, outs):
+        want = orc.frozen_linear_forward(x_np[rows], c, orc.BF16)
+        assert max_rel_err(y[rows, col:col + o].cpu().numpy(), want) <= TOL_16
+        alone = nv.linear_fwd(w, x, torch.float32, orc.BF16)
+        assert max_rel_err(y[:, col:col + o].cpu().numpy(), alone.cpu().numpy()) <= TOL_16
+        want_dx += orc.frozen_linear_backward(dy_np[rows, col:col + o], c, orc.BF16)
+        per_layer_dx += nv.linear_dx(w, dy[:, col:col + o].contiguous(), torch.float32, orc.BF16)
+        col += o
+    assert max_rel_err(dx[rows].cpu().numpy(), want_dx) <= TOL_16
+    assert max_rel_err(dx.cpu().numpy(), per_layer_dx.cpu().numpy()) <= TOL_16
+    # refusals: fp32 compute has no bf16 operand; a short workspace
+    arr = nv._weight_array(ws)
+    y2 = torch.empty(m, sum(outs), device="cuda")
+    scratch = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    rc = nv.lib().caifq_linear_fwd_concat(arr, 3, nv._ptr(x), nv.BF16, m, nv._ptr(y2), nv.F32, nv.BF16, nv._ptr(scratch),
+                                          1024, nv._stream())
+    assert rc == 1 and b"workspace" in nv.lib().caifq_last_error()
+    big = torch.empty(nv.lib().caifq_linear_concat_workspace_bytes(arr, 3), dtype=torch.uint8, device="cuda")
+    rc = nv.lib().caifq_linear_fwd_concat(arr, 3, nv._ptr(x), nv.BF16, m, nv._ptr(y2), nv.F32, nv.F32, nv._ptr(big),
+                                          big.numel(), nv._stream())
+    assert rc == 1 and b"BF16" in nv.lib().caifq_last_error()
