@@ -1058,7 +1058,7 @@ def bench_c4lin(ctx):
         # The collectives run beside the persistent tensor-core kernels: they get SMs of their own.  The
         # kernels' grids are capped (caifq_set_cta_limit) and this workload's communicator is held to
         # as many CTAs as the kernels leave free; other workloads keep the default communicator.
-        nccl_ctas = 16 if world < 4 else 32
+        nccl_ctas = args.c4_nccl_ctas if args.c4_nccl_ctas else (16 if world < 4 else 32)
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         nv.lib().caifq_set_cta_limit(sms - nccl_ctas)
         try:
@@ -1317,6 +1317,8 @@ def main():
     ap.add_argument("--workload", default=None, help="shorthand for --workloads with one entry")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA-graph replay")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--c4-nccl-ctas", type=int, default=None,
+                    help="c4lin on several GPUs: CTAs left to NCCL (default 16 below 4 GPUs, else 32)")
     ap.add_argument("--c2-layers", type=int, default=None,
                     help="layer passes per c2 step instead of 32 (a short step for profiler captures; the line "
                          "then does not describe the configured workload)")
