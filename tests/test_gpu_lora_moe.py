@@ -673,6 +673,8 @@ def test_grouped_sigmoid_routing_bit_exact_with_the_reference_kernels(dtype, use
     (True, False, 16.0, False, 256, 8),    # sigmoid gating, scaled only; rows wider than the softmax block
     (False, True, 1.0, True, 160, 6),      # columns beyond 128: two per thread of the reference's block
     (False, True, 1.0, True, 8, 2),
+    (False, True, 0.5, True, 3, 1),        # a single chosen expert: the normalize Jacobian is zero
+    (True, False, 1.0, False, 5, 5),       # every expert chosen
 ])
 def test_router_backward_bit_exact_with_the_reference_chain(dtype, sigmoid_gate, normalize, scaling, with_aux,
                                                             experts, top_k):
@@ -780,3 +782,22 @@ def test_aux_loss_free_bias_update_equals_the_reference_kernel(dtype, experts):
     assert torch.equal(got, got_off)
     if ref.available():
         assert torch.equal(ref.bias_update_(bias.clone(), counts, 1e-3), got)
+
+
+def test_router_backward_edge_cases():
+    """No tokens: nothing is written.  One token.  Indices outside [0, experts) contribute nothing (the
+    reference's scatter skips them too, src/caif_cuda_kernels_moe.cu:565-569)."""
+    probs = torch.rand(0, 8, device="cuda")
+    idx = torch.zeros(0, 2, dtype=torch.int32, device="cuda")
+    out, _ = nv.moe_router_bwd(torch.zeros(0, 2, device="cuda"), probs, idx)
+    assert out.shape == (0, 8)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    probs = torch.softmax(torch.randn(1, 8, generator=g, device="cuda"), -1)
+    idx = torch.tensor([[2, 99]], dtype=torch.int32, device="cuda")
+    grad_w = torch.tensor([[0.5, -0.25]], device="cuda")
+    got, got_topk = nv.moe_router_bwd(grad_w, probs, idx)
+    want, want_topk = orc.router_backward(grad_w.cpu().numpy(), probs.cpu().numpy(), idx.cpu().numpy())
+    assert np.array_equal(got.cpu().numpy(), want) and np.array_equal(got_topk.cpu().numpy(), want_topk)
+    with pytest.raises(nv.CaifqError, match="top_k"):
+        nv.moe_router_bwd(torch.zeros(2, 40, device="cuda"), torch.rand(2, 64, device="cuda"),
+                          torch.zeros(2, 40, dtype=torch.int32, device="cuda"))
