@@ -115,6 +115,10 @@ int launch_gemm_tn(const void *u, const void *v, void *c, float *scratch, int dt
 int launch_scale(const void *src, void *dst, int dtype, float scale, int64_t n, cudaStream_t s);
 int launch_moe_bias_update(void *bias, const int *counts, int dtype, int experts, float rate, int from_offsets,
                            cudaStream_t s);
+int launch_rmsnorm_fwd(const void *input, const float *gamma, void *output, float *rms_cache, float epsilon, int dtype,
+                       int rows, int dim, cudaStream_t s);
+int launch_rmsnorm_bwd(const void *grad_output, const void *input, const float *gamma, const float *rms_cache,
+                       void *grad_input, float *grad_gamma, int dtype, int rows, int dim, cudaStream_t s);
 int launch_moe_router_bwd(const void *grad_w, const void *probs, const int *indices, const void *balance_bias,
                           const void *z_lse_scaled, void *grad_topk, void *grad_logits, int dtype, int tokens,
                           int experts, int top_k, int sigmoid_gate, int normalize, float scaling, int exact_jacobian,
@@ -1101,6 +1105,27 @@ int caifq_linear_dx_concat(const caifq_weight *ws, int32_t count, const void *dy
 {
   return concat_run(ws, count, true, dy, dy_dtype, m, dx, dx_dtype, compute_dtype, workspace, workspace_bytes,
                     static_cast<cudaStream_t>(stream), "caifq_linear_dx_concat");
+}
+
+int caifq_rmsnorm_fwd(const void *x, const float *gamma, void *y, float *rms_cache, float epsilon, int32_t dtype,
+                      int32_t rows, int32_t dim, void *stream)
+{
+  const char *who = "caifq_rmsnorm_fwd";
+  CAIFQ_CHECK_ARG(rows >= 0 && dim > 0, "%s: bad shape rows=%d dim=%d", who, rows, dim);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(rows == 0 || (x && gamma && y), "%s: null pointer", who);
+  return launch_rmsnorm_fwd(x, gamma, y, rms_cache, epsilon, dtype, rows, dim, static_cast<cudaStream_t>(stream));
+}
+
+int caifq_rmsnorm_bwd(const void *dy, const void *x, const float *gamma, const float *rms_cache, void *dx,
+                      float *grad_gamma, int32_t dtype, int32_t rows, int32_t dim, void *stream)
+{
+  const char *who = "caifq_rmsnorm_bwd";
+  CAIFQ_CHECK_ARG(rows >= 0 && dim > 0, "%s: bad shape rows=%d dim=%d", who, rows, dim);
+  CAIFQ_CHECK_ARG(is_float_dtype(dtype), "%s: dtype must be F32, F16 or BF16", who);
+  CAIFQ_CHECK_ARG(rows == 0 || (dy && x && gamma && rms_cache && dx), "%s: null pointer", who);
+  return launch_rmsnorm_bwd(dy, x, gamma, rms_cache, dx, grad_gamma, dtype, rows, dim,
+                            static_cast<cudaStream_t>(stream));
 }
 
 int caifq_moe_bias_update(void *bias, const int32_t *counts, int32_t from_offsets, int32_t dtype, int32_t experts,

@@ -86,6 +86,8 @@ _SIGNATURES = {
     "caifq_moe_route_grouped": (ctypes.c_int, [_vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "caifq_moe_router_bwd": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
                                             ctypes.c_float, _i32, _vp]),
+    "caifq_rmsnorm_fwd": (ctypes.c_int, [_vp, _vp, _vp, _vp, ctypes.c_float, _i32, _i32, _i32, _vp]),
+    "caifq_rmsnorm_bwd": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "caifq_moe_bias_update": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, ctypes.c_float, _vp]),
     "caifq_moe_aux_losses": (ctypes.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float,
                                             ctypes.c_float, _vp]),
@@ -534,6 +536,31 @@ def moe_bias_update(bias, counts, rate, from_offsets=False):
     _check(lib().caifq_moe_bias_update(_ptr(bias), _ptr(counts), 1 if from_offsets else 0, dtype_code(bias),
                                        bias.numel(), float(rate), _stream()), "moe_bias_update")
     return bias
+
+
+def rmsnorm_fwd(x, gamma, epsilon=1e-5):
+    """Returns (y, rms_cache)."""
+    _need_cuda(x, gamma)
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    y = torch.empty_like(x)
+    rms = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(lib().caifq_rmsnorm_fwd(_ptr(x), _ptr(gamma), _ptr(y), _ptr(rms), float(epsilon), dtype_code(x), rows, dim,
+                                   _stream()), "rmsnorm_fwd")
+    return y, rms
+
+
+def rmsnorm_bwd(dy, x, gamma, rms_cache, grad_gamma=None):
+    """Returns (dx, grad_gamma); grad_gamma is accumulated onto the tensor given (zeros when None)."""
+    _need_cuda(dy, x, gamma, rms_cache, grad_gamma)
+    dim = x.shape[-1]
+    rows = x.numel() // dim
+    dx = torch.empty_like(x)
+    if grad_gamma is None:
+        grad_gamma = torch.zeros(dim, dtype=torch.float32, device=x.device)
+    _check(lib().caifq_rmsnorm_bwd(_ptr(dy), _ptr(x), _ptr(gamma), _ptr(rms_cache), _ptr(dx), _ptr(grad_gamma),
+                                   dtype_code(x), rows, dim, _stream()), "rmsnorm_bwd")
+    return dx, grad_gamma
 
 
 def moe_softmax(logits, bias=None):

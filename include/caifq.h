@@ -346,6 +346,26 @@ CAIFQ_API int caifq_linear_dx_concat(const caifq_weight *ws, int32_t count, cons
                                      int64_t m, void *dx, int32_t dx_dtype, int32_t compute_dtype, void *workspace,
                                      size_t workspace_bytes, void *stream);
 
+/* ---- the norm in front of the frozen projections --------------------------- */
+
+/*
+ * RMSNorm as CAIF_DevicePreNormBlock applies it before a frozen linear
+ * (src/caif_device_pre_norm_block.cpp:97-135; kernels src/caif_cuda_kernels_normalization.cu:46-119, 129-203):
+ *   fwd: rms[r] = sqrt(mean_c x[r,c]^2 + epsilon); y[r,c] = T(x[r,c] / rms[r] * gamma[c]); rms_cache [rows] fp32
+ *        (may be NULL when no backward follows)
+ *   bwd: dx[r,c] = T(rstd * (dy * gamma - x_hat * mean_c(dy * gamma * x_hat))), x_hat = x * rstd, rstd = 1 / rms;
+ *        grad_gamma[c] += sum_r dy[r,c] * x_hat[r,c]  (fp32 [dim], accumulated onto what is there: zero it first,
+ *        as the reference does; may be NULL)
+ * x, y, dy, dx in `dtype`; gamma, rms_cache, grad_gamma fp32.  y, rms_cache and dx are bit-identical to the
+ * reference kernels (same per-thread column order, reduction trees and roundings); grad_gamma is a sum over
+ * rows whose order the reference leaves to its atomics and agrees to rounding.  Rows up to 96 KB (forward) /
+ * 8192 elements (backward).  In place (y == x, dx == dy) is allowed.
+ */
+CAIFQ_API int caifq_rmsnorm_fwd(const void *x, const float *gamma, void *y, float *rms_cache, float epsilon,
+                                int32_t dtype, int32_t rows, int32_t dim, void *stream);
+CAIFQ_API int caifq_rmsnorm_bwd(const void *dy, const void *x, const float *gamma, const float *rms_cache, void *dx,
+                                float *grad_gamma, int32_t dtype, int32_t rows, int32_t dim, void *stream);
+
 /* ---- MoE routing and dispatch -------------------------------------------- */
 
 /* launch_topk, src/caif_cuda_kernels_moe.cu:280-345: descending values, ties to

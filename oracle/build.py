@@ -54,7 +54,8 @@ def build_reference_kernels(force=False):
                os.path.join(ref_src, "caif_cuda_kernels_attention_support.cu"),
                os.path.join(ref_src, "caif_cuda_kernels_elementwise.cu"),
                os.path.join(ref_src, "caif_cuda_kernels_optimizers.cu"),
-               os.path.join(ref_src, "caif_cuda_kernels_activations.cu")]
+               os.path.join(ref_src, "caif_cuda_kernels_activations.cu"),
+               os.path.join(ref_src, "caif_cuda_kernels_normalization.cu")]
     shim = os.path.join(HERE, "ref_shim.cu")
     if not all(os.path.exists(s) for s in sources):
         return REF_SO if os.path.exists(REF_SO) else None

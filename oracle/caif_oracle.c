@@ -943,6 +943,112 @@ ORC_EXPORT void orc_moe_aux_losses(const float *logits, const float *probs, cons
   }
 }
 
+/* RMSNorm, src/caif_cuda_kernels_normalization.cu:46-119 (forward) and 129-203          */
+/* (backward): one block of 256 threads per row, thread t over columns t, t+256, ...    */
+/* with a fused multiply-add per step; warp_reduce_sum is a shuffle-DOWN tree (offsets  */
+/* 16..1; a lane whose partner is out of range adds its own value, only lane 0 is used);*/
+/* the eight warp sums sit in lanes 0..7 of warp 0 and go through the same tree.        */
+/* rms = sqrtf(sum / dim + eps); y = T((x * (1 / rms)) * gamma).  Backward:             */
+/* sum_term = sum((dy * gamma) * x_hat) / dim with x_hat = x * rstd;                    */
+/* dx = T(rstd * (dy * gamma - x_hat * sum_term)), the inner expression fused as the    */
+/* reference build fuses it (`form` 0, pinned on the GPU against its kernel:             */
+/* fma(dy, gamma, -(x_hat sum_term));                                                   */
+/* 1 fma(-x_hat, sum_term, dy gamma), 2 unfused); grad_gamma[c] = sum_r dy * x_hat      */
+/* in row order (the reference's atomics fix no order).                                 */
+static float orc_shfl_down_tree(const float *lanes32)
+{
+  float v[32];
+  memcpy(v, lanes32, sizeof(v));
+  for (int off = 16; off > 0; off >>= 1)
+  {
+    float n[32];
+    for (int l = 0; l < 32; ++l)
+    {
+      n[l] = v[l] + (l + off < 32 ? v[l + off] : v[l]);
+    }
+    memcpy(v, n, sizeof(v));
+  }
+  return v[0];
+}
+
+static float orc_block256_sum(const float *thread_vals)
+{
+  float warp[32];
+  memset(warp, 0, sizeof(warp));
+  for (int w = 0; w < 8; ++w)
+  {
+    warp[w] = orc_shfl_down_tree(thread_vals + 32 * w);
+  }
+  return orc_shfl_down_tree(warp);
+}
+
+ORC_EXPORT void orc_rmsnorm_forward(const float *x, const float *gamma, int rows, int dim, float eps, int dtype,
+                                    float *y, float *rms_out)
+{
+#pragma omp parallel for schedule(static)
+  for (int r = 0; r < rows; ++r)
+  {
+    const float *xr = x + (int64_t)r * dim;
+    float t[256];
+    for (int i = 0; i < 256; ++i)
+    {
+      t[i] = 0.0f;
+      for (int c = i; c < dim; c += 256)
+      {
+        t[i] = fmaf(xr[c], xr[c], t[i]);
+      }
+    }
+    const float rms = sqrtf(orc_block256_sum(t) / (float)dim + eps);
+    rms_out[r] = rms;
+    const float rstd = 1.0f / rms;
+    for (int c = 0; c < dim; ++c)
+    {
+      y[(int64_t)r * dim + c] = orc_round1((xr[c] * rstd) * gamma[c], dtype);
+    }
+  }
+}
+
+ORC_EXPORT void orc_rmsnorm_backward(const float *dy, const float *x, const float *gamma, const float *rms, int rows,
+                                     int dim, int dtype, int form, float *dx, float *grad_gamma)
+{
+  memset(grad_gamma, 0, (size_t)dim * sizeof(float));
+  for (int r = 0; r < rows; ++r)
+  {
+    const float *xr = x + (int64_t)r * dim;
+    const float *gr = dy + (int64_t)r * dim;
+    const float rstd = 1.0f / rms[r];
+    float t[256];
+    for (int i = 0; i < 256; ++i)
+    {
+      t[i] = 0.0f;
+      for (int c = i; c < dim; c += 256)
+      {
+        t[i] = fmaf(gr[c] * gamma[c], xr[c] * rstd, t[i]);
+      }
+    }
+    const float sum_term = orc_block256_sum(t) / (float)dim;
+    for (int c = 0; c < dim; ++c)
+    {
+      const float x_hat = xr[c] * rstd;
+      float inner;
+      if (form == 0)
+      {
+        inner = fmaf(gr[c], gamma[c], -(x_hat * sum_term));
+      }
+      else if (form == 1)
+      {
+        inner = fmaf(-x_hat, sum_term, gr[c] * gamma[c]);
+      }
+      else
+      {
+        inner = gr[c] * gamma[c] - x_hat * sum_term;
+      }
+      dx[(int64_t)r * dim + c] = orc_round1(rstd * inner, dtype);
+      grad_gamma[c] += gr[c] * x_hat;
+    }
+  }
+}
+
 /* Dispatch map: CAIF_Ops::MoEBuildDispatchMapDevice,                        */
 /* src/caif_ops_device.cpp:4876-4950.  counts per expert (indices outside    */
 /* [0,E) ignored) -> capacity clamp -> exclusive prefix sum -> position of   */

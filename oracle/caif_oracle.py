@@ -388,6 +388,35 @@ def moe_aux_losses(logits, probs, counts, top_k, balance_weight, z_weight, dtype
     return losses, bias, lse, zls
 
 
+RMSNORM_FORM = 0   # how the reference build fuses dy * gamma - x_hat * sum_term (see orc_rmsnorm_backward)
+
+
+def rmsnorm_forward(x, gamma, eps=1e-5, dtype=F32):
+    """(y, rms) of the reference's RMSNorm forward kernel (src/caif_cuda_kernels_normalization.cu:46-119)."""
+    x = _c(x, np.float32)
+    g = _c(gamma, np.float32)
+    rows, dim = x.shape
+    y = np.empty_like(x)
+    rms = np.empty(rows, np.float32)
+    lib().orc_rmsnorm_forward(_p(x), _p(g), ctypes.c_int(rows), ctypes.c_int(dim), ctypes.c_float(eps),
+                              ctypes.c_int(dtype), _p(y), _p(rms))
+    return y, rms
+
+
+def rmsnorm_backward(dy, x, gamma, rms, dtype=F32, form=None):
+    """(dx, grad_gamma) of the reference's RMSNorm backward kernel (:129-203)."""
+    dy = _c(dy, np.float32)
+    x = _c(x, np.float32)
+    g = _c(gamma, np.float32)
+    r = _c(rms, np.float32)
+    rows, dim = x.shape
+    dx = np.empty_like(x)
+    gg = np.empty(dim, np.float32)
+    lib().orc_rmsnorm_backward(_p(dy), _p(x), _p(g), _p(r), ctypes.c_int(rows), ctypes.c_int(dim), ctypes.c_int(dtype),
+                               ctypes.c_int(RMSNORM_FORM if form is None else form), _p(dx), _p(gg))
+    return dx, gg
+
+
 def build_dispatch_map(expert_indices, num_experts, capacity=0):
     idx = _c(expert_indices, np.int32)
     tokens, top_k = idx.shape

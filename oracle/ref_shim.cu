@@ -21,6 +21,7 @@
 #include "caif_cuda_kernels_elementwise.cuh"
 #include "caif_cuda_kernels_optimizers.cuh"
 #include "caif_cuda_kernels_activations.cuh"
+#include "caif_cuda_kernels_normalization.cuh"
 
 // The launches of CAIF_DeviceMoERouter::BackwardRoutingAuxAware (src/caif_device_moe_router.cpp:529-733) up to
 // grad_logits, in its order and with its operand order: the normalize Jacobian over the chosen scores,
@@ -300,6 +301,31 @@ void ref_bias_update_bf16(void *bias, const int *counts, int experts, float rate
 {
   launch_moe_bias_update<__nv_bfloat16>(static_cast<__nv_bfloat16 *>(bias), counts, experts, rate,
                                         static_cast<cudaStream_t>(stream));
+}
+
+void ref_rmsnorm_fwd_f32(const float *x, const float *gamma, float *y, float *rms, float eps, int rows, int dim, void *stream)
+{
+  launch_rmsnorm_forward<float>(x, gamma, y, rms, eps, rows, dim, static_cast<cudaStream_t>(stream));
+}
+
+void ref_rmsnorm_fwd_bf16(const void *x, const float *gamma, void *y, float *rms, float eps, int rows, int dim, void *stream)
+{
+  launch_rmsnorm_forward<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(x), gamma, static_cast<__nv_bfloat16 *>(y), rms,
+                                        eps, rows, dim, static_cast<cudaStream_t>(stream));
+}
+
+void ref_rmsnorm_bwd_f32(const float *dy, const float *x, const float *gamma, const float *rms, float *dx, float *gg,
+                         float eps, int rows, int dim, void *stream)
+{
+  launch_rmsnorm_backward<float>(dy, x, gamma, rms, dx, gg, eps, rows, dim, static_cast<cudaStream_t>(stream));
+}
+
+void ref_rmsnorm_bwd_bf16(const void *dy, const void *x, const float *gamma, const float *rms, void *dx, float *gg,
+                          float eps, int rows, int dim, void *stream)
+{
+  launch_rmsnorm_backward<__nv_bfloat16>(static_cast<const __nv_bfloat16 *>(dy), static_cast<const __nv_bfloat16 *>(x),
+                                         gamma, rms, static_cast<__nv_bfloat16 *>(dx), gg, eps, rows, dim,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -234,3 +234,21 @@ def bias_update_(bias, counts, rate):
     """launch_moe_bias_update, in place."""
     _typed("ref_bias_update", bias)(_p(bias), _p(counts), ctypes.c_int(bias.numel()), ctypes.c_float(rate), _s())
     return bias
+
+
+def rmsnorm_fwd(x, gamma, eps):
+    rows, dim = x.shape
+    y = torch.empty_like(x)
+    rms = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _typed("ref_rmsnorm_fwd", x)(_p(x), _p(gamma), _p(y), _p(rms), ctypes.c_float(eps), ctypes.c_int(rows),
+                                 ctypes.c_int(dim), _s())
+    return y, rms
+
+
+def rmsnorm_bwd(dy, x, gamma, rms, eps):
+    rows, dim = x.shape
+    dx = torch.empty_like(x)
+    gg = torch.zeros(dim, dtype=torch.float32, device=x.device)
+    _typed("ref_rmsnorm_bwd", x)(_p(dy), _p(x), _p(gamma), _p(rms), _p(dx), _p(gg), ctypes.c_float(eps),
+                                 ctypes.c_int(rows), ctypes.c_int(dim), _s())
+    return dx, gg

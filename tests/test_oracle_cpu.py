@@ -421,3 +421,22 @@ def test_aux_losses_restatement_against_formulas():
     assert np.isclose(losses[0], want_balance, rtol=1e-5)
     assert np.allclose(bias, bw * experts * counts / (tokens * tokens * top_k), rtol=1e-6)
     assert np.allclose(zls, lse64 * 2 * zw / tokens, rtol=1e-5)
+
+
+def test_rmsnorm_restatement_against_autograd():
+    import torch
+    rng = np.random.default_rng(17)
+    rows, dim = 9, 700
+    x = rng.standard_normal((rows, dim)).astype(np.float32)
+    gamma = (1.0 + 0.1 * rng.standard_normal(dim)).astype(np.float32)
+    dy = rng.standard_normal((rows, dim)).astype(np.float32)
+    y, rms = orc.rmsnorm_forward(x, gamma, 1e-5)
+    xt = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+    gt = torch.tensor(gamma, dtype=torch.float64, requires_grad=True)
+    yt = xt / torch.sqrt((xt * xt).mean(-1, keepdim=True) + 1e-5) * gt
+    yt.backward(torch.tensor(dy, dtype=torch.float64))
+    assert np.max(np.abs(y - yt.detach().numpy())) <= 1e-5
+    for form in (0, 1, 2):
+        dx, gg = orc.rmsnorm_backward(dy, x, gamma, rms, form=form)
+        assert np.max(np.abs(dx - xt.grad.numpy())) <= 1e-5
+        assert np.max(np.abs(gg - gt.grad.numpy())) <= 1e-4
