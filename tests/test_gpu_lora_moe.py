@@ -801,3 +801,28 @@ def test_router_backward_edge_cases():
     with pytest.raises(nv.CaifqError, match="top_k"):
         nv.moe_router_bwd(torch.zeros(2, 40, device="cuda"), torch.rand(2, 64, device="cuda"),
                           torch.zeros(2, 40, dtype=torch.int32, device="cuda"))
+
+
+@pytest.mark.parametrize("storage", [orc.I4, orc.I8])
+def test_dense_gated_ffn_is_the_grouped_call_with_one_expert(storage):
+    """CAIF_DeviceFFN with frozen gate / up / down projections (src/caif_device_ffn.cpp:324-349: gate, up, gated
+    activation, down) is the grouped expert call with a single expert that owns every row: gate + up + SwiGLU in
+    one launch, down in a second, and the mirror for dX."""
+    rng = np.random.default_rng(88 + storage)
+    in_dim, hid, rows = 512, 1408, 4099
+    ws, oracle_ws = [], []
+    for o, i in ((hid, in_dim), (hid, in_dim), (in_dim, hid)):
+        w, codes, scales = make_weight(rng, o, i, storage, std=0.05)
+        ws.append(w)
+        oracle_ws.append(orc.weight_to_compute(codes, scales, storage, i, o, orc.BF16, w.scheme, w.group_size))
+    x_np, x = act(rng, rows, in_dim, orc.BF16)
+    dy_np, dy = act(rng, rows, in_dim, orc.BF16)
+    out, g_out, u_out = nv.grouped_expert_fwd([ws[0]], [ws[1]], [ws[2]], [0, rows], x, orc.BF16)
+    assert nv.last_path() == "umma-grouped"
+    dx = nv.grouped_expert_bwd([ws[0]], [ws[1]], [ws[2]], [0, rows], dy, g_out, u_out, orc.BF16)
+    sample = np.r_[0:8, 2048:2056, rows - 3:rows]
+    want, g, u = orc.frozen_expert_forward(x_np[sample], oracle_ws[0], oracle_ws[1], oracle_ws[2], orc.BF16, orc.BF16)
+    assert max_rel_err(out[sample].float().cpu().numpy(), want) <= 2e-2
+    want_dx = orc.frozen_expert_backward(dy_np[sample], g, u, oracle_ws[0], oracle_ws[1], oracle_ws[2], orc.BF16,
+                                         orc.BF16)
+    assert max_rel_err(dx[sample].float().cpu().numpy(), want_dx) <= 2e-2
