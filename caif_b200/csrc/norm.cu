@@ -117,7 +117,7 @@ __device__ __forceinline__ void row_out(T *dst, const T *src, int dim, bool vec)
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kNormThreads)
+__global__ void __launch_bounds__(kNormThreads, 8)
 rmsnorm_fwd_kernel(const T *__restrict__ input, const float *__restrict__ gamma, T *__restrict__ output,
                    float *__restrict__ rms_cache, float epsilon, int rows, int dim, int vec)
 {
