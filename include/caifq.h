@@ -326,7 +326,7 @@ CAIFQ_API int caifq_lora_linear_bwd_noalloc(const caifq_weight *w, const caifq_l
 /*
  * Several frozen linears that share their input (q / k / v of an attention block, gate / up of an FFN) as ONE
  * tensor-core product over their weights laid one under the other -- the fusion the reference applies to its
- * own non-projection attention path (CHANGES.md:183-187) and SURVEY lists for the frozen projections:
+ * own non-projection attention path (CHANGES.md:183-187), here for the frozen projections:
  *   fwd:  y [m, sum out_i] = x . [W_0; W_1; ...]^T     (columns of layer i start at sum_{j<i} out_j)
  *   dx:   dx [m, in] = dy [m, sum out_i] . [W_0; W_1; ...]   one reduction over all layers' features instead of
  *         one launch per layer accumulating into dx

@@ -2,7 +2,7 @@
 
 The reference's CAIF_DeviceMoELayer (src/caif_device_moe_layer.cpp), built from its own unmodified sources with
 quantized frozen experts, runs forward and backward on the GPU; the same step is then made of this library's
-C-ABI calls in the order INTEGRATION.md gives for that layer (router product, softmax, top-k, normalize, scale,
+C-ABI calls in the order the layer itself works (router product, softmax, top-k, normalize, scale,
 dispatch map, dispatch, grouped experts, combine; combine backward, grouped dX, dispatch backward, auxiliary
 losses, router backward, the router's two products).  Compared: the layer output, grad_input, the router
 weight gradient and both auxiliary losses.  The router backward runs with the reference's operand order of
