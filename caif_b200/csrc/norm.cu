@@ -3,10 +3,12 @@
 // (src/caif_cuda_kernels_normalization.cu:46-119 forward, :129-203 backward) run one 256-thread block per row,
 // thread t owning columns t, t + 256, ..., and read the row twice from global memory with 2- or 4-byte loads.
 //
-// Here a CTA of 256 threads walks rows round robin; a row comes in once with 16-byte loads into shared memory,
-// both passes read it there, the result leaves with 16-byte stores, and the backward pass keeps its share of
-// grad_gamma in registers over all its rows and adds it with one atomic per column at the end (the reference
-// issues one atomic per element).  The arithmetic of y, rms and dx is the reference's, operation for
+// Here a CTA walks rows round robin; a row comes in once with 16-byte loads into shared memory, both passes
+// read it there, the result leaves with 16-byte stores, and the backward pass keeps its share of grad_gamma in
+// registers over all its rows and adds it with one atomic per column at the end (the reference issues one
+// atomic per element).  The usual case (even row length, 16-byte aligned rows) runs on 128 threads that each
+// play two adjacent threads of the reference's block; the kernels with one thread per reference thread take
+// the rest.  The arithmetic of y, rms and dx is the reference's, operation for
 // operation: the same columns per thread in the same order with a fused multiply-add per step, the same
 // shuffle-down tree inside a warp, the eight warp sums folded by the same tree, IEEE sqrt and divisions -- so
 // those three come out bit-identical.  grad_gamma is a sum over rows whose order the reference leaves to its
