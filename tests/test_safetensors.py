@@ -350,3 +350,57 @@ def test_frozen_linear_loaded_from_a_file(tmp_path, storage):
     for layer in (plain, from_file, wrong):
         layer.close()
     f.close()
+
+
+def test_random_files_cross_with_the_safetensors_package(tmp_path):
+    """Seeded random tensor sets (odd names with quotes, backslashes and non-ASCII characters, scalar-like and
+    zero-sized shapes, every standard dtype this library moves) written by one side and read by the other."""
+    from safetensors import safe_open
+    from safetensors.numpy import save_file
+
+    rng = np.random.default_rng(99)
+    np_types = {"F32": np.float32, "F16": np.float16, "I8": np.int8, "U8": np.uint8, "I32": np.int32, "I64": np.int64,
+                "F64": np.float64, "I16": np.int16}
+    alphabet = ["w", "layer", "0", "é", "ß", "weight", "q\"uote", "back\\slash", "tab\tbed", "модель", "層"]
+    for case in range(12):
+        tensors, arrays = [], {}
+        for t in range(int(rng.integers(1, 9))):
+            name = ".".join(rng.choice(alphabet, int(rng.integers(1, 4)))) + ".%d" % t
+            dtype = str(rng.choice(list(np_types)))
+            shape = [int(d) for d in rng.integers(0, 5, int(rng.integers(1, 4)))]
+            arr = (rng.standard_normal(shape) * 50).astype(np_types[dtype])
+            arrays[name] = arr
+            tensors.append((name, dtype, shape, arr.tobytes()))
+        meta = {"k%d" % i: "v \" \\ %d é" % i for i in range(int(rng.integers(0, 3)))}
+        mine = str(tmp_path / ("mine%d.safetensors" % case))
+        hl.save_safetensors(mine, tensors, meta)
+        with safe_open(mine, framework="numpy") as g:
+            assert sorted(g.keys()) == sorted(arrays)
+            assert (g.metadata() or {}) == meta
+            for name, arr in arrays.items():
+                got = g.get_tensor(name)
+                assert got.dtype == arr.dtype and got.shape == arr.shape and got.tobytes() == arr.tobytes()
+        theirs = str(tmp_path / ("theirs%d.safetensors" % case))
+        save_file(arrays, theirs, metadata=meta or None)
+        f = hl.SafeTensors(theirs)
+        assert sorted(f.names()) == sorted(arrays) and f.metadata() == meta
+        for name, arr in arrays.items():
+            info = f.info(name)
+            assert info["shape"] == list(arr.shape) and f.read(name) == arr.tobytes()
+        f.close()
+
+
+def test_index_file_with_escaped_names(tmp_path):
+    """Hugging Face writes model.safetensors.index.json with json.dumps, which escapes non-ASCII characters as
+    \\uXXXX (surrogate pairs beyond the basic plane): the names must come out as the UTF-8 strings the shard holds."""
+    names = ["blöcke.0.w", "層.1.w", "emoji.\U0001F600.w"]
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    hl.save_safetensors(str(d / "shard.safetensors"), [(n, "I8", [3], bytes([i, i + 1, i + 2])) for i, n in enumerate(names)])
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {n: "shard.safetensors" for n in names}}))
+    assert "\\u" in (d / "model.safetensors.index.json").read_text()
+    f = hl.SafeTensors(str(d), directory=True)
+    assert f.names() == sorted(names)
+    for i, n in enumerate(names):
+        assert f.read(n) == bytes([i, i + 1, i + 2])
+    f.close()
