@@ -1126,4 +1126,42 @@ inline void LoadFrozenLinear(CAIF_DeviceFrozenLinearBase &layer, const CAIF_Safe
   layer.LoadFromTensor(std::move(converted));
 }
 
+// ------------------------------------------------ trainable parameters <-> file
+// The trainable tensors of a layer (the LoRA factors of an adapter over a frozen base) under the names
+// ParameterNames(prefix) gives them, in parameter order -- what a fine-tune checkpoint keeps beside the frozen
+// base.  LoadParameters wants every name present with the parameter's dtype and element count.
+inline void SaveParameters(const CAIF_DeviceLayer &layer, const std::string &prefix, const std::string &path,
+                           const std::map<std::string, std::string> &metadata = {})
+{
+  const std::vector<std::string> names = layer.ParameterNames(prefix);
+  auto &mutable_layer = const_cast<CAIF_DeviceLayer &>(layer);
+  if (names.size() != mutable_layer.ParameterTensorCount())
+  {
+    THROW_CAIFE("SaveParameters: ParameterNames and ParameterTensorCount disagree");
+  }
+  std::vector<std::pair<std::string, const CAIF_DeviceTensor *>> list;
+  for (size_t i = 0; i < names.size(); ++i)
+  {
+    list.emplace_back(names[i], &mutable_layer.ParameterTensor(i));
+  }
+  CAIF_SafeTensorsFormat().Save(path, list, metadata);
+}
+
+inline void LoadParameters(CAIF_DeviceLayer &layer, const std::string &prefix, const CAIF_SafeTensorsFile &file,
+                           CAIF_CudaStream &stream)
+{
+  const std::vector<std::string> names = layer.ParameterNames(prefix);
+  for (size_t i = 0; i < names.size(); ++i)
+  {
+    CAIF_DeviceTensor &dst = layer.ParameterTensor(i);
+    CAIF_DeviceTensor src = file.Load(names[i], stream);
+    if (src.Dtype() != dst.Dtype() || src.NumElements() != dst.NumElements())
+    {
+      THROW_CAIFE("LoadParameters: tensor '" + names[i] + "' does not match the parameter's dtype and size");
+    }
+    dst.CopyFromDeviceRaw(src.DeviceDataRaw(), dst.SizeBytes());
+    CAIF_CheckCuda(cudaStreamSynchronize(stream.Handle()), "LoadParameters: sync");
+  }
+}
+
 }   // namespace instance

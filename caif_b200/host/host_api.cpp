@@ -582,6 +582,28 @@ CAIFH_API int caifh_load_frozen_linear(void *layer_handle, void *st_handle, cons
   });
 }
 
+// The layer's trainable tensors to / from a SafeTensors file under ParameterNames(prefix).
+CAIFH_API int caifh_save_parameters(void *layer_handle, const char *prefix, const char *path)
+{
+  return guarded([&] {
+    auto *box = static_cast<LayerBox *>(layer_handle);
+    SaveParameters(*box->layer, prefix != nullptr ? prefix : "", path, {{"framework", "CAIF"}});
+  });
+}
+
+CAIFH_API int caifh_load_parameters(void *layer_handle, const char *prefix, void *st_handle)
+{
+  return guarded([&] {
+    auto *box = static_cast<LayerBox *>(layer_handle);
+    auto *files = static_cast<FileBox *>(st_handle);
+    if (files->is_directory)
+    {
+      THROW_CAIFE("LoadParameters reads one file");
+    }
+    LoadParameters(*box->layer, prefix != nullptr ? prefix : "", *files->file, *box->stream);
+  });
+}
+
 // ------------------------------------------------------------------ name mapping
 CAIFH_API int caifh_mapper_create(void **handle)
 {

@@ -18,7 +18,8 @@ EXPORTS = ["caifh_last_error", "caifh_frozen_linear_create", "caifh_load_weight_
            "caifh_moe_frozen_expert_create", "caifh_destroy", "caifh_st_open", "caifh_st_open_directory",
            "caifh_st_close", "caifh_st_names", "caifh_st_info", "caifh_st_metadata", "caifh_st_read", "caifh_st_save",
            "caifh_st_save_device", "caifh_st_load_device", "caifh_load_frozen_linear", "caifh_mapper_create",
-           "caifh_mapper_destroy", "caifh_mapper_add", "caifh_mapper_translate", "caifh_mapper_query"]
+           "caifh_mapper_destroy", "caifh_mapper_add", "caifh_mapper_translate", "caifh_mapper_query",
+           "caifh_save_parameters", "caifh_load_parameters"]
 
 
 class HostLayerError(RuntimeError):
@@ -118,6 +119,13 @@ class Layer:
         out = torch.empty((self.out_dim, self.in_dim), dtype=torch.float32, device="cuda")
         _check(lib().caifh_frozen_tensor_fp32(self.h, ctypes.c_void_p(out.data_ptr()), ctypes.c_size_t(out.numel() * 4)))
         return out
+
+    def save_parameters(self, path, prefix=""):
+        """The trainable tensors (LoRA A and B) as a SafeTensors file under parameter_names(prefix)."""
+        _check(lib().caifh_save_parameters(self.h, prefix.encode(), path.encode()))
+
+    def load_parameters(self, safetensors_file, prefix=""):
+        _check(lib().caifh_load_parameters(self.h, prefix.encode(), safetensors_file.h))
 
     def close(self):
         if self.h:

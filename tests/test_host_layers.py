@@ -167,3 +167,48 @@ def test_moe_frozen_expert_layer(gated, storage, sd, compute):
     with pytest.raises(hl.HostLayerError, match="input_dim"):
         expert.forward(torch.zeros(m, in_dim + 1, dtype=TORCH_DTYPE[sd], device="cuda"))
     expert.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sd", [nv.F32, nv.BF16])
+def test_adapter_checkpoint_round_trip(tmp_path, sd):
+    """The trainable tensors of an adapter go to a SafeTensors file under their parameter names and come back into
+    a fresh adapter over the same frozen base: same outputs bit for bit; the file is what the safetensors package
+    reads; a file with another rank is refused."""
+    from safetensors.torch import load_file
+    from gpu_util import act, make_weight
+
+    rng = np.random.default_rng(21)
+    in_dim, out_dim, m, rank = 128, 96, 33, 8
+    tdt = nv._CODE_TO_TORCH[sd]
+    weight, codes, scales = make_weight(rng, out_dim, in_dim, orc.I4)
+
+    def fresh(r, seed):
+        layer = hl.Layer(in_dim, out_dim, orc.I4, compute=sd)
+        layer.load_weight(weight.codes, nv.I4)
+        layer.load_scales_from_host(np.ascontiguousarray(scales).tobytes())
+        return layer.wrap_lora(r, 16.0, storage=sd, compute=sd, seed=seed)
+
+    trained = fresh(rank, 3)
+    b = (torch.randn(out_dim, rank, device="cuda") * 0.02).to(tdt)
+    trained.set_parameter(1, b)
+    _, x = act(rng, m, in_dim, sd)
+    want = trained.forward(x).clone()
+    path = str(tmp_path / "adapter.safetensors")
+    trained.save_parameters(path, "blk.q.")
+    on_disk = load_file(path)
+    assert sorted(on_disk) == ["blk.q.lora_a.weight", "blk.q.lora_b.weight"]
+    assert on_disk["blk.q.lora_b.weight"].dtype == tdt and torch.equal(on_disk["blk.q.lora_b.weight"].cuda(), b)
+    restored = fresh(rank, 99)                    # another seed: A differs until the file is loaded
+    assert not torch.equal(restored.forward(x), want)
+    f = hl.SafeTensors(path)
+    restored.load_parameters(f, "blk.q.")
+    assert torch.equal(restored.forward(x), want)
+    other = fresh(4, 3)
+    with pytest.raises(hl.HostLayerError, match="does not match"):
+        other.load_parameters(f, "blk.q.")
+    with pytest.raises(hl.HostLayerError, match="not found"):
+        restored.load_parameters(f, "elsewhere.")
+    f.close()
+    for layer in (trained, restored, other):
+        layer.close()
