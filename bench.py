@@ -755,7 +755,63 @@ def bench_c2(ctx):
     if world == 1:
         # beside the single-call figure, never instead of it: layers that share their input in one launch
         result["multi_weight"] = _c2_multi_weight(ctx, weights, xs)
+        try:
+            result["multi_stream"] = _c2_multi_stream(ctx, weights, xs)
+        except Exception as e:   # informative only: never takes the headline down
+            result["multi_stream"] = {"error": "%s: %s" % (type(e).__name__, e)}
     return result
+
+
+def _c2_multi_stream(ctx, weights, xs, streams=3):
+    """The step's own launches (same calls, same weights and outputs of their own), issued round robin on three
+    streams inside one CUDA graph: what a host gets that keeps the independent projections of a block (q / k / v,
+    gate / up) or of several requests in flight together.  The tail of one launch then overlaps the ramp of the
+    next.  Reported beside the headline, which stays the one-launch-after-the-other figure."""
+    nv, torch, dev = ctx.nv, ctx.torch, ctx.dev
+    outs = {(m, c): torch.empty(m, C2_OUT, dtype=torch.float32, device=dev) for m in C2_MS for c in range(C2_COPIES)}
+    lanes = [torch.cuda.Stream() for _ in range(streams)]
+    passes = 16
+
+    def body():
+        main = torch.cuda.current_stream()
+        for s in lanes:
+            s.wait_stream(main)
+        k = 0
+        for _ in range(passes):
+            for m in C2_MS:
+                for c, w in enumerate(weights):
+                    with torch.cuda.stream(lanes[k % streams]):
+                        nv.linear_fwd(w, xs[m], compute=nv.F32, out=outs[(m, c)])
+                    k += 1
+        for s in lanes:
+            main.wait_stream(s)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        body()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        body()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    a.record()
+    for _ in range(reps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    launches = reps * passes * len(C2_MS) * len(weights)
+    us = a.elapsed_time(b) * 1e3 / launches
+    algo = sum(c2_bytes(m) for m in C2_MS) / len(C2_MS)
+    gbs = algo / us / 1e3
+    return {"workload": "the c2 launches issued round robin on %d streams in one CUDA graph" % streams,
+            "value": gbs, "unit": "GB/s", "us_per_launch_of_throughput": us, "launches_timed": launches,
+            "frac_of_hbm_peak": gbs / ctx.peaks["hbm_gbs"]}
 
 
 def _c2_multi_weight(ctx, weights, xs):
